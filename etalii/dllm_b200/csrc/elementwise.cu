@@ -1,0 +1,160 @@
+// Embedding gather, RMSNorm (optionally of gathered rows), rotary position encoding fused with the cache write,
+// and the residual add. The residual stream is float32 in both precisions; norms and rotations are computed in
+// float32 and rounded once to the output type.
+#include "common.cuh"
+
+// ---- embedding: x[r, :] = float(table[token_r, :]) ----------------------------------------------------------------
+template <typename T>
+__global__ void embed_kernel(float* __restrict__ out, const T* __restrict__ table, const int* __restrict__ tokens,
+                             int hidden, int vocab, int* __restrict__ status) {
+  int row = blockIdx.x;
+  int token = tokens[row];
+  if (token < 0 || token >= vocab) {  // refused, never read out of range
+    if (threadIdx.x == 0) atomicExch(status, 1);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[(size_t)row * hidden + i] = 0.f;
+    return;
+  }
+  const T* src = table + (size_t)token * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[(size_t)row * hidden + i] = to_float(src[i]);
+}
+
+DLLM_EXPORT int dllm_embed(float* out, const void* table, const int* tokens, int rows, int hidden, int vocab,
+                           int dtype, int* status, cudaStream_t stream) {
+  if (rows <= 0) return DLLM_OK;
+  if (hidden <= 0 || vocab <= 0) return DLLM_BAD_ARGUMENT;
+  int threads = hidden >= 256 ? 256 : 64;
+  if (dtype == DLLM_F32)
+    embed_kernel<float><<<rows, threads, 0, stream>>>(out, (const float*)table, tokens, hidden, vocab, status);
+  else if (dtype == DLLM_BF16)
+    embed_kernel<__nv_bfloat16><<<rows, threads, 0, stream>>>(out, (const __nv_bfloat16*)table, tokens, hidden,
+                                                              vocab, status);
+  else
+    return DLLM_BAD_ARGUMENT;
+  return dllm_launch_status();
+}
+
+// ---- RMSNorm: out[r] = x[rows ? rows[r] : r] * (1 / sqrt(mean(x^2) + eps)) * w ---------------------------------------
+// One block per row; each thread sums a strided part, then a fixed-order block reduction, so a row's result does not
+// depend on which other rows are in the launch.
+template <typename T>
+__global__ void rmsnorm_kernel(T* __restrict__ out, const float* __restrict__ x, const float* __restrict__ weight,
+                               const int* __restrict__ rows, int hidden, float eps) {
+  __shared__ float partial[32];
+  int r = blockIdx.x;
+  const float* src = x + (size_t)(rows ? rows[r] : r) * hidden;
+  float sum = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float v = src[i];
+    sum = fmaf(v, v, sum);
+  }
+  sum = warp_sum(sum);
+  int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  if (lane == 0) partial[warp] = sum;
+  __syncthreads();
+  if (warp == 0) {
+    float v = lane < warps ? partial[lane] : 0.f;
+    v = warp_sum(v);
+    if (lane == 0) partial[0] = 1.0f / sqrtf(v / (float)hidden + eps);
+  }
+  __syncthreads();
+  float inv = partial[0];
+  T* dst = out + (size_t)r * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = from_float<T>(src[i] * inv * weight[i]);
+}
+
+DLLM_EXPORT int dllm_rmsnorm(void* out, const float* x, const float* weight, const int* rows, int n_rows, int hidden,
+                             float eps, int out_dtype, cudaStream_t stream) {
+  if (n_rows <= 0) return DLLM_OK;
+  if (hidden <= 0) return DLLM_BAD_ARGUMENT;
+  int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+  if (out_dtype == DLLM_F32)
+    rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>((float*)out, x, weight, rows, hidden, eps);
+  else if (out_dtype == DLLM_BF16)
+    rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>((__nv_bfloat16*)out, x, weight, rows, hidden, eps);
+  else
+    return DLLM_BAD_ARGUMENT;
+  return dllm_launch_status();
+}
+
+// ---- rotary encoding + cache write --------------------------------------------------------------------------------
+// qkv is the float32 output of the fused q/k/v projection, [tokens, (heads + 2 kv_heads) * head_dim]. Queries and
+// keys rotate pairs (i, i + rotary_dim/2) by the angle whose cosine and sine the table holds for the token's
+// position; dimensions beyond rotary_dim pass through. Queries go to q_out, keys and values into the token's
+// place in the paged cache (page_table[slot][pos / page_size], row pos % page_size).
+template <typename T>
+__global__ void rope_cache_kernel(const float* __restrict__ qkv, T* __restrict__ q_out, KvLayout cache,
+                                  const float2* __restrict__ table, int rotary_dim, int heads,
+                                  const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
+                                  const int* __restrict__ slots, int write_cache) {
+  int t = blockIdx.x, h = blockIdx.y;
+  int hd = cache.head_dim, nkv = cache.kv_heads;
+  if (!write_cache && h >= heads) return;
+  int pos = tok_pos[t];
+  const float* src = qkv + ((size_t)t * (heads + 2 * nkv) + h) * hd;
+  T* dst;
+  bool rotate = h < heads + nkv && table != nullptr;
+  if (h < heads) {
+    dst = q_out + ((size_t)t * heads + h) * hd;
+  } else {
+    int which = h < heads + nkv ? 0 : 1;
+    int g = h - heads - which * nkv;
+    int slot = slots[tok_seq[t]];
+    int page = cache.page_table[(size_t)slot * cache.max_pages + pos / cache.page_size];
+    dst = (T*)cache.base + kv_offset(cache, page, which, g, pos % cache.page_size);
+  }
+  int half = rotary_dim / 2;
+  for (int i = threadIdx.x; i < hd; i += blockDim.x) {
+    float v = src[i];
+    if (rotate && i < rotary_dim) {
+      int j = i < half ? i : i - half;
+      float2 cs = table[(size_t)pos * half + j];
+      float a = src[j], b = src[j + half];
+      v = i < half ? fmaf(a, cs.x, -(b * cs.y)) : fmaf(a, cs.y, b * cs.x);
+    }
+    dst[i] = from_float<T>(v);
+  }
+}
+
+DLLM_EXPORT int dllm_rope_cache_write(const float* qkv, void* q_out, void* cache_base, const int* page_table,
+                                      int max_pages, int page_size, int heads, int kv_heads, int head_dim,
+                                      const float* table, int rotary_dim, const int* tok_seq, const int* tok_pos,
+                                      const int* slots, int tokens, int write_cache, int dtype,
+                                      cudaStream_t stream) {
+  if (tokens <= 0) return DLLM_OK;
+  if (heads <= 0 || kv_heads <= 0 || head_dim <= 0 || rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1))
+    return DLLM_BAD_ARGUMENT;
+  KvLayout cache{cache_base, page_table, max_pages, page_size, kv_heads, head_dim};
+  dim3 grid(tokens, heads + 2 * kv_heads);
+  int threads = head_dim >= 128 ? 128 : (head_dim > 32 ? 64 : 32);
+  if (dtype == DLLM_F32)
+    rope_cache_kernel<float><<<grid, threads, 0, stream>>>(qkv, (float*)q_out, cache, (const float2*)table,
+                                                           rotary_dim, heads, tok_seq, tok_pos, slots, write_cache);
+  else if (dtype == DLLM_BF16)
+    rope_cache_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(qkv, (__nv_bfloat16*)q_out, cache,
+                                                                   (const float2*)table, rotary_dim, heads, tok_seq,
+                                                                   tok_pos, slots, write_cache);
+  else
+    return DLLM_BAD_ARGUMENT;
+  return dllm_launch_status();
+}
+
+// ---- residual += update (float32 sum) -----------------------------------------------------------------------------
+template <typename T>
+__global__ void add_residual_kernel(float* __restrict__ residual, const T* __restrict__ update, size_t count) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < count) residual[i] += to_float(update[i]);
+}
+
+DLLM_EXPORT int dllm_add_residual(float* residual, const void* update, long long count, int dtype,
+                                  cudaStream_t stream) {
+  if (count <= 0) return DLLM_OK;
+  unsigned blocks = (unsigned)((count + 255) / 256);
+  if (dtype == DLLM_F32)
+    add_residual_kernel<float><<<blocks, 256, 0, stream>>>(residual, (const float*)update, (size_t)count);
+  else if (dtype == DLLM_BF16)
+    add_residual_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(residual, (const __nv_bfloat16*)update,
+                                                                    (size_t)count);
+  else
+    return DLLM_BAD_ARGUMENT;
+  return dllm_launch_status();
+}

@@ -1,0 +1,159 @@
+"""The engine: a model folder (or a configuration and a seed) in, tokens or logits out, on one CUDA device.
+
+`Engine.from_folder` / `Engine.from_random` build the model; `step` is the one function that runs tokens through it;
+`generate` is the batched generation loop above `step`; `complete` is the reference's single-prompt call
+(src/etalii_dllm/engine.py:416-595 loads, 694-748 completes)."""
+from __future__ import annotations
+
+from typing import Sequence
+
+import torch
+
+from .. import architectures  # noqa: F401  (registers the built-in architectures)
+from ..cache.allocators import CacheError
+from ..config.registry import architecture, load_config
+from ..sampling.options import SamplingOptions
+from ..sampling.sampler import Sampler
+from ..weights.loader import load_weights
+from ..weights.random_init import random_tensors
+from .batch import BatchBuffers
+from .generate import BatchRun, GenerationResult, check_prompts, plan_batches, run_batches
+from .model import Model
+from .runtime import Runtime
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
+           "f32": torch.float32}
+
+
+def parse_dtype(dtype) -> torch.dtype:
+    if isinstance(dtype, torch.dtype):
+        return dtype
+    try:
+        return _DTYPES[str(dtype).lower()]
+    except KeyError:
+        raise ValueError(f"dtype {dtype!r}: use bfloat16 or float32") from None
+
+
+class Engine:
+    def __init__(self, config, tensors, dtype="bfloat16", device="cuda:0", max_tokens: int | None = None,
+                 max_length: int | None = None, max_slots: int | None = None) -> None:
+        """`max_length`: the longest sequence the cache holds (default: the model's max_position_embeddings).
+        `max_tokens`: the most tokens all live sequences hold together, each rounded up to whole pages of 64
+        (default: four sequences of max_length)."""
+        if not torch.cuda.is_available():
+            raise RuntimeError("no CUDA device: this library has no CPU path")
+        self.config = config
+        self.dtype = parse_dtype(dtype)
+        arch = architecture(config.model_type)
+        self.spec = arch.build_spec(config)
+        self.context_length = int(self.spec.max_position)
+        self.max_length = int(min(max_length or self.context_length, self.context_length))
+        self.max_tokens = int(max_tokens or 4 * self.max_length)
+        torch.cuda.set_device(torch.device(device))
+        self.rt = Runtime(device, self.dtype, self.max_length)
+        self.model = Model(self.spec, tensors, self.rt, self.max_tokens, max_slots=max_slots)
+        self.cache = self.model.cache
+        self.vocab_size = self.spec.vocab_size
+        self.buffers = BatchBuffers(self.rt.device)
+        self.sampler = Sampler(self.cache.n_slots, self.vocab_size, self.rt.device)
+        self.steps_run = 0
+
+    # ---- construction ----
+    @classmethod
+    def from_folder(cls, folder: str, dtype="bfloat16", device="cuda:0", **kwargs) -> "Engine":
+        """Loads `folder/config.json` and its safetensors; the model class is chosen by config.json's model_type."""
+        config = load_config(folder)
+        spec = architecture(config.model_type).build_spec(config)
+        return cls(config, load_weights(folder, spec), dtype=dtype, device=device, **kwargs)
+
+    @classmethod
+    def from_random(cls, config, seed: int = 0, dtype="bfloat16", device="cuda:0", std: float = 0.02,
+                    **kwargs) -> "Engine":
+        """A model of `config` with seeded random weights (stored as bfloat16, like `write_random_model`)."""
+        return cls(config, random_tensors(config, seed, torch.bfloat16, std), dtype=dtype, device=device, **kwargs)
+
+    # ---- sequences ----
+    def open(self, count: int = 1) -> list[int]:
+        """Takes cache slots for `count` new sequences."""
+        return self.cache.acquire(count)
+
+    def close(self, slots: Sequence[int]) -> None:
+        """Gives back the slots and everything they hold."""
+        self.cache.release(slots)
+
+    # ---- the step ----
+    def step(self, slots: Sequence[int], new_tokens: Sequence[Sequence[int]],
+             want: Sequence[Sequence[int]] | None = None) -> torch.Tensor | None:
+        """Runs the next tokens of each sequence (whole prompts or single tokens, unequal lengths) as one packed
+        batch from the cache; returns float32 logits [wanted rows, vocab] on the device in the order of `slots` and
+        of `want` (`want[b]` indexes sequence b's new tokens; default: each sequence's last token), or None if no
+        row is wanted. The returned tensor is a work buffer: it is overwritten by the next step."""
+        if len(slots) == 0:
+            return None
+        if len(set(slots)) != len(slots):
+            raise CacheError("a sequence appears twice in one step")  # src/etalii_dllm/transformer.py:405-406
+        if want is None:
+            want = [[len(t) - 1] for t in new_tokens]
+        for tokens, rows in zip(new_tokens, want):
+            if len(tokens) == 0:
+                raise ValueError("a sequence in a step needs at least one token")
+            if min(tokens) < 0 or max(tokens) >= self.vocab_size:
+                raise ValueError(f"a token is outside the vocabulary of {self.vocab_size}")
+            if any(not 0 <= r < len(tokens) for r in rows):
+                raise ValueError("a wanted position is outside the sequence's new tokens")
+        starts = []
+        for slot, tokens in zip(slots, new_tokens):
+            self.cache.reserve(slot, len(tokens))
+            starts.append(self.cache.length(slot))
+        self.cache.sync_tables()
+        batch = self.buffers.fill(slots, new_tokens, starts, want)
+        logits = self.model.forward(batch)
+        for slot, tokens in zip(slots, new_tokens):
+            self.cache.advance(slot, len(tokens))
+        self.steps_run += 1
+        self.last_batch = batch
+        return logits
+
+    # ---- generation ----
+    def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int = 64,
+                 options: SamplingOptions | None = None, stop_token_ids: Sequence[int] | None = None,
+                 ignore_eos: bool = False, max_batch: int | None = None) -> list[GenerationResult]:
+        """Generates for every prompt (lists of token ids), as many batches one after another as the cache needs.
+        Stop ids default to the model's end-of-sequence ids; `stop_token_ids` adds more; `ignore_eos` drops the
+        model's own (src/etalii_dllm/cli.py:427-431). Sequence i draws from the stream of options.seed + i."""
+        options = options or SamplingOptions()
+        prompts = [list(map(int, p)) for p in prompts]
+        window = min(self.context_length, self.max_length)
+        check_prompts(prompts, self.vocab_size, window)
+        stops = set() if ignore_eos else set(self.spec.stop_token_ids)
+        stops.update(int(t) for t in (stop_token_ids or ()))
+        batches = plan_batches([len(p) for p in prompts], max_new_tokens, window, self.cache.page_size,
+                               self.cache.n_pages, self.cache.n_slots, max_batch)
+
+        def make_run(indices):
+            return BatchRun([len(prompts[i]) for i in indices], max_new_tokens, frozenset(stops), window)
+
+        def start(indices):
+            slots = self.open(len(indices))
+            if options.temperature > 0:
+                self.sampler.seed(slots, [options.seed + i for i in indices])
+            return slots
+
+        def step(slots, positions, tokens, first):
+            active = [slots[p] for p in positions]
+            logits = self.step(active, tokens)
+            chosen = self.sampler.choose(logits, self.last_batch.slots, options)
+            return chosen.tolist()
+
+        def finish(slots, positions):
+            if positions is None:  # an error: give everything still held back
+                self.close([s for s in slots if self.cache.slots.is_held(s)])
+            else:
+                self.close([slots[p] for p in positions])
+
+        return run_batches(prompts, batches, make_run, start, step, finish)
+
+    def complete(self, prompt: Sequence[int], max_tokens: int = 64,
+                 options: SamplingOptions | None = None, **kwargs) -> GenerationResult:
+        """One prompt, the reference's call (src/etalii_dllm/engine.py:694-695), with token ids for text."""
+        return self.generate([prompt], max_tokens, options, **kwargs)[0]

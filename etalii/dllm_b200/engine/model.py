@@ -1,0 +1,80 @@
+"""A model put together from a `ModelSpec`: parts built from the registries, weights bound by name, a cache sized for
+what the mixers ask for, and the forward pass of one step over a packed batch."""
+from __future__ import annotations
+
+from typing import Mapping
+
+import torch
+
+from ..cache.paged import PagedCache
+from ..parts.registry import build_part, part_factory
+from ..parts.spec import ModelSpec
+from .runtime import Runtime
+
+
+class Model:
+    def __init__(self, spec: ModelSpec, tensors: Mapping[str, torch.Tensor], rt: Runtime, max_tokens: int,
+                 max_slots: int | None = None, page_size: int = 64) -> None:
+        self.spec, self.rt = spec, rt
+        self.vocab_size, self.hidden_size = spec.vocab_size, spec.hidden_size
+
+        def bound(role, part_spec):
+            part = build_part(role, part_spec)
+            part.bind({local: tensors[name] for local, name in part_spec.names.items()}, rt)
+            return part
+
+        self.embedding = bound("embedding", spec.embedding)
+        self.blocks = []
+        for layer in spec.layers:
+            self.blocks.append(part_factory("block", layer.block)(
+                mixer=bound("mixer", layer.mixer), feed_forward=bound("feed_forward", layer.feed_forward),
+                mixer_norm=bound("norm", layer.mixer_norm), feed_forward_norm=bound("norm", layer.feed_forward_norm)))
+        self.final_norm = bound("norm", spec.final_norm)
+        self.head = bound("head", spec.head)
+        rt.done_loading()
+
+        self.order = spec.run_order()
+        n_entries = max((e.cache for e in self.order), default=-1) + 1
+        needs = [None] * n_entries
+        for entry in self.order:
+            if entry.writes_cache:
+                mixer = self.blocks[entry.layer].mixer
+                needs[entry.cache] = mixer.cache_need() if hasattr(mixer, "cache_need") else None
+        self.cache = PagedCache(needs, max_tokens=max_tokens, max_length=rt.max_length, dtype=rt.dtype,
+                                device=rt.device, page_size=page_size, max_slots=max_slots)
+        self._views = []
+        for entry in self.order:
+            need = needs[entry.cache]
+            if need is None:
+                self._views.append(None)
+            elif need.kind == "kv":
+                self._views.append(self.cache.kv_view(entry.cache))
+            else:
+                self._views.append(self.cache.state(entry.cache))
+
+    def forward(self, batch) -> torch.Tensor:
+        """Runs the batch's tokens through every scheduled layer; returns float32 logits [wanted rows, vocab]
+        (None when no row is wanted: the cache is still filled)."""
+        rt = self.rt
+        x = self.embedding.forward(batch.tokens, batch.n_tokens, rt)
+        for entry, view in zip(self.order, self._views):
+            self.blocks[entry.layer].forward(x, batch, view, rt, entry.writes_cache)
+        if batch.n_want == 0:
+            return None
+        hidden = self.final_norm.forward(x, rt, rows=batch.want_rows, n_rows=batch.n_want, name="final_hidden")
+        return self.head.forward(hidden, rt)
+
+    def weight_bytes(self) -> int:
+        seen, total = set(), 0
+        for block in self.blocks:
+            for part in (block.mixer, block.feed_forward, block.mixer_norm, block.feed_forward_norm):
+                for value in vars(part).values():
+                    if isinstance(value, torch.Tensor) and value.data_ptr() not in seen:
+                        seen.add(value.data_ptr())
+                        total += value.numel() * value.element_size()
+        for part in (self.embedding, self.final_norm, self.head):
+            for value in vars(part).values():
+                if isinstance(value, torch.Tensor) and value.data_ptr() not in seen:
+                    seen.add(value.data_ptr())
+                    total += value.numel() * value.element_size()
+        return total

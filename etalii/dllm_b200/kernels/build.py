@@ -1,0 +1,127 @@
+"""Compiles the CUDA sources of `csrc/` for sm_100a with nvcc and loads them with ctypes.
+
+Each source file becomes one shared library, built the first time one of its kernels is needed and kept beside the
+sources under `csrc/_build/` (named by a hash of the sources and flags, so an edit rebuilds). There is no fallback:
+a missing compiler, a failed build or a library that does not load raises `KernelBuildError`.
+"""
+from __future__ import annotations
+
+import ctypes
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+CSRC = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "csrc")
+ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
+NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
+
+SOURCES = {
+    "elementwise": "elementwise.cu",
+    "gemm_simt": "gemm_simt.cu",
+    "gemm_bf16": "gemm_bf16.cu",
+    "attention": "attention.cu",
+    "sampling": "sampling.cu",
+}
+"""Library name -> source file. A library added here is built by `build_all` and loadable by `library`."""
+
+_loaded: dict[str, ctypes.CDLL] = {}
+_lock = threading.Lock()
+
+
+class KernelBuildError(RuntimeError):
+    pass
+
+
+def _nvcc() -> str:
+    found = shutil.which("nvcc")
+    for candidate in (found, "/usr/local/cuda/bin/nvcc"):
+        if candidate and os.path.isfile(candidate):
+            return candidate
+    raise KernelBuildError("nvcc was not found: the sm_100a kernels cannot be built (there is no fallback path)")
+
+
+def _build_dir() -> str:
+    override = os.environ.get("DLLM_B200_BUILD_DIR")
+    candidates = [override] if override else []
+    candidates.append(os.path.join(CSRC, "_build"))
+    candidates.append(os.path.join(tempfile.gettempdir(), f"dllm_b200_build_{os.getuid()}"))
+    for path in candidates:
+        try:
+            os.makedirs(path, exist_ok=True)
+            probe = os.path.join(path, f".write_{os.getpid()}")
+            with open(probe, "w"):
+                pass
+            os.remove(probe)
+            return path
+        except OSError:
+            continue
+    raise KernelBuildError(f"no writable build directory among {candidates}")
+
+
+def _digest(source: str) -> str:
+    sha = hashlib.sha256()
+    sha.update(" ".join(ARCH_FLAGS + NVCC_FLAGS).encode())
+    headers = sorted(f for f in os.listdir(CSRC) if f.endswith((".cuh", ".h")))
+    for name in [source, *headers]:
+        with open(os.path.join(CSRC, name), "rb") as handle:
+            sha.update(name.encode())
+            sha.update(handle.read())
+    return sha.hexdigest()[:16]
+
+
+def library_path(name: str) -> str:
+    source = SOURCES[name]
+    return os.path.join(_build_dir(), f"libdllm_b200_{name}-{_digest(source)}.so")
+
+
+def compile_library(name: str, verbose: bool = True) -> str:
+    """Builds the library if its file is not there yet; returns the path."""
+    path = library_path(name)
+    if os.path.isfile(path):
+        return path
+    source = os.path.join(CSRC, SOURCES[name])
+    temporary = f"{path}.{os.getpid()}.tmp"
+    command = [_nvcc(), *ARCH_FLAGS, *NVCC_FLAGS, "-I", CSRC, source, "-o", temporary]
+    if verbose:
+        print(f"[dllm_b200] compiling {SOURCES[name]} for sm_100a ...", file=sys.stderr, flush=True)
+    start = time.time()
+    process = subprocess.Popen(command, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    while True:
+        try:
+            output, _ = process.communicate(timeout=10)
+            break
+        except subprocess.TimeoutExpired:
+            if verbose:
+                print(f"[dllm_b200] ... still compiling {SOURCES[name]} ({time.time() - start:.0f} s)",
+                      file=sys.stderr, flush=True)
+    if process.returncode != 0:
+        if os.path.exists(temporary):
+            os.remove(temporary)
+        raise KernelBuildError(f"nvcc failed on {SOURCES[name]}:\n{output}")
+    os.replace(temporary, path)
+    if verbose:
+        print(f"[dllm_b200] built {os.path.basename(path)} in {time.time() - start:.1f} s", file=sys.stderr, flush=True)
+    return path
+
+
+def library(name: str) -> ctypes.CDLL:
+    """The loaded library `name`, compiled first if needed."""
+    with _lock:
+        if name not in _loaded:
+            if name not in SOURCES:
+                raise KernelBuildError(f"no kernel library named {name!r}")
+            path = compile_library(name)
+            try:
+                _loaded[name] = ctypes.CDLL(path)
+            except OSError as error:
+                raise KernelBuildError(f"{path} does not load: {error}") from error
+        return _loaded[name]
+
+
+def build_all(verbose: bool = True) -> list[str]:
+    return [compile_library(name, verbose) for name in SOURCES]

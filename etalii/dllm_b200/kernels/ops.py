@@ -1,0 +1,181 @@
+"""Python entry points of the hand-written kernels. Each takes torch CUDA tensors, checks what the kernel assumes
+(device, dtype, contiguity, sizes), launches on torch's current stream and raises on a refused argument. There is
+no CPU path and no library fallback: a tensor that is not on a CUDA device is an error."""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_double, c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from .build import library
+
+EPI_STORE_F32, EPI_STORE_T, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
+_DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
+_STATUS = {-1: "bad argument", -2: "unsupported size", -3: "kernel launch failed"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_prototypes = {
+    ("elementwise", "dllm_embed"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    ("elementwise", "dllm_rmsnorm"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
+    ("elementwise", "dllm_rope_cache_write"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                               c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                               c_int, c_void_p],
+    ("elementwise", "dllm_add_residual"): [c_void_p, c_void_p, c_longlong, c_int, c_void_p],
+    ("gemm_simt", "dllm_gemm_f32"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    ("gemm_bf16", "dllm_gemm_bf16"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    ("attention", "dllm_attention_general"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                              c_int, c_void_p, c_void_p, c_void_p, c_int, c_float, c_int, c_int,
+                                              c_void_p],
+    ("sampling", "dllm_sample"): [c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                  c_float, c_int, c_double, c_double, c_void_p],
+    ("sampling", "dllm_seed_rng"): [c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+}
+_functions: dict[tuple[str, str], ctypes._CFuncPtr] = {}
+
+
+def _fn(lib: str, name: str):
+    key = (lib, name)
+    found = _functions.get(key)
+    if found is None:
+        found = getattr(library(lib), name)
+        found.argtypes = _prototypes[key]
+        found.restype = c_int
+        _functions[key] = found
+    return found
+
+
+def _check(status: int, what: str, detail: str = "") -> None:
+    if status != 0:
+        raise KernelError(f"{what}: {_STATUS.get(status, status)}{(' (' + detail + ')') if detail else ''}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _cuda(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if t is not None and (not t.is_cuda or not t.is_contiguous()):
+            raise KernelError("kernels take contiguous CUDA tensors only (there is no CPU path)")
+
+
+def _code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODE[dtype]
+    except KeyError:
+        raise KernelError(f"dtype {dtype} is not supported (float32 and bfloat16 are)") from None
+
+
+def embed(out: torch.Tensor, table: torch.Tensor, tokens: torch.Tensor, status: torch.Tensor) -> None:
+    """out[r] = float32(table[tokens[r]]); a token outside the table sets status[0] and gives a zero row."""
+    _cuda(out, table, tokens, status)
+    assert out.dtype == torch.float32 and tokens.dtype == torch.int32 and status.dtype == torch.int32
+    rows, hidden = out.shape
+    assert tokens.numel() >= rows and table.shape[1] == hidden
+    _check(_fn("elementwise", "dllm_embed")(out.data_ptr(), table.data_ptr(), tokens.data_ptr(), rows, hidden,
+                                            table.shape[0], _code(table.dtype), status.data_ptr(), _stream()),
+           "embed")
+
+
+def rmsnorm(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, eps: float,
+            rows: torch.Tensor | None = None) -> None:
+    """out[r] = norm(x[rows[r]] if rows is given else x[r]) * weight; x and weight float32."""
+    _cuda(out, x, weight, rows)
+    assert x.dtype == torch.float32 and weight.dtype == torch.float32 and weight.numel() == x.shape[-1]
+    n = out.shape[0]
+    assert out.shape[-1] == x.shape[-1] and (rows is not None or x.shape[0] >= n)
+    assert rows is None or (rows.dtype == torch.int32 and rows.numel() >= n)
+    _check(_fn("elementwise", "dllm_rmsnorm")(out.data_ptr(), x.data_ptr(), weight.data_ptr(),
+                                              rows.data_ptr() if rows is not None else None, n, x.shape[-1],
+                                              float(eps), _code(out.dtype), _stream()), "rmsnorm")
+
+
+def gemm(c: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int = EPI_STORE_T, kernel: int = 0) -> None:
+    """c = a[M,K] @ w[N,K]^T with float32 accumulation, then the epilogue: EPI_STORE_F32 (c float32), EPI_STORE_T
+    (c in a's dtype), EPI_RESIDUAL (c float32 += product), EPI_SWIGLU (w interleaves gate and up rows; c[M,N/2] =
+    silu(gate) * up in a's dtype). float32 operands run the true 32-bit kernel; bfloat16 the tensor-core kernels."""
+    _cuda(c, a, w)
+    m, k = a.shape
+    n = w.shape[0]
+    assert w.shape[1] == k and a.dtype == w.dtype, (a.shape, w.shape, a.dtype, w.dtype)
+    want_cols = n // 2 if epilogue == EPI_SWIGLU else n
+    want_dtype = torch.float32 if epilogue in (EPI_STORE_F32, EPI_RESIDUAL) else a.dtype
+    assert tuple(c.shape) == (m, want_cols) and c.dtype == want_dtype, (c.shape, c.dtype, m, want_cols, want_dtype)
+    if a.dtype == torch.float32:
+        status = _fn("gemm_simt", "dllm_gemm_f32")(c.data_ptr(), a.data_ptr(), w.data_ptr(), m, n, k, epilogue,
+                                                   _stream())
+    elif a.dtype == torch.bfloat16:
+        status = _fn("gemm_bf16", "dllm_gemm_bf16")(c.data_ptr(), a.data_ptr(), w.data_ptr(), m, n, k, epilogue,
+                                                    kernel, _stream())
+    else:
+        raise KernelError(f"gemm: dtype {a.dtype} is not supported")
+    _check(status, "gemm", f"M={m} N={n} K={k}: K must be a multiple of {4 if a.dtype == torch.float32 else 8}, N even")
+
+
+def rope_cache_write(qkv: torch.Tensor, q_out: torch.Tensor, cache, table: torch.Tensor | None, rotary_dim: int,
+                     heads: int, batch, write_cache: bool = True) -> None:
+    """Rotates queries and keys of qkv (float32 [tokens, (heads + 2 kv_heads) * head_dim]) by the table's angle for
+    each token's position; queries go to q_out, keys and values into the token's place in the paged cache."""
+    _cuda(qkv, q_out, table)
+    tokens = batch.n_tokens
+    assert qkv.dtype == torch.float32 and q_out.dtype == cache.dtype
+    assert qkv.shape[0] >= tokens and qkv.shape[1] == (heads + 2 * cache.kv_heads) * cache.head_dim
+    if table is not None:
+        assert table.dtype == torch.float32 and table.shape[0] > batch.max_position, "position beyond the table"
+        assert table.shape[1] == rotary_dim // 2 and table.shape[2] == 2
+    _check(_fn("elementwise", "dllm_rope_cache_write")(
+        qkv.data_ptr(), q_out.data_ptr(), cache.base_ptr, cache.page_table.data_ptr(), cache.max_pages,
+        cache.page_size, heads, cache.kv_heads, cache.head_dim, table.data_ptr() if table is not None else None,
+        rotary_dim if table is not None else 0, batch.tok_seq.data_ptr(), batch.tok_pos.data_ptr(),
+        batch.slots.data_ptr(), tokens, 1 if write_cache else 0, _code(cache.dtype), _stream()), "rope_cache_write")
+
+
+def attention_general(out: torch.Tensor, q: torch.Tensor, cache, heads: int, scale: float, window: int,
+                      batch) -> None:
+    """Causal attention of every token in the batch over its own sequence's cache (keys up to its position, the
+    last `window` of them if window > 0). out, q: [tokens, heads * head_dim] in the cache's dtype."""
+    _cuda(out, q)
+    assert q.dtype == cache.dtype and out.dtype == cache.dtype
+    _check(_fn("attention", "dllm_attention_general")(
+        out.data_ptr(), q.data_ptr(), cache.base_ptr, cache.page_table.data_ptr(), cache.max_pages, cache.page_size,
+        heads, cache.kv_heads, cache.head_dim, batch.tok_seq.data_ptr(), batch.tok_pos.data_ptr(),
+        batch.slots.data_ptr(), batch.n_tokens, float(scale), int(window or 0), _code(cache.dtype), _stream()),
+        "attention", f"head_dim={cache.head_dim} must be a multiple of 8, at most 256")
+
+
+def add_residual(residual: torch.Tensor, update: torch.Tensor) -> None:
+    """residual (float32) += update, summed in float32."""
+    _cuda(residual, update)
+    assert residual.dtype == torch.float32 and residual.numel() == update.numel()
+    _check(_fn("elementwise", "dllm_add_residual")(residual.data_ptr(), update.data_ptr(), residual.numel(),
+                                                   _code(update.dtype), _stream()), "add_residual")
+
+
+def sample(out_tokens: torch.Tensor, logits: torch.Tensor, scratch: torch.Tensor | None, rng: torch.Tensor | None,
+           rng_rows: torch.Tensor | None, temperature: float, top_k: int = 0, top_p: float = 1.0,
+           min_p: float = 0.0) -> None:
+    """One token per row of logits (float32 [rows, vocab]); see csrc/sampling.cu for the rule."""
+    _cuda(out_tokens, logits, scratch, rng, rng_rows)
+    rows, vocab = logits.shape
+    assert logits.dtype == torch.float32 and out_tokens.dtype == torch.int32 and out_tokens.numel() >= rows
+    if temperature > 0:
+        assert scratch is not None and scratch.dtype == torch.float32 and scratch.numel() >= rows * vocab
+        assert rng is not None and rng.dtype == torch.int64 and rng_rows.dtype == torch.int32
+    _check(_fn("sampling", "dllm_sample")(
+        out_tokens.data_ptr(), logits.data_ptr(), logits.stride(0), rows, vocab,
+        scratch.data_ptr() if scratch is not None else None, rng.data_ptr() if rng is not None else None,
+        rng_rows.data_ptr() if rng_rows is not None else None, float(temperature), int(top_k), float(top_p),
+        float(min_p), _stream()), "sample")
+
+
+def seed_rng(rng: torch.Tensor, rows: torch.Tensor, seeds: torch.Tensor) -> None:
+    """rng[rows[i]] = xoshiro256** state seeded with seeds[i] (int64 bit patterns of unsigned 64-bit seeds)."""
+    _cuda(rng, rows, seeds)
+    assert rng.dtype == torch.int64 and rows.dtype == torch.int32 and seeds.dtype == torch.int64
+    _check(_fn("sampling", "dllm_seed_rng")(rng.data_ptr(), rows.data_ptr(), seeds.data_ptr(), rows.numel(),
+                                            _stream()), "seed_rng")

@@ -1,0 +1,57 @@
+"""Grouped-query attention over the cache: fused q/k/v projection, position encoding fused with the cache write,
+attention of every token over its own sequence, output projection with the residual add in its epilogue
+(reference: src/etalii_dllm/transformer.py:497-543, cpp/include/dllm/nn.hpp:535-569, 733-796)."""
+from __future__ import annotations
+
+import torch
+
+from ..cache.paged import CacheNeed
+from ..kernels import ops
+from .registry import build_part, register_part
+from .spec import ParamSpec
+
+
+class Attention:
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
+                 window: int | None = None, position=None) -> None:
+        if num_heads % num_kv_heads:
+            raise ValueError(f"{num_heads} heads are not a multiple of {num_kv_heads} kv heads")
+        self.hidden_size, self.num_heads, self.num_kv_heads = int(hidden_size), int(num_heads), int(num_kv_heads)
+        self.head_dim, self.scale = int(head_dim), float(scale)
+        self.window = int(window) if window else None
+        self.position = build_part("position", position) if position is not None else None
+        self.w_qkv = self.w_o = None
+
+    @staticmethod
+    def parameters(hidden_size, num_heads, num_kv_heads, head_dim, **_) -> dict[str, ParamSpec]:
+        q, kv = int(num_heads) * int(head_dim), int(num_kv_heads) * int(head_dim)
+        return {"q": ParamSpec((q, hidden_size)), "k": ParamSpec((kv, hidden_size)),
+                "v": ParamSpec((kv, hidden_size)), "o": ParamSpec((hidden_size, q))}
+
+    def cache_need(self) -> CacheNeed:
+        return CacheNeed("kv", kv_heads=self.num_kv_heads, head_dim=self.head_dim, window=self.window)
+
+    def bind(self, tensors, rt) -> None:
+        # one projection for q, k and v: the rows of the three matrices one after another
+        fused = torch.cat([tensors["q"].to(rt.dtype), tensors["k"].to(rt.dtype), tensors["v"].to(rt.dtype)], dim=0)
+        self.w_qkv = fused.contiguous().to(rt.device)
+        self.w_o = rt.to_device(tensors["o"], rt.dtype)
+        if self.position is not None:
+            self.position.bind({}, rt)
+
+    def forward(self, h: torch.Tensor, residual: torch.Tensor, batch, cache, rt, write_cache: bool = True) -> None:
+        """h: normed activations [tokens, hidden]; adds the attention output to `residual` (float32) in place."""
+        n = batch.n_tokens
+        q_size = self.num_heads * self.head_dim
+        qkv = rt.ws.buffer("qkv", (n, q_size + 2 * self.num_kv_heads * self.head_dim), torch.float32)
+        ops.gemm(qkv, h, self.w_qkv, ops.EPI_STORE_F32)
+        q = rt.ws.buffer("q", (n, q_size), rt.dtype)
+        table = self.position.table() if self.position is not None else None
+        rotary_dim = self.position.rotary_dim if self.position is not None else 0
+        ops.rope_cache_write(qkv, q, cache, table, rotary_dim, self.num_heads, batch, write_cache)
+        attended = rt.ws.buffer("attended", (n, q_size), rt.dtype)
+        ops.attention_general(attended, q, cache, self.num_heads, self.scale, self.window or 0, batch)
+        ops.gemm(residual, attended, self.w_o, ops.EPI_RESIDUAL)
+
+
+register_part("mixer", "attention", Attention)

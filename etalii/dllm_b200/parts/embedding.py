@@ -1,0 +1,51 @@
+"""Token embedding (row gather into the float32 residual stream) and the output head (final hidden rows times the
+head matrix, float32 logits). A tied head names the embedding's tensor and shares its device copy
+(reference: src/etalii_dllm/transformer.py:659-663, 427-443)."""
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from .registry import register_part
+from .spec import ParamSpec
+
+
+class TokenEmbedding:
+    def __init__(self, vocab_size: int, hidden_size: int) -> None:
+        self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
+        self.weight = None
+
+    @staticmethod
+    def parameters(vocab_size, hidden_size) -> dict[str, ParamSpec]:
+        return {"weight": ParamSpec((vocab_size, hidden_size))}
+
+    def bind(self, tensors, rt) -> None:
+        self.weight = rt.to_device(tensors["weight"], rt.dtype)
+        self.status = torch.zeros(1, dtype=torch.int32, device=rt.device)
+
+    def forward(self, tokens: torch.Tensor, n_tokens: int, rt) -> torch.Tensor:
+        x = rt.ws.buffer("residual", (n_tokens, self.hidden_size), torch.float32)
+        ops.embed(x, self.weight, tokens, self.status)
+        return x
+
+
+class LinearHead:
+    def __init__(self, vocab_size: int, hidden_size: int) -> None:
+        self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
+        self.weight = None
+
+    @staticmethod
+    def parameters(vocab_size, hidden_size) -> dict[str, ParamSpec]:
+        return {"weight": ParamSpec((vocab_size, hidden_size))}
+
+    def bind(self, tensors, rt) -> None:
+        self.weight = rt.to_device(tensors["weight"], rt.dtype)
+
+    def forward(self, hidden: torch.Tensor, rt) -> torch.Tensor:
+        logits = rt.ws.buffer("logits", (hidden.shape[0], self.vocab_size), torch.float32)
+        ops.gemm(logits, hidden, self.weight, ops.EPI_STORE_F32)
+        return logits
+
+
+register_part("embedding", "token_embedding", TokenEmbedding)
+register_part("head", "linear", LinearHead)

@@ -1,0 +1,36 @@
+"""The SwiGLU feed-forward: down(silu(gate(h)) * up(h)). Gate and up are one matrix product whose rows interleave
+(row 2i = gate_i, row 2i + 1 = up_i) so the product's epilogue applies silu(gate) * up on the accumulators; the down
+projection adds into the residual in its epilogue (reference: src/etalii_dllm/transformer.py:548-558,
+cpp/include/dllm/nn.hpp:467-492)."""
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from .registry import register_part
+from .spec import ParamSpec
+
+
+class SwiGLU:
+    def __init__(self, hidden_size: int, intermediate_size: int) -> None:
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.w_gate_up = self.w_down = None
+
+    @staticmethod
+    def parameters(hidden_size, intermediate_size) -> dict[str, ParamSpec]:
+        return {"gate": ParamSpec((intermediate_size, hidden_size)), "up": ParamSpec((intermediate_size, hidden_size)),
+                "down": ParamSpec((hidden_size, intermediate_size))}
+
+    def bind(self, tensors, rt) -> None:
+        gate, up = tensors["gate"].to(rt.dtype), tensors["up"].to(rt.dtype)
+        fused = torch.stack([gate, up], dim=1).reshape(2 * self.intermediate_size, self.hidden_size)
+        self.w_gate_up = fused.contiguous().to(rt.device)
+        self.w_down = rt.to_device(tensors["down"], rt.dtype)
+
+    def forward(self, h: torch.Tensor, residual: torch.Tensor, batch, rt) -> None:
+        act = rt.ws.buffer("ffn_act", (h.shape[0], self.intermediate_size), rt.dtype)
+        ops.gemm(act, h, self.w_gate_up, ops.EPI_SWIGLU)
+        ops.gemm(residual, act, self.w_down, ops.EPI_RESIDUAL)
+
+
+register_part("feed_forward", "swiglu", SwiGLU)

@@ -1,0 +1,174 @@
+"""The engine against the plain implementation, in float32 and in bfloat16, for two tiny configurations that differ
+in every size and option: whole prompts, token-by-token decoding, unequal batches with slot reuse, long decoding,
+first tokens, generation through the entry point."""
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as P
+from helpers import TOL, PlainLogits, host, make_engine, model_case, prompts_for, rel_error
+
+pytestmark = pytest.mark.gpu
+DTYPES = ["float32", "bfloat16"]
+TAGS = ["a", "b"]
+
+
+@pytest.fixture(scope="module", params=[(t, d) for t in TAGS for d in DTYPES], ids=lambda p: f"{p[0]}-{p[1]}")
+def setup(request):
+    tag, dtype = request.param
+    config, weights = model_case(tag)
+    engine = make_engine(config, weights, dtype, max_tokens=64 * 24)
+    return tag, dtype, config, weights, engine, PlainLogits(config, weights)
+
+
+def test_each_request_alone_and_whole(setup):
+    _, dtype, config, _, engine, plain = setup
+    for prompt in prompts_for(config, (1, 2, 7, 23, 40, 64, 65, 100)):
+        slot = engine.open(1)
+        logits = host(engine.step(slot, [prompt], [list(range(len(prompt)))]))
+        engine.close(slot)
+        assert logits.shape == (len(prompt), config["vocab_size"])
+        assert rel_error(logits, plain(prompt)) <= TOL[dtype], len(prompt)
+    engine.cache.check()
+
+
+def test_last_32_tokens_one_by_one(setup):
+    _, dtype, config, _, engine, plain = setup
+    for prompt in prompts_for(config, (33, 70, 120), seed=3):
+        slot = engine.open(1)
+        head = len(prompt) - 32
+        rows = [host(engine.step(slot, [prompt[:head]]))[0]]
+        for token in prompt[head:]:
+            rows.append(host(engine.step(slot, [[token]]))[0])
+        engine.close(slot)
+        want = plain(prompt)[head - 1:]
+        for index, (got, ref) in enumerate(zip(rows, want)):
+            assert rel_error(got, ref) <= TOL[dtype], (len(prompt), index)
+
+
+def test_unequal_batches_one_after_another(setup):
+    """Batches of unequal lengths; shorter requests end earlier; the next batch reuses their slots and pages."""
+    _, dtype, config, _, engine, plain = setup
+    rng = np.random.default_rng(9)
+    held_before = engine.cache.pages_held()
+    for round_index, lengths in enumerate(((5, 11, 17), (1, 7, 23, 40), (66, 3, 64))):
+        prompts = prompts_for(config, lengths, seed=20 + round_index)
+        decode = [int(rng.integers(2, 9)) for _ in prompts]  # how many tokens each sequence goes on for
+        tails = [rng.integers(0, config["vocab_size"], n).tolist() for n in decode]
+        slots = engine.open(len(prompts))
+        logits = host(engine.step(slots, prompts, [list(range(len(p))) for p in prompts]))
+        offset = 0
+        for prompt in prompts:
+            assert rel_error(logits[offset:offset + len(prompt)], plain(prompt)) <= TOL[dtype]
+            offset += len(prompt)
+        live = list(range(len(prompts)))
+        for step in range(max(decode)):
+            live = [i for i in live if step < decode[i]]
+            got = host(engine.step([slots[i] for i in live], [[tails[i][step]] for i in live]))
+            for row, i in enumerate(live):
+                context = prompts[i] + tails[i][:step + 1]
+                assert rel_error(got[row], plain(context)[-1]) <= TOL[dtype], (round_index, i, step)
+            ended = [i for i in live if step + 1 == decode[i]]
+            engine.close([slots[i] for i in ended])
+        engine.cache.check()
+        assert engine.cache.pages_held() == held_before and engine.cache.slots.held == 0
+
+
+def test_long_decoding(setup):
+    _, dtype, config, _, engine, plain = setup
+    tokens = prompts_for(config, (100,), seed=5)[0]
+    slot = engine.open(1)
+    engine.step(slot, [tokens[:3]], [[]])
+    reference = plain(tokens)
+    for index in range(3, len(tokens)):
+        got = host(engine.step(slot, [[tokens[index]]]))[0]
+        if index % 8 == 0 or index >= 60:
+            assert rel_error(got, reference[index]) <= TOL[dtype], index
+    engine.close(slot)
+
+
+def test_first_tokens_of_a_sequence(setup):
+    _, dtype, config, _, engine, plain = setup
+    tokens = prompts_for(config, (6,), seed=6)[0]
+    slot = engine.open(1)
+    for index, token in enumerate(tokens):
+        got = host(engine.step(slot, [[token]]))[0]
+        assert rel_error(got, plain(tokens[:index + 1])[-1]) <= TOL[dtype], index
+    engine.close(slot)
+
+
+def test_chunked_prompt_equals_whole(setup):
+    _, dtype, config, _, engine, plain = setup
+    prompt = prompts_for(config, (90,), seed=8)[0]
+    slot = engine.open(1)
+    parts = [prompt[:10], prompt[10:64], prompt[64:65], prompt[65:]]
+    rows = []
+    for part in parts:
+        rows.append(host(engine.step(slot, [part], [list(range(len(part)))])))
+    engine.close(slot)
+    assert rel_error(np.concatenate(rows), plain(prompt)) <= TOL[dtype]
+
+
+def test_float32_logits_do_not_depend_on_the_cut(setup):
+    """In 32-bit a position's logits are the same bits alone, in a batch, decoded one by one, in a reused slot."""
+    _, dtype, config, _, engine, _ = setup
+    if dtype != "float32":
+        pytest.skip("bit equality is the float32 path's property")
+    prompts = prompts_for(config, (9, 30, 70), seed=12)
+    alone = []
+    for prompt in prompts:
+        slot = engine.open(1)
+        alone.append(engine.step(slot, [prompt], [list(range(len(prompt)))]).clone())
+        engine.close(slot)
+    slots = engine.open(3)
+    together = engine.step(slots[::-1], prompts[::-1], [list(range(len(p))) for p in prompts[::-1]]).clone()
+    engine.close(slots)
+    assert torch.equal(together, torch.cat(alone[::-1]))
+    slot = engine.open(1)
+    engine.step(slot, [prompts[2][:40]], [[]])
+    rows = [engine.step(slot, [[t]]).clone() for t in prompts[2][40:]]
+    engine.close(slot)
+    assert torch.equal(torch.cat(rows), alone[2][40:])
+
+
+def test_greedy_generation_through_the_entry_point(setup):
+    from etalii.dllm_b200 import SamplingOptions
+
+    tag, dtype, config, weights, engine, plain = setup
+    prompts = prompts_for(config, (5, 11, 17, 3, 40), seed=30)
+    results = engine.generate(prompts, 8, SamplingOptions(), ignore_eos=True, max_batch=3)
+    for prompt, result in zip(prompts, results):
+        assert result.finish_reason == "length" and result.prompt_tokens == len(prompt) and len(result.tokens) == 8
+        if dtype == "float32":
+            assert list(result.tokens) == P.generate(config, weights, prompt, 8)[0]
+        else:  # each chosen token must be (nearly) the best token of the plain logits for the same context
+            context = list(prompt)
+            for token in result.tokens:
+                ref = plain(context)[-1]
+                assert ref[token] >= ref.max() - 2 * TOL[dtype] * np.abs(ref).max()
+                context.append(token)
+    assert engine.cache.slots.held == 0
+    engine.cache.check()
+
+
+def test_sampled_generation_and_stop_tokens(setup):
+    from etalii.dllm_b200 import SamplingOptions
+
+    tag, dtype, config, weights, engine, _ = setup
+    if dtype != "float32":
+        pytest.skip("seeded draws are compared token for token in float32")
+    prompts = prompts_for(config, (1, 7, 23, 40), seed=31)
+    options = SamplingOptions(temperature=0.8, seed=5)
+    results = engine.generate(prompts, 12, options, ignore_eos=True)
+    for index, (prompt, result) in enumerate(zip(prompts, results)):
+        want, _ = P.generate(config, weights, prompt, 12, temperature=0.8, seed=5 + index)
+        assert list(result.tokens) == want
+    # a stop token ends its sequence early and is not part of the output; the others go on
+    stop = results[1].tokens[3]
+    stopped = engine.generate(prompts, 12, options, ignore_eos=True, stop_token_ids=[stop])
+    for index, (prompt, result) in enumerate(zip(prompts, stopped)):
+        want, reason = P.generate(config, weights, prompt, 12, temperature=0.8, seed=5 + index, stop_tokens=[stop])
+        assert list(result.tokens) == want and result.finish_reason == reason
+    assert stopped[1].finish_reason == "stop" and len(stopped[1].tokens) <= 3
+    alone = engine.generate([prompts[2]], 12, SamplingOptions(temperature=0.8, seed=7))
+    assert alone[0].tokens == engine.generate(prompts, 12, SamplingOptions(temperature=0.8, seed=5))[2].tokens

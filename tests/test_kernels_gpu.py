@@ -1,0 +1,252 @@
+"""Each kernel alone against its plain reference (tests/plain_kernels.py), at sizes other than the engine's."""
+import numpy as np
+import pytest
+import torch
+
+import plain_kernels as PK
+from helpers import rel_error
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def ops():
+    from etalii.dllm_b200.kernels import ops as module
+
+    return module
+
+
+def _randn(shape, dtype, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed(dtype):
+    table = _randn((37, 72), dtype, 0)
+    tokens = torch.tensor([0, 36, 5, 5, 17], dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.empty((5, 72), dtype=torch.float32, device=DEV)
+    ops().embed(out, table, tokens, status)
+    assert torch.equal(out, table[tokens.long()].float()) and int(status[0]) == 0
+    bad = torch.tensor([3, 37, -1], dtype=torch.int32, device=DEV)
+    out3 = torch.empty((3, 72), dtype=torch.float32, device=DEV)
+    ops().embed(out3, table, bad, status)
+    assert int(status[0]) == 1 and torch.equal(out3[1], torch.zeros(72, device=DEV))
+    assert torch.equal(out3[0], table[3].float())
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-6), (torch.bfloat16, 8e-3)])
+@pytest.mark.parametrize("hidden,eps", [(72, 1e-5), (1000, 1e-6), (4096, 1e-2)])
+def test_rmsnorm(dtype, tol, hidden, eps):
+    x = _randn((9, hidden), torch.float32, 1, 3.0)
+    w = _randn((hidden,), torch.float32, 2) + 1
+    out = torch.empty((9, hidden), dtype=dtype, device=DEV)
+    ref = torch.empty_like(out)
+    ops().rmsnorm(out, x, w, eps)
+    PK.rmsnorm(ref, x, w, eps)
+    assert rel_error(out.float().cpu(), ref.float().cpu()) <= tol
+    rows = torch.tensor([8, 0, 3], dtype=torch.int32, device=DEV)
+    out3 = torch.empty((3, hidden), dtype=dtype, device=DEV)
+    ops().rmsnorm(out3, x, w, eps, rows)
+    assert torch.equal(out3, out[rows.long()])  # a gathered row has the same bits as the row in place
+
+
+GEMM_SHAPES = [(1, 64, 64), (3, 130, 72), (16, 96, 144), (17, 200, 136), (77, 384, 160), (130, 66, 1544), (300, 258, 576)]
+
+
+@pytest.mark.parametrize("m,n,k", GEMM_SHAPES)
+@pytest.mark.parametrize("epilogue", [0, 1, 2, 3])
+def test_gemm_f32(m, n, k, epilogue):
+    a, w = _randn((m, k), torch.float32, 3), _randn((n, k), torch.float32, 4, 0.2)
+    cols = n // 2 if epilogue == 3 else n
+    c = _randn((m, cols), torch.float32, 5)
+    ref = c.clone()
+    ops().gemm(c, a, w, epilogue)
+    PK.gemm(ref, a, w, epilogue)
+    assert rel_error(c.cpu(), ref.cpu()) <= 2e-6
+
+
+def test_gemm_f32_rows_do_not_depend_on_the_batch():
+    a, w = _randn((150, 136), torch.float32, 6), _randn((200, 136), torch.float32, 7)
+    whole = torch.empty((150, 200), dtype=torch.float32, device=DEV)
+    ops().gemm(whole, a, w, 0)
+    for rows in ([149], [0, 64, 65], list(range(70, 90))):
+        part = torch.empty((len(rows), 200), dtype=torch.float32, device=DEV)
+        ops().gemm(part, a[rows].contiguous(), w, 0)
+        assert torch.equal(part, whole[rows])
+
+
+@pytest.mark.parametrize("m,n,k", GEMM_SHAPES)
+@pytest.mark.parametrize("epilogue", [0, 1, 2, 3])
+@pytest.mark.parametrize("kernel", [1, 2])
+def test_gemm_bf16(m, n, k, epilogue, kernel):
+    if kernel == 2 and m > 16:
+        pytest.skip("the weight-streaming kernel takes at most 16 rows")
+    a, w = _randn((m, k), torch.bfloat16, 3), _randn((n, k), torch.bfloat16, 4, 0.2)
+    cols = n // 2 if epilogue == 3 else n
+    c = _randn((m, cols), torch.float32 if epilogue in (0, 2) else torch.bfloat16, 5)
+    ref = c.clone()
+    ops().gemm(c, a, w, epilogue, kernel)
+    PK.gemm(ref, a, w, epilogue)
+    assert rel_error(c.float().cpu(), ref.float().cpu()) <= (2e-5 if epilogue in (0, 2) else 8e-3)
+
+
+def test_gemm_refuses_sizes_it_cannot_run():
+    from etalii.dllm_b200.kernels.ops import KernelError
+
+    a, w = _randn((4, 12), torch.bfloat16, 1), _randn((8, 12), torch.bfloat16, 2)
+    with pytest.raises(KernelError):
+        ops().gemm(torch.empty((4, 8), dtype=torch.bfloat16, device=DEV), a, w, 1)
+    with pytest.raises(KernelError):
+        ops().gemm(torch.empty((4, 8), dtype=torch.float32), a.cpu(), w.cpu(), 0)  # no CPU path
+
+
+def _cache_and_batch(dtype, kv_heads, head_dim, lengths, new, window=None, seed=0):
+    """A cache whose sequences' pages interleave, filled with random keys and values up to each length, and the
+    batch of the last `new[b]` tokens of each sequence."""
+    from etalii.dllm_b200.cache.paged import CacheNeed, PagedCache
+    from etalii.dllm_b200.engine.batch import BatchBuffers
+
+    cache = PagedCache([CacheNeed("kv", kv_heads, head_dim, window)], max_tokens=64 * 40, max_length=1024,
+                       dtype=dtype, device=DEV)
+    slots = cache.acquire(len(lengths) + 1)[1:]  # slot 0 stays unused: slots are not sequence indices
+    grown = [0] * len(lengths)
+    while any(g < n for g, n in zip(grown, lengths)):  # grow round-robin so pages interleave
+        for i, slot in enumerate(slots):
+            step = min(50, lengths[i] - grown[i])
+            if step > 0:
+                cache.reserve(slot, step)
+                cache.advance(slot, step)
+                grown[i] += step
+    cache.sync_tables()
+    view = cache.kv_view(0)
+    g = torch.Generator().manual_seed(seed)
+    view.storage.copy_((torch.randn(view.storage.shape, generator=g)).to(dtype))
+    starts = [n - k for n, k in zip(lengths, new)]
+    batch = BatchBuffers(DEV).fill(slots, [[1] * k for k in new], starts, [[] for _ in new])
+    return cache, view, batch
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 5e-6), (torch.bfloat16, 8e-3)])
+@pytest.mark.parametrize("heads,kv_heads,head_dim,window", [(4, 2, 16, None), (6, 3, 24, None), (9, 3, 64, None),
+                                                           (8, 1, 128, 70), (5, 5, 40, 33)])
+def test_attention_general(dtype, tol, heads, kv_heads, head_dim, window):
+    lengths, new = [130, 67, 1, 200], [130, 1, 1, 9]
+    cache, view, batch = _cache_and_batch(dtype, kv_heads, head_dim, lengths, new, window)
+    n = batch.n_tokens
+    q = _randn((n, heads * head_dim), dtype, 9)
+    out = torch.zeros((n, heads * head_dim), dtype=dtype, device=DEV)
+    ref = torch.zeros((n, heads * head_dim), dtype=dtype)
+    ops().attention_general(out, q, view, heads, 0.3, window or 0, batch)
+    view_cpu = type(view)(view.storage.cpu(), view.page_table.cpu(), view.page_size, kv_heads, head_dim, window)
+    cpu_batch = type("B", (), {"n_tokens": n, "tok_pos": batch.tok_pos.cpu(), "tok_seq": batch.tok_seq.cpu(),
+                               "slots": batch.slots.cpu()})
+    PK.attention_general(ref, q.cpu(), view_cpu, heads, 0.3, window or 0, cpu_batch)
+    assert rel_error(out.float().cpu(), ref.float()) <= tol
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_finds_a_far_key(dtype):
+    """One key among hundreds matches the query: the output must be that key's value, wherever its page lies."""
+    heads, kv_heads, hd = 4, 2, 32
+    cache, view, batch = _cache_and_batch(dtype, kv_heads, hd, [700], [1])
+    view.storage.mul_(0.05)
+    slot = batch.h_slots[0]
+    for target in (0, 63, 64, 333, 698):
+        page = int(view.page_table[slot, target // 64])
+        saved = view.storage[page].clone()
+        view.storage[page, 0, :, target % 64, :] = 4.0
+        view.storage[page, 1, :, target % 64, :] = 7.0
+        q = torch.full((1, heads * hd), 4.0, dtype=dtype, device=DEV)
+        out = torch.zeros_like(q)
+        ops().attention_general(out, q, view, heads, 1.0, 0, batch)
+        assert torch.allclose(out.float(), torch.full_like(out, 7.0).float(), atol=0.05), target
+        view.storage[page] = saved
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-6), (torch.bfloat16, 8e-3)])
+@pytest.mark.parametrize("heads,kv_heads,head_dim,rotary", [(4, 2, 16, 16), (6, 3, 24, 24), (2, 1, 64, 32)])
+def test_rope_cache_write(dtype, tol, heads, kv_heads, head_dim, rotary):
+    lengths, new = [70, 5, 129], [70, 1, 3]
+    cache, view, batch = _cache_and_batch(dtype, kv_heads, head_dim, lengths, new)
+    n = batch.n_tokens
+    angles = torch.arange(256, dtype=torch.float64)[:, None] * torch.rand(rotary // 2, dtype=torch.float64)[None]
+    table = torch.stack([angles.cos(), angles.sin()], -1).float().to(DEV)
+    qkv = _randn((n, (heads + 2 * kv_heads) * head_dim), torch.float32, 4)
+    q = torch.zeros((n, heads * head_dim), dtype=dtype, device=DEV)
+    before = view.storage.clone()
+    ops().rope_cache_write(qkv, q, view, table, rotary, heads, batch, True)
+    ref_view = type(view)(before.cpu().clone(), view.page_table.cpu(), view.page_size, kv_heads, head_dim, None)
+    ref_q = torch.zeros((n, heads * head_dim), dtype=dtype)
+    cpu_batch = type("B", (), {"n_tokens": n, "tok_pos": batch.tok_pos.cpu(), "tok_seq": batch.tok_seq.cpu(),
+                               "slots": batch.slots.cpu()})
+    PK.rope_cache_write(qkv.cpu(), ref_q, ref_view, table.cpu(), rotary, heads, cpu_batch, True)
+    assert rel_error(q.float().cpu(), ref_q.float()) <= tol
+    assert rel_error(view.storage.float().cpu(), ref_view.storage.float()) <= tol
+    # only the new tokens' rows changed
+    changed = (view.storage != before).any(dim=-1).sum().item()
+    assert changed <= n * kv_heads * 2
+    q2 = torch.zeros_like(q)
+    snapshot = view.storage.clone()
+    ops().rope_cache_write(qkv, q2, view, table, rotary, heads, batch, False)
+    assert torch.equal(q2, q) and torch.equal(view.storage, snapshot)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_add_residual(dtype):
+    x = _randn((7, 33), torch.float32, 1)
+    u = _randn((7, 33), dtype, 2)
+    want = x + u.float()
+    ops().add_residual(x, u)
+    assert torch.equal(x, want)
+
+
+def _sample_both(logits, options, seeds):
+    """Tokens chosen by the kernel and by the plain sampler for each row, three draws per row."""
+    import plain_llama as P
+
+    rows = logits.shape[0]
+    dev = logits.to(DEV)
+    rng = torch.zeros((rows + 3, 4), dtype=torch.int64, device=DEV)
+    stream_rows = torch.arange(rows, dtype=torch.int32, device=DEV) + 2
+    wrapped = torch.tensor([((s % 2**64) + 2**63) % 2**64 - 2**63 for s in seeds], dtype=torch.int64, device=DEV)
+    ops().seed_rng(rng, stream_rows, wrapped)
+    scratch = torch.empty(rows * logits.shape[1], dtype=torch.float32, device=DEV)
+    got, want = [], []
+    randoms = [P.Random(s) for s in seeds]
+    for _ in range(3):
+        out = torch.empty(rows, dtype=torch.int32, device=DEV)
+        ops().sample(out, dev, scratch, rng, stream_rows, options["temperature"], options.get("top_k", 0),
+                     options.get("top_p", 1.0), options.get("min_p", 0.0))
+        got.append(out.tolist())
+        want.append([P.sample(logits[r].numpy(), randoms[r], **options) for r in range(rows)])
+    return got, want
+
+
+@pytest.mark.parametrize("options", [
+    {"temperature": 0.0}, {"temperature": 0.8}, {"temperature": 1.5, "top_k": 7},
+    {"temperature": 1.0, "top_p": 0.6}, {"temperature": 2.0, "min_p": 0.05},
+    {"temperature": 1.3, "top_k": 20, "top_p": 0.9, "min_p": 0.02}, {"temperature": 0.3, "top_k": 1},
+])
+@pytest.mark.parametrize("vocab", [384, 5000, 49153])
+def test_sample_matches_plain_sampler(options, vocab):
+    g = torch.Generator().manual_seed(vocab)
+    logits = torch.randn((6, vocab), generator=g) * 3
+    seeds = [0, 1, 2**64 + 5, 12345678901234567890, 7, 99]
+    got, want = _sample_both(logits, options, seeds)
+    assert got == want
+
+
+def test_sample_ties_go_to_the_lower_id():
+    logits = torch.zeros((4, 1000))
+    logits[0, [5, 700]] = 3.0      # two equal maxima
+    logits[1, :] = 1.0             # all equal
+    logits[2, [999, 0, 500]] = 2.0
+    logits[3, 10:20] = 5.0
+    got, want = _sample_both(logits, {"temperature": 0.0}, [0, 0, 0, 0])
+    assert got == want and got[0] == [5, 0, 0, 10]
+    for options in ({"temperature": 1.0}, {"temperature": 1.0, "top_k": 3}, {"temperature": 0.7, "top_p": 0.5},
+                    {"temperature": 1.0, "min_p": 1.0}):
+        got, want = _sample_both(logits, options, [3, 4, 5, 6])
+        assert got == want, options
