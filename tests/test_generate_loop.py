@@ -1,0 +1,99 @@
+"""The generation loop's decisions (no GPU), driven with a scripted model."""
+import pytest
+
+from etalii.dllm_b200.engine.generate import (BatchRun, ContextLengthError, GenerationResult, check_prompts,
+                                              plan_batches, run_batches)
+
+
+def test_plan_batches_fits_pages_and_slots():
+    assert plan_batches([10, 10, 10], 10, 1000, 64, 100, 8) == [[0, 1, 2]]
+    assert plan_batches([10, 10, 10], 10, 1000, 64, 2, 8) == [[0, 1], [2]]
+    assert plan_batches([10] * 5, 10, 1000, 64, 100, 8, max_batch=2) == [[0, 1], [2, 3], [4]]
+    assert plan_batches([100, 10], 1000, 128, 64, 3, 8) == [[0], [1]]  # a sequence is capped by the window
+    with pytest.raises(ContextLengthError):
+        plan_batches([100], 100, 1000, 64, 2, 8)
+
+
+def test_check_prompts():
+    check_prompts([[1, 2], [3]], 10, 5)
+    with pytest.raises(ContextLengthError, match="5 tokens; the context window holds 5"):
+        check_prompts([[1] * 5], 10, 5)
+    with pytest.raises(ValueError, match="outside the vocabulary"):
+        check_prompts([[1, 10]], 10, 5)
+    with pytest.raises(ValueError, match="empty"):
+        check_prompts([[]], 10, 5)
+
+
+def test_batch_run_rules():
+    run = BatchRun([3, 5, 2], max_new_tokens=3, stop_ids=frozenset({9}), context_length=7)
+    assert run.active == [0, 1, 2]
+    assert run.accept([4, 9, 4]) == [1]           # a stop token ends its sequence and is not output
+    assert run.active == [0, 2]
+    assert run.accept([5, 5]) == []
+    assert run.accept([6, 9]) == [0, 2]           # max_new_tokens reached; a late stop token
+    results = run.results()
+    assert [r.tokens for r in results] == [(4, 5, 6), (), (4, 5)]
+    assert [r.finish_reason for r in results] == ["length", "stop", "stop"]
+    assert [r.prompt_tokens for r in results] == [3, 5, 2]
+    window = BatchRun([5], max_new_tokens=10, stop_ids=frozenset(), context_length=7)
+    assert window.accept([1]) == [] and window.accept([1]) == [0]  # the context is full at 7 tokens
+    assert window.results()[0].finish_reason == "length" and len(window.results()[0].tokens) == 2
+    nothing = BatchRun([4], max_new_tokens=0, stop_ids=frozenset(), context_length=9)
+    assert nothing.active == [] and nothing.results()[0] == GenerationResult((), 4, "length")
+
+
+def test_fingerprint_is_the_hash_of_int32_ids():
+    import hashlib
+
+    result = GenerationResult((1, 2, 300), 2, "stop")
+    assert result.fingerprint == hashlib.sha256(bytes([1, 0, 0, 0, 2, 0, 0, 0, 44, 1, 0, 0])).hexdigest()
+
+
+class Scripted:
+    """A stand-in for the device side: sequence i answers token (last fed + 1); records what it was asked."""
+
+    def __init__(self):
+        self.open, self.log, self.next_handle = {}, [], 0
+
+    def start(self, indices):
+        self.next_handle += 1
+        self.open[self.next_handle] = set(range(len(indices)))
+        return self.next_handle
+
+    def step(self, handle, positions, tokens, first):
+        assert set(positions) <= self.open[handle]
+        assert all(len(t) == 1 for t in tokens) or first
+        self.log.append((handle, list(positions), [len(t) for t in tokens]))
+        return [t[-1] + 1 for t in tokens]
+
+    def finish(self, handle, positions):
+        for p in (positions if positions is not None else list(self.open[handle])):
+            self.open[handle].remove(p)  # KeyError if something is given back twice
+
+
+def test_run_batches_shorter_requests_end_earlier_and_everything_is_given_back():
+    prompts = [[10, 11], [20], [30, 31, 32], [40]]
+    fake = Scripted()
+
+    def make_run(indices):
+        return BatchRun([len(prompts[i]) for i in indices], 4, frozenset({22, 42}), 100)
+
+    results = run_batches(prompts, [[0, 1], [2, 3]], make_run, fake.start, fake.step, fake.finish)
+    assert [r.tokens for r in results] == [(12, 13, 14, 15), (21,), (33, 34, 35, 36), (41,)]
+    assert [r.finish_reason for r in results] == ["length", "stop", "length", "stop"]
+    assert all(not left for left in fake.open.values())
+    # the first step carries whole prompts, later steps one token each, and only for sequences still running
+    assert fake.log[0] == (1, [0, 1], [2, 1]) and fake.log[1] == (1, [0, 1], [1, 1]) and fake.log[2] == (1, [0], [1])
+    assert fake.log[4][0] == 2
+
+
+def test_run_batches_gives_back_on_error():
+    fake = Scripted()
+
+    def failing(handle, positions, tokens, first):
+        raise RuntimeError("device lost")
+
+    with pytest.raises(RuntimeError):
+        run_batches([[1], [2]], [[0, 1]], lambda ix: BatchRun([1, 1], 2, frozenset(), 10), fake.start, failing,
+                    fake.finish)
+    assert all(not left for left in fake.open.values())
