@@ -1,0 +1,260 @@
+"""Measures decode and prefill throughput of the engine on one B200 and prints ONE JSON line.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
+
+Default workload: the SmolLM2-135M shape (30 layers, hidden 576, 9 heads, 3 kv heads, head_dim 64, intermediate 1536,
+vocabulary 49152, tied head) with seeded random bfloat16 weights; a batch of 8 sequences with unequal prompt lengths
+(128 to 2,048 seeded random tokens) inside a context of 8,192. A "step" is one decode step of the whole batch
+(model, greedy token choice, feedback), replayed as a CUDA graph; `value` is decoded tokens per second over exactly K
+steps timed with CUDA events. `e2e` is the same through `Engine.generate` with host token lists in and out.
+`prefill` is one 2,048-token prompt in one step. `roofline` relates the decode step to HBM bandwidth: every weight
+read once plus the cache of the live sequences, over the step's time. `points` repeats the decode at batch 1 and 64.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SMOLLM2_135M = {
+    "model_type": "llama", "num_hidden_layers": 30, "hidden_size": 576, "num_attention_heads": 9,
+    "num_key_value_heads": 3, "head_dim": 64, "intermediate_size": 1536, "vocab_size": 49152,
+    "rope_theta": 100000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "max_position_embeddings": 8192,
+    "hidden_act": "silu", "bos_token_id": 1, "eos_token_id": 2,
+}
+FULL_LAYERS = SMOLLM2_135M["num_hidden_layers"]
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        with open(path) as handle:
+            data = json.load(handle)
+        return {"hbm_gbs": float(data["hbm_gbs"]), "bf16_tflops": float(data["bf16_tflops"]), "source": "measured"}
+    return dict(FALLBACK_PEAKS, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.samples, self.process = [], None
+
+    def __enter__(self):
+        try:
+            self.process = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.process = None
+        return self
+
+    def _read(self):
+        for line in self.process.stdout:
+            self.samples.append([part.strip() for part in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.process is not None:
+            time.sleep(0.15)
+            self.process.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        clocks = sorted(int(s[0]) for s in self.samples if s and s[0].isdigit())
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({name for s in self.samples if len(s) >= 6
+                          for name, flag in zip(names, s[2:6]) if flag.lower().startswith("active")})
+        top = max((int(s[1]) for s in self.samples if len(s) > 1 and s[1].isdigit()), default=None)
+        return {"sm_mhz": clocks[len(clocks) // 2] if clocks else None, "sm_max_mhz": top, "reasons": reasons,
+                "samples": len(clocks)}
+
+
+def make_prompts(batch, vocab, seed):
+    import numpy as np
+
+    rng = np.random.default_rng(seed)
+    lengths = rng.integers(128, PREFILL_TOKENS + 1, batch).tolist()
+    lengths[0] = PREFILL_TOKENS if batch > 1 else 1088  # the longest length is always present; batch 1: the mean
+    return [rng.integers(0, vocab, n).tolist() for n in lengths]
+
+
+def decode_run(engine, prompts, steps, warmup):
+    """Device-timed decode: returns (milliseconds for `steps` steps, launches per step, cached tokens at the end)."""
+    import torch
+
+    from etalii.dllm_b200 import SamplingOptions
+
+    slots = engine.open(len(prompts))
+    tokens = []
+    for begin in range(0, len(prompts), 8):  # prompts enter the cache eight at a time
+        part = slice(begin, begin + 8)
+        logits = engine.step(slots[part], prompts[part])
+        tokens += engine.sampler.choose(logits, engine.last_batch.slots, SamplingOptions()).tolist()
+    graph = engine._decode_graph(len(prompts), SamplingOptions())
+    done = 0
+    while done < warmup:  # warm-up steps (the first run also captures the graph)
+        n = min(graph.CAPACITY, warmup - done)
+        tokens = engine.decode(slots, tokens, n)[-1]
+        done += n
+    total_ms, done = 0.0, 0
+    while done < steps:
+        n = min(graph.CAPACITY, steps - done)
+        engine.decode_start(graph, slots, tokens, n)
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        graph.replay(n)
+        end.record()
+        torch.cuda.synchronize()
+        total_ms += begin.elapsed_time(end)
+        tokens = graph.tokens(n)[-1]
+        done += n
+    cached = sum(engine.cache.length(s) for s in slots)
+    engine.close(slots)
+    return total_ms, graph.launches_per_step, cached
+
+
+def prefill_run(engine, vocab, warmup, repeats=5):
+    import numpy as np
+    import torch
+
+    prompt = np.random.default_rng(7).integers(0, vocab, PREFILL_TOKENS).tolist()
+    times = []
+    for index in range(warmup + repeats):
+        slot = engine.open(1)
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        engine.step(slot, [prompt])
+        end.record()
+        torch.cuda.synchronize()
+        engine.close(slot)
+        if index >= warmup:
+            times.append(begin.elapsed_time(end))
+    return sum(times) / len(times)
+
+
+def model_numbers(config, layers):
+    h, i, v = config["hidden_size"], config["intermediate_size"], config["vocab_size"]
+    nh, nkv, hd = config["num_attention_heads"], config["num_key_value_heads"], config["head_dim"]
+    per_layer = h * (nh + 2 * nkv) * hd + nh * hd * h + 3 * h * i
+    matrix_params = layers * per_layer
+    norm_params = (2 * layers + 1) * h
+    kv_bytes_per_token = layers * 2 * nkv * hd * 2
+    t = PREFILL_TOKENS
+    prefill_flops = 2 * matrix_params * t + layers * 4 * hd * nh * t * (t + 1) // 2 + 2 * h * v
+    return {"matrix_params": matrix_params, "head_params": v * h, "norm_params": norm_params,
+            "kv_bytes_per_token": kv_bytes_per_token, "prefill_flops": prefill_flops}
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=64)
+    parser.add_argument("--warmup", type=int, default=8)
+    parser.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the full model (named in config)")
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    parser.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 decode points")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference does not install offline: its build needs scikit-build-core with nanobind, "
+                          "and nanobind is not in the wheelhouse"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py measures one GPU: --gpus {args.gpus} is not supported (this library runs on a single device)")
+        return 2
+    warmup = max(3, args.warmup)
+
+    import torch
+
+    from etalii.dllm_b200 import SamplingOptions
+    from etalii.dllm_b200.config.registry import config_from_dict
+    from etalii.dllm_b200.engine.engine import Engine
+    from etalii.dllm_b200.kernels import ops
+
+    config_dict = dict(SMOLLM2_135M, num_hidden_layers=args.layers)
+    config = config_from_dict(config_dict)
+    numbers = model_numbers(config_dict, args.layers)
+    cache_tokens = 64 * (PREFILL_TOKENS + 64 * ((warmup + args.steps) // 64 + 3))
+    engine = Engine.from_random(config, seed=0, dtype="bfloat16", device="cuda:0", max_tokens=cache_tokens,
+                                max_length=config_dict["max_position_embeddings"])
+    peak = peaks()
+    vocab = config_dict["vocab_size"]
+
+    prompts = make_prompts(args.batch, vocab, seed=1)
+    decode_run(engine, prompts, 4, 3)  # builds kernels, work buffers and the graph before anything is timed
+    with ClockSampler() as clocks:
+        ms, launches_per_step, cached = decode_run(engine, prompts, args.steps, warmup)
+    ms_per_step = ms / args.steps
+    value = args.batch * args.steps / (ms / 1e3)
+
+    weight_bytes = 2 * (numbers["matrix_params"] + numbers["head_params"]) + 4 * numbers["norm_params"]
+    mean_cached = cached - args.batch * args.steps / 2  # halfway through the timed steps
+    step_bytes = weight_bytes + mean_cached * numbers["kv_bytes_per_token"]
+    achieved = step_bytes / (ms_per_step / 1e3) / 1e9
+
+    prefill_ms = prefill_run(engine, vocab, warmup=3)
+    prefill = {"value": round(PREFILL_TOKENS / (prefill_ms / 1e3), 1), "tokens": PREFILL_TOKENS,
+               "ms": round(prefill_ms, 4),
+               "frac": round(numbers["prefill_flops"] / (prefill_ms / 1e3) / (peak["bf16_tflops"] * 1e12), 5)}
+
+    # end to end through the public entry point: host token lists in, host token lists out
+    engine.generate(prompts, 20, SamplingOptions(), ignore_eos=True)
+    engine.generate(prompts, args.steps + 1, SamplingOptions(), ignore_eos=True)
+    stats = engine.stats
+    graph = engine._decode_graph(args.batch, SamplingOptions())
+    e2e = {"value": round(stats["decode_tokens"] / stats["decode_s"], 1), "unit": "tokens/s",
+           "h2d_bytes_per_step": round(graph.host.numel() * 4 / engine.decode_chunk, 1),
+           "d2h_bytes_per_step": args.batch * 4}
+
+    points = {}
+    if not args.no_points:
+        for name, batch in (("decode_b1", 1), ("decode_b64", 64)):
+            batch_prompts = make_prompts(batch, vocab, seed=2 + batch)
+            decode_run(engine, batch_prompts, 4, 3)
+            point_ms, _, _ = decode_run(engine, batch_prompts, args.steps, warmup)
+            points[name] = round(batch * args.steps / (point_ms / 1e3), 1)
+
+    line = {
+        "metric": "decode tokens/s (SmolLM2-135M shape, batch 8, bf16, random weights)", "value": round(value, 1),
+        "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
+        "ms_per_step": round(ms_per_step, 5), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: seeded random token ids, seeded random weights N(0, 0.02)",
+        "config": {
+            "model": "SmolLM2-135M shape (llama)", "global_batch": args.batch, "seq_len": config_dict["max_position_embeddings"],
+            "parallelism": "single GPU", "layers": args.layers, "layers_full_model": FULL_LAYERS,
+            "hidden": config_dict["hidden_size"], "heads": config_dict["num_attention_heads"],
+            "kv_heads": config_dict["num_key_value_heads"], "head_dim": config_dict["head_dim"],
+            "intermediate": config_dict["intermediate_size"], "vocab": vocab,
+            "prompt_lengths": "128-2048 unequal", "mean_cached_tokens_per_seq": round(mean_cached / args.batch, 1),
+            "l2": "inputs larger than L2 (weights 269 MB + cache per step)", "sampling": "greedy, on device",
+            "decode": "CUDA graph per batch size", "peaks": peak["source"],
+        },
+        "clocks": clocks.summary(),
+        "e2e": e2e,
+        "gpu_launches": int(launches_per_step * args.steps),
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peak["hbm_gbs"], 4)},
+        "points": points,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -158,3 +158,28 @@ DLLM_EXPORT int dllm_add_residual(float* residual, const void* update, long long
     return DLLM_BAD_ARGUMENT;
   return dllm_launch_status();
 }
+
+// ---- decode feedback: the chosen tokens become the next step's input, positions move on by one -------------------
+// Lets single-token steps follow one another on the device without the host: tokens[b] = chosen[b], positions and
+// cached lengths + 1, and the chosen tokens are appended to `history` ([capacity, batch]) at row *counter.
+__global__ void decode_advance_kernel(int* __restrict__ tokens, int* __restrict__ tok_pos, int* __restrict__ start,
+                                      const int* __restrict__ chosen, int* __restrict__ history,
+                                      int* __restrict__ counter, int batch, int capacity) {
+  int row = *counter;
+  for (int b = threadIdx.x; b < batch; b += blockDim.x) {
+    int token = chosen[b];
+    tokens[b] = token;
+    tok_pos[b] += 1;
+    start[b] += 1;
+    if (row < capacity) history[(size_t)row * batch + b] = token;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) *counter = row + 1;
+}
+
+DLLM_EXPORT int dllm_decode_advance(int* tokens, int* tok_pos, int* start, const int* chosen, int* history,
+                                    int* counter, int batch, int capacity, cudaStream_t stream) {
+  if (batch <= 0) return DLLM_OK;
+  decode_advance_kernel<<<1, 256, 0, stream>>>(tokens, tok_pos, start, chosen, history, counter, batch, capacity);
+  return dllm_launch_status();
+}

@@ -1,0 +1,93 @@
+"""Single-token steps that follow one another on the device: model step, token choice and feedback of the chosen
+token into the next step's input, captured once per batch size as a CUDA graph and replayed. The host only fills the
+batch's fixed buffers before a run of steps and reads the chosen tokens after it."""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from ..kernels import ops
+from .batch import StepBatch
+
+
+class DecodeGraph:
+    CAPACITY = 64
+    """Most steps one run may take before the host reads the tokens."""
+
+    def __init__(self, engine, batch_size: int, options, use_graph: bool = True) -> None:
+        self.engine, self.b, self.options, self.use_graph = engine, batch_size, options, use_graph
+        b = batch_size
+        device = engine.rt.device
+        self.host = torch.empty(7 * b + 2, dtype=torch.int32).pin_memory()
+        self.meta = torch.zeros(7 * b + 2, dtype=torch.int32, device=device)
+        self.history = torch.zeros(self.CAPACITY * b, dtype=torch.int32, device=device)
+        self.chosen = torch.zeros(b, dtype=torch.int32, device=device)
+        batch = StepBatch()
+        o = 0
+        batch.tokens = self.meta[o:o + b]; o += b
+        batch.tok_seq = self.meta[o:o + b]; o += b
+        batch.tok_pos = self.meta[o:o + b]; o += b
+        batch.cu_seqlens = self.meta[o:o + b + 1]; o += b + 1
+        batch.slots = self.meta[o:o + b]; o += b
+        batch.start = self.meta[o:o + b]; o += b
+        batch.want_rows = self.meta[o:o + b]; o += b
+        self.counter = self.meta[o:o + 1]
+        batch.n_seqs = batch.n_tokens = batch.n_want = b
+        batch.h_new = [1] * b
+        batch.max_new = 1
+        batch.is_decode = True
+        # the captured step serves every length up to the cache's longest sequence
+        batch.max_context = engine.max_length
+        batch.max_position = engine.max_length - 1
+        self.batch = batch
+        self.graph = None
+        self.generation = -1
+        self.launches_per_step = 0
+
+    def _body(self) -> None:
+        logits = self.engine.model.forward(self.batch)
+        self.engine.sampler.choose(logits, self.batch.slots, self.options, out=self.chosen)
+        ops.decode_advance(self.batch.tokens, self.batch.tok_pos, self.batch.start, self.chosen, self.history,
+                           self.counter, self.b)
+
+    def load(self, slots, tokens, starts) -> None:
+        """Fills the fixed buffers: each sequence's slot, next input token and cached length."""
+        b = self.b
+        host = self.host.numpy()
+        arange = np.arange(b, dtype=np.int32)
+        host[0:b] = tokens
+        host[b:2 * b] = arange
+        host[2 * b:3 * b] = starts
+        host[3 * b:4 * b + 1] = np.arange(b + 1, dtype=np.int32)
+        host[4 * b + 1:5 * b + 1] = slots
+        host[5 * b + 1:6 * b + 1] = starts
+        host[6 * b + 1:7 * b + 1] = arange
+        host[7 * b + 1] = 0
+        self.batch.h_slots, self.batch.h_start = list(slots), list(starts)
+        self.meta.copy_(self.host, non_blocking=True)
+
+    def replay(self, steps: int) -> None:
+        """Runs `steps` single-token steps (after `load`); the cache must already have room for them."""
+        ws = self.engine.rt.ws
+        if self.use_graph and (self.graph is None or self.generation != ws.generation):
+            before = ops.launches
+            self._body()  # once outside a capture: builds kernels, sizes work buffers
+            self.launches_per_step = ops.launches - before
+            steps -= 1
+            torch.cuda.synchronize()
+            if steps > 0:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    self._body()
+                self.graph, self.generation = graph, ws.generation
+        for _ in range(steps):
+            if self.use_graph:
+                self.graph.replay()
+            else:
+                before = ops.launches
+                self._body()
+                self.launches_per_step = ops.launches - before
+
+    def tokens(self, steps: int) -> list[list[int]]:
+        """The tokens chosen by the last `steps` steps since `load`: [step][sequence]."""
+        return self.history[: steps * self.b].view(steps, self.b).tolist()

@@ -5,6 +5,7 @@
 (src/etalii_dllm/engine.py:416-595 loads, 694-748 completes)."""
 from __future__ import annotations
 
+import time
 from typing import Sequence
 
 import torch
@@ -17,6 +18,7 @@ from ..sampling.sampler import Sampler
 from ..weights.loader import load_weights
 from ..weights.random_init import random_tensors
 from .batch import BatchBuffers
+from .decode import DecodeGraph
 from .generate import BatchRun, GenerationResult, check_prompts, plan_batches, run_batches
 from .model import Model
 from .runtime import Runtime
@@ -36,10 +38,12 @@ def parse_dtype(dtype) -> torch.dtype:
 
 class Engine:
     def __init__(self, config, tensors, dtype="bfloat16", device="cuda:0", max_tokens: int | None = None,
-                 max_length: int | None = None, max_slots: int | None = None) -> None:
+                 max_length: int | None = None, max_slots: int | None = None, cuda_graphs: bool = True,
+                 decode_chunk: int = 16) -> None:
         """`max_length`: the longest sequence the cache holds (default: the model's max_position_embeddings).
         `max_tokens`: the most tokens all live sequences hold together, each rounded up to whole pages of 64
-        (default: four sequences of max_length)."""
+        (default: four sequences of max_length). `cuda_graphs`: replay decode steps as CUDA graphs (turn off for
+        parts that cannot be captured). `decode_chunk`: decode steps between looks at the chosen tokens."""
         if not torch.cuda.is_available():
             raise RuntimeError("no CUDA device: this library has no CPU path")
         self.config = config
@@ -57,6 +61,10 @@ class Engine:
         self.buffers = BatchBuffers(self.rt.device)
         self.sampler = Sampler(self.cache.n_slots, self.vocab_size, self.rt.device)
         self.steps_run = 0
+        self.cuda_graphs = bool(cuda_graphs)
+        self.decode_chunk = int(decode_chunk)
+        self._graphs: dict = {}
+        self.stats: dict = {}
 
     # ---- construction ----
     @classmethod
@@ -114,6 +122,39 @@ class Engine:
         self.last_batch = batch
         return logits
 
+    def decode(self, slots: Sequence[int], tokens: Sequence[int], steps: int,
+               options: SamplingOptions | None = None) -> list[list[int]]:
+        """Runs `steps` single-token steps for the sequences in `slots`, starting from `tokens` (each sequence's
+        latest token, not yet in the cache); every step's chosen token is the next step's input, on the device.
+        Returns the chosen tokens [step][sequence]. Uses one CUDA graph per batch size and sampling options."""
+        graph = self._decode_graph(len(slots), options or SamplingOptions())
+        self.decode_start(graph, slots, tokens, steps)
+        graph.replay(steps)
+        return graph.tokens(steps)
+
+    def decode_start(self, graph, slots, tokens, steps: int) -> None:
+        """Makes cache room for `steps` more tokens of each sequence and loads the graph's fixed buffers."""
+        if steps > graph.CAPACITY:
+            raise ValueError(f"at most {graph.CAPACITY} steps per run")
+        if len(set(slots)) != len(slots):
+            raise CacheError("a sequence appears twice in one step")
+        starts = []
+        for slot in slots:
+            self.cache.reserve(slot, steps)
+            starts.append(self.cache.length(slot))
+        self.cache.sync_tables()
+        graph.load(slots, tokens, starts)
+        for slot in slots:
+            self.cache.advance(slot, steps)
+        self.steps_run += steps
+
+    def _decode_graph(self, batch_size: int, options: SamplingOptions):
+        key = (batch_size, options.temperature, options.top_k, options.top_p, options.min_p)
+        graph = self._graphs.get(key)
+        if graph is None:
+            graph = self._graphs[key] = DecodeGraph(self, batch_size, options, use_graph=self.cuda_graphs)
+        return graph
+
     # ---- generation ----
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int = 64,
                  options: SamplingOptions | None = None, stop_token_ids: Sequence[int] | None = None,
@@ -122,6 +163,8 @@ class Engine:
         Stop ids default to the model's end-of-sequence ids; `stop_token_ids` adds more; `ignore_eos` drops the
         model's own (src/etalii_dllm/cli.py:427-431). Sequence i draws from the stream of options.seed + i."""
         options = options or SamplingOptions()
+        stats = self.stats = {"prefill_s": 0.0, "prefill_tokens": 0, "decode_s": 0.0, "decode_steps": 0,
+                              "decode_tokens": 0}
         prompts = [list(map(int, p)) for p in prompts]
         window = min(self.context_length, self.max_length)
         check_prompts(prompts, self.vocab_size, window)
@@ -139,11 +182,21 @@ class Engine:
                 self.sampler.seed(slots, [options.seed + i for i in indices])
             return slots
 
-        def step(slots, positions, tokens, first):
-            active = [slots[p] for p in positions]
-            logits = self.step(active, tokens)
-            chosen = self.sampler.choose(logits, self.last_batch.slots, options)
-            return chosen.tolist()
+        def prefill(slots, positions, tokens):
+            began = time.perf_counter()
+            logits = self.step([slots[p] for p in positions], tokens)
+            chosen = self.sampler.choose(logits, self.last_batch.slots, options).tolist()
+            stats["prefill_s"] += time.perf_counter() - began
+            stats["prefill_tokens"] += sum(len(t) for t in tokens)
+            return chosen
+
+        def decode(slots, positions, last_tokens, steps):
+            began = time.perf_counter()
+            out = self.decode([slots[p] for p in positions], last_tokens, steps, options)
+            stats["decode_s"] += time.perf_counter() - began
+            stats["decode_steps"] += steps
+            stats["decode_tokens"] += steps * len(positions)
+            return out
 
         def finish(slots, positions):
             if positions is None:  # an error: give everything still held back
@@ -151,7 +204,7 @@ class Engine:
             else:
                 self.close([slots[p] for p in positions])
 
-        return run_batches(prompts, batches, make_run, start, step, finish)
+        return run_batches(prompts, batches, make_run, start, prefill, decode, finish, chunk=self.decode_chunk)
 
     def complete(self, prompt: Sequence[int], max_tokens: int = 64,
                  options: SamplingOptions | None = None, **kwargs) -> GenerationResult:

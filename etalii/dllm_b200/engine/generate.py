@@ -110,35 +110,56 @@ class BatchRun:
         self.active = still
         return ended
 
+    def steps_left(self) -> int:
+        """How many more tokens every active sequence may still produce before a length limit ends one."""
+        return min(min(self.max_new_tokens - len(self.outputs[p]),
+                       self.context_length - self.prompt_lengths[p] - len(self.outputs[p]))
+                   for p in self.active)
+
     def results(self) -> list[GenerationResult]:
         return [GenerationResult(tuple(out), n, reason or "length")
                 for out, n, reason in zip(self.outputs, self.prompt_lengths, self.finish)]
 
 
-def run_batches(prompts: Sequence[Sequence[int]], batches: Sequence[Sequence[int]], make_run: Callable[[list[int]], BatchRun],
-                start: Callable, step: Callable, finish: Callable) -> list[GenerationResult]:
-    """Drives batches one after another. `start(indices) -> handle` takes cache room for a batch,
-    `step(handle, positions, tokens_per_position, first) -> chosen tokens` runs one model step for the named batch
-    positions and `finish(handle, positions)` gives back what ended sequences hold."""
+def run_batches(prompts: Sequence[Sequence[int]], batches: Sequence[Sequence[int]],
+                make_run: Callable[[list[int]], BatchRun], start: Callable, prefill: Callable, decode: Callable,
+                finish: Callable, chunk: int = 16) -> list[GenerationResult]:
+    """Drives batches one after another. `start(indices) -> handle` takes cache room for a batch;
+    `prefill(handle, positions, prompts) -> tokens` runs the whole prompts of the named batch positions and chooses
+    each one's first token; `decode(handle, positions, last_tokens, steps) -> [step][position] tokens` runs up to
+    `steps` single-token steps without looking at the tokens in between; `finish(handle, positions)` gives back
+    what ended sequences hold (None: everything, after an error).
+
+    A sequence that ends inside a run of decode steps keeps its place until the run is over; what was chosen for
+    it after its end is dropped."""
     results: list[GenerationResult | None] = [None] * len(prompts)
     for indices in batches:
         run = make_run(list(indices))
         handle = start(list(indices))
         try:
-            feed = [list(prompts[i]) for i in indices]
+            idle = [p for p in range(len(indices)) if p not in run.active]
+            if idle:
+                finish(handle, idle)
+            last: dict[int, int] = {}
             first = True
             while run.active:
                 positions = list(run.active)
-                chosen = step(handle, positions, [feed[p] for p in positions], first)
-                ended = run.accept(chosen)
-                for p, token in zip(positions, chosen):
-                    feed[p] = [int(token)]
+                if first:
+                    steps = [prefill(handle, positions, [list(prompts[indices[p]]) for p in positions])]
+                    first = False
+                else:
+                    steps = decode(handle, positions, [last[p] for p in positions], min(chunk, run.steps_left()))
+                ended: list[int] = []
+                for chosen in steps:
+                    by_position = dict(zip(positions, chosen))
+                    live = list(run.active)
+                    if not live:
+                        break
+                    ended += run.accept([by_position[p] for p in live])
+                    for p in live:
+                        last[p] = int(by_position[p])
                 if ended:
                     finish(handle, ended)
-                first = False
-            idle = [p for p in range(len(indices)) if run.max_new_tokens <= 0]
-            if idle:
-                finish(handle, idle)
         except BaseException:
             finish(handle, None)
             raise

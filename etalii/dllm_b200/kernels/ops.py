@@ -26,6 +26,8 @@ _prototypes = {
                                                c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                                c_int, c_void_p],
     ("elementwise", "dllm_add_residual"): [c_void_p, c_void_p, c_longlong, c_int, c_void_p],
+    ("elementwise", "dllm_decode_advance"): [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                             c_void_p],
     ("gemm_simt", "dllm_gemm_f32"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     ("gemm_bf16", "dllm_gemm_bf16"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     ("attention", "dllm_attention_general"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
@@ -36,6 +38,10 @@ _prototypes = {
     ("sampling", "dllm_seed_rng"): [c_void_p, c_void_p, c_void_p, c_int, c_void_p],
 }
 _functions: dict[tuple[str, str], ctypes._CFuncPtr] = {}
+
+
+launches = 0
+"""How many kernels this module has launched (every call below launches exactly one)."""
 
 
 def _fn(lib: str, name: str):
@@ -50,6 +56,8 @@ def _fn(lib: str, name: str):
 
 
 def _check(status: int, what: str, detail: str = "") -> None:
+    global launches
+    launches += 1
     if status != 0:
         raise KernelError(f"{what}: {_STATUS.get(status, status)}{(' (' + detail + ')') if detail else ''}")
 
@@ -179,3 +187,12 @@ def seed_rng(rng: torch.Tensor, rows: torch.Tensor, seeds: torch.Tensor) -> None
     assert rng.dtype == torch.int64 and rows.dtype == torch.int32 and seeds.dtype == torch.int64
     _check(_fn("sampling", "dllm_seed_rng")(rng.data_ptr(), rows.data_ptr(), seeds.data_ptr(), rows.numel(),
                                             _stream()), "seed_rng")
+
+
+def decode_advance(tokens: torch.Tensor, tok_pos: torch.Tensor, start: torch.Tensor, chosen: torch.Tensor,
+                   history: torch.Tensor, counter: torch.Tensor, batch: int) -> None:
+    """tokens = chosen; positions and cached lengths + 1; history[counter] = chosen; counter + 1 (all int32)."""
+    _cuda(tokens, tok_pos, start, chosen, history, counter)
+    _check(_fn("elementwise", "dllm_decode_advance")(
+        tokens.data_ptr(), tok_pos.data_ptr(), start.data_ptr(), chosen.data_ptr(), history.data_ptr(),
+        counter.data_ptr(), batch, history.numel() // batch, _stream()), "decode_advance")

@@ -125,3 +125,13 @@ def seed_rng(rng, rows, seeds):
     for row, seed in zip(rows.tolist(), seeds.tolist()):
         _Rng.store(fresh, row, P.Random(int(seed) % (1 << 64)))
     rng.copy_(fresh)
+
+
+def decode_advance(tokens, tok_pos, start, chosen, history, counter, batch):
+    row = int(counter[0])
+    tokens[:batch] = chosen[:batch]
+    tok_pos[:batch] += 1
+    start[:batch] += 1
+    if row < history.numel() // batch:
+        history[row * batch:(row + 1) * batch] = chosen[:batch]
+    counter[0] = row + 1

@@ -50,7 +50,7 @@ def test_fingerprint_is_the_hash_of_int32_ids():
 
 
 class Scripted:
-    """A stand-in for the device side: sequence i answers token (last fed + 1); records what it was asked."""
+    """A stand-in for the device side: a sequence answers (last fed token + 1); records what it was asked."""
 
     def __init__(self):
         self.open, self.log, self.next_handle = {}, [], 0
@@ -60,40 +60,57 @@ class Scripted:
         self.open[self.next_handle] = set(range(len(indices)))
         return self.next_handle
 
-    def step(self, handle, positions, tokens, first):
+    def prefill(self, handle, positions, prompts):
         assert set(positions) <= self.open[handle]
-        assert all(len(t) == 1 for t in tokens) or first
-        self.log.append((handle, list(positions), [len(t) for t in tokens]))
-        return [t[-1] + 1 for t in tokens]
+        self.log.append(("prefill", handle, list(positions), [len(p) for p in prompts]))
+        return [p[-1] + 1 for p in prompts]
+
+    def decode(self, handle, positions, last, steps):
+        assert set(positions) <= self.open[handle] and steps >= 1
+        self.log.append(("decode", handle, list(positions), steps))
+        return [[t + 1 + k for t in last] for k in range(steps)]
 
     def finish(self, handle, positions):
         for p in (positions if positions is not None else list(self.open[handle])):
             self.open[handle].remove(p)  # KeyError if something is given back twice
 
 
-def test_run_batches_shorter_requests_end_earlier_and_everything_is_given_back():
+def _run(prompts, batches, fake, max_new, stops, window=100, chunk=16):
+    def make_run(indices):
+        return BatchRun([len(prompts[i]) for i in indices], max_new, frozenset(stops), window)
+
+    return run_batches(prompts, batches, make_run, fake.start, fake.prefill, fake.decode, fake.finish, chunk=chunk)
+
+
+@pytest.mark.parametrize("chunk", [1, 2, 16])
+def test_run_batches_shorter_requests_end_earlier_and_everything_is_given_back(chunk):
     prompts = [[10, 11], [20], [30, 31, 32], [40]]
     fake = Scripted()
-
-    def make_run(indices):
-        return BatchRun([len(prompts[i]) for i in indices], 4, frozenset({22, 42}), 100)
-
-    results = run_batches(prompts, [[0, 1], [2, 3]], make_run, fake.start, fake.step, fake.finish)
-    assert [r.tokens for r in results] == [(12, 13, 14, 15), (21,), (33, 34, 35, 36), (41,)]
+    results = _run(prompts, [[0, 1], [2, 3]], fake, 4, {23, 42}, chunk=chunk)
+    assert [r.tokens for r in results] == [(12, 13, 14, 15), (21, 22), (33, 34, 35, 36), (41,)]
     assert [r.finish_reason for r in results] == ["length", "stop", "length", "stop"]
     assert all(not left for left in fake.open.values())
-    # the first step carries whole prompts, later steps one token each, and only for sequences still running
-    assert fake.log[0] == (1, [0, 1], [2, 1]) and fake.log[1] == (1, [0, 1], [1, 1]) and fake.log[2] == (1, [0], [1])
-    assert fake.log[4][0] == 2
+    assert fake.log[0] == ("prefill", 1, [0, 1], [2, 1])
+    if chunk == 1:  # one token each per step, and only for sequences still running
+        assert fake.log[1:4] == [("decode", 1, [0, 1], 1), ("decode", 1, [0, 1], 1), ("decode", 1, [0], 1)]
+    else:  # never more steps in a run than every active sequence may still take
+        assert all(entry[3] <= 3 for entry in fake.log if entry[0] == "decode")
+
+
+def test_zero_max_tokens_runs_nothing():
+    fake = Scripted()
+    results = _run([[1, 2], [3]], [[0, 1]], fake, 0, set())
+    assert [r.tokens for r in results] == [(), ()] and fake.log == []
+    assert all(not left for left in fake.open.values())
 
 
 def test_run_batches_gives_back_on_error():
     fake = Scripted()
 
-    def failing(handle, positions, tokens, first):
+    def failing(handle, positions, prompts):
         raise RuntimeError("device lost")
 
     with pytest.raises(RuntimeError):
         run_batches([[1], [2]], [[0, 1]], lambda ix: BatchRun([1, 1], 2, frozenset(), 10), fake.start, failing,
-                    fake.finish)
+                    fake.decode, fake.finish)
     assert all(not left for left in fake.open.values())
