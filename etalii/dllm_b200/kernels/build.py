@@ -25,6 +25,7 @@ SOURCES = {
     "gemm_simt": "gemm_simt.cu",
     "gemm_bf16": "gemm_bf16.cu",
     "attention": "attention.cu",
+    "attention_decode": "attention_decode.cu",
     "sampling": "sampling.cu",
 }
 """Library name -> source file. A library added here is built by `build_all` and loadable by `library`."""

@@ -11,6 +11,15 @@ from .registry import build_part, register_part
 from .spec import ParamSpec
 
 
+def decode_chunk(sequences: int, kv_heads: int, max_context: int) -> int:
+    """Keys per block of the decode kernel: small chunks spread few sequences over the whole device, larger ones
+    keep the number of blocks (one per chunk, kv head and sequence) in bounds."""
+    for chunk in (64, 128, 256, 512):
+        if -(-max_context // chunk) * kv_heads * sequences <= 8192:
+            return chunk
+    return 1024
+
+
 class Attention:
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
                  window: int | None = None, position=None) -> None:
@@ -50,7 +59,14 @@ class Attention:
         rotary_dim = self.position.rotary_dim if self.position is not None else 0
         ops.rope_cache_write(qkv, q, cache, table, rotary_dim, self.num_heads, batch, write_cache)
         attended = rt.ws.buffer("attended", (n, q_size), rt.dtype)
-        ops.attention_general(attended, q, cache, self.num_heads, self.scale, self.window or 0, batch)
+        if batch.is_decode and rt.dtype == torch.bfloat16:
+            chunk = decode_chunk(batch.n_seqs, self.num_kv_heads, batch.max_context)
+            scratch = rt.ws.buffer("attention_scratch", (ops.attention_decode_scratch(
+                batch.n_seqs, self.num_heads, self.head_dim, chunk, batch.max_context),), torch.float32)
+            ops.attention_decode(attended, q, cache, self.num_heads, self.scale, self.window or 0, batch, chunk,
+                                 scratch)
+        else:
+            ops.attention_general(attended, q, cache, self.num_heads, self.scale, self.window or 0, batch)
         ops.gemm(residual, attended, self.w_o, ops.EPI_RESIDUAL)
 
 

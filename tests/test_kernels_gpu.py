@@ -250,3 +250,46 @@ def test_sample_ties_go_to_the_lower_id():
                     {"temperature": 1.0, "min_p": 1.0}):
         got, want = _sample_both(logits, options, [3, 4, 5, 6])
         assert got == want, options
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,window", [(4, 2, 16, None), (6, 3, 24, None), (9, 3, 64, None),
+                                                           (8, 1, 128, 70), (5, 5, 40, 33), (12, 1, 256, None),
+                                                           (20, 2, 96, 300)])
+@pytest.mark.parametrize("chunk", [64, 256])
+def test_attention_decode(heads, kv_heads, head_dim, window, chunk):
+    lengths = [130, 67, 1, 700, 64, 65]
+    cache, view, batch = _cache_and_batch(torch.bfloat16, kv_heads, head_dim, lengths, [1] * len(lengths), window)
+    n = batch.n_tokens
+    q = _randn((n, heads * head_dim), torch.bfloat16, 9)
+    out = torch.zeros((n, heads * head_dim), dtype=torch.bfloat16, device=DEV)
+    ref = torch.zeros((n, heads * head_dim), dtype=torch.bfloat16)
+    batch.max_context = 1024  # sized for more than any sequence holds, as under a CUDA graph
+    scratch = torch.full((ops().attention_decode_scratch(n, heads, head_dim, chunk, 1024),), float("nan"),
+                         dtype=torch.float32, device=DEV)
+    ops().attention_decode(out, q, view, heads, 0.3, window or 0, batch, chunk, scratch)
+    view_cpu = type(view)(view.storage.cpu(), view.page_table.cpu(), view.page_size, kv_heads, head_dim, window)
+    cpu_batch = type("B", (), {"n_tokens": n, "tok_pos": batch.tok_pos.cpu(), "tok_seq": batch.tok_seq.cpu(),
+                               "slots": batch.slots.cpu()})
+    PK.attention_general(ref, q.cpu(), view_cpu, heads, 0.3, window or 0, cpu_batch)
+    assert rel_error(out.float().cpu(), ref.float()) <= 8e-3
+    general = torch.zeros_like(out)
+    ops().attention_general(general, q, view, heads, 0.3, window or 0, batch)
+    assert rel_error(out.float().cpu(), general.float().cpu()) <= 8e-3
+
+
+def test_attention_decode_finds_a_far_key():
+    heads, kv_heads, hd = 4, 2, 32
+    cache, view, batch = _cache_and_batch(torch.bfloat16, kv_heads, hd, [700], [1])
+    view.storage.mul_(0.05)
+    slot = batch.h_slots[0]
+    scratch = torch.zeros(ops().attention_decode_scratch(1, heads, hd, 64, 700), dtype=torch.float32, device=DEV)
+    for target in (0, 63, 64, 333, 698, 699):
+        page = int(view.page_table[slot, target // 64])
+        saved = view.storage[page].clone()
+        view.storage[page, 0, :, target % 64, :] = 4.0
+        view.storage[page, 1, :, target % 64, :] = 7.0
+        q = torch.full((1, heads * hd), 4.0, dtype=torch.bfloat16, device=DEV)
+        out = torch.zeros_like(q)
+        ops().attention_decode(out, q, view, heads, 1.0, 0, batch, 64, scratch)
+        assert torch.allclose(out.float(), torch.full_like(out, 7.0).float(), atol=0.05), target
+        view.storage[page] = saved
