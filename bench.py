@@ -168,6 +168,8 @@ def main() -> int:
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
     parser.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 decode points")
+    parser.add_argument("--profile", choices=("decode", "prefill"),
+                        help="run only a few decode steps (or one prefill) and print no JSON: a small case for ncu")
     args = parser.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -196,6 +198,13 @@ def main() -> int:
     vocab = config_dict["vocab_size"]
 
     prompts = make_prompts(args.batch, vocab, seed=1)
+    if args.profile == "decode":
+        ms, launches, _ = decode_run(engine, prompts, args.steps, 3)
+        print(f"profile decode: {args.steps} steps, {ms / args.steps:.4f} ms per step, {launches} launches per step")
+        return 0
+    if args.profile == "prefill":
+        print(f"profile prefill: {prefill_run(engine, vocab, warmup=1, repeats=1):.4f} ms")
+        return 0
     decode_run(engine, prompts, 4, 3)  # builds kernels, work buffers and the graph before anything is timed
     with ClockSampler() as clocks:
         ms, launches_per_step, cached = decode_run(engine, prompts, args.steps, warmup)

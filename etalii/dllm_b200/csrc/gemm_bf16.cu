@@ -1,9 +1,6 @@
-// bfloat16 matrix products with float32 accumulation, two kernels:
-//   - a tensor-core tile kernel (mma.sync m16n8k16, cp.async 3-stage pipeline) for any M;
-//   - a weight-streaming kernel for M <= 16 (decode): each warp reads whole rows of W once with 16-byte loads and
-//     keeps M accumulators per row, so the step's time is the time to read W.
-// Both end in the shared epilogues (store, residual add in float32, SwiGLU). K must be a multiple of 8 (16-byte
-// rows) and N even; anything else is refused.
+// bfloat16 matrix product with float32 accumulation on the tensor cores (mma.sync m16n8k16, cp.async 3-stage
+// pipeline), for any M, ending in the shared epilogues (store, residual add in float32, SwiGLU). K must be a
+// multiple of 8 (16-byte rows) and N even; anything else is refused. (Decode-sized products run in gemv.cu.)
 #include "gemm_common.cuh"
 
 namespace {
@@ -118,88 +115,6 @@ __global__ void __launch_bounds__(THREADS) gemm_bf16_mma_kernel(void* __restrict
     }
 }
 
-// ---------------------------------------------------------------------------------------------------------------
-// weight-streaming kernel for M <= 16
-// ---------------------------------------------------------------------------------------------------------------
-constexpr int GV_WARPS = 8, GV_ROWS = 4;  // rows of W per warp pass
-
-__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
-  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    float2 x = __bfloat1622float2(p[i]);
-    f[2 * i] = x.x;
-    f[2 * i + 1] = x.y;
-  }
-}
-
-template <int MT, int EPI>
-__global__ void __launch_bounds__(GV_WARPS * 32) gemv_bf16_kernel(void* __restrict__ c, const bf16* __restrict__ a,
-                                                                  const bf16* __restrict__ w, int M, int N, int K) {
-  int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  int chunks = K >> 3;
-  int groups = (N + GV_ROWS - 1) / GV_ROWS;
-  for (int group = blockIdx.x * GV_WARPS + warp; group < groups; group += gridDim.x * GV_WARPS) {
-    int n0 = group * GV_ROWS;
-    float acc[GV_ROWS][MT];
-#pragma unroll
-    for (int r = 0; r < GV_ROWS; ++r)
-#pragma unroll
-      for (int m = 0; m < MT; ++m) acc[r][m] = 0.f;
-    const uint4* wrow[GV_ROWS];
-#pragma unroll
-    for (int r = 0; r < GV_ROWS; ++r) wrow[r] = (const uint4*)(w + (size_t)min(n0 + r, N - 1) * K);
-    for (int ch = lane; ch < chunks; ch += 32) {
-      float wf[GV_ROWS][8];
-#pragma unroll
-      for (int r = 0; r < GV_ROWS; ++r) {
-        uint4 v = __ldg(wrow[r] + ch);
-        unpack8(v, wf[r]);
-      }
-#pragma unroll
-      for (int m = 0; m < MT; ++m) {
-        float xf[8];
-        if (m < M) {
-          uint4 v = *((const uint4*)(a + (size_t)m * K) + ch);
-          unpack8(v, xf);
-        } else {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) xf[i] = 0.f;
-        }
-#pragma unroll
-        for (int r = 0; r < GV_ROWS; ++r)
-#pragma unroll
-          for (int i = 0; i < 8; ++i) acc[r][m] = fmaf(xf[i], wf[r][i], acc[r][m]);
-      }
-    }
-#pragma unroll
-    for (int r = 0; r < GV_ROWS; ++r)
-#pragma unroll
-      for (int m = 0; m < MT; ++m) acc[r][m] = warp_sum(acc[r][m]);
-    // lane m writes row m's results
-#pragma unroll
-    for (int m = 0; m < MT; ++m) {
-      if (lane == m && m < M) {
-#pragma unroll
-        for (int r = 0; r < GV_ROWS; r += 2) epilogue_pair<EPI, bf16>(c, m, n0 + r, M, N, acc[r][m], acc[r + 1][m]);
-      }
-    }
-  }
-}
-
-template <int EPI>
-int launch_gemv(void* c, const bf16* a, const bf16* w, int M, int N, int K, cudaStream_t stream) {
-  int groups = (N + GV_ROWS - 1) / GV_ROWS;
-  int blocks = (groups + GV_WARPS - 1) / GV_WARPS;
-  if (blocks > 148 * 16) blocks = 148 * 16;
-  if (M <= 1) gemv_bf16_kernel<1, EPI><<<blocks, GV_WARPS * 32, 0, stream>>>(c, a, w, M, N, K);
-  else if (M <= 2) gemv_bf16_kernel<2, EPI><<<blocks, GV_WARPS * 32, 0, stream>>>(c, a, w, M, N, K);
-  else if (M <= 4) gemv_bf16_kernel<4, EPI><<<blocks, GV_WARPS * 32, 0, stream>>>(c, a, w, M, N, K);
-  else if (M <= 8) gemv_bf16_kernel<8, EPI><<<blocks, GV_WARPS * 32, 0, stream>>>(c, a, w, M, N, K);
-  else gemv_bf16_kernel<16, EPI><<<blocks, GV_WARPS * 32, 0, stream>>>(c, a, w, M, N, K);
-  return dllm_launch_status();
-}
-
 template <int EPI>
 int launch_mma(void* c, const bf16* a, const bf16* w, int M, int N, int K, cudaStream_t stream) {
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
@@ -209,23 +124,17 @@ int launch_mma(void* c, const bf16* a, const bf16* w, int M, int N, int K, cudaS
 }
 }  // namespace
 
-// C = A[M,K] * W[N,K]^T, bfloat16 operands, float32 accumulation. `kernel`: 0 chooses by M, 1 forces the tile
-// kernel, 2 forces the weight-streaming kernel (M <= 16 only).
-DLLM_EXPORT int dllm_gemm_bf16(void* c, const void* a, const void* w, int M, int N, int K, int epilogue, int kernel,
+// C = A[M,K] * W[N,K]^T, bfloat16 operands, float32 accumulation.
+DLLM_EXPORT int dllm_gemm_bf16(void* c, const void* a, const void* w, int M, int N, int K, int epilogue,
                                cudaStream_t stream) {
   if (M <= 0 || N <= 0) return DLLM_OK;
   if (K <= 0 || (K & 7) || (N & 1)) return DLLM_UNSUPPORTED_SIZE;
-  if (kernel == 2 && M > 16) return DLLM_UNSUPPORTED_SIZE;
-  bool stream_weights = kernel == 2 || (kernel == 0 && M <= 16);
   const bf16 *ap = (const bf16*)a, *wp = (const bf16*)w;
-#define DLLM_DISPATCH(E)                                                                  \
-  return stream_weights ? launch_gemv<E>(c, ap, wp, M, N, K, stream) : launch_mma<E>(c, ap, wp, M, N, K, stream)
   switch (epilogue) {
-    case EPI_STORE_F32: DLLM_DISPATCH(EPI_STORE_F32);
-    case EPI_STORE_T: DLLM_DISPATCH(EPI_STORE_T);
-    case EPI_RESIDUAL: DLLM_DISPATCH(EPI_RESIDUAL);
-    case EPI_SWIGLU: DLLM_DISPATCH(EPI_SWIGLU);
+    case EPI_STORE_F32: return launch_mma<EPI_STORE_F32>(c, ap, wp, M, N, K, stream);
+    case EPI_STORE_T: return launch_mma<EPI_STORE_T>(c, ap, wp, M, N, K, stream);
+    case EPI_RESIDUAL: return launch_mma<EPI_RESIDUAL>(c, ap, wp, M, N, K, stream);
+    case EPI_SWIGLU: return launch_mma<EPI_SWIGLU>(c, ap, wp, M, N, K, stream);
     default: return DLLM_BAD_ARGUMENT;
   }
-#undef DLLM_DISPATCH
 }

@@ -61,6 +61,9 @@ class Model:
             self.blocks[entry.layer].forward(x, batch, view, rt, entry.writes_cache)
         if batch.n_want == 0:
             return None
+        if batch.is_decode and batch.n_want == batch.n_tokens and hasattr(self.final_norm, "lazy") \
+                and getattr(self.head, "accepts_pending_norm", False):
+            return self.head.forward(self.final_norm.lazy(x, rt), rt)  # every row is wanted, in order: no gather
         hidden = self.final_norm.forward(x, rt, rows=batch.want_rows, n_rows=batch.n_want, name="final_hidden")
         return self.head.forward(hidden, rt)
 

@@ -24,6 +24,7 @@ SOURCES = {
     "elementwise": "elementwise.cu",
     "gemm_simt": "gemm_simt.cu",
     "gemm_bf16": "gemm_bf16.cu",
+    "gemv": "gemv.cu",
     "attention": "attention.cu",
     "attention_decode": "attention_decode.cu",
     "sampling": "sampling.cu",

@@ -29,7 +29,12 @@ _prototypes = {
     ("elementwise", "dllm_decode_advance"): [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                              c_void_p],
     ("gemm_simt", "dllm_gemm_f32"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
-    ("gemm_bf16", "dllm_gemm_bf16"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    ("gemm_bf16", "dllm_gemm_bf16"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    ("gemv", "dllm_gemv_bf16"): [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int,
+                                 c_void_p],
+    ("gemv", "dllm_gemv_qkv_rope"): [c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                                     c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p,
+                                     c_void_p, c_void_p, c_int, c_void_p],
     ("attention", "dllm_attention_general"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                               c_int, c_void_p, c_void_p, c_void_p, c_int, c_float, c_int, c_int,
                                               c_void_p],
@@ -106,26 +111,69 @@ def rmsnorm(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, eps: float
                                               float(eps), _code(out.dtype), _stream()), "rmsnorm")
 
 
-def gemm(c: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int = EPI_STORE_T, kernel: int = 0) -> None:
+GEMV_MAX_ROWS = 16
+"""Products with at most this many activation rows run in the weight-streaming kernel."""
+
+
+def gemm(c: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int = EPI_STORE_T, kernel: int = 0,
+         norm_weight: torch.Tensor | None = None, eps: float = 0.0) -> None:
     """c = a[M,K] @ w[N,K]^T with float32 accumulation, then the epilogue: EPI_STORE_F32 (c float32), EPI_STORE_T
-    (c in a's dtype), EPI_RESIDUAL (c float32 += product), EPI_SWIGLU (w interleaves gate and up rows; c[M,N/2] =
-    silu(gate) * up in a's dtype). float32 operands run the true 32-bit kernel; bfloat16 the tensor-core kernels."""
-    _cuda(c, a, w)
+    (c in the weights' dtype), EPI_RESIDUAL (c float32 += product), EPI_SWIGLU (w interleaves gate and up rows;
+    c[M,N/2] = silu(gate) * up). float32 weights run the true 32-bit kernel; bfloat16 the tensor-core tile kernel
+    or, for M <= 16, the weight-streaming kernel (`kernel`: 0 chooses by M, 1 forces tiles, 2 forces streaming).
+    With `norm_weight` (streaming kernel only), `a` is the float32 residual stream and is RMS-normed on the way in."""
+    _cuda(c, a, w, norm_weight)
     m, k = a.shape
     n = w.shape[0]
-    assert w.shape[1] == k and a.dtype == w.dtype, (a.shape, w.shape, a.dtype, w.dtype)
+    assert w.shape[1] == k, (a.shape, w.shape)
     want_cols = n // 2 if epilogue == EPI_SWIGLU else n
-    want_dtype = torch.float32 if epilogue in (EPI_STORE_F32, EPI_RESIDUAL) else a.dtype
+    want_dtype = torch.float32 if epilogue in (EPI_STORE_F32, EPI_RESIDUAL) else w.dtype
     assert tuple(c.shape) == (m, want_cols) and c.dtype == want_dtype, (c.shape, c.dtype, m, want_cols, want_dtype)
-    if a.dtype == torch.float32:
+    detail = f"M={m} N={n} K={k}: K must be a multiple of {4 if w.dtype == torch.float32 else 8}, N even"
+    if w.dtype == torch.float32:
+        assert a.dtype == torch.float32 and norm_weight is None
         status = _fn("gemm_simt", "dllm_gemm_f32")(c.data_ptr(), a.data_ptr(), w.data_ptr(), m, n, k, epilogue,
                                                    _stream())
-    elif a.dtype == torch.bfloat16:
-        status = _fn("gemm_bf16", "dllm_gemm_bf16")(c.data_ptr(), a.data_ptr(), w.data_ptr(), m, n, k, epilogue,
-                                                    kernel, _stream())
+    elif w.dtype == torch.bfloat16:
+        streaming = kernel == 2 or (kernel == 0 and m <= GEMV_MAX_ROWS)
+        if streaming:
+            if norm_weight is not None:
+                assert a.dtype == torch.float32 and norm_weight.dtype == torch.float32 and norm_weight.numel() == k
+            else:
+                assert a.dtype == torch.bfloat16
+            status = _fn("gemv", "dllm_gemv_bf16")(
+                c.data_ptr(), a.data_ptr(), norm_weight.data_ptr() if norm_weight is not None else None, float(eps),
+                w.data_ptr(), m, n, k, epilogue, _stream())
+            detail += f", M at most {GEMV_MAX_ROWS}"
+        else:
+            assert a.dtype == torch.bfloat16 and norm_weight is None
+            status = _fn("gemm_bf16", "dllm_gemm_bf16")(c.data_ptr(), a.data_ptr(), w.data_ptr(), m, n, k, epilogue,
+                                                        _stream())
     else:
-        raise KernelError(f"gemm: dtype {a.dtype} is not supported")
-    _check(status, "gemm", f"M={m} N={n} K={k}: K must be a multiple of {4 if a.dtype == torch.float32 else 8}, N even")
+        raise KernelError(f"gemm: dtype {w.dtype} is not supported")
+    _check(status, "gemm", detail)
+
+
+def gemv_qkv_rope(a: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, cache, table: torch.Tensor | None,
+                  rotary_dim: int, heads: int, batch, write_cache: bool = True,
+                  norm_weight: torch.Tensor | None = None, eps: float = 0.0) -> None:
+    """The q/k/v projection of at most 16 tokens in one kernel (bfloat16): optional RMSNorm of the float32 residual
+    in front, rotation of q and k, q to q_out, k and v into the paged cache."""
+    _cuda(a, w, q_out, table, norm_weight)
+    m, k = batch.n_tokens, a.shape[1]
+    assert w.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16 and q_out.dtype == torch.bfloat16
+    assert w.shape == ((heads + 2 * cache.kv_heads) * cache.head_dim, k) and a.shape[0] >= m
+    assert a.dtype == (torch.float32 if norm_weight is not None else torch.bfloat16)
+    if table is not None:
+        assert table.dtype == torch.float32 and table.shape[0] > batch.max_position, "position beyond the table"
+        assert table.shape[1] == rotary_dim // 2 and table.shape[2] == 2
+    _check(_fn("gemv", "dllm_gemv_qkv_rope")(
+        a.data_ptr(), norm_weight.data_ptr() if norm_weight is not None else None, float(eps), w.data_ptr(), m, k,
+        q_out.data_ptr(), cache.base_ptr, cache.page_table.data_ptr(), cache.max_pages, cache.page_size, heads,
+        cache.kv_heads, cache.head_dim, table.data_ptr() if table is not None else None,
+        rotary_dim if table is not None else 0, batch.tok_seq.data_ptr(), batch.tok_pos.data_ptr(),
+        batch.slots.data_ptr(), 1 if write_cache else 0, _stream()),
+        "gemv_qkv_rope", f"M={m} (at most 16), K={k} (multiple of 8), head_dim and rotary_dim multiples of 4")
 
 
 def rope_cache_write(qkv: torch.Tensor, q_out: torch.Tensor, cache, table: torch.Tensor | None, rotary_dim: int,

@@ -7,6 +7,7 @@ import torch
 
 from ..cache.paged import CacheNeed
 from ..kernels import ops
+from .norm import NormedInput, project
 from .registry import build_part, register_part
 from .spec import ParamSpec
 
@@ -21,6 +22,8 @@ def decode_chunk(sequences: int, kv_heads: int, max_context: int) -> int:
 
 
 class Attention:
+    accepts_pending_norm = True
+
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
                  window: int | None = None, position=None) -> None:
         if num_heads % num_kv_heads:
@@ -52,12 +55,18 @@ class Attention:
         """h: normed activations [tokens, hidden]; adds the attention output to `residual` (float32) in place."""
         n = batch.n_tokens
         q_size = self.num_heads * self.head_dim
-        qkv = rt.ws.buffer("qkv", (n, q_size + 2 * self.num_kv_heads * self.head_dim), torch.float32)
-        ops.gemm(qkv, h, self.w_qkv, ops.EPI_STORE_F32)
         q = rt.ws.buffer("q", (n, q_size), rt.dtype)
         table = self.position.table() if self.position is not None else None
         rotary_dim = self.position.rotary_dim if self.position is not None else 0
-        ops.rope_cache_write(qkv, q, cache, table, rotary_dim, self.num_heads, batch, write_cache)
+        if rt.dtype == torch.bfloat16 and n <= ops.GEMV_MAX_ROWS and self.head_dim % 4 == 0 and rotary_dim % 4 == 0:
+            # decode-sized: norm, projection, rotation and cache write in one kernel
+            pending = isinstance(h, NormedInput)
+            ops.gemv_qkv_rope(h.x if pending else h, self.w_qkv, q, cache, table, rotary_dim, self.num_heads, batch,
+                              write_cache, norm_weight=h.weight if pending else None, eps=h.eps if pending else 0.0)
+        else:
+            qkv = rt.ws.buffer("qkv", (n, q_size + 2 * self.num_kv_heads * self.head_dim), torch.float32)
+            project(qkv, h, self.w_qkv, ops.EPI_STORE_F32)
+            ops.rope_cache_write(qkv, q, cache, table, rotary_dim, self.num_heads, batch, write_cache)
         attended = rt.ws.buffer("attended", (n, q_size), rt.dtype)
         if batch.is_decode and rt.dtype == torch.bfloat16:
             chunk = decode_chunk(batch.n_seqs, self.num_kv_heads, batch.max_context)

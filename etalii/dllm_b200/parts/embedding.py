@@ -6,6 +6,7 @@ from __future__ import annotations
 import torch
 
 from ..kernels import ops
+from .norm import project
 from .registry import register_part
 from .spec import ParamSpec
 
@@ -30,6 +31,8 @@ class TokenEmbedding:
 
 
 class LinearHead:
+    accepts_pending_norm = True
+
     def __init__(self, vocab_size: int, hidden_size: int) -> None:
         self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
         self.weight = None
@@ -41,9 +44,10 @@ class LinearHead:
     def bind(self, tensors, rt) -> None:
         self.weight = rt.to_device(tensors["weight"], rt.dtype)
 
-    def forward(self, hidden: torch.Tensor, rt) -> torch.Tensor:
+    def forward(self, hidden, rt) -> torch.Tensor:
+        """hidden: final-normed rows, or the norm still pending (`NormedInput`)."""
         logits = rt.ws.buffer("logits", (hidden.shape[0], self.vocab_size), torch.float32)
-        ops.gemm(logits, hidden, self.weight, ops.EPI_STORE_F32)
+        project(logits, hidden, self.weight, ops.EPI_STORE_F32)
         return logits
 
 

@@ -7,11 +7,14 @@ from __future__ import annotations
 import torch
 
 from ..kernels import ops
+from .norm import project
 from .registry import register_part
 from .spec import ParamSpec
 
 
 class SwiGLU:
+    accepts_pending_norm = True
+
     def __init__(self, hidden_size: int, intermediate_size: int) -> None:
         self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
         self.w_gate_up = self.w_down = None
@@ -29,7 +32,7 @@ class SwiGLU:
 
     def forward(self, h: torch.Tensor, residual: torch.Tensor, batch, rt) -> None:
         act = rt.ws.buffer("ffn_act", (h.shape[0], self.intermediate_size), rt.dtype)
-        ops.gemm(act, h, self.w_gate_up, ops.EPI_SWIGLU)
+        project(act, h, self.w_gate_up, ops.EPI_SWIGLU)
         ops.gemm(residual, act, self.w_down, ops.EPI_RESIDUAL)
 
 

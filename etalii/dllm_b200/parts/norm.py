@@ -9,6 +9,23 @@ from .registry import register_part
 from .spec import ParamSpec
 
 
+class NormedInput:
+    """A norm's output that has not been computed yet: the float32 rows and the norm's weight and eps. A consumer
+    whose kernel can apply the norm on the way in (the decode-sized products) takes it as it is; anyone else calls
+    `tensor()` and gets the normed activations, computed once."""
+
+    def __init__(self, norm: "RMSNorm", x: torch.Tensor, rt) -> None:
+        self.norm, self.x, self.rt = norm, x, rt
+        self.weight, self.eps = norm.weight, norm.eps
+        self.shape = x.shape
+        self._tensor = None
+
+    def tensor(self) -> torch.Tensor:
+        if self._tensor is None:
+            self._tensor = self.norm.forward(self.x, self.rt)
+        return self._tensor
+
+
 class RMSNorm:
     def __init__(self, hidden_size: int, eps: float) -> None:
         self.hidden_size, self.eps = int(hidden_size), float(eps)
@@ -29,6 +46,21 @@ class RMSNorm:
         out = rt.ws.buffer(name, (n, self.hidden_size), rt.dtype)
         ops.rmsnorm(out, x, self.weight, self.eps, rows)
         return out
+
+
+    def lazy(self, x: torch.Tensor, rt) -> NormedInput:
+        return NormedInput(self, x, rt)
+
+
+def project(out: torch.Tensor, h, w: torch.Tensor, epilogue: int) -> None:
+    """out = epilogue(h @ w^T). `h` is a tensor of activations or a `NormedInput`; a decode-sized bfloat16 product
+    applies the pending norm inside the kernel, anything else computes the normed activations first."""
+    if isinstance(h, NormedInput):
+        if w.dtype == torch.bfloat16 and h.shape[0] <= ops.GEMV_MAX_ROWS:
+            ops.gemm(out, h.x, w, epilogue, norm_weight=h.weight, eps=h.eps)
+            return
+        h = h.tensor()
+    ops.gemm(out, h, w, epilogue)
 
 
 register_part("norm", "rmsnorm", RMSNorm)

@@ -27,7 +27,11 @@ def rmsnorm(out, x, weight, eps, rows=None):
     out.copy_((src * inv * weight.double()).to(out.dtype))
 
 
-def gemm(c, a, w, epilogue=EPI_STORE_T, kernel=0):
+def gemm(c, a, w, epilogue=EPI_STORE_T, kernel=0, norm_weight=None, eps=0.0):
+    if norm_weight is not None:
+        normed = torch.empty(a.shape, dtype=torch.float64, device=a.device)
+        rmsnorm(normed, a, norm_weight, eps)
+        a = normed
     prod = a.double() @ w.double().T
     if epilogue == EPI_RESIDUAL:
         c.copy_((c.double() + prod).float())
@@ -135,3 +139,14 @@ def decode_advance(tokens, tok_pos, start, chosen, history, counter, batch):
     if row < history.numel() // batch:
         history[row * batch:(row + 1) * batch] = chosen[:batch]
     counter[0] = row + 1
+
+
+def gemv_qkv_rope(a, w, q_out, cache, table, rotary_dim, heads, batch, write_cache=True, norm_weight=None, eps=0.0):
+    n = batch.n_tokens
+    qkv = torch.empty((n, w.shape[0]), dtype=torch.float32, device=a.device)
+    gemm(qkv, a[:n], w, EPI_STORE_F32, norm_weight=norm_weight, eps=eps)
+    rope_cache_write(qkv, q_out, cache, table, rotary_dim, heads, batch, write_cache)
+
+
+def attention_decode(out, q, cache, heads, scale, window, batch, chunk, scratch):
+    attention_general(out, q, cache, heads, scale, window, batch)

@@ -293,3 +293,56 @@ def test_attention_decode_finds_a_far_key():
         ops().attention_decode(out, q, view, heads, 1.0, 0, batch, 64, scratch)
         assert torch.allclose(out.float(), torch.full_like(out, 7.0).float(), atol=0.05), target
         view.storage[page] = saved
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 64, 64), (3, 130, 72), (8, 576, 1536), (16, 96, 144), (5, 3072, 576)])
+@pytest.mark.parametrize("epilogue", [0, 1, 2, 3])
+def test_gemv_with_the_norm_in_front(m, n, k, epilogue):
+    x = _randn((m, k), torch.float32, 3, 2.0)
+    nw = _randn((k,), torch.float32, 8) * 0.1 + 1
+    w = _randn((n, k), torch.bfloat16, 4, 0.2)
+    cols = n // 2 if epilogue == 3 else n
+    c = _randn((m, cols), torch.float32 if epilogue in (0, 2) else torch.bfloat16, 5)
+    ref = c.clone()
+    ops().gemm(c, x, w, epilogue, norm_weight=nw, eps=1e-5)
+    normed = torch.empty((m, k), dtype=torch.float64, device=DEV)
+    PK.rmsnorm(normed, x, nw, 1e-5)
+    PK.gemm(ref, normed, w, epilogue)
+    assert rel_error(c.float().cpu(), ref.float().cpu()) <= (2e-5 if epilogue in (0, 2) else 8e-3)
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,rotary", [(4, 2, 16, 16), (6, 3, 24, 24), (2, 1, 64, 32),
+                                                           (9, 3, 64, 64), (3, 1, 128, 0)])
+@pytest.mark.parametrize("normed", [False, True])
+def test_gemv_qkv_rope(heads, kv_heads, head_dim, rotary, normed):
+    lengths, new, k = [70, 5, 129, 64], [1, 1, 3, 2], 136
+    cache, view, batch = _cache_and_batch(torch.bfloat16, kv_heads, head_dim, lengths, new)
+    n = batch.n_tokens
+    table = None
+    if rotary:
+        angles = torch.arange(256, dtype=torch.float64)[:, None] * torch.rand(rotary // 2, dtype=torch.float64)[None]
+        table = torch.stack([angles.cos(), angles.sin()], -1).float().to(DEV)
+    w = _randn(((heads + 2 * kv_heads) * head_dim, k), torch.bfloat16, 4, 0.2)
+    x = _randn((n, k), torch.float32 if normed else torch.bfloat16, 6)
+    nw = _randn((k,), torch.float32, 8) * 0.1 + 1
+    q = torch.zeros((n, heads * head_dim), dtype=torch.bfloat16, device=DEV)
+    before = view.storage.clone()
+    ops().gemv_qkv_rope(x, w, q, view, table, rotary, heads, batch, True, norm_weight=nw if normed else None,
+                        eps=1e-6)
+    h = x.double()
+    if normed:
+        h = torch.empty((n, k), dtype=torch.float64, device=DEV)
+        PK.rmsnorm(h, x, nw, 1e-6)
+    qkv = (h @ w.double().T).float().cpu()
+    ref_view = type(view)(before.cpu().clone(), view.page_table.cpu(), view.page_size, kv_heads, head_dim, None)
+    ref_q = torch.zeros((n, heads * head_dim), dtype=torch.bfloat16)
+    cpu_batch = type("B", (), {"n_tokens": n, "tok_pos": batch.tok_pos.cpu(), "tok_seq": batch.tok_seq.cpu(),
+                               "slots": batch.slots.cpu()})
+    PK.rope_cache_write(qkv, ref_q, ref_view, table.cpu() if rotary else None, rotary, heads, cpu_batch, True)
+    assert rel_error(q.float().cpu(), ref_q.float()) <= 8e-3
+    assert rel_error(view.storage.float().cpu(), ref_view.storage.float()) <= 8e-3
+    assert (view.storage != before).any(dim=-1).sum().item() <= n * kv_heads * 2
+    q2, snapshot = torch.zeros_like(q), view.storage.clone()
+    ops().gemv_qkv_rope(x, w, q2, view, table, rotary, heads, batch, False, norm_weight=nw if normed else None,
+                        eps=1e-6)
+    assert torch.equal(q2, q) and torch.equal(view.storage, snapshot)
