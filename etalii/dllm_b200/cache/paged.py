@@ -66,7 +66,8 @@ class _KvGroup:
         self.pages_of: list[list[int | None]] = [[] for _ in range(n_slots)]
         self.storage = self.table = None
         if device is not None:
-            self.storage = torch.empty((len(entries), n_pages, 2, need.kv_heads, page_size, need.head_dim),
+            # zeros, not garbage: a blockwise kernel multiplies masked rows of a page by probability 0
+            self.storage = torch.zeros((len(entries), n_pages, 2, need.kv_heads, page_size, need.head_dim),
                                        dtype=dtype, device=device)
             self.table = torch.zeros((n_slots, max_pages), dtype=torch.int32, device=device)
         self.dirty: set[int] = set()

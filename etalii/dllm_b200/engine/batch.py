@@ -11,7 +11,7 @@ import torch
 
 class StepBatch:
     __slots__ = ("n_seqs", "n_tokens", "n_want", "tokens", "tok_seq", "tok_pos", "cu_seqlens", "slots", "start",
-                 "want_rows", "h_slots", "h_new", "h_start", "max_new", "max_position", "max_context", "is_decode")
+                 "want_rows", "tile_seq", "tile_first", "n_tiles", "h_slots", "h_new", "h_start", "max_new", "max_position", "max_context", "is_decode")
 
 
 class BatchBuffers:
@@ -19,6 +19,7 @@ class BatchBuffers:
     staging buffers lets a step be prepared while the copy of the previous one may still be in flight."""
 
     RING = 4
+    TILE = 64
 
     def __init__(self, device, capacity: int = 4096) -> None:
         self.device = device
@@ -40,7 +41,11 @@ class BatchBuffers:
         counts = [len(t) for t in new_tokens]
         n = sum(counts)
         r = sum(len(w) for w in want)
-        total = 3 * n + (b + 1) + 2 * b + r
+        # tiles of up to TILE new tokens of one sequence for the prefill attention, the longest contexts first
+        tiles = [(i, first) for i, c in enumerate(counts) for first in range(0, c, self.TILE)]
+        tiles.sort(key=lambda t: -(starts[t[0]] + t[1]))
+        nt = len(tiles)
+        total = 3 * n + (b + 1) + 2 * b + r + 2 * nt
         if total > self.capacity:
             self._grow(max(total, 2 * self.capacity))
         ring = self._ring
@@ -61,6 +66,8 @@ class BatchBuffers:
         host[o:o + b] = np.asarray(starts, dtype=np.int32); o += b
         rows = [cu[i] + w for i, ws in enumerate(want) for w in ws]
         host[o:o + r] = np.asarray(rows, dtype=np.int32) if r else np.zeros(0, np.int32); o += r
+        host[o:o + nt] = [t[0] for t in tiles]; o += nt
+        host[o:o + nt] = [t[1] for t in tiles]; o += nt
         self.dev[:total].copy_(self.host[ring][:total], non_blocking=True)
         event = torch.cuda.Event()
         event.record()
@@ -76,6 +83,9 @@ class BatchBuffers:
         batch.slots = self.dev[o:o + b]; o += b
         batch.start = self.dev[o:o + b]; o += b
         batch.want_rows = self.dev[o:o + r]; o += r
+        batch.tile_seq = self.dev[o:o + nt]; o += nt
+        batch.tile_first = self.dev[o:o + nt]; o += nt
+        batch.n_tiles = nt
         batch.h_slots, batch.h_new, batch.h_start = list(slots), counts, list(starts)
         batch.max_new = max(counts) if counts else 0
         batch.max_context = max((s + c for s, c in zip(starts, counts)), default=0)

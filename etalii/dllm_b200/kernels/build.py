@@ -27,6 +27,7 @@ SOURCES = {
     "gemv": "gemv.cu",
     "attention": "attention.cu",
     "attention_decode": "attention_decode.cu",
+    "attention_prefill": "attention_prefill.cu",
     "sampling": "sampling.cu",
 }
 """Library name -> source file. A library added here is built by `build_all` and loadable by `library`."""

@@ -41,6 +41,9 @@ _prototypes = {
     ("attention_decode", "dllm_attention_decode"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                                     c_int, c_void_p, c_void_p, c_int, c_float, c_int, c_int, c_int,
                                                     c_void_p, c_void_p],
+    ("attention_prefill", "dllm_attention_prefill"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                                      c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                      c_int, c_float, c_int, c_void_p],
     ("sampling", "dllm_sample"): [c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                   c_float, c_int, c_double, c_double, c_void_p],
     ("sampling", "dllm_seed_rng"): [c_void_p, c_void_p, c_void_p, c_int, c_void_p],
@@ -270,3 +273,22 @@ def attention_decode(out: torch.Tensor, q: torch.Tensor, cache, heads: int, scal
         "attention_decode", f"head_dim={cache.head_dim} must be a multiple of 8, at most 256")
     global launches
     launches += 1  # two kernels: partial results, then the combination
+
+
+def attention_prefill_supported(cache) -> bool:
+    return cache.dtype == torch.bfloat16 and cache.head_dim % 16 == 0 and cache.head_dim <= 128 \
+        and cache.page_size == 64
+
+
+def attention_prefill(out: torch.Tensor, q: torch.Tensor, cache, heads: int, scale: float, window: int,
+                      batch) -> None:
+    """Blockwise causal attention of the batch's new tokens over their sequences' caches on the tensor cores
+    (bfloat16, head_dim a multiple of 16 up to 128, pages of 64 positions)."""
+    _cuda(out, q)
+    assert attention_prefill_supported(cache) and q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+    _check(_fn("attention_prefill", "dllm_attention_prefill")(
+        out.data_ptr(), q.data_ptr(), cache.base_ptr, cache.page_table.data_ptr(), cache.max_pages, cache.page_size,
+        heads, cache.kv_heads, cache.head_dim, batch.tile_seq.data_ptr(), batch.tile_first.data_ptr(),
+        batch.cu_seqlens.data_ptr(), batch.start.data_ptr(), batch.slots.data_ptr(), batch.n_tiles, float(scale),
+        int(window or 0), _stream()), "attention_prefill",
+        f"head_dim={cache.head_dim} must be a multiple of 16, at most 128; pages of 64")

@@ -74,6 +74,8 @@ class Attention:
                 batch.n_seqs, self.num_heads, self.head_dim, chunk, batch.max_context),), torch.float32)
             ops.attention_decode(attended, q, cache, self.num_heads, self.scale, self.window or 0, batch, chunk,
                                  scratch)
+        elif not batch.is_decode and ops.attention_prefill_supported(cache):
+            ops.attention_prefill(attended, q, cache, self.num_heads, self.scale, self.window or 0, batch)
         else:
             ops.attention_general(attended, q, cache, self.num_heads, self.scale, self.window or 0, batch)
         ops.gemm(residual, attended, self.w_o, ops.EPI_RESIDUAL)

@@ -150,3 +150,11 @@ def gemv_qkv_rope(a, w, q_out, cache, table, rotary_dim, heads, batch, write_cac
 
 def attention_decode(out, q, cache, heads, scale, window, batch, chunk, scratch):
     attention_general(out, q, cache, heads, scale, window, batch)
+
+
+def attention_prefill(out, q, cache, heads, scale, window, batch):
+    attention_general(out, q, cache, heads, scale, window, batch)
+
+
+def attention_prefill_supported(cache):
+    return False

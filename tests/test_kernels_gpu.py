@@ -346,3 +346,42 @@ def test_gemv_qkv_rope(heads, kv_heads, head_dim, rotary, normed):
     ops().gemv_qkv_rope(x, w, q2, view, table, rotary, heads, batch, False, norm_weight=nw if normed else None,
                         eps=1e-6)
     assert torch.equal(q2, q) and torch.equal(view.storage, snapshot)
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,window", [(4, 2, 16, None), (9, 3, 64, None), (8, 1, 128, 70),
+                                                           (6, 2, 48, 33), (5, 5, 32, None), (2, 2, 96, 130)])
+def test_attention_prefill(heads, kv_heads, head_dim, window):
+    """Whole prompts, prompts that go on from a cached prefix, single tokens and tile edges, in one batch."""
+    lengths, new = [130, 200, 1, 64, 65, 300, 77], [130, 9, 1, 64, 65, 128, 1]
+    cache, view, batch = _cache_and_batch(torch.bfloat16, kv_heads, head_dim, lengths, new, window)
+    n = batch.n_tokens
+    q = _randn((n, heads * head_dim), torch.bfloat16, 9)
+    out = torch.zeros((n, heads * head_dim), dtype=torch.bfloat16, device=DEV)
+    ref = torch.zeros((n, heads * head_dim), dtype=torch.bfloat16)
+    ops().attention_prefill(out, q, view, heads, 0.3, window or 0, batch)
+    view_cpu = type(view)(view.storage.cpu(), view.page_table.cpu(), view.page_size, kv_heads, head_dim, window)
+    cpu_batch = type("B", (), {"n_tokens": n, "tok_pos": batch.tok_pos.cpu(), "tok_seq": batch.tok_seq.cpu(),
+                               "slots": batch.slots.cpu()})
+    PK.attention_general(ref, q.cpu(), view_cpu, heads, 0.3, window or 0, cpu_batch)
+    assert rel_error(out.float().cpu(), ref.float()) <= 8e-3
+    worst = (out.float().cpu() - ref.float()).abs().max(dim=1).values
+    assert worst.max() <= 8e-3 * ref.float().abs().max(), int(worst.argmax())
+
+
+def test_attention_prefill_finds_a_far_key_and_ignores_what_lies_beyond():
+    heads, kv_heads, hd = 4, 2, 32
+    cache, view, batch = _cache_and_batch(torch.bfloat16, kv_heads, hd, [700], [100])
+    view.storage.mul_(0.05)
+    slot = batch.h_slots[0]
+    last_page = int(view.page_table[slot, 699 // 64])
+    view.storage[last_page, :, :, 700 % 64:, :] = 1e4  # rows of the last page beyond the sequence's length
+    for target in (0, 63, 64, 333, 599):
+        page = int(view.page_table[slot, target // 64])
+        saved = view.storage[page].clone()
+        view.storage[page, 0, :, target % 64, :] = 4.0
+        view.storage[page, 1, :, target % 64, :] = 7.0
+        q = torch.full((100, heads * hd), 4.0, dtype=torch.bfloat16, device=DEV)
+        out = torch.zeros_like(q)
+        ops().attention_prefill(out, q, view, heads, 1.0, 0, batch)
+        assert torch.allclose(out.float(), torch.full_like(out, 7.0).float(), atol=0.05), target
+        view.storage[page] = saved
