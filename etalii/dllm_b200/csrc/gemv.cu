@@ -1,11 +1,13 @@
 // Weight-streaming products for decode (at most 16 rows of activations, bfloat16 weights): C = X * W^T where reading
-// W once is the whole cost. A block owns four output columns (rows of W) and splits the reduction over its threads:
-// every thread loads 16 bytes of each of the four rows, so a matrix with few rows still spreads over the whole
-// device and each row is in flight at once; partial sums meet in shared memory in a fixed order.
+// W once is the whole cost. A block owns 16 output columns (16 rows of W) and splits the reduction over its warps.
+// The products run on the tensor cores with W as the 16-row operand (mma.sync m16n8k16, "swap A and B"): a thread
+// loads 16 bytes of two rows of W and 16 bytes of one row of X per 32 values of k, all loads of a warp are issued
+// before the first product, and no shuffle reduction is needed; the warps' partial tiles meet in shared memory in
+// warp order. The k positions inside a 32-block are permuted the same way for W and X, which a sum does not see.
 //
 // Fused around the product, to save kernels and memory traffic in the decode step:
-//   - in front: RMSNorm of the float32 residual stream (the block sums x^2 itself; the normed activations never
-//     touch memory): x' = x * rsqrt(mean(x^2) + eps) * norm_weight, in float32;
+//   - in front: RMSNorm of the float32 residual stream (the block sums x^2 itself; x * norm_weight is rounded to
+//     bfloat16 as the product's operand and 1/rms is applied to the float32 result);
 //   - behind: store (float32 or bfloat16), residual add in float32, SwiGLU on interleaved gate/up rows, or rotary
 //     position encoding of q/k and the write of k and v into the paged cache (q/k/v projection).
 #include "gemm_common.cuh"
@@ -14,7 +16,8 @@
 
 namespace {
 typedef __nv_bfloat16 bf16;
-constexpr int THREADS = 128, WARPS = THREADS / 32, ROWS = 4;
+constexpr int TILE = 16;       // rows of W per block
+constexpr int MAX_STEPS = 8;   // 32-value k steps a warp keeps in flight at once
 
 struct RopeArgs {
   bf16* q_out;           // [tokens, heads * head_dim]
@@ -27,171 +30,193 @@ struct RopeArgs {
   int write_cache;
 };
 
-__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
-  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    float2 x = __bfloat1622float2(p[i]);
-    f[2 * i] = x.x;
-    f[2 * i + 1] = x.y;
-  }
+__device__ __forceinline__ void mma_bf16(float* c, const unsigned* a, unsigned b0, unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
 }
 
-// The four rows of W a block owns. For the q/k/v projection with rotation, a block of a rotated head owns two
-// rotary pairs: dims (j, j+1) and (j + half, j+1 + half); elsewhere four consecutive rows.
+// The row of W behind tile row r (0..15) of block `item`. In the q/k/v projection a rotated head's tile holds eight
+// dimensions and their rotary partners (r and r + 8 are a pair); everywhere else 16 consecutive rows.
 template <int EPI>
-__device__ __forceinline__ void block_rows(int item, int N, const RopeArgs& r, int* rows, int& head, int& dim0,
-                                           bool& paired) {
-  paired = false;
-  head = 0;
-  dim0 = 0;
+__device__ __forceinline__ int tile_row(int item, int r, int N, const RopeArgs& rope, int& head, int& dim0,
+                                        bool& paired) {
   if (EPI == EPI_QKV_ROPE) {
-    int hd = r.cache.head_dim, per_head = hd / 4;
+    int hd = rope.cache.head_dim, per_head = hd / TILE;
     head = item / per_head;
     int it = item % per_head;
-    bool rotated = r.table != nullptr && head < r.heads + r.cache.kv_heads;
-    int half = r.rotary_dim / 2;
-    if (rotated && it < r.rotary_dim / 4) {
-      paired = true;
-      dim0 = it * 2;
-      rows[0] = head * hd + dim0; rows[1] = rows[0] + 1; rows[2] = rows[0] + half; rows[3] = rows[2] + 1;
-    } else {
-      dim0 = it * 4;
-      for (int i = 0; i < 4; ++i) rows[i] = head * hd + dim0 + i;
+    bool rotated = rope.table != nullptr && head < rope.heads + rope.cache.kv_heads;
+    paired = rotated && it < rope.rotary_dim / TILE;
+    if (paired) {
+      dim0 = it * 8;
+      return head * hd + dim0 + (r & 7) + (r >> 3) * (rope.rotary_dim / 2);
     }
-  } else {
-    for (int i = 0; i < 4; ++i) rows[i] = min(item * ROWS + i, N - 1);
+    dim0 = it * TILE;
+    return head * hd + dim0 + r;
   }
+  head = 0; dim0 = 0; paired = false;
+  return min(item * TILE + r, N - 1);
 }
 
-template <int MT, int EPI, bool NORM>
-__global__ void __launch_bounds__(THREADS) gemv_kernel(void* __restrict__ c, const void* __restrict__ a,
-                                                       const float* __restrict__ norm_w, float eps,
-                                                       const bf16* __restrict__ w, int M, int N, int K, RopeArgs rope) {
-  __shared__ float red[WARPS][ROWS + 1][MT];
+template <int WARPS, int NT, int EPI, bool NORM>
+__global__ void __launch_bounds__(WARPS * 32) gemv_kernel(void* __restrict__ c, const void* __restrict__ a,
+                                                          const float* __restrict__ norm_w, float eps,
+                                                          const bf16* __restrict__ w, int M, int N, int K,
+                                                          RopeArgs rope) {
+  __shared__ float red[WARPS][TILE][NT * 8 + 1];
+  __shared__ float red_ss[WARPS][NT * 8];
   int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  int rows[ROWS], head, dim0;
+  int g = lane >> 2, t = lane & 3;
+  int head, dim0;
   bool paired;
-  block_rows<EPI>(blockIdx.x, N, rope, rows, head, dim0, paired);
-  float acc[ROWS][MT], ss[MT];
+  int row_lo = tile_row<EPI>(blockIdx.x, g, N, rope, head, dim0, paired);
+  int row_hi = tile_row<EPI>(blockIdx.x, g + 8, N, rope, head, dim0, paired);
+  const uint4* w_lo = (const uint4*)(w + (size_t)row_lo * K);
+  const uint4* w_hi = (const uint4*)(w + (size_t)row_hi * K);
+  int chunks = K >> 3;                   // 16-byte pieces of a row
+  int steps = (chunks + 3) >> 2;         // k steps of 32 values
+  int per_warp = (steps + WARPS - 1) / WARPS;
+  int s_begin = warp * per_warp, s_end = min(steps, s_begin + per_warp);
+
+  float acc[NT][4];
+  float ss[NT];
 #pragma unroll
-  for (int m = 0; m < MT; ++m) {
-    ss[m] = 0.f;
+  for (int n = 0; n < NT; ++n) {
+    ss[n] = 0.f;
 #pragma unroll
-    for (int r = 0; r < ROWS; ++r) acc[r][m] = 0.f;
+    for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
   }
-  int chunks = K >> 3;
-  for (int ch = tid; ch < chunks; ch += THREADS) {
-    float wf[ROWS][8];
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+  for (int s0 = s_begin; s0 < s_end; s0 += MAX_STEPS) {
+    uint4 wl[MAX_STEPS], wh[MAX_STEPS], xb[MAX_STEPS][NT];
+    // every load of this stretch is issued before the first product
 #pragma unroll
-    for (int r = 0; r < ROWS; ++r) {
-      uint4 v = __ldg((const uint4*)(w + (size_t)rows[r] * K) + ch);
-      unpack8(v, wf[r]);
-    }
-    float nw[8];
-    if (NORM) {
-      float4 n0 = __ldg((const float4*)(norm_w) + 2 * ch), n1 = __ldg((const float4*)(norm_w) + 2 * ch + 1);
-      nw[0] = n0.x; nw[1] = n0.y; nw[2] = n0.z; nw[3] = n0.w; nw[4] = n1.x; nw[5] = n1.y; nw[6] = n1.z; nw[7] = n1.w;
+    for (int i = 0; i < MAX_STEPS; ++i) {
+      int ch = (s0 + i) * 4 + t;
+      bool ok = s0 + i < s_end && ch < chunks;
+      wl[i] = ok ? __ldg(w_lo + ch) : zero;
+      wh[i] = ok ? __ldg(w_hi + ch) : zero;
     }
 #pragma unroll
-    for (int m = 0; m < MT; ++m) {
-      if (m >= M) break;
-      float xf[8];
-      if (NORM) {
-        const float4* xp = (const float4*)((const float*)a + (size_t)m * K) + 2 * ch;
-        float4 x0 = xp[0], x1 = xp[1];
-        xf[0] = x0.x; xf[1] = x0.y; xf[2] = x0.z; xf[3] = x0.w; xf[4] = x1.x; xf[5] = x1.y; xf[6] = x1.z; xf[7] = x1.w;
+    for (int i = 0; i < MAX_STEPS; ++i) {
+      int ch = (s0 + i) * 4 + t;
+      bool ok = s0 + i < s_end && ch < chunks;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          ss[m] = fmaf(xf[i], xf[i], ss[m]);
-          xf[i] *= nw[i];
+      for (int n = 0; n < NT; ++n) {
+        int m = n * 8 + g;
+        xb[i][n] = zero;
+        if (!ok || m >= M) continue;
+        if (NORM) {
+          const float4* xp = (const float4*)((const float*)a + (size_t)m * K) + 2 * ch;
+          float4 x0 = xp[0], x1 = xp[1];
+          float4 n0 = __ldg((const float4*)norm_w + 2 * ch), n1 = __ldg((const float4*)norm_w + 2 * ch + 1);
+          ss[n] = fmaf(x0.x, x0.x, ss[n]); ss[n] = fmaf(x0.y, x0.y, ss[n]);
+          ss[n] = fmaf(x0.z, x0.z, ss[n]); ss[n] = fmaf(x0.w, x0.w, ss[n]);
+          ss[n] = fmaf(x1.x, x1.x, ss[n]); ss[n] = fmaf(x1.y, x1.y, ss[n]);
+          ss[n] = fmaf(x1.z, x1.z, ss[n]); ss[n] = fmaf(x1.w, x1.w, ss[n]);
+          xb[i][n] = make_uint4(pack_bf16(x0.x * n0.x, x0.y * n0.y), pack_bf16(x0.z * n0.z, x0.w * n0.w),
+                                pack_bf16(x1.x * n1.x, x1.y * n1.y), pack_bf16(x1.z * n1.z, x1.w * n1.w));
+        } else {
+          xb[i][n] = *((const uint4*)((const bf16*)a + (size_t)m * K) + ch);
         }
-      } else {
-        uint4 v = *((const uint4*)((const bf16*)a + (size_t)m * K) + ch);
-        unpack8(v, xf);
       }
+    }
 #pragma unroll
-      for (int r = 0; r < ROWS; ++r)
+    for (int i = 0; i < MAX_STEPS; ++i) {
+      unsigned a0[4] = {wl[i].x, wh[i].x, wl[i].y, wh[i].y};
+      unsigned a1[4] = {wl[i].z, wh[i].z, wl[i].w, wh[i].w};
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[r][m] = fmaf(xf[i], wf[r][i], acc[r][m]);
+      for (int n = 0; n < NT; ++n) {
+        mma_bf16(acc[n], a0, xb[i][n].x, xb[i][n].y);
+        mma_bf16(acc[n], a1, xb[i][n].z, xb[i][n].w);
+      }
     }
   }
-  // warp sums, then the warps in order
+  // partial tiles and partial sums of squares to shared memory
 #pragma unroll
-  for (int m = 0; m < MT; ++m) {
-#pragma unroll
-    for (int r = 0; r < ROWS; ++r) acc[r][m] = warp_sum(acc[r][m]);
-    if (NORM) ss[m] = warp_sum(ss[m]);
-  }
-  if (lane == 0) {
-#pragma unroll
-    for (int m = 0; m < MT; ++m) {
-#pragma unroll
-      for (int r = 0; r < ROWS; ++r) red[warp][r][m] = acc[r][m];
-      red[warp][ROWS][m] = ss[m];
+  for (int n = 0; n < NT; ++n) {
+    red[warp][g][n * 8 + 2 * t] = acc[n][0];
+    red[warp][g][n * 8 + 2 * t + 1] = acc[n][1];
+    red[warp][g + 8][n * 8 + 2 * t] = acc[n][2];
+    red[warp][g + 8][n * 8 + 2 * t + 1] = acc[n][3];
+    if (NORM) {
+      float v = ss[n];
+      v += __shfl_xor_sync(0xffffffffu, v, 1);
+      v += __shfl_xor_sync(0xffffffffu, v, 2);
+      if (t == 0) red_ss[warp][n * 8 + g] = v;
     }
   }
   __syncthreads();
-  if (tid >= MT || tid >= M) return;
-  int m = tid;
-  float out[ROWS], sumsq = 0.f;
+
+  // one thread per (pair of tile rows, token): rows (2p, 2p+1), or (p, p + 8) for rotary pairs
+  for (int idx = tid; idx < 8 * NT * 8; idx += WARPS * 32) {
+    int p = idx / (NT * 8), m = idx % (NT * 8);
+    if (m >= M) continue;
+    int r0 = (EPI == EPI_QKV_ROPE) ? p : 2 * p, r1 = (EPI == EPI_QKV_ROPE) ? p + 8 : 2 * p + 1;
+    float v0 = 0.f, v1 = 0.f, sumsq = 0.f;
 #pragma unroll
-  for (int r = 0; r < ROWS; ++r) out[r] = 0.f;
-#pragma unroll
-  for (int wi = 0; wi < WARPS; ++wi) {
-#pragma unroll
-    for (int r = 0; r < ROWS; ++r) out[r] += red[wi][r][m];
-    sumsq += red[wi][ROWS][m];
-  }
-  if (NORM) {
-    float inv = 1.0f / sqrtf(sumsq / (float)K + eps);
-#pragma unroll
-    for (int r = 0; r < ROWS; ++r) out[r] *= inv;
-  }
-  if (EPI == EPI_QKV_ROPE) {
-    int hd = rope.cache.head_dim, nkv = rope.cache.kv_heads, heads = rope.heads;
-    int pos = rope.tok_pos[m];
-    int dims[ROWS];
-    if (paired) {
-      int half = rope.rotary_dim / 2;
-      float2 cs0 = rope.table[(size_t)pos * half + dim0], cs1 = rope.table[(size_t)pos * half + dim0 + 1];
-      float a0 = out[0], a1 = out[1], b0 = out[2], b1 = out[3];
-      out[0] = fmaf(a0, cs0.x, -(b0 * cs0.y)); out[2] = fmaf(a0, cs0.y, b0 * cs0.x);
-      out[1] = fmaf(a1, cs1.x, -(b1 * cs1.y)); out[3] = fmaf(a1, cs1.y, b1 * cs1.x);
-      dims[0] = dim0; dims[1] = dim0 + 1; dims[2] = dim0 + half; dims[3] = dim0 + half + 1;
-    } else {
-      for (int i = 0; i < ROWS; ++i) dims[i] = dim0 + i;
+    for (int wi = 0; wi < WARPS; ++wi) {
+      v0 += red[wi][r0][m];
+      v1 += red[wi][r1][m];
+      if (NORM) sumsq += red_ss[wi][m];
     }
-    bf16* dst;
-    if (head < heads) {
-      dst = rope.q_out + ((size_t)m * heads + head) * hd;
-    } else {
-      if (!rope.write_cache) return;
-      int which = head < heads + nkv ? 0 : 1;
-      int g = head - heads - which * nkv;
-      int slot = rope.slots[rope.tok_seq[m]];
-      int page = rope.cache.page_table[(size_t)slot * rope.cache.max_pages + pos / rope.cache.page_size];
-      dst = (bf16*)rope.cache.base + kv_offset(rope.cache, page, which, g, pos % rope.cache.page_size);
+    if (NORM) {
+      float inv = 1.0f / sqrtf(sumsq / (float)K + eps);
+      v0 *= inv;
+      v1 *= inv;
     }
-#pragma unroll
-    for (int i = 0; i < ROWS; ++i) dst[dims[i]] = __float2bfloat16_rn(out[i]);
-  } else {
-    int n0 = blockIdx.x * ROWS;
-    epilogue_pair<EPI, bf16>(c, m, n0, M, N, out[0], out[1]);
-    epilogue_pair<EPI, bf16>(c, m, n0 + 2, M, N, out[2], out[3]);
+    if (EPI == EPI_QKV_ROPE) {
+      int hd = rope.cache.head_dim, nkv = rope.cache.kv_heads, heads = rope.heads;
+      int pos = rope.tok_pos[m];
+      int d0, d1;
+      if (paired) {
+        int half = rope.rotary_dim / 2;
+        d0 = dim0 + p;
+        d1 = d0 + half;
+        float2 cs = rope.table[(size_t)pos * half + d0];
+        float x = v0, y = v1;
+        v0 = fmaf(x, cs.x, -(y * cs.y));
+        v1 = fmaf(x, cs.y, y * cs.x);
+      } else {
+        d0 = dim0 + p;
+        d1 = d0 + 8;
+      }
+      bf16* dst;
+      if (head < heads) {
+        dst = rope.q_out + ((size_t)m * heads + head) * hd;
+      } else {
+        if (!rope.write_cache) continue;
+        int which = head < heads + nkv ? 0 : 1;
+        int kvh = head - heads - which * nkv;
+        int slot = rope.slots[rope.tok_seq[m]];
+        int page = rope.cache.page_table[(size_t)slot * rope.cache.max_pages + pos / rope.cache.page_size];
+        dst = (bf16*)rope.cache.base + kv_offset(rope.cache, page, which, kvh, pos % rope.cache.page_size);
+      }
+      dst[d0] = __float2bfloat16_rn(v0);
+      dst[d1] = __float2bfloat16_rn(v1);
+    } else {
+      epilogue_pair<EPI, bf16>(c, m, blockIdx.x * TILE + 2 * p, M, N, v0, v1);
+    }
   }
 }
 
 template <int EPI, bool NORM>
 int launch(void* c, const void* a, const float* norm_w, float eps, const bf16* w, int M, int N, int K,
            const RopeArgs& rope, cudaStream_t stream) {
-  int items = (N + ROWS - 1) / ROWS;
-#define DLLM_GO(MT) gemv_kernel<MT, EPI, NORM><<<items, THREADS, 0, stream>>>(c, a, norm_w, eps, w, M, N, K, rope)
-  if (M <= 1) DLLM_GO(1);
-  else if (M <= 2) DLLM_GO(2);
-  else if (M <= 4) DLLM_GO(4);
-  else if (M <= 8) DLLM_GO(8);
-  else DLLM_GO(16);
+  int items = (N + TILE - 1) / TILE;
+  bool wide = K >= 1024;
+#define DLLM_GO(WARPS, NT) \
+  gemv_kernel<WARPS, NT, EPI, NORM><<<items, WARPS * 32, 0, stream>>>(c, a, norm_w, eps, w, M, N, K, rope)
+  if (M <= 8) {
+    if (wide) DLLM_GO(8, 1); else DLLM_GO(4, 1);
+  } else {
+    if (wide) DLLM_GO(8, 2); else DLLM_GO(4, 2);
+  }
 #undef DLLM_GO
   return dllm_launch_status();
 }
@@ -223,15 +248,15 @@ DLLM_EXPORT int dllm_gemv_bf16(void* c, const void* a, const float* norm_w, floa
 
 // The q/k/v projection of a decode step in one kernel: optional RMSNorm in front, rotation of q and k by the
 // table's angle for each token's position, q to q_out, k and v into the token's place in the paged cache.
-// W is [(heads + 2 kv_heads) * head_dim, K]. head_dim and rotary_dim must be multiples of 4.
+// W is [(heads + 2 kv_heads) * head_dim, K]. head_dim and rotary_dim must be multiples of 16.
 DLLM_EXPORT int dllm_gemv_qkv_rope(const void* a, const float* norm_w, float eps, const void* w, int M, int K,
                                    void* q_out, void* cache_base, const int* page_table, int max_pages, int page_size,
                                    int heads, int kv_heads, int head_dim, const float* table, int rotary_dim,
                                    const int* tok_seq, const int* tok_pos, const int* slots, int write_cache,
                                    cudaStream_t stream) {
   if (M <= 0) return DLLM_OK;
-  if (M > 16 || K <= 0 || (K & 7) || heads <= 0 || kv_heads <= 0 || head_dim <= 0 || (head_dim & 3) ||
-      rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 3))
+  if (M > 16 || K <= 0 || (K & 7) || heads <= 0 || kv_heads <= 0 || head_dim <= 0 || (head_dim & 15) ||
+      rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 15))
     return DLLM_UNSUPPORTED_SIZE;
   RopeArgs rope{(bf16*)q_out, KvLayout{cache_base, page_table, max_pages, page_size, kv_heads, head_dim},
                 (const float2*)table, table ? rotary_dim : 0, heads, tok_seq, tok_pos, slots, write_cache};

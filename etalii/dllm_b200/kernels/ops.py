@@ -176,7 +176,7 @@ def gemv_qkv_rope(a: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, cache, 
         cache.kv_heads, cache.head_dim, table.data_ptr() if table is not None else None,
         rotary_dim if table is not None else 0, batch.tok_seq.data_ptr(), batch.tok_pos.data_ptr(),
         batch.slots.data_ptr(), 1 if write_cache else 0, _stream()),
-        "gemv_qkv_rope", f"M={m} (at most 16), K={k} (multiple of 8), head_dim and rotary_dim multiples of 4")
+        "gemv_qkv_rope", f"M={m} (at most 16), K={k} (multiple of 8), head_dim and rotary_dim multiples of 16")
 
 
 def rope_cache_write(qkv: torch.Tensor, q_out: torch.Tensor, cache, table: torch.Tensor | None, rotary_dim: int,

@@ -58,7 +58,7 @@ class Attention:
         q = rt.ws.buffer("q", (n, q_size), rt.dtype)
         table = self.position.table() if self.position is not None else None
         rotary_dim = self.position.rotary_dim if self.position is not None else 0
-        if rt.dtype == torch.bfloat16 and n <= ops.GEMV_MAX_ROWS and self.head_dim % 4 == 0 and rotary_dim % 4 == 0:
+        if rt.dtype == torch.bfloat16 and n <= ops.GEMV_MAX_ROWS and self.head_dim % 16 == 0 and rotary_dim % 16 == 0:
             # decode-sized: norm, projection, rotation and cache write in one kernel
             pending = isinstance(h, NormedInput)
             ops.gemv_qkv_rope(h.x if pending else h, self.w_qkv, q, cache, table, rotary_dim, self.num_heads, batch,

@@ -308,10 +308,11 @@ def test_gemv_with_the_norm_in_front(m, n, k, epilogue):
     normed = torch.empty((m, k), dtype=torch.float64, device=DEV)
     PK.rmsnorm(normed, x, nw, 1e-5)
     PK.gemm(ref, normed, w, epilogue)
-    assert rel_error(c.float().cpu(), ref.float().cpu()) <= (2e-5 if epilogue in (0, 2) else 8e-3)
+    # the normed activations are the bfloat16 operand of a tensor-core product (as when the norm runs on its own)
+    assert rel_error(c.float().cpu(), ref.float().cpu()) <= 8e-3
 
 
-@pytest.mark.parametrize("heads,kv_heads,head_dim,rotary", [(4, 2, 16, 16), (6, 3, 24, 24), (2, 1, 64, 32),
+@pytest.mark.parametrize("heads,kv_heads,head_dim,rotary", [(4, 2, 16, 16), (6, 3, 48, 32), (2, 1, 64, 32),
                                                            (9, 3, 64, 64), (3, 1, 128, 0)])
 @pytest.mark.parametrize("normed", [False, True])
 def test_gemv_qkv_rope(heads, kv_heads, head_dim, rotary, normed):
@@ -385,3 +386,13 @@ def test_attention_prefill_finds_a_far_key_and_ignores_what_lies_beyond():
         ops().attention_prefill(out, q, view, heads, 1.0, 0, batch)
         assert torch.allclose(out.float(), torch.full_like(out, 7.0).float(), atol=0.05), target
         view.storage[page] = saved
+
+
+def test_gemv_qkv_rope_refuses_head_sizes_it_cannot_pair():
+    from etalii.dllm_b200.kernels.ops import KernelError
+
+    cache, view, batch = _cache_and_batch(torch.bfloat16, 3, 24, [5], [1])
+    w = _randn(((6 + 6) * 24, 64), torch.bfloat16, 1)
+    with pytest.raises(KernelError, match="multiples of 16"):
+        ops().gemv_qkv_rope(_randn((1, 64), torch.bfloat16, 2), w, torch.zeros((1, 144), dtype=torch.bfloat16,
+                            device=DEV), view, None, 0, 6, batch)
