@@ -6,6 +6,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define DLLM_OK 0
 #define DLLM_BAD_ARGUMENT (-1)
@@ -19,6 +20,40 @@
 
 static inline int dllm_launch_status() {
   return cudaGetLastError() == cudaSuccess ? DLLM_OK : DLLM_LAUNCH_FAILED;
+}
+
+// ---- programmatic dependent launch ----------------------------------------------------------------------------
+// Kernels of the decode step are launched so that the next kernel's blocks may start while this one still runs:
+// a kernel first lets its dependents go (`pdl_launch_dependents`), may read what no earlier kernel of the step
+// writes (weights, tables), and must call `pdl_wait` before it touches anything an earlier kernel produced and
+// before its own first write. Launched without the attribute both calls do nothing. DLLM_B200_PDL=0 turns the
+// attribute off.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+static inline bool dllm_pdl_enabled() {
+  static int enabled = -1;
+  if (enabled < 0) {
+    const char* v = getenv("DLLM_B200_PDL");
+    enabled = (v && v[0] == '0') ? 0 : 1;
+  }
+  return enabled == 1;
+}
+
+template <typename... KArgs, typename... Args>
+static inline int dllm_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                  Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = dllm_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&config, kernel, KArgs(args)...) == cudaSuccess ? DLLM_OK : DLLM_LAUNCH_FAILED;
 }
 
 __device__ __forceinline__ float to_float(float v) { return v; }

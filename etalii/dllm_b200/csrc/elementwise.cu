@@ -8,6 +8,8 @@ template <typename T>
 __global__ void embed_kernel(float* __restrict__ out, const T* __restrict__ table, const int* __restrict__ tokens,
                              int hidden, int vocab, int* __restrict__ status) {
   int row = blockIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
   int token = tokens[row];
   if (token < 0 || token >= vocab) {  // refused, never read out of range
     if (threadIdx.x == 0) atomicExch(status, 1);
@@ -24,13 +26,12 @@ DLLM_EXPORT int dllm_embed(float* out, const void* table, const int* tokens, int
   if (hidden <= 0 || vocab <= 0) return DLLM_BAD_ARGUMENT;
   int threads = hidden >= 256 ? 256 : 64;
   if (dtype == DLLM_F32)
-    embed_kernel<float><<<rows, threads, 0, stream>>>(out, (const float*)table, tokens, hidden, vocab, status);
-  else if (dtype == DLLM_BF16)
-    embed_kernel<__nv_bfloat16><<<rows, threads, 0, stream>>>(out, (const __nv_bfloat16*)table, tokens, hidden,
-                                                              vocab, status);
-  else
-    return DLLM_BAD_ARGUMENT;
-  return dllm_launch_status();
+    return dllm_launch_pdl(embed_kernel<float>, dim3(rows), dim3(threads), 0, stream, out, (const float*)table,
+                           tokens, hidden, vocab, status);
+  if (dtype == DLLM_BF16)
+    return dllm_launch_pdl(embed_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), 0, stream, out,
+                           (const __nv_bfloat16*)table, tokens, hidden, vocab, status);
+  return DLLM_BAD_ARGUMENT;
 }
 
 // ---- RMSNorm: out[r] = x[rows ? rows[r] : r] * (1 / sqrt(mean(x^2) + eps)) * w ---------------------------------------
@@ -165,6 +166,7 @@ DLLM_EXPORT int dllm_add_residual(float* residual, const void* update, long long
 __global__ void decode_advance_kernel(int* __restrict__ tokens, int* __restrict__ tok_pos, int* __restrict__ start,
                                       const int* __restrict__ chosen, int* __restrict__ history,
                                       int* __restrict__ counter, int batch, int capacity) {
+  pdl_wait();
   int row = *counter;
   for (int b = threadIdx.x; b < batch; b += blockDim.x) {
     int token = chosen[b];
@@ -180,6 +182,6 @@ __global__ void decode_advance_kernel(int* __restrict__ tokens, int* __restrict_
 DLLM_EXPORT int dllm_decode_advance(int* tokens, int* tok_pos, int* start, const int* chosen, int* history,
                                     int* counter, int batch, int capacity, cudaStream_t stream) {
   if (batch <= 0) return DLLM_OK;
-  decode_advance_kernel<<<1, 256, 0, stream>>>(tokens, tok_pos, start, chosen, history, counter, batch, capacity);
-  return dllm_launch_status();
+  return dllm_launch_pdl(decode_advance_kernel, dim3(1), dim3(256), 0, stream, tokens, tok_pos, start, chosen,
+                         history, counter, batch, capacity);
 }

@@ -92,6 +92,7 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(void* __restrict__ c, 
     for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
   }
   const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+  pdl_launch_dependents();
   for (int s0 = s_begin; s0 < s_end; s0 += MAX_STEPS) {
     uint4 wl[MAX_STEPS], wh[MAX_STEPS], xb[MAX_STEPS][NT];
     // every load of this stretch is issued before the first product
@@ -102,6 +103,7 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(void* __restrict__ c, 
       wl[i] = ok ? __ldg(w_lo + ch) : zero;
       wh[i] = ok ? __ldg(w_hi + ch) : zero;
     }
+    pdl_wait();  // the weights above are nobody's output; the activations below are the previous kernel's
 #pragma unroll
     for (int i = 0; i < MAX_STEPS; ++i) {
       int ch = (s0 + i) * 4 + t;
@@ -137,6 +139,7 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(void* __restrict__ c, 
       }
     }
   }
+  pdl_wait();  // (a warp without work has not waited yet)
   // partial tiles and partial sums of squares to shared memory
 #pragma unroll
   for (int n = 0; n < NT; ++n) {
@@ -210,15 +213,15 @@ int launch(void* c, const void* a, const float* norm_w, float eps, const bf16* w
            const RopeArgs& rope, cudaStream_t stream) {
   int items = (N + TILE - 1) / TILE;
   bool wide = K >= 1024;
-#define DLLM_GO(WARPS, NT) \
-  gemv_kernel<WARPS, NT, EPI, NORM><<<items, WARPS * 32, 0, stream>>>(c, a, norm_w, eps, w, M, N, K, rope)
+#define DLLM_GO(WARPS, NT)                                                                                    \
+  return dllm_launch_pdl(gemv_kernel<WARPS, NT, EPI, NORM>, dim3(items), dim3(WARPS * 32), 0, stream, c, a, norm_w, \
+                         eps, w, M, N, K, rope)
   if (M <= 8) {
     if (wide) DLLM_GO(8, 1); else DLLM_GO(4, 1);
   } else {
     if (wide) DLLM_GO(8, 2); else DLLM_GO(4, 2);
   }
 #undef DLLM_GO
-  return dllm_launch_status();
 }
 
 template <bool NORM>

@@ -151,6 +151,8 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(
     float temperature, int top_k, double top_p, double min_p) {
   __shared__ Shared sh;
   int row = blockIdx.x, tid = threadIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
   const float* l = logits + (size_t)row * row_stride;
   float best = -INFINITY;
   int best_i = 0x7fffffff;
@@ -277,9 +279,8 @@ DLLM_EXPORT int dllm_sample(int* out_tokens, const float* logits, long long row_
   if (rows <= 0) return DLLM_OK;
   if (vocab <= 0 || temperature < 0.f || !(top_p > 0.0) || min_p < 0.0 || top_k < 0) return DLLM_BAD_ARGUMENT;
   if (temperature > 0.f && (scratch == nullptr || rng == nullptr || rng_rows == nullptr)) return DLLM_BAD_ARGUMENT;
-  sample_kernel<<<rows, THREADS, 0, stream>>>(out_tokens, logits, row_stride, vocab, scratch, rng, rng_rows,
-                                              temperature, top_k, top_p, min_p);
-  return dllm_launch_status();
+  return dllm_launch_pdl(sample_kernel, dim3(rows), dim3(THREADS), 0, stream, out_tokens, logits, row_stride, vocab,
+                         scratch, rng, rng_rows, temperature, top_k, top_p, min_p);
 }
 
 // rng[rows[i]] = xoshiro256** state from SplitMix64(seeds[i]).

@@ -29,6 +29,15 @@ class Workspace:
             self.generation += 1
         return have[:count].view(*shape)
 
+    def zeros(self, name: str, count: int, dtype) -> torch.Tensor:
+        """A buffer that starts as zeros and is kept between steps (kernels that use it leave it zero)."""
+        have = self._buffers.get(name)
+        if have is None or have.dtype != dtype or have.numel() < count:
+            have = torch.zeros(max(count, 256), dtype=dtype, device=self.device)
+            self._buffers[name] = have
+            self.generation += 1
+        return have[:count]
+
     def bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self._buffers.values())
 

@@ -40,7 +40,7 @@ _prototypes = {
                                               c_void_p],
     ("attention_decode", "dllm_attention_decode"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                                     c_int, c_void_p, c_void_p, c_int, c_float, c_int, c_int, c_int,
-                                                    c_void_p, c_void_p],
+                                                    c_void_p, c_void_p, c_void_p],
     ("attention_prefill", "dllm_attention_prefill"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                                       c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                       c_int, c_float, c_int, c_void_p],
@@ -258,21 +258,22 @@ def attention_decode_scratch(sequences: int, heads: int, head_dim: int, chunk: i
 
 
 def attention_decode(out: torch.Tensor, q: torch.Tensor, cache, heads: int, scale: float, window: int, batch,
-                     chunk: int, scratch: torch.Tensor) -> None:
+                     chunk: int, scratch: torch.Tensor, tickets: torch.Tensor) -> None:
     """Attention for a batch in which every sequence brings one token (bfloat16): keys are split into chunks of
     `chunk` positions across blocks, every block serves all query heads of its kv head, partial results are combined
-    in chunk order. Serves any length up to batch.max_context."""
-    _cuda(out, q, scratch)
+    in chunk order by the block that finishes last. Serves any length up to batch.max_context. `tickets`: int32
+    zeros, one per (sequence, kv head); the kernel leaves them zero."""
+    _cuda(out, q, scratch, tickets)
+    assert tickets.dtype == torch.int32 and tickets.numel() >= batch.n_seqs * cache.kv_heads
     assert cache.dtype == torch.bfloat16 and q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
     assert batch.n_tokens == batch.n_seqs and scratch.dtype == torch.float32
     assert scratch.numel() >= attention_decode_scratch(batch.n_seqs, heads, cache.head_dim, chunk, batch.max_context)
     _check(_fn("attention_decode", "dllm_attention_decode")(
         out.data_ptr(), q.data_ptr(), cache.base_ptr, cache.page_table.data_ptr(), cache.max_pages, cache.page_size,
         heads, cache.kv_heads, cache.head_dim, batch.tok_pos.data_ptr(), batch.slots.data_ptr(), batch.n_seqs,
-        float(scale), int(window or 0), int(chunk), int(batch.max_context), scratch.data_ptr(), _stream()),
+        float(scale), int(window or 0), int(chunk), int(batch.max_context), scratch.data_ptr(),
+        tickets.data_ptr(), _stream()),
         "attention_decode", f"head_dim={cache.head_dim} must be a multiple of 8, at most 256")
-    global launches
-    launches += 1  # two kernels: partial results, then the combination
 
 
 def attention_prefill_supported(cache) -> bool:

@@ -12,9 +12,12 @@ from .registry import build_part, register_part
 from .spec import ParamSpec
 
 
-def decode_chunk(sequences: int, kv_heads: int, max_context: int) -> int:
-    """Keys per block of the decode kernel: small chunks spread few sequences over the whole device, larger ones
-    keep the number of blocks (one per chunk, kv head and sequence) in bounds."""
+def decode_chunk(sequences: int, kv_heads: int, max_context: int, head_dim: int = 0) -> int:
+    """Keys per block of the decode kernel. Head sizes the tensor-core kernel takes (multiples of 16 up to 128) use
+    its fixed 256; otherwise small chunks spread few sequences over the whole device and larger ones keep the
+    number of blocks (one per chunk, kv head and sequence) in bounds."""
+    if head_dim and head_dim % 16 == 0 and head_dim <= 128:
+        return 256
     for chunk in (64, 128, 256, 512):
         if -(-max_context // chunk) * kv_heads * sequences <= 8192:
             return chunk
@@ -69,11 +72,12 @@ class Attention:
             ops.rope_cache_write(qkv, q, cache, table, rotary_dim, self.num_heads, batch, write_cache)
         attended = rt.ws.buffer("attended", (n, q_size), rt.dtype)
         if batch.is_decode and rt.dtype == torch.bfloat16:
-            chunk = decode_chunk(batch.n_seqs, self.num_kv_heads, batch.max_context)
+            chunk = decode_chunk(batch.n_seqs, self.num_kv_heads, batch.max_context, self.head_dim)
             scratch = rt.ws.buffer("attention_scratch", (ops.attention_decode_scratch(
                 batch.n_seqs, self.num_heads, self.head_dim, chunk, batch.max_context),), torch.float32)
+            tickets = rt.ws.zeros("attention_tickets", batch.n_seqs * self.num_kv_heads, torch.int32)
             ops.attention_decode(attended, q, cache, self.num_heads, self.scale, self.window or 0, batch, chunk,
-                                 scratch)
+                                 scratch, tickets)
         elif not batch.is_decode and ops.attention_prefill_supported(cache):
             ops.attention_prefill(attended, q, cache, self.num_heads, self.scale, self.window or 0, batch)
         else:

@@ -148,7 +148,7 @@ def gemv_qkv_rope(a, w, q_out, cache, table, rotary_dim, heads, batch, write_cac
     rope_cache_write(qkv, q_out, cache, table, rotary_dim, heads, batch, write_cache)
 
 
-def attention_decode(out, q, cache, heads, scale, window, batch, chunk, scratch):
+def attention_decode(out, q, cache, heads, scale, window, batch, chunk, scratch, tickets):
     attention_general(out, q, cache, heads, scale, window, batch)
 
 

@@ -266,7 +266,11 @@ def test_attention_decode(heads, kv_heads, head_dim, window, chunk):
     batch.max_context = 1024  # sized for more than any sequence holds, as under a CUDA graph
     scratch = torch.full((ops().attention_decode_scratch(n, heads, head_dim, chunk, 1024),), float("nan"),
                          dtype=torch.float32, device=DEV)
-    ops().attention_decode(out, q, view, heads, 0.3, window or 0, batch, chunk, scratch)
+    tickets = torch.zeros(n * kv_heads, dtype=torch.int32, device=DEV)
+    ops().attention_decode(out, q, view, heads, 0.3, window or 0, batch, chunk, scratch, tickets)
+    again = torch.zeros_like(out)
+    ops().attention_decode(again, q, view, heads, 0.3, window or 0, batch, chunk, scratch, tickets)
+    assert int(tickets.abs().sum()) == 0 and torch.equal(again, out)  # the counters are back at zero; same bits
     view_cpu = type(view)(view.storage.cpu(), view.page_table.cpu(), view.page_size, kv_heads, head_dim, window)
     cpu_batch = type("B", (), {"n_tokens": n, "tok_pos": batch.tok_pos.cpu(), "tok_seq": batch.tok_seq.cpu(),
                                "slots": batch.slots.cpu()})
@@ -290,7 +294,8 @@ def test_attention_decode_finds_a_far_key():
         view.storage[page, 1, :, target % 64, :] = 7.0
         q = torch.full((1, heads * hd), 4.0, dtype=torch.bfloat16, device=DEV)
         out = torch.zeros_like(q)
-        ops().attention_decode(out, q, view, heads, 1.0, 0, batch, 64, scratch)
+        ops().attention_decode(out, q, view, heads, 1.0, 0, batch, 64, scratch,
+                               torch.zeros(kv_heads, dtype=torch.int32, device=DEV))
         assert torch.allclose(out.float(), torch.full_like(out, 7.0).float(), atol=0.05), target
         view.storage[page] = saved
 
