@@ -173,8 +173,8 @@ def main() -> int:
     args = parser.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference does not install offline: its build needs scikit-build-core with nanobind, "
-                          "and nanobind is not in the wheelhouse"}))
+                          "the reference does not install offline: pip finds no numpy in the wheelhouse, and with "
+                          "--no-deps its wheel build fails in CMake because nanobind is not installed"}))
         return 0
     if args.gpus != 1:
         print(f"bench.py measures one GPU: --gpus {args.gpus} is not supported (this library runs on a single device)")

@@ -30,6 +30,22 @@ struct RopeArgs {
   int write_cache;
 };
 
+// Weights that a later kernel of the step will stream: every block asks the L2 cache for its share of them while
+// its own loads are in flight, so that the later kernel reads from L2 instead of waiting on DRAM.
+struct Prefetch {
+  const char* ptr;
+  size_t bytes;
+};
+
+__device__ __forceinline__ void prefetch_share(const Prefetch& pf) {
+  if (pf.ptr == nullptr) return;
+  size_t lines = (pf.bytes + 127) / 128;
+  size_t per_block = (lines + gridDim.x - 1) / gridDim.x;
+  size_t begin = (size_t)blockIdx.x * per_block, end = min(lines, begin + per_block);
+  for (size_t line = begin + threadIdx.x; line < end; line += blockDim.x)
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(pf.ptr + line * 128));
+}
+
 __device__ __forceinline__ void mma_bf16(float* c, const unsigned* a, unsigned b0, unsigned b1) {
   asm volatile(
       "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
@@ -67,7 +83,7 @@ template <int WARPS, int NT, int EPI, bool NORM>
 __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(void* __restrict__ c, const void* __restrict__ a,
                                                           const float* __restrict__ norm_w, float eps,
                                                           const bf16* __restrict__ w, int M, int N, int K,
-                                                          RopeArgs rope) {
+                                                          RopeArgs rope, Prefetch pf) {
   __shared__ float red[WARPS][TILE][NT * 8 + 1];
   __shared__ float red_ss[WARPS][NT * 8];
   int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -103,6 +119,7 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(void* __restrict__ c, 
       wl[i] = ok ? __ldg(w_lo + ch) : zero;
       wh[i] = ok ? __ldg(w_hi + ch) : zero;
     }
+    if (s0 == s_begin) prefetch_share(pf);
     pdl_wait();  // the weights above are nobody's output; the activations below are the previous kernel's
 #pragma unroll
     for (int i = 0; i < MAX_STEPS; ++i) {
@@ -210,12 +227,12 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(void* __restrict__ c, 
 
 template <int EPI, bool NORM>
 int launch(void* c, const void* a, const float* norm_w, float eps, const bf16* w, int M, int N, int K,
-           const RopeArgs& rope, cudaStream_t stream) {
+           const RopeArgs& rope, const Prefetch& pf, cudaStream_t stream) {
   int items = (N + TILE - 1) / TILE;
   bool wide = K >= 1024;
 #define DLLM_GO(WARPS, NT)                                                                                    \
   return dllm_launch_pdl(gemv_kernel<WARPS, NT, EPI, NORM>, dim3(items), dim3(WARPS * 32), 0, stream, c, a, norm_w, \
-                         eps, w, M, N, K, rope)
+                         eps, w, M, N, K, rope, pf)
   if (M <= 8) {
     if (wide) DLLM_GO(8, 1); else DLLM_GO(4, 1);
   } else {
@@ -226,13 +243,13 @@ int launch(void* c, const void* a, const float* norm_w, float eps, const bf16* w
 
 template <bool NORM>
 int dispatch(void* c, const void* a, const float* norm_w, float eps, const bf16* w, int M, int N, int K, int epilogue,
-             const RopeArgs& rope, cudaStream_t stream) {
+             const RopeArgs& rope, const Prefetch& pf, cudaStream_t stream) {
   switch (epilogue) {
-    case EPI_STORE_F32: return launch<EPI_STORE_F32, NORM>(c, a, norm_w, eps, w, M, N, K, rope, stream);
-    case EPI_STORE_T: return launch<EPI_STORE_T, NORM>(c, a, norm_w, eps, w, M, N, K, rope, stream);
-    case EPI_RESIDUAL: return launch<EPI_RESIDUAL, NORM>(c, a, norm_w, eps, w, M, N, K, rope, stream);
-    case EPI_SWIGLU: return launch<EPI_SWIGLU, NORM>(c, a, norm_w, eps, w, M, N, K, rope, stream);
-    case EPI_QKV_ROPE: return launch<EPI_QKV_ROPE, NORM>(c, a, norm_w, eps, w, M, N, K, rope, stream);
+    case EPI_STORE_F32: return launch<EPI_STORE_F32, NORM>(c, a, norm_w, eps, w, M, N, K, rope, pf, stream);
+    case EPI_STORE_T: return launch<EPI_STORE_T, NORM>(c, a, norm_w, eps, w, M, N, K, rope, pf, stream);
+    case EPI_RESIDUAL: return launch<EPI_RESIDUAL, NORM>(c, a, norm_w, eps, w, M, N, K, rope, pf, stream);
+    case EPI_SWIGLU: return launch<EPI_SWIGLU, NORM>(c, a, norm_w, eps, w, M, N, K, rope, pf, stream);
+    case EPI_QKV_ROPE: return launch<EPI_QKV_ROPE, NORM>(c, a, norm_w, eps, w, M, N, K, rope, pf, stream);
     default: return DLLM_BAD_ARGUMENT;
   }
 }
@@ -240,13 +257,16 @@ int dispatch(void* c, const void* a, const float* norm_w, float eps, const bf16*
 
 // C = X[M,K] * W[N,K]^T for M <= 16. With norm_w != null, X is the float32 residual stream and is RMS-normed on
 // the way in; else X is bfloat16. Epilogues 0..3 as the tile kernels; K a multiple of 8, N even.
+// prefetch_ptr / prefetch_bytes: optional memory (weights a later kernel reads) to bring into L2 meanwhile.
 DLLM_EXPORT int dllm_gemv_bf16(void* c, const void* a, const float* norm_w, float eps, const void* w, int M, int N,
-                               int K, int epilogue, cudaStream_t stream) {
+                               int K, int epilogue, const void* prefetch_ptr, long long prefetch_bytes,
+                               cudaStream_t stream) {
   if (M <= 0 || N <= 0) return DLLM_OK;
   if (M > 16 || K <= 0 || (K & 7) || (N & 1) || epilogue < 0 || epilogue > EPI_SWIGLU) return DLLM_UNSUPPORTED_SIZE;
   RopeArgs rope{};
-  return norm_w ? dispatch<true>(c, a, norm_w, eps, (const bf16*)w, M, N, K, epilogue, rope, stream)
-                : dispatch<false>(c, a, nullptr, eps, (const bf16*)w, M, N, K, epilogue, rope, stream);
+  Prefetch pf{(const char*)prefetch_ptr, prefetch_ptr ? (size_t)prefetch_bytes : 0};
+  return norm_w ? dispatch<true>(c, a, norm_w, eps, (const bf16*)w, M, N, K, epilogue, rope, pf, stream)
+                : dispatch<false>(c, a, nullptr, eps, (const bf16*)w, M, N, K, epilogue, rope, pf, stream);
 }
 
 // The q/k/v projection of a decode step in one kernel: optional RMSNorm in front, rotation of q and k by the
@@ -256,7 +276,7 @@ DLLM_EXPORT int dllm_gemv_qkv_rope(const void* a, const float* norm_w, float eps
                                    void* q_out, void* cache_base, const int* page_table, int max_pages, int page_size,
                                    int heads, int kv_heads, int head_dim, const float* table, int rotary_dim,
                                    const int* tok_seq, const int* tok_pos, const int* slots, int write_cache,
-                                   cudaStream_t stream) {
+                                   const void* prefetch_ptr, long long prefetch_bytes, cudaStream_t stream) {
   if (M <= 0) return DLLM_OK;
   if (M > 16 || K <= 0 || (K & 7) || heads <= 0 || kv_heads <= 0 || head_dim <= 0 || (head_dim & 15) ||
       rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 15))
@@ -264,6 +284,7 @@ DLLM_EXPORT int dllm_gemv_qkv_rope(const void* a, const float* norm_w, float eps
   RopeArgs rope{(bf16*)q_out, KvLayout{cache_base, page_table, max_pages, page_size, kv_heads, head_dim},
                 (const float2*)table, table ? rotary_dim : 0, heads, tok_seq, tok_pos, slots, write_cache};
   int N = (heads + 2 * kv_heads) * head_dim;
-  return norm_w ? dispatch<true>(nullptr, a, norm_w, eps, (const bf16*)w, M, N, K, EPI_QKV_ROPE, rope, stream)
-                : dispatch<false>(nullptr, a, nullptr, eps, (const bf16*)w, M, N, K, EPI_QKV_ROPE, rope, stream);
+  Prefetch pf{(const char*)prefetch_ptr, prefetch_ptr ? (size_t)prefetch_bytes : 0};
+  return norm_w ? dispatch<true>(nullptr, a, norm_w, eps, (const bf16*)w, M, N, K, EPI_QKV_ROPE, rope, pf, stream)
+                : dispatch<false>(nullptr, a, nullptr, eps, (const bf16*)w, M, N, K, EPI_QKV_ROPE, rope, pf, stream);
 }

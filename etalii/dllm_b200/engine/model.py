@@ -52,6 +52,24 @@ class Model:
             else:
                 self._views.append(self.cache.state(entry.cache))
 
+        self._plan_prefetch()
+
+    def _plan_prefetch(self, ahead: int = 4) -> None:
+        """Tells the decode-sized products which weights come `ahead` products later in the run order, so that they
+        can be brought into L2 before they are needed (kernels/ops.py::prefetch_hints)."""
+        from ..kernels import ops
+
+        order = []
+        for entry in self.order:
+            block = self.blocks[entry.layer]
+            for part in (block.mixer, block.feed_forward):
+                order += [v for v in vars(part).values()
+                          if isinstance(v, torch.Tensor) and v.dim() == 2 and v.dtype == torch.bfloat16]
+        order += [v for v in vars(self.head).values() if isinstance(v, torch.Tensor) and v.dim() == 2
+                  and v.dtype == torch.bfloat16]
+        for index, tensor in enumerate(order[:-ahead] if len(order) > ahead else []):
+            ops.prefetch_hints[tensor.data_ptr()] = order[index + ahead]
+
     def forward(self, batch) -> torch.Tensor:
         """Runs the batch's tokens through every scheduled layer; returns float32 logits [wanted rows, vocab]
         (None when no row is wanted: the cache is still filled)."""

@@ -31,10 +31,10 @@ _prototypes = {
     ("gemm_simt", "dllm_gemm_f32"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     ("gemm_bf16", "dllm_gemm_bf16"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     ("gemv", "dllm_gemv_bf16"): [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int,
-                                 c_void_p],
+                                 c_void_p, c_longlong, c_void_p],
     ("gemv", "dllm_gemv_qkv_rope"): [c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_void_p, c_void_p,
                                      c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p,
-                                     c_void_p, c_void_p, c_int, c_void_p],
+                                     c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_void_p],
     ("attention", "dllm_attention_general"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                               c_int, c_void_p, c_void_p, c_void_p, c_int, c_float, c_int, c_int,
                                               c_void_p],
@@ -114,6 +114,16 @@ def rmsnorm(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, eps: float
                                               float(eps), _code(out.dtype), _stream()), "rmsnorm")
 
 
+prefetch_hints: dict[int, torch.Tensor] = {}
+"""Weight tensor (by address) -> the weight tensor a later kernel of the step streams. A decode-sized product whose
+weights are a key asks the L2 cache for the value while it runs. The model fills this from its run order."""
+
+
+def _prefetch_of(w: torch.Tensor):
+    hint = prefetch_hints.get(w.data_ptr())
+    return (hint.data_ptr(), hint.numel() * hint.element_size()) if hint is not None else (None, 0)
+
+
 GEMV_MAX_ROWS = 16
 """Products with at most this many activation rows run in the weight-streaming kernel."""
 
@@ -146,7 +156,7 @@ def gemm(c: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int = EPI_
                 assert a.dtype == torch.bfloat16
             status = _fn("gemv", "dllm_gemv_bf16")(
                 c.data_ptr(), a.data_ptr(), norm_weight.data_ptr() if norm_weight is not None else None, float(eps),
-                w.data_ptr(), m, n, k, epilogue, _stream())
+                w.data_ptr(), m, n, k, epilogue, *_prefetch_of(w), _stream())
             detail += f", M at most {GEMV_MAX_ROWS}"
         else:
             assert a.dtype == torch.bfloat16 and norm_weight is None
@@ -175,7 +185,7 @@ def gemv_qkv_rope(a: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, cache, 
         q_out.data_ptr(), cache.base_ptr, cache.page_table.data_ptr(), cache.max_pages, cache.page_size, heads,
         cache.kv_heads, cache.head_dim, table.data_ptr() if table is not None else None,
         rotary_dim if table is not None else 0, batch.tok_seq.data_ptr(), batch.tok_pos.data_ptr(),
-        batch.slots.data_ptr(), 1 if write_cache else 0, _stream()),
+        batch.slots.data_ptr(), 1 if write_cache else 0, *_prefetch_of(w), _stream()),
         "gemv_qkv_rope", f"M={m} (at most 16), K={k} (multiple of 8), head_dim and rotary_dim multiples of 16")
 
 
