@@ -1,0 +1,255 @@
+// bfloat16 matrix product on the 5th-generation tensor cores: C = A[M,K] * W[N,K]^T, float32 accumulation in tensor
+// memory. One block computes a 128 x BN tile of C:
+//   warp 0   one lane issues TMA loads (cp.async.bulk.tensor.2d, 128-byte swizzle) of 128x64 tiles of A and BNx64
+//            tiles of W into a ring of shared-memory stages, signalled by mbarriers (expect_tx / complete_tx);
+//   warp 1   allocates tensor memory; one lane issues tcgen05.mma (cta_group::1, kind::f16, M=128, N=BN, K=16) four
+//            per stage and commits each stage back to the producer (tcgen05.commit -> mbarrier), then commits the
+//            whole accumulator to the epilogue;
+//   warps 2-5 read the accumulator (tcgen05.ld 32x32b, a lane per row) and apply the epilogue: store float32 or
+//            bfloat16, add into the float32 residual, or SwiGLU on interleaved gate/up columns.
+// Rows of A beyond M and columns of K beyond the matrix are zero-filled by TMA; rows of W beyond N give columns
+// that are never stored. No multicast, no clusters. Every wait on an mbarrier is bounded: after the limit the role
+// records a status word and leaves, the block still frees its tensor memory, and the host raises.
+#include <cuda.h>
+
+#include "gemm_common.cuh"
+
+namespace {
+typedef __nv_bfloat16 bf16;
+constexpr int BM = 128, BK = 64, UMMA_K = 16;
+constexpr int THREADS = 192;
+constexpr long long WAIT_LIMIT_CYCLES = 2000000000ll;  // about a second
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait: false if the phase did not complete within the limit.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity) {
+  unsigned addr = smem_u32(bar);
+  long long begin = clock64();
+  for (unsigned i = 0;; ++i) {
+    unsigned done;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+    if (done) return true;
+    if ((i & 63) == 63 && clock64() - begin > WAIT_LIMIT_CYCLES) return false;
+  }
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tcgen05_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+// Shared-memory matrix descriptor of a K-major tile with 128-byte rows and 128-byte swizzle: start address / 16,
+// stride between 8-row groups 1024 bytes, descriptor version 1, swizzle mode 2 (128 bytes).
+__device__ __forceinline__ uint64_t smem_desc(unsigned addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)1 << 16;                 // leading byte offset (unused for swizzled K-major), 16 bytes
+  d |= (uint64_t)(1024 >> 4) << 32;       // stride byte offset
+  d |= (uint64_t)1 << 46;                 // descriptor version
+  d |= (uint64_t)2 << 61;                 // 128-byte swizzle
+  return d;
+}
+// Instruction descriptor, kind::f16: D float32, A and B bfloat16, both K-major, N / 8 at bit 17, M / 16 at bit 24.
+__host__ __device__ constexpr unsigned instr_desc(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
+}
+__device__ __forceinline__ void umma(unsigned tmem_d, uint64_t adesc, uint64_t bdesc, unsigned idesc, unsigned acc) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void tmem_load16(unsigned taddr, unsigned* v) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+template <int BN> struct Shape {
+  static constexpr int STAGES = BN >= 128 ? 5 : 6;
+  static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
+  static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;  // a power of two, at least 32
+  static constexpr size_t SMEM = (size_t)STAGES * (A_BYTES + B_BYTES) + 1024;
+};
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                               const __grid_constant__ CUtensorMap map_w,
+                                                               void* __restrict__ c, int M, int N, int K,
+                                                               int* __restrict__ status) {
+  typedef Shape<BN> S;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);  // swizzle atoms: 1 KB
+  __shared__ uint64_t full_bar[S::STAGES], empty_bar[S::STAGES], acc_bar;
+  __shared__ unsigned tmem_base_s;
+  int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  int k_tiles = (K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    mbar_init(&acc_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {  // tensor memory for the accumulator: BN columns of 128 lanes
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&tmem_base_s)), "r"((unsigned)S::TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  unsigned tmem_base = tmem_base_s;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+      for (int kt = 0; kt < k_tiles; ++kt) {
+        int s = kt % S::STAGES;
+        if (kt >= S::STAGES && !mbar_wait(&empty_bar[s], ((kt / S::STAGES) - 1) & 1)) { *(volatile int*)status = 2; break; }
+        mbar_expect_tx(&full_bar[s], S::A_BYTES + S::B_BYTES);
+        unsigned char* a_dst = tiles + (size_t)s * (S::A_BYTES + S::B_BYTES);
+        tma_load_2d(a_dst, &map_a, &full_bar[s], kt * BK, m0);
+        tma_load_2d(a_dst + S::A_BYTES, &map_w, &full_bar[s], kt * BK, n0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr unsigned idesc = instr_desc(BN);
+      bool ok = true;
+      for (int kt = 0; kt < k_tiles && ok; ++kt) {
+        int s = kt % S::STAGES;
+        if (!mbar_wait(&full_bar[s], (kt / S::STAGES) & 1)) { *(volatile int*)status = 3; ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        unsigned a_addr = smem_u32(tiles + (size_t)s * (S::A_BYTES + S::B_BYTES));
+        unsigned b_addr = a_addr + S::A_BYTES;
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) {
+          uint64_t adesc = smem_desc(a_addr + k * UMMA_K * 2), bdesc = smem_desc(b_addr + k * UMMA_K * 2);
+          umma(tmem_base, adesc, bdesc, idesc, (kt > 0 || k > 0) ? 1u : 0u);
+        }
+        tcgen05_commit(&empty_bar[s]);  // the stage is free once these products have read it
+      }
+      tcgen05_commit(&acc_bar);         // the accumulator is complete once every product has finished
+    }
+  } else {
+    // epilogue warps 2..5: warp w may read tensor-memory lanes 32 * (w % 4) .. + 31
+    int quarter = warp & 3;
+    int m = m0 + quarter * 32 + lane;
+    bool ready = mbar_wait(&acc_bar, 0);
+    if (!ready && lane == 0) *(volatile int*)status = 4;
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ready) {
+#pragma unroll
+      for (int col = 0; col < BN; col += 16) {
+        unsigned v[16];
+        tmem_load16(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)col, v);
+        if (m < M) {
+#pragma unroll
+          for (int i = 0; i < 16; i += 2)
+            epilogue_pair<EPI, bf16>(c, m, n0 + col + i, M, N, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((unsigned)S::TMEM_COLS)
+                 : "memory");
+  }
+}
+
+// ---- host side: tensor maps through the driver entry point (no link against libcuda) ---------------------------
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encoder() {
+  static EncodeTiled fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &result) == cudaSuccess &&
+        result == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiled)p;
+  }
+  return fn;
+}
+
+// A [rows, cols] bfloat16 row-major matrix, boxes of box_rows x 64 columns, 128-byte swizzle, zero fill outside.
+bool make_map(CUtensorMap* map, const void* base, int rows, int cols, int box_rows) {
+  EncodeTiled encode = encoder();
+  if (encode == nullptr) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, int EPI>
+int launch(void* c, const void* a, const void* w, int M, int N, int K, int* status, cudaStream_t stream) {
+  alignas(64) CUtensorMap map_a, map_w;
+  if (!make_map(&map_a, a, M, K, BM) || !make_map(&map_w, w, N, K, BN)) return DLLM_LAUNCH_FAILED;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)Shape<BN>::SMEM) != cudaSuccess)
+      return DLLM_LAUNCH_FAILED;
+    configured = true;
+  }
+  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+  gemm_tcgen05_kernel<BN, EPI><<<grid, THREADS, Shape<BN>::SMEM, stream>>>(map_a, map_w, c, M, N, K, status);
+  return dllm_launch_status();
+}
+
+template <int BN>
+int dispatch(void* c, const void* a, const void* w, int M, int N, int K, int epilogue, int* status,
+             cudaStream_t stream) {
+  switch (epilogue) {
+    case EPI_STORE_F32: return launch<BN, EPI_STORE_F32>(c, a, w, M, N, K, status, stream);
+    case EPI_STORE_T: return launch<BN, EPI_STORE_T>(c, a, w, M, N, K, status, stream);
+    case EPI_RESIDUAL: return launch<BN, EPI_RESIDUAL>(c, a, w, M, N, K, status, stream);
+    case EPI_SWIGLU: return launch<BN, EPI_SWIGLU>(c, a, w, M, N, K, status, stream);
+    default: return DLLM_BAD_ARGUMENT;
+  }
+}
+}  // namespace
+
+// C = A[M,K] * W[N,K]^T (bfloat16, float32 accumulation in tensor memory). K must be a multiple of 8 (16-byte row
+// pitch for TMA), N even, and A and W 16-byte aligned. `tile_n`: 32, 64 or 128 columns of C per block (0 chooses).
+// `status` is a word the device can write (device or pinned host memory); the kernel sets it non-zero if one of its
+// bounded waits ran out (2: producer, 3: product issuer, 4: epilogue).
+DLLM_EXPORT int dllm_gemm_tcgen05(void* c, const void* a, const void* w, int M, int N, int K, int epilogue, int tile_n,
+                                  int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return DLLM_OK;
+  if (K <= 0 || (K & 7) || (N & 1) || ((uintptr_t)a & 15) || ((uintptr_t)w & 15) || status == nullptr)
+    return DLLM_UNSUPPORTED_SIZE;
+  if ((M + BM - 1) / BM > 65535) return DLLM_UNSUPPORTED_SIZE;
+  if (tile_n == 0) tile_n = M <= 256 ? 32 : ((N % 128 == 0 && N >= 2048) ? 128 : 64);
+  switch (tile_n) {
+    case 32: return dispatch<32>(c, a, w, M, N, K, epilogue, status, stream);
+    case 64: return dispatch<64>(c, a, w, M, N, K, epilogue, status, stream);
+    case 128: return dispatch<128>(c, a, w, M, N, K, epilogue, status, stream);
+    default: return DLLM_BAD_ARGUMENT;
+  }
+}

@@ -30,6 +30,8 @@ _prototypes = {
                                              c_void_p],
     ("gemm_simt", "dllm_gemm_f32"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     ("gemm_bf16", "dllm_gemm_bf16"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    ("gemm_tcgen05", "dllm_gemm_tcgen05"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                            c_void_p],
     ("gemv", "dllm_gemv_bf16"): [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int,
                                  c_void_p, c_longlong, c_void_p],
     ("gemv", "dllm_gemv_qkv_rope"): [c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_void_p, c_void_p,
@@ -124,16 +126,37 @@ def _prefetch_of(w: torch.Tensor):
     return (hint.data_ptr(), hint.numel() * hint.element_size()) if hint is not None else (None, 0)
 
 
+_async_status = None
+
+
+def _status_word() -> torch.Tensor:
+    """A pinned host word that kernels with bounded waits set when a wait runs out; the host can read it at any
+    time without a synchronisation."""
+    global _async_status
+    if _async_status is None:
+        _async_status = torch.zeros(1, dtype=torch.int32).pin_memory()
+    return _async_status
+
+
+def raise_if_failed() -> None:
+    """Raises if a kernel reported that one of its bounded waits ran out (its results are then not valid)."""
+    if _async_status is not None and int(_async_status[0]) != 0:
+        code = int(_async_status[0])
+        _async_status[0] = 0
+        raise KernelError(f"a tcgen05 product gave up waiting on an mbarrier (role code {code}); results are invalid")
+
+
 GEMV_MAX_ROWS = 16
 """Products with at most this many activation rows run in the weight-streaming kernel."""
 
 
 def gemm(c: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int = EPI_STORE_T, kernel: int = 0,
-         norm_weight: torch.Tensor | None = None, eps: float = 0.0) -> None:
+         norm_weight: torch.Tensor | None = None, eps: float = 0.0, tile_n: int = 0) -> None:
     """c = a[M,K] @ w[N,K]^T with float32 accumulation, then the epilogue: EPI_STORE_F32 (c float32), EPI_STORE_T
     (c in the weights' dtype), EPI_RESIDUAL (c float32 += product), EPI_SWIGLU (w interleaves gate and up rows;
-    c[M,N/2] = silu(gate) * up). float32 weights run the true 32-bit kernel; bfloat16 the tensor-core tile kernel
-    or, for M <= 16, the weight-streaming kernel (`kernel`: 0 chooses by M, 1 forces tiles, 2 forces streaming).
+    c[M,N/2] = silu(gate) * up). float32 weights run the true 32-bit kernel; bfloat16 the tcgen05/TMA tile kernel
+    or, for M <= 16, the weight-streaming kernel (`kernel`: 0 chooses by M, 1 forces the mma.sync tile kernel, 2
+    forces streaming, 3 forces tcgen05; `tile_n` picks the tcgen05 tile width).
     With `norm_weight` (streaming kernel only), `a` is the float32 residual stream and is RMS-normed on the way in."""
     _cuda(c, a, w, norm_weight)
     m, k = a.shape
@@ -158,10 +181,15 @@ def gemm(c: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int = EPI_
                 c.data_ptr(), a.data_ptr(), norm_weight.data_ptr() if norm_weight is not None else None, float(eps),
                 w.data_ptr(), m, n, k, epilogue, *_prefetch_of(w), _stream())
             detail += f", M at most {GEMV_MAX_ROWS}"
-        else:
+        elif kernel == 1:
             assert a.dtype == torch.bfloat16 and norm_weight is None
             status = _fn("gemm_bf16", "dllm_gemm_bf16")(c.data_ptr(), a.data_ptr(), w.data_ptr(), m, n, k, epilogue,
                                                         _stream())
+        else:
+            assert a.dtype == torch.bfloat16 and norm_weight is None
+            status = _fn("gemm_tcgen05", "dllm_gemm_tcgen05")(
+                c.data_ptr(), a.data_ptr(), w.data_ptr(), m, n, k, epilogue, tile_n, _status_word().data_ptr(),
+                _stream())
     else:
         raise KernelError(f"gemm: dtype {w.dtype} is not supported")
     _check(status, "gemm", detail)

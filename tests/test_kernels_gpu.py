@@ -401,3 +401,18 @@ def test_gemv_qkv_rope_refuses_head_sizes_it_cannot_pair():
     with pytest.raises(KernelError, match="multiples of 16"):
         ops().gemv_qkv_rope(_randn((1, 64), torch.bfloat16, 2), w, torch.zeros((1, 144), dtype=torch.bfloat16,
                             device=DEV), view, None, 0, 6, batch)
+
+
+@pytest.mark.parametrize("m,n,k", GEMM_SHAPES + [(2048, 576, 576), (1000, 960, 1536), (64, 3072, 576), (129, 192, 72)])
+@pytest.mark.parametrize("epilogue", [0, 1, 2, 3])
+@pytest.mark.parametrize("tile_n", [32, 64, 128])
+def test_gemm_tcgen05(m, n, k, epilogue, tile_n):
+    a, w = _randn((m, k), torch.bfloat16, 3), _randn((n, k), torch.bfloat16, 4, 0.2)
+    cols = n // 2 if epilogue == 3 else n
+    c = _randn((m, cols), torch.float32 if epilogue in (0, 2) else torch.bfloat16, 5)
+    ref = c.clone()
+    ops().gemm(c, a, w, epilogue, kernel=3, tile_n=tile_n)
+    torch.cuda.synchronize()
+    ops().raise_if_failed()
+    PK.gemm(ref, a, w, epilogue)
+    assert rel_error(c.float().cpu(), ref.float().cpu()) <= (2e-5 if epilogue in (0, 2) else 8e-3)
