@@ -12,6 +12,7 @@
 namespace {
 typedef __nv_bfloat16 bf16;
 constexpr int BM = 64, BN = 64, WARPS = 4, THREADS = WARPS * 32;
+constexpr int MAX_TILES = 512;  // page indices kept in shared memory (32,768 positions); beyond: read as needed
 
 __device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid) {
   unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -74,9 +75,13 @@ __global__ void __launch_bounds__(THREADS) prefill_kernel(
   int last_pos = pos0 + rows - 1;                                   // last query's position
   int kt_end = last_pos / BN;                                       // last key tile any query of the tile sees
   int kt_begin = (window > 0 && pos0 + 1 > window) ? (pos0 + 1 - window) / BN : 0;
+  // the pages of the key tiles this block will read, fetched once (not one dependent load per tile)
+  __shared__ int page_s[MAX_TILES];
+  for (int i = tid; i <= kt_end - kt_begin && i < MAX_TILES; i += THREADS) page_s[i] = pages[kt_begin + i];
+  __syncthreads();
 
   auto load_kv = [&](int stage, int kt) {
-    int page = pages[kt];
+    int page = kt - kt_begin < MAX_TILES ? page_s[kt - kt_begin] : pages[kt];
     const bf16* ksrc = base + kv_offset(cache, page, 0, g, 0);
     const bf16* vsrc = base + kv_offset(cache, page, 1, g, 0);
     for (int idx = tid; idx < BN * (HD / 8); idx += THREADS) {

@@ -63,10 +63,67 @@ __global__ void rmsnorm_kernel(T* __restrict__ out, const float* __restrict__ x,
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = from_float<T>(src[i] * inv * weight[i]);
 }
 
+__device__ __forceinline__ void store4(float* dst, float a, float b, float c, float d) {
+  *reinterpret_cast<float4*>(dst) = make_float4(a, b, c, d);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* dst, float a, float b, float c, float d) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+  uint2 packed = make_uint2(*reinterpret_cast<unsigned*>(&lo), *reinterpret_cast<unsigned*>(&hi));
+  *reinterpret_cast<uint2*>(dst) = packed;
+}
+
+// Narrow rows (hidden a multiple of 4, at most 4096 floats): one warp per row, the row kept in registers between
+// the sum and the scaling, 16-byte loads. Lane l holds floats 4*(l + 32*i) ..; the sum is a fixed tree.
+template <typename T>
+__global__ void __launch_bounds__(256) rmsnorm_warp_kernel(T* __restrict__ out, const float* __restrict__ x,
+                                                           const float* __restrict__ weight,
+                                                           const int* __restrict__ rows, int n_rows, int hidden,
+                                                           float eps) {
+  int lane = threadIdx.x & 31;
+  int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= n_rows) return;
+  const float4* src = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * hidden);
+  int vecs = hidden >> 2;
+  float4 v[32];
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    int idx = lane + 32 * i;
+    if (idx < vecs) {
+      v[i] = src[idx];
+      sum = fmaf(v[i].x, v[i].x, sum); sum = fmaf(v[i].y, v[i].y, sum);
+      sum = fmaf(v[i].z, v[i].z, sum); sum = fmaf(v[i].w, v[i].w, sum);
+    }
+  }
+  sum = warp_sum(sum);
+  float inv = 1.0f / sqrtf(sum / (float)hidden + eps);
+  const float4* wv = reinterpret_cast<const float4*>(weight);
+  T* dst = out + (size_t)r * hidden;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    int idx = lane + 32 * i;
+    if (idx < vecs) {
+      float4 w4 = wv[idx];
+      store4(dst + 4 * idx, v[i].x * inv * w4.x, v[i].y * inv * w4.y, v[i].z * inv * w4.z, v[i].w * inv * w4.w);
+    }
+  }
+}
+
 DLLM_EXPORT int dllm_rmsnorm(void* out, const float* x, const float* weight, const int* rows, int n_rows, int hidden,
                              float eps, int out_dtype, cudaStream_t stream) {
   if (n_rows <= 0) return DLLM_OK;
   if (hidden <= 0) return DLLM_BAD_ARGUMENT;
+  if ((hidden & 3) == 0 && hidden <= 4096) {  // whatever the number of rows, so a row has the same bits everywhere
+    int blocks = (n_rows + 7) / 8;
+    if (out_dtype == DLLM_F32)
+      rmsnorm_warp_kernel<float><<<blocks, 256, 0, stream>>>((float*)out, x, weight, rows, n_rows, hidden, eps);
+    else if (out_dtype == DLLM_BF16)
+      rmsnorm_warp_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((__nv_bfloat16*)out, x, weight, rows, n_rows,
+                                                                     hidden, eps);
+    else
+      return DLLM_BAD_ARGUMENT;
+    return dllm_launch_status();
+  }
   int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
   if (out_dtype == DLLM_F32)
     rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>((float*)out, x, weight, rows, hidden, eps);

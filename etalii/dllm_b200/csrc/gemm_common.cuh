@@ -25,6 +25,13 @@ __device__ __forceinline__ float silu_f32(float g) {
   return g * s;
 }
 
+// The same function with the hardware's approximate exponential and reciprocal (relative error about 2^-21, far
+// below bfloat16's 2^-9): used where the result is rounded to bfloat16 anyway. Large negative g gives -0, never NaN.
+__device__ __forceinline__ float silu_fast(float g) { return g * __frcp_rn(1.0f + __expf(-g)); }
+
+template <typename T> __device__ __forceinline__ float silu_for(float g) { return silu_f32(g); }
+template <> __device__ __forceinline__ float silu_for<__nv_bfloat16>(float g) { return silu_fast(g); }
+
 // Stores the pair of adjacent columns (n, n+1) of row m. n is even.
 template <int EPI, typename T>
 __device__ __forceinline__ void epilogue_pair(void* __restrict__ c, int m, int n, int M, int N, float v0, float v1) {
@@ -44,6 +51,56 @@ __device__ __forceinline__ void epilogue_pair(void* __restrict__ c, int m, int n
     if (second) dst[1] += v1;
   } else {
     T* dst = (T*)c + (size_t)m * (N / 2) + (n >> 1);
-    dst[0] = from_float<T>(silu_f32(v0) * v1);
+    dst[0] = from_float<T>(silu_for<T>(v0) * v1);
   }
+}
+
+// Sixteen consecutive columns n .. n+15 of row m held by one thread (n a multiple of 16): vector stores when the
+// row piece is whole and 16-byte aligned, else the pairwise path.
+template <int EPI, typename T>
+__device__ __forceinline__ void epilogue_row16(void* __restrict__ c, int m, int n, int M, int N, const float* v) {
+  if (m >= M || n >= N) return;
+  bool whole = n + 16 <= N;
+  if (EPI == EPI_STORE_F32 || EPI == EPI_RESIDUAL) {
+    float* dst = (float*)c + (size_t)m * N + n;
+    if (whole && (N & 3) == 0) {
+#pragma unroll
+      for (int i = 0; i < 16; i += 4) {
+        float4 o = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+        if (EPI == EPI_RESIDUAL) {
+          float4 r = *reinterpret_cast<float4*>(dst + i);
+          o.x += r.x; o.y += r.y; o.z += r.z; o.w += r.w;
+        }
+        *reinterpret_cast<float4*>(dst + i) = o;
+      }
+      return;
+    }
+  } else if (EPI == EPI_STORE_T) {
+    if (whole && (N & 7) == 0 && sizeof(T) == 2) {
+      uint4 lo, hi;
+      __nv_bfloat162* pl = reinterpret_cast<__nv_bfloat162*>(&lo);
+      __nv_bfloat162* ph = reinterpret_cast<__nv_bfloat162*>(&hi);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        pl[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        ph[i] = __floats2bfloat162_rn(v[8 + 2 * i], v[8 + 2 * i + 1]);
+      }
+      uint4* dst = reinterpret_cast<uint4*>((__nv_bfloat16*)c + (size_t)m * N + n);
+      dst[0] = lo;
+      dst[1] = hi;
+      return;
+    }
+  } else {  // SwiGLU: eight outputs
+    if (whole && (N & 15) == 0 && sizeof(T) == 2) {
+      uint4 o;
+      __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        po[i] = __floats2bfloat162_rn(silu_for<T>(v[4 * i]) * v[4 * i + 1], silu_for<T>(v[4 * i + 2]) * v[4 * i + 3]);
+      *reinterpret_cast<uint4*>((__nv_bfloat16*)c + (size_t)m * (N / 2) + (n >> 1)) = o;
+      return;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 16; i += 2) epilogue_pair<EPI, T>(c, m, n + i, M, N, v[i], v[i + 1]);
 }

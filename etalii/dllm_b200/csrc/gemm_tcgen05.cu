@@ -35,10 +35,10 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity) {
   for (unsigned i = 0;; ++i) {
     unsigned done;
     asm volatile(
-        "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
         : "=r"(done) : "r"(addr), "r"(parity) : "memory");
     if (done) return true;
-    if ((i & 63) == 63 && clock64() - begin > WAIT_LIMIT_CYCLES) return false;
+    if (clock64() - begin > WAIT_LIMIT_CYCLES) return false;  // try_wait itself pauses between looks
   }
 }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
@@ -81,7 +81,7 @@ __device__ __forceinline__ void tmem_load16(unsigned taddr, unsigned* v) {
 }
 
 template <int BN> struct Shape {
-  static constexpr int STAGES = BN >= 128 ? 5 : 6;
+  static constexpr int STAGES = BN >= 128 ? 3 : 4;  // about 96 KB a block: two blocks share an SM
   static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
   static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;  // a power of two, at least 32
   static constexpr size_t SMEM = (size_t)STAGES * (A_BYTES + B_BYTES) + 1024;
@@ -160,11 +160,10 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
       for (int col = 0; col < BN; col += 16) {
         unsigned v[16];
         tmem_load16(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)col, v);
-        if (m < M) {
+        float f[16];
 #pragma unroll
-          for (int i = 0; i < 16; i += 2)
-            epilogue_pair<EPI, bf16>(c, m, n0 + col + i, M, N, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
-        }
+        for (int i = 0; i < 16; ++i) f[i] = __uint_as_float(v[i]);
+        epilogue_row16<EPI, bf16>(c, m, n0 + col, M, N, f);
       }
     }
   }
