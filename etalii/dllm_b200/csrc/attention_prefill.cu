@@ -1,7 +1,8 @@
 // Prefill attention over the paged cache (bfloat16), blockwise with an online softmax, on the tensor cores
-// (mma.sync m16n8k16). A block takes 64 consecutive new tokens of one sequence and one query head; its four warps own
-// 16 queries each. Key/value tiles are whole cache pages (64 positions), copied to shared memory with cp.async,
-// double buffered. Scores, the running maximum and sum and the output accumulate in float32; probabilities are
+// (mma.sync m16n8k16). A block takes 64 consecutive new tokens of one sequence and one query head. Its eight warps
+// form two groups of four; in a group every warp owns 16 queries, and the two groups take alternate key/value tiles
+// (the longest query tile's serial chain of tiles is halved) and are merged at the end. Key/value tiles are whole
+// cache pages (64 positions), copied to shared memory with cp.async, double buffered per group. Scores, the running maximum and sum and the output accumulate in float32; probabilities are
 // rounded to bfloat16 only as the operand of the second product. Causal and window masks are applied per element.
 // Tiles of queries never straddle sequences: the host lists (sequence, first token) per tile.
 //
@@ -11,7 +12,7 @@
 
 namespace {
 typedef __nv_bfloat16 bf16;
-constexpr int BM = 64, BN = 64, WARPS = 4, THREADS = WARPS * 32;
+constexpr int BM = 64, BN = 64, WARPS = 4, GROUPS = 2, THREADS = GROUPS * WARPS * 32;
 constexpr int MAX_TILES = 512;  // page indices kept in shared memory (32,768 positions); beyond: read as needed
 
 __device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid) {
@@ -50,8 +51,9 @@ __global__ void __launch_bounds__(THREADS) prefill_kernel(
   constexpr int LD = HD + 8;  // padded row, keeps 16-byte alignment
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* q_s = reinterpret_cast<bf16*>(smem_raw);            // [BM][LD]
-  bf16* k_s = q_s + BM * LD;                                 // [2][BN][LD]
-  bf16* v_s = k_s + 2 * BN * LD;                             // [2][BN][LD]
+  int group = threadIdx.x / (WARPS * 32);                    // which half of the key tiles this warp works on
+  bf16* k_s = q_s + BM * LD + (size_t)group * 4 * BN * LD;   // per group: [2][BN][LD]
+  bf16* v_s = k_s + 2 * BN * LD;                             // per group: [2][BN][LD]
   int tile = blockIdx.x, h = blockIdx.y;
   int b = tile_seq[tile], q0 = tile_first[tile];
   int hd = cache.head_dim;
@@ -62,11 +64,12 @@ __global__ void __launch_bounds__(THREADS) prefill_kernel(
   int pos0 = start[b] + q0;                // absolute position of the tile's first query
   const int* pages = cache.page_table + (size_t)slots[b] * cache.max_pages;
   const bf16* base = (const bf16*)cache.base;
-  int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  int tid = threadIdx.x % (WARPS * 32), lane = tid & 31, warp = tid >> 5;  // within the group
   int chunks = hd >> 3;                    // 16-byte pieces of a real row
+  auto group_sync = [&]() { asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "r"(WARPS * 32) : "memory"); };
 
   // queries -> shared memory (rows beyond the tile and dims beyond head_dim are zero)
-  for (int idx = tid; idx < BM * (HD / 8); idx += THREADS) {
+  for (int idx = threadIdx.x; idx < BM * (HD / 8); idx += THREADS) {
     int r = idx / (HD / 8), c = idx % (HD / 8);
     bool ok = r < rows && c < chunks;
     const bf16* src = ok ? q + ((size_t)(tok0 + r) * heads + h) * hd + c * 8 : q;
@@ -77,22 +80,25 @@ __global__ void __launch_bounds__(THREADS) prefill_kernel(
   int kt_begin = (window > 0 && pos0 + 1 > window) ? (pos0 + 1 - window) / BN : 0;
   // the pages of the key tiles this block will read, fetched once (not one dependent load per tile)
   __shared__ int page_s[MAX_TILES];
-  for (int i = tid; i <= kt_end - kt_begin && i < MAX_TILES; i += THREADS) page_s[i] = pages[kt_begin + i];
+  for (int i = threadIdx.x; i <= kt_end - kt_begin && i < MAX_TILES; i += THREADS) page_s[i] = pages[kt_begin + i];
   __syncthreads();
 
   auto load_kv = [&](int stage, int kt) {
     int page = kt - kt_begin < MAX_TILES ? page_s[kt - kt_begin] : pages[kt];
     const bf16* ksrc = base + kv_offset(cache, page, 0, g, 0);
     const bf16* vsrc = base + kv_offset(cache, page, 1, g, 0);
-    for (int idx = tid; idx < BN * (HD / 8); idx += THREADS) {
+    for (int idx = tid; idx < BN * (HD / 8); idx += WARPS * 32) {
       int r = idx / (HD / 8), c = idx % (HD / 8);
       bool ok = c < chunks;
       cp_async_16(k_s + (stage * BN + r) * LD + c * 8, ok ? ksrc + (size_t)r * hd + c * 8 : ksrc, ok);
       cp_async_16(v_s + (stage * BN + r) * LD + c * 8, ok ? vsrc + (size_t)r * hd + c * 8 : vsrc, ok);
     }
   };
-  load_kv(0, kt_begin);
+  int kt_first = kt_begin + group;          // this group's tiles: kt_first, kt_first + GROUPS, ...
+  if (kt_first <= kt_end) load_kv(0, kt_first);
   cp_async_commit();
+  cp_async_wait<0>();
+  __syncthreads();  // the queries were copied by all threads of the block: both groups may read them from here on
 
   float o_acc[HD / 8][4];
 #pragma unroll
@@ -104,13 +110,15 @@ __global__ void __launch_bounds__(THREADS) prefill_kernel(
   int gq = lane >> 2, tq = lane & 3;
   int row_pos[2] = {pos0 + warp * 16 + gq, pos0 + warp * 16 + gq + 8};  // positions of this thread's two rows
 
-  for (int kt = kt_begin; kt <= kt_end; ++kt) {
-    int stage = (kt - kt_begin) & 1;
-    if (kt + 1 <= kt_end) load_kv(stage ^ 1, kt + 1);
+  bool have_q = false;
+  for (int kt = kt_first; kt <= kt_end; kt += GROUPS) {
+    int stage = ((kt - kt_first) / GROUPS) & 1;
+    if (kt + GROUPS <= kt_end) load_kv(stage ^ 1, kt + GROUPS);
     cp_async_commit();
     cp_async_wait<1>();
-    __syncthreads();
-    if (kt == kt_begin) {
+    group_sync();
+    if (!have_q) {
+      have_q = true;
 #pragma unroll
       for (int ks = 0; ks < HD / 16; ++ks)
         ldmatrix_x4(q_frag[ks], q_s + (warp * 16 + (lane & 15)) * LD + ks * 16 + (lane >> 4) * 8);
@@ -192,15 +200,47 @@ __global__ void __launch_bounds__(THREADS) prefill_kernel(
         mma_bf16(o_acc[2 * np + 1], p_frag[kk], bfr[2], bfr[3]);
       }
     }
-    __syncthreads();  // the stage is free for the load after next
+    group_sync();  // the stage is free for the load after next
   }
   cp_async_wait<0>();
-  // normalise and store
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
     l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
   }
+  // merge the second group into the first through shared memory (the key/value space is free now)
+  __syncthreads();
+  float* ex_o = reinterpret_cast<float*>(q_s + BM * LD);          // [WARPS*32 threads][HD/8*4] outputs
+  float* ex_ml = ex_o + (size_t)WARPS * 32 * (HD / 2);            // [threads][4]: m0, m1, l0, l1
+  if (group == 1) {
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) ex_o[(size_t)(i * 4 + j) * (WARPS * 32) + tid] = o_acc[i][j];
+    ex_ml[0 * WARPS * 32 + tid] = m_run[0]; ex_ml[1 * WARPS * 32 + tid] = m_run[1];
+    ex_ml[2 * WARPS * 32 + tid] = l_run[0]; ex_ml[3 * WARPS * 32 + tid] = l_run[1];
+  }
+  __syncthreads();
+  if (group == 1) return;
+  {
+    float other_m[2] = {ex_ml[0 * WARPS * 32 + tid], ex_ml[1 * WARPS * 32 + tid]};
+    float other_l[2] = {ex_ml[2 * WARPS * 32 + tid], ex_ml[3 * WARPS * 32 + tid]};
+    float mine[2], theirs[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      float m = fmaxf(m_run[i], other_m[i]);
+      float m_use = m == -INFINITY ? 0.f : m;
+      mine[i] = exp2f(m_run[i] - m_use);
+      theirs[i] = exp2f(other_m[i] - m_use);
+      l_run[i] = l_run[i] * mine[i] + other_l[i] * theirs[i];
+    }
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        o_acc[i][j] = o_acc[i][j] * mine[j >> 1] + ex_o[(size_t)(i * 4 + j) * (WARPS * 32) + tid] * theirs[j >> 1];
+  }
+  // normalise and store
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
     int r = warp * 16 + gq + half * 8;
@@ -220,7 +260,7 @@ template <int HD>
 int launch(void* out, const void* q, const KvLayout& cache, const int* tile_seq, const int* tile_first,
            const int* cu_seqlens, const int* start, const int* slots, int tiles, int heads, float scale, int window,
            cudaStream_t stream) {
-  size_t smem = (size_t)(BM + 4 * BN) * (HD + 8) * sizeof(bf16);
+  size_t smem = (size_t)(BM + GROUPS * 4 * BN) * (HD + 8) * sizeof(bf16);
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
