@@ -29,6 +29,7 @@ SOURCES = {
     "attention": "attention.cu",
     "attention_decode": "attention_decode.cu",
     "attention_prefill": "attention_prefill.cu",
+    "attention_decode_static": "attention_decode_static.cu",
     "sampling": "sampling.cu",
 }
 """Library name -> source file. A library added here is built by `build_all` and loadable by `library`."""
@@ -71,7 +72,13 @@ def _digest(source: str) -> str:
     sha = hashlib.sha256()
     sha.update(" ".join(ARCH_FLAGS + NVCC_FLAGS).encode())
     headers = sorted(f for f in os.listdir(CSRC) if f.endswith((".cuh", ".h")))
-    for name in [source, *headers]:
+    included = []  # other sources this one includes as text
+    with open(os.path.join(CSRC, source), encoding="utf-8") as handle:
+        for line in handle:
+            line = line.strip()
+            if line.startswith("#include \"") and line.endswith(".cu\""):
+                included.append(line.split("\"")[1])
+    for name in [source, *included, *headers]:
         with open(os.path.join(CSRC, name), "rb") as handle:
             sha.update(name.encode())
             sha.update(handle.read())
