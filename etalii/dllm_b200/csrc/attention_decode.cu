@@ -255,10 +255,11 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attention_mma_kernel(
   int key0 = c * MMA_CHUNK + warp * TILE_KEYS;     // this warp's page of keys
   bool warp_on = key0 < hi && key0 + TILE_KEYS > lo;
   int page = warp_on ? pages[key0 / TILE_KEYS] : 0;
-  pdl_wait();  // the queries and this step's keys and values come from the projection kernel before this one
   bf16* k_s = kv_s + (size_t)warp * 2 * TILE_KEYS * LD;
   bf16* v_s = k_s + TILE_KEYS * LD;
   int chunks16 = hd >> 3;
+  // Keys and values of earlier steps do not change any more: copy the page before waiting for the kernel that
+  // writes this step's row, then (below) read that one row again.
   if (warp_on) {
     const bf16* ksrc = (const bf16*)cache.base + kv_offset(cache, page, 0, g, 0);
     const bf16* vsrc = (const bf16*)cache.base + kv_offset(cache, page, 1, g, 0);
@@ -273,6 +274,20 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attention_mma_kernel(
       }
     }
     asm volatile("cp.async.commit_group;\n" ::);
+  }
+  pdl_wait();  // the queries and this step's key and value come from the projection kernel before this one
+  int newest = end - 1;
+  if (warp_on && newest >= key0 && newest < key0 + TILE_KEYS) {
+    asm volatile("cp.async.wait_group 0;\n" ::);
+    __syncwarp();
+    int r = newest - key0;
+    const bf16* ksrc = (const bf16*)cache.base + kv_offset(cache, page, 0, g, r);
+    const bf16* vsrc = (const bf16*)cache.base + kv_offset(cache, page, 1, g, r);
+    for (int cc = lane; cc < chunks16; cc += 32) {
+      *reinterpret_cast<uint4*>(k_s + r * LD + cc * 8) = __ldcg(reinterpret_cast<const uint4*>(ksrc + cc * 8));
+      *reinterpret_cast<uint4*>(v_s + r * LD + cc * 8) = __ldcg(reinterpret_cast<const uint4*>(vsrc + cc * 8));
+    }
+    __syncwarp();
   }
   float* red_o = reinterpret_cast<float*>(smem_raw);  // after the products: [WARPS][16][HD] partial outputs
 

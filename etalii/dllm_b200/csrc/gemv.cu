@@ -1,4 +1,4 @@
-// Weight-streaming products for decode (at most 16 rows of activations, bfloat16 weights): C = X * W^T where reading
+// Weight-streaming products for decode (at most 64 rows of activations, bfloat16 weights): C = X * W^T where reading
 // W once is the whole cost. A block owns 16 output columns (16 rows of W) and splits the reduction over its warps.
 // The products run on the tensor cores with W as the 16-row operand (mma.sync m16n8k16, "swap A and B"): a thread
 // loads 16 bytes of two rows of W and 16 bytes of one row of X per 32 values of k, all loads of a warp are issued
@@ -17,7 +17,6 @@
 namespace {
 typedef __nv_bfloat16 bf16;
 constexpr int TILE = 16;       // rows of W per block
-constexpr int MAX_STEPS = 8;   // 32-value k steps a warp keeps in flight at once
 
 struct RopeArgs {
   bf16* q_out;           // [tokens, heads * head_dim]
@@ -79,11 +78,42 @@ __device__ __forceinline__ int tile_row(int item, int r, int N, const RopeArgs& 
   return min(item * TILE + r, N - 1);
 }
 
+// What a thread's first epilogue item needs from memory besides the product: fetched right after the wait on the
+// previous kernel, so that the latency runs under the products instead of after them.
+template <int EPI, int NT>
+struct Early {
+  float r0 = 0.f, r1 = 0.f;   // residual values (EPI_RESIDUAL)
+  int have = 0;
+  int pos = 0, page = 0;      // position and cache page of the token (EPI_QKV_ROPE)
+  float2 cs = make_float2(1.f, 0.f);
+  __device__ __forceinline__ void load(const void* c, int tid, int M, int N, int item, const RopeArgs& rope,
+                                       bool paired, int dim0) {
+    int p = tid / (NT * 8), m = tid % (NT * 8);
+    if (p >= 8 || m >= M) return;
+    if (EPI == EPI_RESIDUAL) {
+      int n = item * TILE + 2 * p;
+      if (n < N) {
+        const float* src = (const float*)c + (size_t)m * N + n;
+        r0 = src[0];
+        have = 1;
+        if (n + 1 < N) { r1 = src[1]; have = 2; }
+      }
+    } else if (EPI == EPI_QKV_ROPE) {
+      pos = rope.tok_pos[m];
+      if (paired) cs = rope.table[(size_t)pos * (rope.rotary_dim / 2) + dim0 + p];
+      int slot = rope.slots[rope.tok_seq[m]];
+      page = rope.cache.page_table[(size_t)slot * rope.cache.max_pages + pos / rope.cache.page_size];
+    }
+  }
+};
+
 template <int WARPS, int NT, int EPI, bool NORM>
 __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(void* __restrict__ c, const void* __restrict__ a,
                                                           const float* __restrict__ norm_w, float eps,
                                                           const bf16* __restrict__ w, int M, int N, int K,
                                                           RopeArgs rope, Prefetch pf) {
+  // 32-value k steps whose loads a warp issues before the first product (fewer when more tokens need registers)
+  constexpr int MAX_STEPS = NT == 1 ? 8 : (NT == 2 ? 4 : 2);
   __shared__ float red[WARPS][TILE][NT * 8 + 1];
   __shared__ float red_ss[WARPS][NT * 8];
   int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -108,6 +138,7 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(void* __restrict__ c, 
     for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
   }
   const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+  Early<EPI, NT> early;
   pdl_launch_dependents();
   for (int s0 = s_begin; s0 < s_end; s0 += MAX_STEPS) {
     uint4 wl[MAX_STEPS], wh[MAX_STEPS], xb[MAX_STEPS][NT];
@@ -119,8 +150,11 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(void* __restrict__ c, 
       wl[i] = ok ? __ldg(w_lo + ch) : zero;
       wh[i] = ok ? __ldg(w_hi + ch) : zero;
     }
-    if (s0 == s_begin) prefetch_share(pf);
-    pdl_wait();  // the weights above are nobody's output; the activations below are the previous kernel's
+    if (s0 == s_begin) {
+      prefetch_share(pf);
+      pdl_wait();  // the weights above are nobody's output; everything below may be the previous kernel's
+      early.load(c, tid, M, N, blockIdx.x, rope, paired, dim0);
+    }
 #pragma unroll
     for (int i = 0; i < MAX_STEPS; ++i) {
       int ch = (s0 + i) * 4 + t;
@@ -156,7 +190,10 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(void* __restrict__ c, 
       }
     }
   }
-  pdl_wait();  // (a warp without work has not waited yet)
+  if (s_begin >= s_end) {  // a warp without work has not waited yet
+    pdl_wait();
+    early.load(c, tid, M, N, blockIdx.x, rope, paired, dim0);
+  }
   // partial tiles and partial sums of squares to shared memory
 #pragma unroll
   for (int n = 0; n < NT; ++n) {
@@ -190,15 +227,16 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(void* __restrict__ c, 
       v0 *= inv;
       v1 *= inv;
     }
+    bool first_item = idx == tid;  // what `early` fetched belongs to each thread's first item
     if (EPI == EPI_QKV_ROPE) {
       int hd = rope.cache.head_dim, nkv = rope.cache.kv_heads, heads = rope.heads;
-      int pos = rope.tok_pos[m];
+      int pos = first_item ? early.pos : rope.tok_pos[m];
       int d0, d1;
       if (paired) {
         int half = rope.rotary_dim / 2;
         d0 = dim0 + p;
         d1 = d0 + half;
-        float2 cs = rope.table[(size_t)pos * half + d0];
+        float2 cs = first_item ? early.cs : rope.table[(size_t)pos * half + d0];
         float x = v0, y = v1;
         v0 = fmaf(x, cs.x, -(y * cs.y));
         v1 = fmaf(x, cs.y, y * cs.x);
@@ -213,12 +251,17 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(void* __restrict__ c, 
         if (!rope.write_cache) continue;
         int which = head < heads + nkv ? 0 : 1;
         int kvh = head - heads - which * nkv;
-        int slot = rope.slots[rope.tok_seq[m]];
-        int page = rope.cache.page_table[(size_t)slot * rope.cache.max_pages + pos / rope.cache.page_size];
+        int page = first_item ? early.page
+                              : rope.cache.page_table[(size_t)rope.slots[rope.tok_seq[m]] * rope.cache.max_pages +
+                                                      pos / rope.cache.page_size];
         dst = (bf16*)rope.cache.base + kv_offset(rope.cache, page, which, kvh, pos % rope.cache.page_size);
       }
       dst[d0] = __float2bfloat16_rn(v0);
       dst[d1] = __float2bfloat16_rn(v1);
+    } else if (EPI == EPI_RESIDUAL && first_item && early.have) {
+      float* dst = (float*)c + (size_t)m * N + blockIdx.x * TILE + 2 * p;
+      dst[0] = early.r0 + v0;
+      if (early.have > 1) dst[1] = early.r1 + v1;
     } else {
       epilogue_pair<EPI, bf16>(c, m, blockIdx.x * TILE + 2 * p, M, N, v0, v1);
     }
@@ -235,8 +278,12 @@ int launch(void* c, const void* a, const float* norm_w, float eps, const bf16* w
                          eps, w, M, N, K, rope, pf)
   if (M <= 8) {
     if (wide) DLLM_GO(8, 1); else DLLM_GO(4, 1);
-  } else {
+  } else if (M <= 16) {
     if (wide) DLLM_GO(8, 2); else DLLM_GO(4, 2);
+  } else if (M <= 32) {
+    if (wide) DLLM_GO(8, 4); else DLLM_GO(4, 4);
+  } else {
+    if (wide) DLLM_GO(8, 8); else DLLM_GO(4, 8);
   }
 #undef DLLM_GO
 }
@@ -255,14 +302,14 @@ int dispatch(void* c, const void* a, const float* norm_w, float eps, const bf16*
 }
 }  // namespace
 
-// C = X[M,K] * W[N,K]^T for M <= 16. With norm_w != null, X is the float32 residual stream and is RMS-normed on
+// C = X[M,K] * W[N,K]^T for M <= 64. With norm_w != null, X is the float32 residual stream and is RMS-normed on
 // the way in; else X is bfloat16. Epilogues 0..3 as the tile kernels; K a multiple of 8, N even.
 // prefetch_ptr / prefetch_bytes: optional memory (weights a later kernel reads) to bring into L2 meanwhile.
 DLLM_EXPORT int dllm_gemv_bf16(void* c, const void* a, const float* norm_w, float eps, const void* w, int M, int N,
                                int K, int epilogue, const void* prefetch_ptr, long long prefetch_bytes,
                                cudaStream_t stream) {
   if (M <= 0 || N <= 0) return DLLM_OK;
-  if (M > 16 || K <= 0 || (K & 7) || (N & 1) || epilogue < 0 || epilogue > EPI_SWIGLU) return DLLM_UNSUPPORTED_SIZE;
+  if (M > 64 || K <= 0 || (K & 7) || (N & 1) || epilogue < 0 || epilogue > EPI_SWIGLU) return DLLM_UNSUPPORTED_SIZE;
   RopeArgs rope{};
   Prefetch pf{(const char*)prefetch_ptr, prefetch_ptr ? (size_t)prefetch_bytes : 0};
   return norm_w ? dispatch<true>(c, a, norm_w, eps, (const bf16*)w, M, N, K, epilogue, rope, pf, stream)
@@ -278,7 +325,7 @@ DLLM_EXPORT int dllm_gemv_qkv_rope(const void* a, const float* norm_w, float eps
                                    const int* tok_seq, const int* tok_pos, const int* slots, int write_cache,
                                    const void* prefetch_ptr, long long prefetch_bytes, cudaStream_t stream) {
   if (M <= 0) return DLLM_OK;
-  if (M > 16 || K <= 0 || (K & 7) || heads <= 0 || kv_heads <= 0 || head_dim <= 0 || (head_dim & 15) ||
+  if (M > 64 || K <= 0 || (K & 7) || heads <= 0 || kv_heads <= 0 || head_dim <= 0 || (head_dim & 15) ||
       rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 15))
     return DLLM_UNSUPPORTED_SIZE;
   RopeArgs rope{(bf16*)q_out, KvLayout{cache_base, page_table, max_pages, page_size, kv_heads, head_dim},

@@ -115,6 +115,13 @@ def compile_library(name: str, verbose: bool = True) -> str:
             os.remove(temporary)
         raise KernelBuildError(f"nvcc failed on {SOURCES[name]}:\n{output}")
     os.replace(temporary, path)
+    prefix = f"libdllm_b200_{name}-"
+    for stale in os.listdir(os.path.dirname(path)):  # older builds of the same source
+        if stale.startswith(prefix) and stale.endswith(".so") and stale != os.path.basename(path):
+            try:
+                os.remove(os.path.join(os.path.dirname(path), stale))
+            except OSError:
+                pass
     if verbose:
         print(f"[dllm_b200] built {os.path.basename(path)} in {time.time() - start:.1f} s", file=sys.stderr, flush=True)
     return path

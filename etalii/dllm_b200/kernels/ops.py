@@ -147,7 +147,8 @@ def raise_if_failed() -> None:
 
 
 GEMV_MAX_ROWS = 16
-"""Products with at most this many activation rows run in the weight-streaming kernel."""
+"""Products with at most this many activation rows run in the weight-streaming kernel (the kernel itself takes up to
+64 rows, but beyond 16 every block re-reads more activations than weights and the tile kernel is faster)."""
 
 
 def gemm(c: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int = EPI_STORE_T, kernel: int = 0,
@@ -155,7 +156,7 @@ def gemm(c: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int = EPI_
     """c = a[M,K] @ w[N,K]^T with float32 accumulation, then the epilogue: EPI_STORE_F32 (c float32), EPI_STORE_T
     (c in the weights' dtype), EPI_RESIDUAL (c float32 += product), EPI_SWIGLU (w interleaves gate and up rows;
     c[M,N/2] = silu(gate) * up). float32 weights run the true 32-bit kernel; bfloat16 the tcgen05/TMA tile kernel
-    or, for M <= 16, the weight-streaming kernel (`kernel`: 0 chooses by M, 1 forces the mma.sync tile kernel, 2
+    or, for M <= 64, the weight-streaming kernel (`kernel`: 0 chooses by M, 1 forces the mma.sync tile kernel, 2
     forces streaming, 3 forces tcgen05; `tile_n` picks the tcgen05 tile width).
     With `norm_weight` (streaming kernel only), `a` is the float32 residual stream and is RMS-normed on the way in."""
     _cuda(c, a, w, norm_weight)
@@ -171,7 +172,7 @@ def gemm(c: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int = EPI_
         status = _fn("gemm_simt", "dllm_gemm_f32")(c.data_ptr(), a.data_ptr(), w.data_ptr(), m, n, k, epilogue,
                                                    _stream())
     elif w.dtype == torch.bfloat16:
-        streaming = kernel == 2 or (kernel == 0 and m <= GEMV_MAX_ROWS)
+        streaming = (kernel == 2 and m <= 64) or (kernel == 0 and m <= GEMV_MAX_ROWS)
         if streaming:
             if norm_weight is not None:
                 assert a.dtype == torch.float32 and norm_weight.dtype == torch.float32 and norm_weight.numel() == k
@@ -214,7 +215,7 @@ def gemv_qkv_rope(a: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, cache, 
         cache.kv_heads, cache.head_dim, table.data_ptr() if table is not None else None,
         rotary_dim if table is not None else 0, batch.tok_seq.data_ptr(), batch.tok_pos.data_ptr(),
         batch.slots.data_ptr(), 1 if write_cache else 0, *_prefetch_of(w), _stream()),
-        "gemv_qkv_rope", f"M={m} (at most 16), K={k} (multiple of 8), head_dim and rotary_dim multiples of 16")
+        "gemv_qkv_rope", f"M={m} (at most 64), K={k} (multiple of 8), head_dim and rotary_dim multiples of 16")
 
 
 def rope_cache_write(qkv: torch.Tensor, q_out: torch.Tensor, cache, table: torch.Tensor | None, rotary_dim: int,

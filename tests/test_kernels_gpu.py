@@ -52,7 +52,7 @@ def test_rmsnorm(dtype, tol, hidden, eps):
     assert torch.equal(out3, out[rows.long()])  # a gathered row has the same bits as the row in place
 
 
-GEMM_SHAPES = [(1, 64, 64), (3, 130, 72), (16, 96, 144), (17, 200, 136), (77, 384, 160), (130, 66, 1544), (300, 258, 576)]
+GEMM_SHAPES = [(1, 64, 64), (3, 130, 72), (16, 96, 144), (17, 200, 136), (40, 576, 1536), (64, 130, 72), (77, 384, 160), (130, 66, 1544), (300, 258, 576)]
 
 
 @pytest.mark.parametrize("m,n,k", GEMM_SHAPES)
@@ -81,8 +81,8 @@ def test_gemm_f32_rows_do_not_depend_on_the_batch():
 @pytest.mark.parametrize("epilogue", [0, 1, 2, 3])
 @pytest.mark.parametrize("kernel", [1, 2])
 def test_gemm_bf16(m, n, k, epilogue, kernel):
-    if kernel == 2 and m > 16:
-        pytest.skip("the weight-streaming kernel takes at most 16 rows")
+    if kernel == 2 and m > 64:
+        pytest.skip("the weight-streaming kernel takes at most 64 rows")
     a, w = _randn((m, k), torch.bfloat16, 3), _randn((n, k), torch.bfloat16, 4, 0.2)
     cols = n // 2 if epilogue == 3 else n
     c = _randn((m, cols), torch.float32 if epilogue in (0, 2) else torch.bfloat16, 5)
@@ -300,7 +300,8 @@ def test_attention_decode_finds_a_far_key():
         view.storage[page] = saved
 
 
-@pytest.mark.parametrize("m,n,k", [(1, 64, 64), (3, 130, 72), (8, 576, 1536), (16, 96, 144), (5, 3072, 576)])
+@pytest.mark.parametrize("m,n,k", [(1, 64, 64), (3, 130, 72), (8, 576, 1536), (16, 96, 144), (5, 3072, 576),
+                                   (17, 200, 136), (33, 576, 576), (64, 960, 576), (50, 66, 1544)])
 @pytest.mark.parametrize("epilogue", [0, 1, 2, 3])
 def test_gemv_with_the_norm_in_front(m, n, k, epilogue):
     x = _randn((m, k), torch.float32, 3, 2.0)
@@ -309,7 +310,7 @@ def test_gemv_with_the_norm_in_front(m, n, k, epilogue):
     cols = n // 2 if epilogue == 3 else n
     c = _randn((m, cols), torch.float32 if epilogue in (0, 2) else torch.bfloat16, 5)
     ref = c.clone()
-    ops().gemm(c, x, w, epilogue, norm_weight=nw, eps=1e-5)
+    ops().gemm(c, x, w, epilogue, kernel=2, norm_weight=nw, eps=1e-5)  # the streaming kernel, also above 16 rows
     normed = torch.empty((m, k), dtype=torch.float64, device=DEV)
     PK.rmsnorm(normed, x, nw, 1e-5)
     PK.gemm(ref, normed, w, epilogue)
@@ -320,8 +321,9 @@ def test_gemv_with_the_norm_in_front(m, n, k, epilogue):
 @pytest.mark.parametrize("heads,kv_heads,head_dim,rotary", [(4, 2, 16, 16), (6, 3, 48, 32), (2, 1, 64, 32),
                                                            (9, 3, 64, 64), (3, 1, 128, 0)])
 @pytest.mark.parametrize("normed", [False, True])
-def test_gemv_qkv_rope(heads, kv_heads, head_dim, rotary, normed):
-    lengths, new, k = [70, 5, 129, 64], [1, 1, 3, 2], 136
+@pytest.mark.parametrize("rows_extra", [1, 40])
+def test_gemv_qkv_rope(heads, kv_heads, head_dim, rotary, normed, rows_extra):
+    lengths, new, k = [70, 5, 129, 64, 200, 33], [1, 1, 3, 2, rows_extra, 1], 136
     cache, view, batch = _cache_and_batch(torch.bfloat16, kv_heads, head_dim, lengths, new)
     n = batch.n_tokens
     table = None
