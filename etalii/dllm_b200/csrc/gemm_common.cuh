@@ -11,6 +11,19 @@
 #define EPI_STORE_T 1
 #define EPI_RESIDUAL 2
 #define EPI_SWIGLU 3
+#define EPI_QKV_ROPE 4  // q/k/v projection: rotate q and k, q to its buffer, k and v into the paged cache
+
+// What the q/k/v epilogue needs: where queries go, where the cache is, the rotation table, who the tokens are.
+struct RopeArgs {
+  __nv_bfloat16* q_out;  // [tokens, heads * head_dim]
+  KvLayout cache;
+  const float2* table;   // [positions, rotary_dim / 2] (cos, sin) or null
+  int rotary_dim, heads;
+  const int* tok_seq;
+  const int* tok_pos;
+  const int* slots;
+  int write_cache;
+};
 
 // silu(g) = g * sigmoid(g), sigmoid as 1/(1+e^-g) for g >= 0 and e^g/(1+e^g) below, in float32; the product with
 // `up` is a separate float32 multiply of the rounded activation.

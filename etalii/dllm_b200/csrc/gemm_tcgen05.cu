@@ -91,7 +91,7 @@ template <int BN, int EPI>
 __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                const __grid_constant__ CUtensorMap map_w,
                                                                void* __restrict__ c, int M, int N, int K,
-                                                               int* __restrict__ status) {
+                                                               int* __restrict__ status, RopeArgs rope) {
   typedef Shape<BN> S;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);  // swizzle atoms: 1 KB
@@ -155,7 +155,50 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
     bool ready = mbar_wait(&acc_bar, 0);
     if (!ready && lane == 0) *(volatile int*)status = 4;
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (ready) {
+    if (ready && EPI == EPI_QKV_ROPE) {
+      // the tile is one head (BN == head_dim): the thread holds its token's whole head, rotates the pairs
+      // (i, i + rotary_dim / 2) and writes the query, or the key / value into the token's cache row
+      float f[BN];
+#pragma unroll
+      for (int col = 0; col < BN; col += 16) {
+        unsigned v[16];
+        tmem_load16(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)col, v);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) f[col + i] = __uint_as_float(v[i]);
+      }
+      int head = blockIdx.x, heads = rope.heads, nkv = rope.cache.kv_heads;
+      if (m < M && (head < heads || rope.write_cache)) {
+        int pos = rope.tok_pos[m];
+        if (rope.table != nullptr && head < heads + nkv) {
+          const float2* cs = rope.table + (size_t)pos * (rope.rotary_dim / 2);
+#pragma unroll
+          for (int i = 0; i < BN / 2; ++i) {  // rotary_dim == head_dim here: the partner sits half a head away
+            float2 t = cs[i];
+            float x = f[i], y = f[i + BN / 2];
+            f[i] = fmaf(x, t.x, -(y * t.y));
+            f[i + BN / 2] = fmaf(x, t.y, y * t.x);
+          }
+        }
+        bf16* dst;
+        if (head < heads) {
+          dst = rope.q_out + ((size_t)m * heads + head) * BN;
+        } else {
+          int which = head < heads + nkv ? 0 : 1;
+          int kvh = head - heads - which * nkv;
+          int slot = rope.slots[rope.tok_seq[m]];
+          int page = rope.cache.page_table[(size_t)slot * rope.cache.max_pages + pos / rope.cache.page_size];
+          dst = (bf16*)rope.cache.base + kv_offset(rope.cache, page, which, kvh, pos % rope.cache.page_size);
+        }
+#pragma unroll
+        for (int i = 0; i < BN; i += 8) {
+          uint4 o;
+          __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) po[j] = __floats2bfloat162_rn(f[i + 2 * j], f[i + 2 * j + 1]);
+          *reinterpret_cast<uint4*>(dst + i) = o;
+        }
+      }
+    } else if (ready) {
 #pragma unroll
       for (int col = 0; col < BN; col += 16) {
         unsigned v[16];
@@ -206,7 +249,8 @@ bool make_map(CUtensorMap* map, const void* base, int rows, int cols, int box_ro
 }
 
 template <int BN, int EPI>
-int launch(void* c, const void* a, const void* w, int M, int N, int K, int* status, cudaStream_t stream) {
+int launch(void* c, const void* a, const void* w, int M, int N, int K, int* status, cudaStream_t stream,
+           const RopeArgs& rope = RopeArgs{}) {
   alignas(64) CUtensorMap map_a, map_w;
   if (!make_map(&map_a, a, M, K, BM) || !make_map(&map_w, w, N, K, BN)) return DLLM_LAUNCH_FAILED;
   static bool configured = false;
@@ -217,7 +261,7 @@ int launch(void* c, const void* a, const void* w, int M, int N, int K, int* stat
     configured = true;
   }
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-  gemm_tcgen05_kernel<BN, EPI><<<grid, THREADS, Shape<BN>::SMEM, stream>>>(map_a, map_w, c, M, N, K, status);
+  gemm_tcgen05_kernel<BN, EPI><<<grid, THREADS, Shape<BN>::SMEM, stream>>>(map_a, map_w, c, M, N, K, status, rope);
   return dllm_launch_status();
 }
 
@@ -250,5 +294,30 @@ DLLM_EXPORT int dllm_gemm_tcgen05(void* c, const void* a, const void* w, int M, 
     case 64: return dispatch<64>(c, a, w, M, N, K, epilogue, status, stream);
     case 128: return dispatch<128>(c, a, w, M, N, K, epilogue, status, stream);
     default: return DLLM_BAD_ARGUMENT;
+  }
+}
+
+// The q/k/v projection of a prefill-sized step in one kernel: W is [(heads + 2 kv_heads) * head_dim, K], every tile
+// of the product is one head (head_dim 32, 64 or 128; rotary_dim equal to head_dim, or no table), its epilogue
+// rotates q and k by the table's angle for each token's position and writes q to q_out and k, v into the paged cache.
+DLLM_EXPORT int dllm_gemm_tcgen05_qkv_rope(const void* a, const void* w, int M, int K, void* q_out, void* cache_base,
+                                           const int* page_table, int max_pages, int page_size, int heads,
+                                           int kv_heads, int head_dim, const float* table, int rotary_dim,
+                                           const int* tok_seq, const int* tok_pos, const int* slots, int write_cache,
+                                           int* status, cudaStream_t stream) {
+  if (M <= 0) return DLLM_OK;
+  if (K <= 0 || (K & 7) || ((uintptr_t)a & 15) || ((uintptr_t)w & 15) || status == nullptr || heads <= 0 ||
+      kv_heads <= 0)
+    return DLLM_UNSUPPORTED_SIZE;
+  if ((head_dim != 32 && head_dim != 64 && head_dim != 128) || (table != nullptr && rotary_dim != head_dim))
+    return DLLM_UNSUPPORTED_SIZE;
+  if ((M + BM - 1) / BM > 65535) return DLLM_UNSUPPORTED_SIZE;
+  RopeArgs rope{(bf16*)q_out, KvLayout{cache_base, page_table, max_pages, page_size, kv_heads, head_dim},
+                (const float2*)table, table ? rotary_dim : 0, heads, tok_seq, tok_pos, slots, write_cache};
+  int N = (heads + 2 * kv_heads) * head_dim;
+  switch (head_dim) {
+    case 32: return launch<32, EPI_QKV_ROPE>(nullptr, a, w, M, N, K, status, stream, rope);
+    case 64: return launch<64, EPI_QKV_ROPE>(nullptr, a, w, M, N, K, status, stream, rope);
+    default: return launch<128, EPI_QKV_ROPE>(nullptr, a, w, M, N, K, status, stream, rope);
   }
 }

@@ -12,22 +12,10 @@
 //     position encoding of q/k and the write of k and v into the paged cache (q/k/v projection).
 #include "gemm_common.cuh"
 
-#define EPI_QKV_ROPE 4
-
 namespace {
 typedef __nv_bfloat16 bf16;
 constexpr int TILE = 16;       // rows of W per block
 
-struct RopeArgs {
-  bf16* q_out;           // [tokens, heads * head_dim]
-  KvLayout cache;
-  const float2* table;   // [positions, rotary_dim / 2] (cos, sin) or null
-  int rotary_dim, heads;
-  const int* tok_seq;
-  const int* tok_pos;
-  const int* slots;
-  int write_cache;
-};
 
 // Weights that a later kernel of the step will stream: every block asks the L2 cache for its share of them while
 // its own loads are in flight, so that the later kernel reads from L2 instead of waiting on DRAM.

@@ -32,6 +32,9 @@ _prototypes = {
     ("gemm_bf16", "dllm_gemm_bf16"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     ("gemm_tcgen05", "dllm_gemm_tcgen05"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                             c_void_p],
+    ("gemm_tcgen05", "dllm_gemm_tcgen05_qkv_rope"): [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                                     c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p,
+                                                     c_void_p, c_void_p, c_int, c_void_p, c_void_p],
     ("gemv", "dllm_gemv_bf16"): [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int,
                                  c_void_p, c_longlong, c_void_p],
     ("gemv", "dllm_gemv_qkv_rope"): [c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_void_p, c_void_p,
@@ -194,6 +197,32 @@ def gemm(c: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int = EPI_
     else:
         raise KernelError(f"gemm: dtype {w.dtype} is not supported")
     _check(status, "gemm", detail)
+
+
+def gemm_qkv_rope_supported(cache, rotary_dim: int, has_table: bool) -> bool:
+    """Whether the tile kernel can end in the rotation and cache write: one head per tile, full rotation."""
+    return cache.dtype == torch.bfloat16 and cache.head_dim in (32, 64, 128) and \
+        (not has_table or rotary_dim == cache.head_dim)
+
+
+def gemm_qkv_rope(a: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, cache, table: torch.Tensor | None,
+                  rotary_dim: int, heads: int, batch, write_cache: bool = True) -> None:
+    """The q/k/v projection of a prefill-sized step in the tcgen05 tile kernel, ending in the rotation of q and k and
+    the write of k and v into the paged cache (no float32 q/k/v in memory, no separate rotation kernel)."""
+    _cuda(a, w, q_out, table)
+    m, k = batch.n_tokens, a.shape[1]
+    assert gemm_qkv_rope_supported(cache, rotary_dim, table is not None)
+    assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and q_out.dtype == torch.bfloat16
+    assert w.shape == ((heads + 2 * cache.kv_heads) * cache.head_dim, k) and a.shape[0] >= m
+    if table is not None:
+        assert table.dtype == torch.float32 and table.shape[0] > batch.max_position, "position beyond the table"
+        assert table.shape[1] == rotary_dim // 2 and table.shape[2] == 2
+    _check(_fn("gemm_tcgen05", "dllm_gemm_tcgen05_qkv_rope")(
+        a.data_ptr(), w.data_ptr(), m, k, q_out.data_ptr(), cache.base_ptr, cache.page_table.data_ptr(),
+        cache.max_pages, cache.page_size, heads, cache.kv_heads, cache.head_dim,
+        table.data_ptr() if table is not None else None, rotary_dim if table is not None else 0,
+        batch.tok_seq.data_ptr(), batch.tok_pos.data_ptr(), batch.slots.data_ptr(), 1 if write_cache else 0,
+        _status_word().data_ptr(), _stream()), "gemm_qkv_rope", f"M={m} K={k} head_dim={cache.head_dim}")
 
 
 def gemv_qkv_rope(a: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, cache, table: torch.Tensor | None,

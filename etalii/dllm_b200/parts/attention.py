@@ -66,6 +66,10 @@ class Attention:
             pending = isinstance(h, NormedInput)
             ops.gemv_qkv_rope(h.x if pending else h, self.w_qkv, q, cache, table, rotary_dim, self.num_heads, batch,
                               write_cache, norm_weight=h.weight if pending else None, eps=h.eps if pending else 0.0)
+        elif rt.dtype == torch.bfloat16 and ops.gemm_qkv_rope_supported(cache, rotary_dim, table is not None):
+            # prefill-sized: the tile product ends in rotation and cache write
+            hidden = h.tensor() if isinstance(h, NormedInput) else h
+            ops.gemm_qkv_rope(hidden, self.w_qkv, q, cache, table, rotary_dim, self.num_heads, batch, write_cache)
         else:
             qkv = rt.ws.buffer("qkv", (n, q_size + 2 * self.num_kv_heads * self.head_dim), torch.float32)
             project(qkv, h, self.w_qkv, ops.EPI_STORE_F32)

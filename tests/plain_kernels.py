@@ -158,3 +158,11 @@ def attention_prefill(out, q, cache, heads, scale, window, batch):
 
 def attention_prefill_supported(cache):
     return False
+
+
+def gemm_qkv_rope(a, w, q_out, cache, table, rotary_dim, heads, batch, write_cache=True):
+    gemv_qkv_rope(a, w, q_out, cache, table, rotary_dim, heads, batch, write_cache)
+
+
+def gemm_qkv_rope_supported(cache, rotary_dim, has_table):
+    return False

@@ -418,3 +418,34 @@ def test_gemm_tcgen05(m, n, k, epilogue, tile_n):
     ops().raise_if_failed()
     PK.gemm(ref, a, w, epilogue)
     assert rel_error(c.float().cpu(), ref.float().cpu()) <= (2e-5 if epilogue in (0, 2) else 8e-3)
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,rotary", [(9, 3, 64, 64), (4, 2, 32, 32), (5, 1, 128, 128),
+                                                           (3, 3, 64, 0)])
+def test_gemm_qkv_rope(heads, kv_heads, head_dim, rotary):
+    lengths, new, k = [300, 70, 5, 129], [300, 70, 1, 9], 136
+    cache, view, batch = _cache_and_batch(torch.bfloat16, kv_heads, head_dim, lengths, new)
+    n = batch.n_tokens
+    table = None
+    if rotary:
+        angles = torch.arange(400, dtype=torch.float64)[:, None] * torch.rand(rotary // 2, dtype=torch.float64)[None]
+        table = torch.stack([angles.cos(), angles.sin()], -1).float().to(DEV)
+    w = _randn(((heads + 2 * kv_heads) * head_dim, k), torch.bfloat16, 4, 0.2)
+    x = _randn((n, k), torch.bfloat16, 6)
+    q = torch.zeros((n, heads * head_dim), dtype=torch.bfloat16, device=DEV)
+    before = view.storage.clone()
+    ops().gemm_qkv_rope(x, w, q, view, table, rotary, heads, batch, True)
+    torch.cuda.synchronize()
+    ops().raise_if_failed()
+    qkv = (x.double() @ w.double().T).float().cpu()
+    ref_view = type(view)(before.cpu().clone(), view.page_table.cpu(), view.page_size, kv_heads, head_dim, None)
+    ref_q = torch.zeros((n, heads * head_dim), dtype=torch.bfloat16)
+    cpu_batch = type("B", (), {"n_tokens": n, "tok_pos": batch.tok_pos.cpu(), "tok_seq": batch.tok_seq.cpu(),
+                               "slots": batch.slots.cpu()})
+    PK.rope_cache_write(qkv, ref_q, ref_view, table.cpu() if rotary else None, rotary, heads, cpu_batch, True)
+    assert rel_error(q.float().cpu(), ref_q.float()) <= 8e-3
+    assert rel_error(view.storage.float().cpu(), ref_view.storage.float()) <= 8e-3
+    assert (view.storage != before).any(dim=-1).sum().item() <= n * kv_heads * 2
+    q2, snapshot = torch.zeros_like(q), view.storage.clone()
+    ops().gemm_qkv_rope(x, w, q2, view, table, rotary, heads, batch, False)
+    assert torch.equal(q2, q) and torch.equal(view.storage, snapshot)
