@@ -162,7 +162,7 @@ def model_numbers(config, layers):
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=64)
+    parser.add_argument("--steps", type=int, default=256)
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the full model (named in config)")
     parser.add_argument("--batch", type=int, default=8)

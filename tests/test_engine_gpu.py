@@ -172,3 +172,51 @@ def test_sampled_generation_and_stop_tokens(setup):
     assert stopped[1].finish_reason == "stop" and len(stopped[1].tokens) <= 3
     alone = engine.generate([prompts[2]], 12, SamplingOptions(temperature=0.8, seed=7))
     assert alone[0].tokens == engine.generate(prompts, 12, SamplingOptions(temperature=0.8, seed=5))[2].tokens
+
+
+SIZES = [
+    # heads, kv_heads, head_dim, hidden, intermediate, vocab, window-less Llama layers
+    dict(num_attention_heads=8, num_key_value_heads=1, head_dim=32, hidden_size=72, intermediate_size=200, vocab_size=130),
+    dict(num_attention_heads=4, num_key_value_heads=2, head_dim=128, hidden_size=96, intermediate_size=136, vocab_size=514),
+    dict(num_attention_heads=3, num_key_value_heads=3, head_dim=80, hidden_size=120, intermediate_size=96, vocab_size=90),
+    dict(num_attention_heads=34, num_key_value_heads=2, head_dim=16, hidden_size=64, intermediate_size=72, vocab_size=258),
+    dict(num_attention_heads=2, num_key_value_heads=1, head_dim=256, hidden_size=40, intermediate_size=48, vocab_size=66),
+    dict(num_attention_heads=5, num_key_value_heads=5, head_dim=144, hidden_size=56, intermediate_size=64, vocab_size=100),
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("sizes", SIZES, ids=lambda s: f"h{s['num_attention_heads']}k{s['num_key_value_heads']}d{s['head_dim']}")
+def test_other_sizes(sizes, dtype):
+    """Head sizes in steps of 16 (and one that is not), any number of heads and groups, widths and vocabularies that
+    are no power of two: whole prompts in a batch, then single tokens, against the plain implementation."""
+    config = dict(P.TINY_A, num_hidden_layers=1, tie_word_embeddings=False, max_position_embeddings=512, **sizes)
+    weights = P.random_weights(config, seed=7, std=0.08)
+    engine = make_engine(config, weights, dtype, max_tokens=64 * 12)
+    plain = PlainLogits(config, weights)
+    prompts = prompts_for(config, (70, 3, 129), seed=13)
+    slots = engine.open(3)
+    logits = host(engine.step(slots, prompts, [list(range(len(p))) for p in prompts]))
+    offset = 0
+    for prompt in prompts:
+        assert rel_error(logits[offset:offset + len(prompt)], plain(prompt)) <= TOL[dtype]
+        offset += len(prompt)
+    tails = prompts_for(config, (3, 3, 3), seed=14)
+    for step in range(3):
+        got = host(engine.step(slots, [[t[step]] for t in tails]))
+        for row, (prompt, tail) in enumerate(zip(prompts, tails)):
+            assert rel_error(got[row], plain(prompt + tail[:step + 1])[-1]) <= TOL[dtype], (row, step)
+    engine.close(slots)
+    chosen = engine.generate(prompts[:2], 4, ignore_eos=True)  # the CUDA-graph decode path at these sizes
+    assert all(len(r.tokens) == 4 for r in chosen)
+
+
+def test_sizes_the_kernels_refuse_are_clear_errors():
+    from etalii.dllm_b200.kernels.ops import KernelError
+
+    config = dict(P.TINY_A, num_hidden_layers=1, vocab_size=131, tie_word_embeddings=False)  # an odd vocabulary
+    weights = P.random_weights(config, seed=1)
+    engine = make_engine(config, weights, "bfloat16", max_tokens=128)
+    slot = engine.open(1)
+    with pytest.raises(KernelError, match="N even"):
+        engine.step(slot, [[1, 2, 3]])
