@@ -102,7 +102,8 @@ def decode_run(engine, prompts, steps, warmup):
         part = slice(begin, begin + 8)
         logits = engine.step(slots[part], prompts[part])
         tokens += engine.sampler.choose(logits, engine.last_batch.slots, SamplingOptions()).tolist()
-    graph = engine._decode_graph(len(prompts), SamplingOptions())
+    longest = max(len(p) for p in prompts) + warmup + steps + 1
+    graph = engine._decode_graph(len(prompts), SamplingOptions(), longest)
     done = 0
     while done < warmup:  # warm-up steps (the first run also captures the graph)
         n = min(graph.CAPACITY, warmup - done)
@@ -225,7 +226,7 @@ def main() -> int:
     engine.generate(prompts, 20, SamplingOptions(), ignore_eos=True)
     engine.generate(prompts, args.steps + 1, SamplingOptions(), ignore_eos=True)
     stats = engine.stats
-    graph = engine._decode_graph(args.batch, SamplingOptions())
+    graph = next(g for g in engine._graphs.values() if g.b == args.batch)
     e2e = {"value": round(stats["decode_tokens"] / stats["decode_s"], 1), "unit": "tokens/s",
            "h2d_bytes_per_step": round(graph.host.numel() * 4 / engine.decode_chunk, 1),
            "d2h_bytes_per_step": args.batch * 4}

@@ -14,7 +14,7 @@ class DecodeGraph:
     CAPACITY = 64
     """Most steps one run may take before the host reads the tokens."""
 
-    def __init__(self, engine, batch_size: int, options, use_graph: bool = True) -> None:
+    def __init__(self, engine, batch_size: int, options, use_graph: bool = True, max_context: int | None = None) -> None:
         self.engine, self.b, self.options, self.use_graph = engine, batch_size, options, use_graph
         b = batch_size
         device = engine.rt.device
@@ -36,9 +36,9 @@ class DecodeGraph:
         batch.h_new = [1] * b
         batch.max_new = 1
         batch.is_decode = True
-        # the captured step serves every length up to the cache's longest sequence
-        batch.max_context = engine.max_length
-        batch.max_position = engine.max_length - 1
+        # the captured step serves every length up to this bound (attention launches blocks for all of it)
+        batch.max_context = min(int(max_context or engine.max_length), engine.max_length)
+        batch.max_position = batch.max_context - 1
         self.batch = batch
         self.graph = None
         self.generation = -1

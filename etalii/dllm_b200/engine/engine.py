@@ -127,7 +127,8 @@ class Engine:
         """Runs `steps` single-token steps for the sequences in `slots`, starting from `tokens` (each sequence's
         latest token, not yet in the cache); every step's chosen token is the next step's input, on the device.
         Returns the chosen tokens [step][sequence]. Uses one CUDA graph per batch size and sampling options."""
-        graph = self._decode_graph(len(slots), options or SamplingOptions())
+        graph = self._decode_graph(len(slots), options or SamplingOptions(),
+                                   max(self.cache.length(s) for s in slots) + steps)
         self.decode_start(graph, slots, tokens, steps)
         graph.replay(steps)
         return graph.tokens(steps)
@@ -136,6 +137,8 @@ class Engine:
         """Makes cache room for `steps` more tokens of each sequence and loads the graph's fixed buffers."""
         if steps > graph.CAPACITY:
             raise ValueError(f"at most {graph.CAPACITY} steps per run")
+        if max(self.cache.length(s) for s in slots) + steps > graph.batch.max_context:
+            raise ValueError("the sequences outgrow the context this decode graph was captured for")
         if len(set(slots)) != len(slots):
             raise CacheError("a sequence appears twice in one step")
         starts = []
@@ -148,11 +151,18 @@ class Engine:
             self.cache.advance(slot, steps)
         self.steps_run += steps
 
-    def _decode_graph(self, batch_size: int, options: SamplingOptions):
-        key = (batch_size, options.temperature, options.top_k, options.top_p, options.min_p)
+    CONTEXT_BUCKET = 1024
+    """Decode graphs are captured for contexts up to a multiple of this; a batch that outgrows its bucket moves to
+    the next graph (so attention does not launch blocks for the whole cache when contexts are short)."""
+
+    def _decode_graph(self, batch_size: int, options: SamplingOptions, longest: int | None = None):
+        bound = self.max_length if longest is None else \
+            min(self.max_length, -(-int(longest) // self.CONTEXT_BUCKET) * self.CONTEXT_BUCKET)
+        key = (batch_size, bound, options.temperature, options.top_k, options.top_p, options.min_p)
         graph = self._graphs.get(key)
         if graph is None:
-            graph = self._graphs[key] = DecodeGraph(self, batch_size, options, use_graph=self.cuda_graphs)
+            graph = self._graphs[key] = DecodeGraph(self, batch_size, options, use_graph=self.cuda_graphs,
+                                                    max_context=bound)
         return graph
 
     # ---- generation ----
