@@ -263,14 +263,24 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attention_mma_kernel(
   if (warp_on) {
     const bf16* ksrc = (const bf16*)cache.base + kv_offset(cache, page, 0, g, 0);
     const bf16* vsrc = (const bf16*)cache.base + kv_offset(cache, page, 1, g, 0);
-    for (int idx = lane; idx < TILE_KEYS * (HD / 8); idx += 32) {
-      int r = idx / (HD / 8), cc = idx % (HD / 8);
-      if (cc < chunks16) {
-        cp_async_16(k_s + r * LD + cc * 8, ksrc + (size_t)r * hd + cc * 8);
-        cp_async_16(v_s + r * LD + cc * 8, vsrc + (size_t)r * hd + cc * 8);
-      } else {
-        *reinterpret_cast<uint4*>(k_s + r * LD + cc * 8) = make_uint4(0u, 0u, 0u, 0u);
-        *reinterpret_cast<uint4*>(v_s + r * LD + cc * 8) = make_uint4(0u, 0u, 0u, 0u);
+    if (hd == HD) {  // the page is one flat piece: 16-byte piece i goes to row i / (HD/8), column i % (HD/8)
+#pragma unroll
+      for (int i = 0; i < TILE_KEYS * (HD / 8) / 32; ++i) {
+        int idx = lane + 32 * i;
+        int dst = (idx / (HD / 8)) * LD + (idx % (HD / 8)) * 8;
+        cp_async_16(k_s + dst, ksrc + idx * 8);
+        cp_async_16(v_s + dst, vsrc + idx * 8);
+      }
+    } else {
+      for (int idx = lane; idx < TILE_KEYS * (HD / 8); idx += 32) {
+        int r = idx / (HD / 8), cc = idx % (HD / 8);
+        if (cc < chunks16) {
+          cp_async_16(k_s + r * LD + cc * 8, ksrc + (size_t)r * hd + cc * 8);
+          cp_async_16(v_s + r * LD + cc * 8, vsrc + (size_t)r * hd + cc * 8);
+        } else {
+          *reinterpret_cast<uint4*>(k_s + r * LD + cc * 8) = make_uint4(0u, 0u, 0u, 0u);
+          *reinterpret_cast<uint4*>(v_s + r * LD + cc * 8) = make_uint4(0u, 0u, 0u, 0u);
+        }
       }
     }
     asm volatile("cp.async.commit_group;\n" ::);
@@ -333,26 +343,34 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attention_mma_kernel(
           mma_bf16(s[2 * jp + 1], q_frag[ks], bfr[2], bfr[3]);
         }
       }
-      // masks (keys outside [lo, hi)), maximum, probabilities, sum
+      // masks (keys outside [lo, hi), only in a tile that holds an edge), maximum, probabilities, sum; the
+      // scale (with log2 e folded in) is applied inside the exponent: p = 2^(s * scale - max * scale)
+      if (key0 < lo || key0 + TILE_KEYS > hi) {
+#pragma unroll
+        for (int j = 0; j < TILE_KEYS / 8; ++j)
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            int key = key0 + j * 8 + tq * 2 + (r & 1);
+            if (key < lo || key >= hi) s[j][r] = -INFINITY;
+          }
+      }
 #pragma unroll
       for (int j = 0; j < TILE_KEYS / 8; ++j)
 #pragma unroll
-        for (int r = 0; r < 4; ++r) {
-          int key = key0 + j * 8 + tq * 2 + (r & 1);
-          float v = (key >= lo && key < hi) ? s[j][r] * scale_log2 : -INFINITY;
-          s[j][r] = v;
-          m_row[r >> 1] = fmaxf(m_row[r >> 1], v);
-        }
+        for (int r = 0; r < 4; ++r) m_row[r >> 1] = fmaxf(m_row[r >> 1], s[j][r]);
+      float neg_max[2];
 #pragma unroll
       for (int i = 0; i < 2; ++i) {
         m_row[i] = fmaxf(m_row[i], __shfl_xor_sync(0xffffffffu, m_row[i], 1));
         m_row[i] = fmaxf(m_row[i], __shfl_xor_sync(0xffffffffu, m_row[i], 2));
+        m_row[i] *= scale_log2;  // from here on the maximum is in the scaled log2 domain, like the partial results
+        neg_max[i] = -m_row[i];
       }
       unsigned p_frag[TILE_KEYS / 16][4];
 #pragma unroll
       for (int j = 0; j < TILE_KEYS / 8; ++j) {
-        float p0 = exp2f(s[j][0] - m_row[0]), p1 = exp2f(s[j][1] - m_row[0]);
-        float p2 = exp2f(s[j][2] - m_row[1]), p3 = exp2f(s[j][3] - m_row[1]);
+        float p0 = fast_exp2(fmaf(s[j][0], scale_log2, neg_max[0])), p1 = fast_exp2(fmaf(s[j][1], scale_log2, neg_max[0]));
+        float p2 = fast_exp2(fmaf(s[j][2], scale_log2, neg_max[1])), p3 = fast_exp2(fmaf(s[j][3], scale_log2, neg_max[1]));
         l_row[0] += p0 + p1;
         l_row[1] += p2 + p3;
         p_frag[j >> 1][(j & 1) * 2 + 0] = pack_bf16(p0, p1);
@@ -385,8 +403,8 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attention_mma_kernel(
       int d = i * 8 + tq * 2;
       float* lo_row = red_o + ((size_t)warp * 16 + gq) * HD + d;
       float* hi_row = red_o + ((size_t)warp * 16 + gq + 8) * HD + d;
-      lo_row[0] = o_acc[i][0]; lo_row[1] = o_acc[i][1];
-      hi_row[0] = o_acc[i][2]; hi_row[1] = o_acc[i][3];
+      *reinterpret_cast<float2*>(lo_row) = make_float2(o_acc[i][0], o_acc[i][1]);
+      *reinterpret_cast<float2*>(hi_row) = make_float2(o_acc[i][2], o_acc[i][3]);
     }
     __syncthreads();
     for (int idx = threadIdx.x; idx < nh * hd; idx += WARPS * 32) {
@@ -397,7 +415,7 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attention_mma_kernel(
       float o = 0.f, l = 0.f;
 #pragma unroll
       for (int w = 0; w < WARPS; ++w) {
-        float f = sm_ml[w][h][0] == -INFINITY ? 0.f : exp2f(sm_ml[w][h][0] - m);
+        float f = sm_ml[w][h][0] == -INFINITY ? 0.f : fast_exp2(sm_ml[w][h][0] - m);
         o = fmaf(red_o[((size_t)w * 16 + h) * HD + d], f, o);
         l = fmaf(sm_ml[w][h][1], f, l);
       }
@@ -447,7 +465,7 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attention_mma_kernel(
     m = warp_max(m);
     float l = 0.f;
     for (int cc = c_lo + lane; cc < c_hi; cc += 32)
-      l = fmaf(__ldcg(&part_ml[(row0 + cc) * 2 + 1]), exp2f(__ldcg(&part_ml[(row0 + cc) * 2]) - m), l);
+      l = fmaf(__ldcg(&part_ml[(row0 + cc) * 2 + 1]), fast_exp2(__ldcg(&part_ml[(row0 + cc) * 2]) - m), l);
     l = warp_sum(l);
     if (lane == 0) { sm_m[h] = m; sm_inv[h] = 1.0f / l; }
   }
@@ -458,7 +476,7 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attention_mma_kernel(
     float m = sm_m[h], o = 0.f;
 #pragma unroll 4
     for (int cc = c_lo; cc < c_hi; ++cc)
-      o = fmaf(__ldcg(&part_o[(row0 + cc) * hd + d]), exp2f(__ldcg(&part_ml[(row0 + cc) * 2]) - m), o);
+      o = fmaf(__ldcg(&part_o[(row0 + cc) * hd + d]), fast_exp2(__ldcg(&part_ml[(row0 + cc) * 2]) - m), o);
     out[((size_t)b * heads + g * group + h) * hd + d] = __float2bfloat16_rn(o * sm_inv[h]);
   }
 }

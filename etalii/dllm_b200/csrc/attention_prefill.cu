@@ -145,27 +145,29 @@ __global__ void __launch_bounds__(THREADS) prefill_kernel(
     int key0 = kt * BN;
     bool need_mask = key0 + BN - 1 > pos0 + warp * 16 || (window > 0 && key0 < pos0 + warp * 16 + 16 - window);
     float tile_max[2] = {-INFINITY, -INFINITY};
+    if (need_mask) {
+#pragma unroll
+      for (int j = 0; j < BN / 8; ++j)
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          int key = key0 + j * 8 + tq * 2 + (r & 1);
+          int qp = row_pos[r >> 1];
+          if (key > qp || (window > 0 && key < qp + 1 - window)) s[j][r] = -INFINITY;
+        }
+    }
 #pragma unroll
     for (int j = 0; j < BN / 8; ++j)
 #pragma unroll
-      for (int r = 0; r < 4; ++r) {
-        float v = s[j][r] * scale_log2;
-        if (need_mask) {
-          int key = key0 + j * 8 + tq * 2 + (r & 1);
-          int qp = row_pos[r >> 1];
-          if (key > qp || (window > 0 && key < qp + 1 - window)) v = -INFINITY;
-        }
-        s[j][r] = v;
-        tile_max[r >> 1] = fmaxf(tile_max[r >> 1], v);
-      }
+      for (int r = 0; r < 4; ++r) tile_max[r >> 1] = fmaxf(tile_max[r >> 1], s[j][r]);
     float corr[2];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
       tile_max[i] = fmaxf(tile_max[i], __shfl_xor_sync(0xffffffffu, tile_max[i], 1));
       tile_max[i] = fmaxf(tile_max[i], __shfl_xor_sync(0xffffffffu, tile_max[i], 2));
+      tile_max[i] *= scale_log2;  // maxima live in the scaled log2 domain; the scores are scaled inside the exponent
       float m_new = fmaxf(m_run[i], tile_max[i]);
       float m_use = m_new == -INFINITY ? 0.f : m_new;  // a row that sees nothing in this tile (and nothing before)
-      corr[i] = exp2f(m_run[i] - m_use);
+      corr[i] = fast_exp2(m_run[i] - m_use);
       m_run[i] = m_new;
       tile_max[i] = m_use;
     }
@@ -173,8 +175,8 @@ __global__ void __launch_bounds__(THREADS) prefill_kernel(
     unsigned p_frag[BN / 16][4];
 #pragma unroll
     for (int j = 0; j < BN / 8; ++j) {
-      float p0 = exp2f(s[j][0] - tile_max[0]), p1 = exp2f(s[j][1] - tile_max[0]);
-      float p2 = exp2f(s[j][2] - tile_max[1]), p3 = exp2f(s[j][3] - tile_max[1]);
+      float p0 = fast_exp2(fmaf(s[j][0], scale_log2, -tile_max[0])), p1 = fast_exp2(fmaf(s[j][1], scale_log2, -tile_max[0]));
+      float p2 = fast_exp2(fmaf(s[j][2], scale_log2, -tile_max[1])), p3 = fast_exp2(fmaf(s[j][3], scale_log2, -tile_max[1]));
       row_sum[0] += p0 + p1;
       row_sum[1] += p2 + p3;
       p_frag[j >> 1][(j & 1) * 2 + 0] = pack_bf16(p0, p1);
@@ -230,8 +232,8 @@ __global__ void __launch_bounds__(THREADS) prefill_kernel(
     for (int i = 0; i < 2; ++i) {
       float m = fmaxf(m_run[i], other_m[i]);
       float m_use = m == -INFINITY ? 0.f : m;
-      mine[i] = exp2f(m_run[i] - m_use);
-      theirs[i] = exp2f(other_m[i] - m_use);
+      mine[i] = fast_exp2(m_run[i] - m_use);
+      theirs[i] = fast_exp2(other_m[i] - m_use);
       l_run[i] = l_run[i] * mine[i] + other_l[i] * theirs[i];
     }
 #pragma unroll
