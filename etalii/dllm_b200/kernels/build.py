@@ -28,6 +28,7 @@ SOURCES = {
     "gemm_tcgen05": "gemm_tcgen05.cu",
     "attention": "attention.cu",
     "attention_decode": "attention_decode.cu",
+    "attention_decode_cluster": "attention_decode_cluster.cu",
     "attention_prefill": "attention_prefill.cu",
     "attention_decode_static": "attention_decode_static.cu",
     "sampling": "sampling.cu",

@@ -46,6 +46,9 @@ _prototypes = {
     ("attention_decode", "dllm_attention_decode"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                                     c_int, c_void_p, c_void_p, c_int, c_float, c_int, c_int, c_int,
                                                     c_void_p, c_void_p, c_void_p],
+    ("attention_decode_cluster", "dllm_attention_decode_cluster"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                                                    c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                                                    c_int, c_float, c_int, c_void_p],
     ("attention_prefill", "dllm_attention_prefill"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                                       c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                       c_int, c_float, c_int, c_void_p],
@@ -360,4 +363,24 @@ def attention_prefill(out: torch.Tensor, q: torch.Tensor, cache, heads: int, sca
         heads, cache.kv_heads, cache.head_dim, batch.tile_seq.data_ptr(), batch.tile_first.data_ptr(),
         batch.cu_seqlens.data_ptr(), batch.start.data_ptr(), batch.slots.data_ptr(), batch.n_tiles, float(scale),
         int(window or 0), _stream()), "attention_prefill",
+        f"head_dim={cache.head_dim} must be a multiple of 16, at most 128; pages of 64")
+
+
+def attention_decode_cluster_supported(cache) -> bool:
+    return cache.dtype == torch.bfloat16 and cache.head_dim % 16 == 0 and cache.head_dim <= 128 \
+        and cache.page_size == 64
+
+
+def attention_decode_cluster(out: torch.Tensor, q: torch.Tensor, cache, heads: int, scale: float, window: int,
+                             batch) -> None:
+    """Attention for a batch in which every sequence brings one token (bfloat16, head_dim a multiple of 16 up to
+    128): a cluster of eight blocks per (sequence, kv head) splits the keys and combines through distributed shared
+    memory; no scratch, and a launch shape that does not depend on the context length."""
+    _cuda(out, q)
+    assert attention_decode_cluster_supported(cache) and q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+    assert batch.n_tokens == batch.n_seqs
+    _check(_fn("attention_decode_cluster", "dllm_attention_decode_cluster")(
+        out.data_ptr(), q.data_ptr(), cache.base_ptr, cache.page_table.data_ptr(), cache.max_pages, cache.page_size,
+        heads, cache.kv_heads, cache.head_dim, batch.tok_pos.data_ptr(), batch.slots.data_ptr(), batch.n_seqs,
+        float(scale), int(window or 0), _stream()), "attention_decode_cluster",
         f"head_dim={cache.head_dim} must be a multiple of 16, at most 128; pages of 64")

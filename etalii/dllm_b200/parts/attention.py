@@ -75,7 +75,9 @@ class Attention:
             project(qkv, h, self.w_qkv, ops.EPI_STORE_F32)
             ops.rope_cache_write(qkv, q, cache, table, rotary_dim, self.num_heads, batch, write_cache)
         attended = rt.ws.buffer("attended", (n, q_size), rt.dtype)
-        if batch.is_decode and rt.dtype == torch.bfloat16:
+        if batch.is_decode and rt.dtype == torch.bfloat16 and ops.attention_decode_cluster_supported(cache):
+            ops.attention_decode_cluster(attended, q, cache, self.num_heads, self.scale, self.window or 0, batch)
+        elif batch.is_decode and rt.dtype == torch.bfloat16:
             chunk = decode_chunk(batch.n_seqs, self.num_kv_heads, batch.max_context, self.head_dim)
             scratch = rt.ws.buffer("attention_scratch", (ops.attention_decode_scratch(
                 batch.n_seqs, self.num_heads, self.head_dim, chunk, batch.max_context),), torch.float32)

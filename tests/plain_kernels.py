@@ -166,3 +166,11 @@ def gemm_qkv_rope(a, w, q_out, cache, table, rotary_dim, heads, batch, write_cac
 
 def gemm_qkv_rope_supported(cache, rotary_dim, has_table):
     return False
+
+
+def attention_decode_cluster(out, q, cache, heads, scale, window, batch):
+    attention_general(out, q, cache, heads, scale, window, batch)
+
+
+def attention_decode_cluster_supported(cache):
+    return False

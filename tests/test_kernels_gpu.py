@@ -449,3 +449,52 @@ def test_gemm_qkv_rope(heads, kv_heads, head_dim, rotary):
     q2, snapshot = torch.zeros_like(q), view.storage.clone()
     ops().gemm_qkv_rope(x, w, q2, view, table, rotary, heads, batch, False)
     assert torch.equal(q2, q) and torch.equal(view.storage, snapshot)
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,window", [(4, 2, 16, None), (9, 3, 64, None), (8, 1, 128, 70),
+                                                           (6, 2, 48, 33), (34, 2, 32, None), (20, 2, 96, 300)])
+@pytest.mark.parametrize("lengths", [[130, 67, 1, 700, 64, 65], [2100, 2048, 2049, 4500]])
+def test_attention_decode_cluster(heads, kv_heads, head_dim, window, lengths):
+    from etalii.dllm_b200.cache.paged import CacheNeed, PagedCache
+    from etalii.dllm_b200.engine.batch import BatchBuffers
+
+    cache = PagedCache([CacheNeed("kv", kv_heads, head_dim, window)], max_tokens=64 * 200, max_length=8192,
+                       dtype=torch.bfloat16, device=DEV)
+    slots = cache.acquire(len(lengths))
+    for slot, n in zip(slots, lengths):
+        cache.reserve(slot, n)
+        cache.advance(slot, n)
+    cache.sync_tables()
+    view = cache.kv_view(0)
+    g = torch.Generator().manual_seed(3)
+    view.storage.copy_(torch.randn(view.storage.shape, generator=g).to(torch.bfloat16))
+    batch = BatchBuffers(DEV).fill(slots, [[1]] * len(lengths), [n - 1 for n in lengths], [[] for _ in lengths])
+    n = batch.n_tokens
+    q = _randn((n, heads * head_dim), torch.bfloat16, 9)
+    out = torch.zeros((n, heads * head_dim), dtype=torch.bfloat16, device=DEV)
+    ops().attention_decode_cluster(out, q, view, heads, 0.3, window or 0, batch)
+    general = torch.zeros_like(out)
+    ops().attention_general(general, q, view, heads, 0.3, window or 0, batch)  # itself checked against the plain one
+    assert rel_error(out.float().cpu(), general.float().cpu()) <= 8e-3
+    worst = (out.float() - general.float()).abs().max(dim=1).values
+    assert float(worst.max()) <= 8e-3 * float(general.float().abs().max()), int(worst.argmax())
+    again = torch.zeros_like(out)
+    ops().attention_decode_cluster(again, q, view, heads, 0.3, window or 0, batch)
+    assert torch.equal(again, out)
+
+
+def test_attention_decode_cluster_finds_a_far_key():
+    heads, kv_heads, hd = 4, 2, 32
+    cache, view, batch = _cache_and_batch(torch.bfloat16, kv_heads, hd, [700], [1])
+    view.storage.mul_(0.05)
+    slot = batch.h_slots[0]
+    for target in (0, 63, 64, 333, 698, 699):
+        page = int(view.page_table[slot, target // 64])
+        saved = view.storage[page].clone()
+        view.storage[page, 0, :, target % 64, :] = 4.0
+        view.storage[page, 1, :, target % 64, :] = 7.0
+        q = torch.full((1, heads * hd), 4.0, dtype=torch.bfloat16, device=DEV)
+        out = torch.zeros_like(q)
+        ops().attention_decode_cluster(out, q, view, heads, 1.0, 0, batch)
+        assert torch.allclose(out.float(), torch.full_like(out, 7.0).float(), atol=0.05), target
+        view.storage[page] = saved
