@@ -101,7 +101,7 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(void* __restrict__ c, 
                                                           const bf16* __restrict__ w, int M, int N, int K,
                                                           RopeArgs rope, Prefetch pf) {
   // 32-value k steps whose loads a warp issues before the first product (fewer when more tokens need registers)
-  constexpr int MAX_STEPS = NT == 1 ? 8 : (NT == 2 ? 4 : 2);
+  constexpr int MAX_STEPS = NORM ? (NT == 1 ? 6 : (NT == 2 ? 3 : 1)) : (NT == 1 ? 8 : (NT == 2 ? 4 : 2));
   __shared__ float red[WARPS][TILE][NT * 8 + 1];
   __shared__ float red_ss[WARPS][NT * 8];
   int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -143,27 +143,52 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(void* __restrict__ c, 
       pdl_wait();  // the weights above are nobody's output; everything below may be the previous kernel's
       early.load(c, tid, M, N, blockIdx.x, rope, paired, dim0);
     }
+    if (NORM) {
+      // all loads of the stretch first (activations and norm weights), then the arithmetic: a step's loads must
+      // not wait behind the previous step's sums
+      float4 xr[MAX_STEPS][NT][2], nr[MAX_STEPS][2];
 #pragma unroll
-    for (int i = 0; i < MAX_STEPS; ++i) {
-      int ch = (s0 + i) * 4 + t;
-      bool ok = s0 + i < s_end && ch < chunks;
+      for (int i = 0; i < MAX_STEPS; ++i) {
+        int ch = (s0 + i) * 4 + t;
+        bool ok = s0 + i < s_end && ch < chunks;
+        nr[i][0] = nr[i][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (ok) {
+          nr[i][0] = __ldg((const float4*)norm_w + 2 * ch);
+          nr[i][1] = __ldg((const float4*)norm_w + 2 * ch + 1);
+        }
 #pragma unroll
-      for (int n = 0; n < NT; ++n) {
-        int m = n * 8 + g;
-        xb[i][n] = zero;
-        if (!ok || m >= M) continue;
-        if (NORM) {
-          const float4* xp = (const float4*)((const float*)a + (size_t)m * K) + 2 * ch;
-          float4 x0 = xp[0], x1 = xp[1];
-          float4 n0 = __ldg((const float4*)norm_w + 2 * ch), n1 = __ldg((const float4*)norm_w + 2 * ch + 1);
+        for (int n = 0; n < NT; ++n) {
+          int m = n * 8 + g;
+          xr[i][n][0] = xr[i][n][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (ok && m < M) {
+            const float4* xp = (const float4*)((const float*)a + (size_t)m * K) + 2 * ch;
+            xr[i][n][0] = xp[0];
+            xr[i][n][1] = xp[1];
+          }
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < MAX_STEPS; ++i) {
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+          float4 x0 = xr[i][n][0], x1 = xr[i][n][1], n0 = nr[i][0], n1 = nr[i][1];
           ss[n] = fmaf(x0.x, x0.x, ss[n]); ss[n] = fmaf(x0.y, x0.y, ss[n]);
           ss[n] = fmaf(x0.z, x0.z, ss[n]); ss[n] = fmaf(x0.w, x0.w, ss[n]);
           ss[n] = fmaf(x1.x, x1.x, ss[n]); ss[n] = fmaf(x1.y, x1.y, ss[n]);
           ss[n] = fmaf(x1.z, x1.z, ss[n]); ss[n] = fmaf(x1.w, x1.w, ss[n]);
           xb[i][n] = make_uint4(pack_bf16(x0.x * n0.x, x0.y * n0.y), pack_bf16(x0.z * n0.z, x0.w * n0.w),
                                 pack_bf16(x1.x * n1.x, x1.y * n1.y), pack_bf16(x1.z * n1.z, x1.w * n1.w));
-        } else {
-          xb[i][n] = *((const uint4*)((const bf16*)a + (size_t)m * K) + ch);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < MAX_STEPS; ++i) {
+        int ch = (s0 + i) * 4 + t;
+        bool ok = s0 + i < s_end && ch < chunks;
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+          int m = n * 8 + g;
+          xb[i][n] = (ok && m < M) ? *((const uint4*)((const bf16*)a + (size_t)m * K) + ch) : zero;
         }
       }
     }
