@@ -220,3 +220,27 @@ def test_sizes_the_kernels_refuse_are_clear_errors():
     slot = engine.open(1)
     with pytest.raises(KernelError, match="N even"):
         engine.step(slot, [[1, 2, 3]])
+
+
+def test_long_generation_through_the_graph_path(setup):
+    """Well over a hundred tokens through `generate` (CUDA-graph decode in runs of 16 steps, new cache pages on
+    the way, sequences of unequal length) against the plain implementation."""
+    from etalii.dllm_b200 import SamplingOptions
+
+    tag, dtype, config, weights, engine, plain = setup
+    if tag != "a":
+        pytest.skip("Tiny A's context of 128 is the one that a long generation fills")
+    prompts = prompts_for(config, (3, 60, 20), seed=40)
+    results = engine.generate(prompts, 200, SamplingOptions(), ignore_eos=True)
+    for prompt, result in zip(prompts, results):
+        # the context window (128) ends the generation: prompt + output == window
+        assert result.finish_reason == "length" and len(prompt) + len(result.tokens) == 128
+        if dtype == "float32":
+            assert list(result.tokens) == P.generate(config, weights, prompt, 200)[0]
+        else:
+            context = list(prompt) + list(result.tokens)
+            for index in (len(prompt), len(prompt) + 40, 126):  # spot checks along the way
+                ref = plain(context[:index])[-1]
+                assert ref[context[index]] >= ref.max() - 2 * TOL[dtype] * np.abs(ref).max(), index
+    assert engine.cache.slots.held == 0
+    engine.cache.check()
