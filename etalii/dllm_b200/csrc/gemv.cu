@@ -95,7 +95,7 @@ struct Early {
   }
 };
 
-template <int WARPS, int NT, int EPI, bool NORM>
+template <int WARPS, int NT, int EPI, bool NORM, bool PIPE>
 __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(void* __restrict__ c, const void* __restrict__ a,
                                                           const float* __restrict__ norm_w, float eps,
                                                           const bf16* __restrict__ w, int M, int N, int K,
@@ -128,16 +128,22 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(void* __restrict__ c, 
   const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
   Early<EPI, NT> early;
   pdl_launch_dependents();
-  for (int s0 = s_begin; s0 < s_end; s0 += MAX_STEPS) {
-    uint4 wl[MAX_STEPS], wh[MAX_STEPS], xb[MAX_STEPS][NT];
-    // every load of this stretch is issued before the first product
+  // A stretch is MAX_STEPS k steps. Every load of a stretch is issued before its first product. For long rows
+  // (PIPE: a warp has more than one stretch) the weights of the NEXT stretch are requested before this stretch's
+  // products start, so that the row streams without pauses.
+  uint4 wl[MAX_STEPS], wh[MAX_STEPS];
+  auto load_weights = [&](int s0, uint4* lo, uint4* hi) {
 #pragma unroll
     for (int i = 0; i < MAX_STEPS; ++i) {
       int ch = (s0 + i) * 4 + t;
       bool ok = s0 + i < s_end && ch < chunks;
-      wl[i] = ok ? __ldg(w_lo + ch) : zero;
-      wh[i] = ok ? __ldg(w_hi + ch) : zero;
+      lo[i] = ok ? __ldg(w_lo + ch) : zero;
+      hi[i] = ok ? __ldg(w_hi + ch) : zero;
     }
+  };
+  if (s_begin < s_end) load_weights(s_begin, wl, wh);
+  for (int s0 = s_begin; s0 < s_end; s0 += MAX_STEPS) {
+    uint4 xb[MAX_STEPS][NT];
     if (s0 == s_begin) {
       prefetch_share(pf);
       pdl_wait();  // the weights above are nobody's output; everything below may be the previous kernel's
@@ -192,6 +198,9 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(void* __restrict__ c, 
         }
       }
     }
+    uint4 wl_next[PIPE ? MAX_STEPS : 1], wh_next[PIPE ? MAX_STEPS : 1];
+    bool more = PIPE && s0 + MAX_STEPS < s_end;
+    if (PIPE && more) load_weights(s0 + MAX_STEPS, wl_next, wh_next);
 #pragma unroll
     for (int i = 0; i < MAX_STEPS; ++i) {
       unsigned a0[4] = {wl[i].x, wh[i].x, wl[i].y, wh[i].y};
@@ -201,6 +210,14 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(void* __restrict__ c, 
         mma_bf16(acc[n], a0, xb[i][n].x, xb[i][n].y);
         mma_bf16(acc[n], a1, xb[i][n].z, xb[i][n].w);
       }
+    }
+    if (PIPE) {
+      if (more) {
+#pragma unroll
+        for (int i = 0; i < MAX_STEPS; ++i) { wl[i] = wl_next[PIPE ? i : 0]; wh[i] = wh_next[PIPE ? i : 0]; }
+      }
+    } else if (s0 + MAX_STEPS < s_end) {
+      load_weights(s0 + MAX_STEPS, wl, wh);
     }
   }
   if (s_begin >= s_end) {  // a warp without work has not waited yet
@@ -286,18 +303,19 @@ int launch(void* c, const void* a, const float* norm_w, float eps, const bf16* w
            const RopeArgs& rope, const Prefetch& pf, cudaStream_t stream) {
   int items = (N + TILE - 1) / TILE;
   bool wide = K >= 1024;
-#define DLLM_GO(WARPS, NT)                                                                                    \
-  return dllm_launch_pdl(gemv_kernel<WARPS, NT, EPI, NORM>, dim3(items), dim3(WARPS * 32), 0, stream, c, a, norm_w, \
-                         eps, w, M, N, K, rope, pf)
-  if (M <= 8) {
-    if (wide) DLLM_GO(8, 1); else DLLM_GO(4, 1);
-  } else if (M <= 16) {
-    if (wide) DLLM_GO(8, 2); else DLLM_GO(4, 2);
-  } else if (M <= 32) {
-    if (wide) DLLM_GO(8, 4); else DLLM_GO(4, 4);
-  } else {
-    if (wide) DLLM_GO(8, 8); else DLLM_GO(4, 8);
-  }
+  bool longrows = K > 2048;  // a warp has more than one stretch of k steps: stream the next stretch early
+#define DLLM_GO(WARPS, NT, PIPE)                                                                               \
+  return dllm_launch_pdl(gemv_kernel<WARPS, NT, EPI, NORM, PIPE>, dim3(items), dim3(WARPS * 32), 0, stream, c, a, \
+                         norm_w, eps, w, M, N, K, rope, pf)
+#define DLLM_PICK(NT)                    \
+  if (longrows) DLLM_GO(8, NT, true);    \
+  else if (wide) DLLM_GO(8, NT, false);  \
+  else DLLM_GO(4, NT, false)
+  if (M <= 8) { DLLM_PICK(1); }
+  else if (M <= 16) { DLLM_PICK(2); }
+  else if (M <= 32) { DLLM_PICK(4); }
+  else { DLLM_PICK(8); }
+#undef DLLM_PICK
 #undef DLLM_GO
 }
 

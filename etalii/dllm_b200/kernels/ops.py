@@ -127,9 +127,15 @@ prefetch_hints: dict[int, torch.Tensor] = {}
 weights are a key asks the L2 cache for the value while it runs. The model fills this from its run order."""
 
 
+PREFETCH_LIMIT = 16 << 20
+"""Larger weights are not asked into L2 ahead of time: four products of them would not fit there anyway."""
+
+
 def _prefetch_of(w: torch.Tensor):
     hint = prefetch_hints.get(w.data_ptr())
-    return (hint.data_ptr(), hint.numel() * hint.element_size()) if hint is not None else (None, 0)
+    if hint is None or hint.numel() * hint.element_size() > PREFETCH_LIMIT:
+        return (None, 0)
+    return (hint.data_ptr(), hint.numel() * hint.element_size())
 
 
 _async_status = None
