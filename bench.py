@@ -144,7 +144,7 @@ def prefill_run(engine, vocab, warmup, repeats=5):
         engine.close(slot)
         if index >= warmup:
             times.append(begin.elapsed_time(end))
-    return sum(times) / len(times)
+    return sorted(times)[len(times) // 2]  # the median: the step is launched from Python, host jitter shows in the mean
 
 
 def model_numbers(config, layers):

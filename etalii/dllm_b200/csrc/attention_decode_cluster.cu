@@ -4,12 +4,12 @@
 // output on the tensor cores (mma.sync m16n8k16; the 16 rows are the query heads of the kv group) with a running
 // maximum and sum over its pages. The warps meet in shared memory, the blocks through distributed shared memory
 // (mapa + ld.shared::cluster between two cluster barriers): no scratch in global memory, no atomics, and a launch
-// shape (8, kv heads, sequences) that does not depend on the context length. head_dim: a multiple of 16 up to 128.
+// shape (blocks per pair, kv heads, sequences) that does not depend on the context length. head_dim: a multiple of 16 up to 128.
 #include "common.cuh"
 
 namespace {
 typedef __nv_bfloat16 bf16;
-constexpr int WARPS = 4, CLUSTER = 8, TILE_KEYS = 64;
+constexpr int TILE_KEYS = 64;
 
 __device__ __forceinline__ void cp_async_16(void* smem, const void* gmem) {
   unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -48,7 +48,10 @@ __device__ __forceinline__ float remote_float(const float* local, unsigned rank)
   return v;
 }
 
-template <int HD>
+// CLUSTER blocks of WARPS warps serve one (sequence, kv head). Few (sequence, kv head) pairs: many blocks per pair
+// (8 x 4 warps) to fill the device and shorten every chain of pages; many pairs: one block of 8 warps per pair,
+// no exchange between blocks at all.
+template <int HD, int CLUSTER, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32) decode_attention_cluster_kernel(
     bf16* __restrict__ out, const bf16* __restrict__ q, KvLayout cache, const int* __restrict__ tok_pos,
     const int* __restrict__ slots, int heads, float scale_log2, int window) {
@@ -272,7 +275,7 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attention_cluster_kernel(
   }
 }
 
-template <int HD>
+template <int HD, int CLUSTER, int WARPS>
 int launch(void* out, const void* q, const KvLayout& cache, const int* tok_pos, const int* slots, int heads,
            int sequences, float scale, int window, cudaStream_t stream) {
   size_t kv_bytes = (size_t)WARPS * 2 * TILE_KEYS * (HD + 8) * sizeof(bf16);
@@ -280,7 +283,7 @@ int launch(void* out, const void* q, const KvLayout& cache, const int* tok_pos, 
   size_t smem = kv_bytes > red_bytes ? kv_bytes : red_bytes;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(decode_attention_cluster_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(decode_attention_cluster_kernel<HD, CLUSTER, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)smem) != cudaSuccess)
       return DLLM_LAUNCH_FAILED;
     configured = true;
@@ -299,7 +302,7 @@ int launch(void* out, const void* q, const KvLayout& cache, const int* tok_pos, 
   attributes[1].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attributes;
   config.numAttrs = dllm_pdl_enabled() ? 2 : 1;
-  return cudaLaunchKernelEx(&config, decode_attention_cluster_kernel<HD>, (bf16*)out, (const bf16*)q, cache, tok_pos,
+  return cudaLaunchKernelEx(&config, decode_attention_cluster_kernel<HD, CLUSTER, WARPS>, (bf16*)out, (const bf16*)q, cache, tok_pos,
                             slots, heads, scale * 1.4426950408889634f, window) == cudaSuccess
              ? DLLM_OK
              : DLLM_LAUNCH_FAILED;
@@ -318,7 +321,11 @@ DLLM_EXPORT int dllm_attention_decode_cluster(void* out, const void* q, void* ca
       kv_heads > 65535)
     return DLLM_UNSUPPORTED_SIZE;
   KvLayout cache{cache_base, page_table, max_pages, page_size, kv_heads, head_dim};
-  if (head_dim <= 32) return launch<32>(out, q, cache, tok_pos, slots, heads, sequences, scale, window, stream);
-  if (head_dim <= 64) return launch<64>(out, q, cache, tok_pos, slots, heads, sequences, scale, window, stream);
-  return launch<128>(out, q, cache, tok_pos, slots, heads, sequences, scale, window, stream);
+  bool many = (long long)sequences * kv_heads >= 128;  // enough pairs to fill the device without splitting the keys
+#define DLLM_GO(HD, CL, NW) \
+  return launch<HD, CL, NW>(out, q, cache, tok_pos, slots, heads, sequences, scale, window, stream)
+  if (head_dim <= 32) { if (many) DLLM_GO(32, 1, 8); else DLLM_GO(32, 8, 4); }
+  if (head_dim <= 64) { if (many) DLLM_GO(64, 1, 8); else DLLM_GO(64, 8, 4); }
+  if (many) DLLM_GO(128, 1, 4); else DLLM_GO(128, 8, 4);
+#undef DLLM_GO
 }

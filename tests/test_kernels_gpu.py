@@ -453,12 +453,14 @@ def test_gemm_qkv_rope(heads, kv_heads, head_dim, rotary):
 
 @pytest.mark.parametrize("heads,kv_heads,head_dim,window", [(4, 2, 16, None), (9, 3, 64, None), (8, 1, 128, 70),
                                                            (6, 2, 48, 33), (34, 2, 32, None), (20, 2, 96, 300)])
-@pytest.mark.parametrize("lengths", [[130, 67, 1, 700, 64, 65], [2100, 2048, 2049, 4500]])
+@pytest.mark.parametrize("lengths", [[130, 67, 1, 700, 64, 65], [2100, 2048, 2049, 4500],
+                                     [1 + (37 * i * i) % 190 for i in range(130)]],
+                         ids=["short", "long", "many"])
 def test_attention_decode_cluster(heads, kv_heads, head_dim, window, lengths):
     from etalii.dllm_b200.cache.paged import CacheNeed, PagedCache
     from etalii.dllm_b200.engine.batch import BatchBuffers
 
-    cache = PagedCache([CacheNeed("kv", kv_heads, head_dim, window)], max_tokens=64 * 200, max_length=8192,
+    cache = PagedCache([CacheNeed("kv", kv_heads, head_dim, window)], max_tokens=64 * 420, max_length=8192,
                        dtype=torch.bfloat16, device=DEV)
     slots = cache.acquire(len(lengths))
     for slot, n in zip(slots, lengths):
