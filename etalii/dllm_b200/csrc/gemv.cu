@@ -102,8 +102,10 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(void* __restrict__ c, 
                                                           RopeArgs rope, Prefetch pf) {
   // 32-value k steps whose loads a warp issues before the first product (fewer when more tokens need registers)
   constexpr int MAX_STEPS = NORM ? (NT == 1 ? 6 : (NT == 2 ? 3 : 1)) : (NT == 1 ? 8 : (NT == 2 ? 4 : 2));
-  __shared__ float red[WARPS][TILE][NT * 8 + 1];
-  __shared__ float red_ss[WARPS][NT * 8];
+  // exchange space of the warps: [WARPS][TILE][NT * 8 + 1] partial tiles, then [WARPS][NT * 8] sums of squares
+  extern __shared__ float exchange[];
+  float (*red)[TILE][NT * 8 + 1] = reinterpret_cast<float (*)[TILE][NT * 8 + 1]>(exchange);
+  float (*red_ss)[NT * 8] = reinterpret_cast<float (*)[NT * 8]>(exchange + WARPS * TILE * (NT * 8 + 1));
   int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   int g = lane >> 2, t = lane & 3;
   int head, dim0;
@@ -298,23 +300,44 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(void* __restrict__ c, 
   }
 }
 
+template <int WARPS, int NT, int EPI, bool NORM, bool PIPE>
+int launch_one(int items, void* c, const void* a, const float* norm_w, float eps, const bf16* w, int M, int N, int K,
+               const RopeArgs& rope, const Prefetch& pf, cudaStream_t stream) {
+  size_t smem = (size_t)(WARPS * TILE * (NT * 8 + 1) + WARPS * NT * 8) * sizeof(float);
+  if (smem > 48 * 1024) {
+    static bool configured = false;
+    if (!configured) {
+      if (cudaFuncSetAttribute(gemv_kernel<WARPS, NT, EPI, NORM, PIPE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               (int)smem) != cudaSuccess)
+        return DLLM_LAUNCH_FAILED;
+      configured = true;
+    }
+  }
+  return dllm_launch_pdl(gemv_kernel<WARPS, NT, EPI, NORM, PIPE>, dim3(items), dim3(WARPS * 32), smem, stream, c, a,
+                         norm_w, eps, w, M, N, K, rope, pf);
+}
+
 template <int EPI, bool NORM>
 int launch(void* c, const void* a, const float* norm_w, float eps, const bf16* w, int M, int N, int K,
            const RopeArgs& rope, const Prefetch& pf, cudaStream_t stream) {
   int items = (N + TILE - 1) / TILE;
   bool wide = K >= 1024;
   bool longrows = K > 2048;  // a warp has more than one stretch of k steps: stream the next stretch early
-#define DLLM_GO(WARPS, NT, PIPE)                                                                               \
-  return dllm_launch_pdl(gemv_kernel<WARPS, NT, EPI, NORM, PIPE>, dim3(items), dim3(WARPS * 32), 0, stream, c, a, \
-                         norm_w, eps, w, M, N, K, rope, pf)
+#define DLLM_GO(WARPS, NT, PIPE)                                                                          \
+  return launch_one<WARPS, NT, EPI, NORM, PIPE>(items, c, a, norm_w, eps, w, M, N, K, rope, pf, stream)
 #define DLLM_PICK(NT)                    \
   if (longrows) DLLM_GO(8, NT, true);    \
   else if (wide) DLLM_GO(8, NT, false);  \
   else DLLM_GO(4, NT, false)
+  // many tokens leave few registers for loads in flight: sixteen warps split the reduction instead
+#define DLLM_PICK_MANY(NT)               \
+  if (longrows) DLLM_GO(16, NT, true);   \
+  else DLLM_GO(16, NT, false)
   if (M <= 8) { DLLM_PICK(1); }
   else if (M <= 16) { DLLM_PICK(2); }
-  else if (M <= 32) { DLLM_PICK(4); }
-  else { DLLM_PICK(8); }
+  else if (M <= 32) { DLLM_PICK_MANY(4); }
+  else { DLLM_PICK_MANY(8); }
+#undef DLLM_PICK_MANY
 #undef DLLM_PICK
 #undef DLLM_GO
 }

@@ -158,9 +158,8 @@ def raise_if_failed() -> None:
         raise KernelError(f"a tcgen05 product gave up waiting on an mbarrier (role code {code}); results are invalid")
 
 
-GEMV_MAX_ROWS = 16
-"""Products with at most this many activation rows run in the weight-streaming kernel (the kernel itself takes up to
-64 rows, but beyond 16 every block re-reads more activations than weights and the tile kernel is faster)."""
+GEMV_MAX_ROWS = 64
+"""Products with at most this many activation rows run in the weight-streaming kernel."""
 
 
 def gemm(c: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int = EPI_STORE_T, kernel: int = 0,
