@@ -159,7 +159,14 @@ def raise_if_failed() -> None:
 
 
 GEMV_MAX_ROWS = 64
-"""Products with at most this many activation rows run in the weight-streaming kernel."""
+"""The weight-streaming kernel takes at most this many activation rows."""
+
+
+def streams(rows: int, outputs: int) -> bool:
+    """Whether a bfloat16 product of `rows` activation rows and `outputs` weight rows runs in the weight-streaming
+    kernel: always up to 16 rows; up to 64 rows unless the matrix has so many rows that its blocks (16 weight rows
+    each) would together re-read the activations far more often than the weights."""
+    return rows <= 16 or (rows <= GEMV_MAX_ROWS and outputs <= 4096)
 
 
 def gemm(c: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int = EPI_STORE_T, kernel: int = 0,
@@ -183,7 +190,7 @@ def gemm(c: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int = EPI_
         status = _fn("gemm_simt", "dllm_gemm_f32")(c.data_ptr(), a.data_ptr(), w.data_ptr(), m, n, k, epilogue,
                                                    _stream())
     elif w.dtype == torch.bfloat16:
-        streaming = (kernel == 2 and m <= 64) or (kernel == 0 and m <= GEMV_MAX_ROWS)
+        streaming = (kernel == 2 and m <= GEMV_MAX_ROWS) or (kernel == 0 and streams(m, n))
         if streaming:
             if norm_weight is not None:
                 assert a.dtype == torch.float32 and norm_weight.dtype == torch.float32 and norm_weight.numel() == k

@@ -174,3 +174,7 @@ def attention_decode_cluster(out, q, cache, heads, scale, window, batch):
 
 def attention_decode_cluster_supported(cache):
     return False
+
+
+def streams(rows, outputs):
+    return rows <= 16 or (rows <= 64 and outputs <= 4096)
