@@ -67,13 +67,17 @@ class Model:
                           if isinstance(v, torch.Tensor) and v.dim() == 2 and v.dtype == torch.bfloat16]
         order += [v for v in vars(self.head).values() if isinstance(v, torch.Tensor) and v.dim() == 2
                   and v.dtype == torch.bfloat16]
+        self._prefetch = {}
         for index, tensor in enumerate(order[:-ahead] if len(order) > ahead else []):
-            ops.prefetch_hints[tensor.data_ptr()] = order[index + ahead]
+            self._prefetch[tensor.data_ptr()] = order[index + ahead]
 
     def forward(self, batch) -> torch.Tensor:
         """Runs the batch's tokens through every scheduled layer; returns float32 logits [wanted rows, vocab]
         (None when no row is wanted: the cache is still filled)."""
+        from ..kernels import ops
+
         rt = self.rt
+        ops.prefetch_hints = self._prefetch  # this model's hints (they live and die with the model)
         x = self.embedding.forward(batch.tokens, batch.n_tokens, rt)
         for entry, view in zip(self.order, self._views):
             self.blocks[entry.layer].forward(x, batch, view, rt, entry.writes_cache)

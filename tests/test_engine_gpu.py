@@ -244,3 +244,34 @@ def test_long_generation_through_the_graph_path(setup):
                 assert ref[context[index]] >= ref.max() - 2 * TOL[dtype] * np.abs(ref).max(), index
     assert engine.cache.slots.held == 0
     engine.cache.check()
+
+
+@pytest.fixture(scope="module")
+def long_case():
+    config = dict(P.TINY_B, num_hidden_layers=1, max_position_embeddings=8192, vocab_size=128, num_attention_heads=4,
+                  num_key_value_heads=2, head_dim=16, hidden_size=64, intermediate_size=96)
+    config["rope_scaling"] = dict(config["rope_scaling"], original_max_position_embeddings=2048)
+    weights = P.random_weights(config, seed=3, std=0.08)
+    tokens = prompts_for(config, (5010,), seed=50)[0]
+    return config, weights, tokens, P.forward(config, weights, tokens)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_context(long_case, dtype):
+    """Five thousand positions: many pages per sequence, rotary angles far out, several rounds of the decode
+    attention's key split; a whole prompt, a prompt that goes on from a cached prefix, then single tokens."""
+    config, weights, tokens, reference = long_case
+    engine = make_engine(config, weights, dtype, max_tokens=64 * 170, max_length=8192)
+    slots = engine.open(2)
+    rows = list(range(0, 5000, 97)) + [4999]
+    whole = host(engine.step([slots[0]], [tokens[:5000]], [rows]))
+    assert rel_error(whole, reference[rows]) <= TOL[dtype]
+    engine.step([slots[1]], [tokens[:3000]], [[]])
+    rest = host(engine.step([slots[1]], [tokens[3000:5000]], [[0, 1000, 1999]]))
+    assert rel_error(rest, reference[[3000, 4000, 4999]]) <= TOL[dtype]
+    for index in range(5000, 5010):
+        got = host(engine.step(slots, [[tokens[index]], [tokens[index]]]))
+        assert rel_error(got[0], reference[index]) <= TOL[dtype], index
+        assert rel_error(got[1], reference[index]) <= TOL[dtype], index
+    engine.close(slots)
+    engine.cache.check()
