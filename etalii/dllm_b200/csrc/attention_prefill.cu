@@ -83,15 +83,27 @@ __global__ void __launch_bounds__(THREADS) prefill_kernel(
   for (int i = threadIdx.x; i <= kt_end - kt_begin && i < MAX_TILES; i += THREADS) page_s[i] = pages[kt_begin + i];
   __syncthreads();
 
+  const int flat_dst = (tid / (HD / 8)) * LD + (tid % (HD / 8)) * 8, flat_src = tid * 8;
   auto load_kv = [&](int stage, int kt) {
     int page = kt - kt_begin < MAX_TILES ? page_s[kt - kt_begin] : pages[kt];
     const bf16* ksrc = base + kv_offset(cache, page, 0, g, 0);
     const bf16* vsrc = base + kv_offset(cache, page, 1, g, 0);
-    for (int idx = tid; idx < BN * (HD / 8); idx += WARPS * 32) {
-      int r = idx / (HD / 8), c = idx % (HD / 8);
-      bool ok = c < chunks;
-      cp_async_16(k_s + (stage * BN + r) * LD + c * 8, ok ? ksrc + (size_t)r * hd + c * 8 : ksrc, ok);
-      cp_async_16(v_s + (stage * BN + r) * LD + c * 8, ok ? vsrc + (size_t)r * hd + c * 8 : vsrc, ok);
+    if (hd == HD) {
+      // the page is one flat piece; each thread's pieces sit at fixed offsets (computed once, below)
+#pragma unroll
+      for (int i = 0; i < BN * (HD / 8) / (WARPS * 32); ++i) {
+        int dst = stage * BN * LD + flat_dst + i * ((WARPS * 32) / (HD / 8)) * LD;
+        int src = flat_src + i * (WARPS * 32) * 8;
+        cp_async_16(k_s + dst, ksrc + src, true);
+        cp_async_16(v_s + dst, vsrc + src, true);
+      }
+    } else {
+      for (int idx = tid; idx < BN * (HD / 8); idx += WARPS * 32) {
+        int r = idx / (HD / 8), c = idx % (HD / 8);
+        bool ok = c < chunks;
+        cp_async_16(k_s + (stage * BN + r) * LD + c * 8, ok ? ksrc + (size_t)r * hd + c * 8 : ksrc, ok);
+        cp_async_16(v_s + (stage * BN + r) * LD + c * 8, ok ? vsrc + (size_t)r * hd + c * 8 : vsrc, ok);
+      }
     }
   };
   int kt_first = kt_begin + group;          // this group's tiles: kt_first, kt_first + GROUPS, ...
