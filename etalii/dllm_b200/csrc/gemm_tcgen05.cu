@@ -1,5 +1,6 @@
 // bfloat16 matrix product on the 5th-generation tensor cores: C = A[M,K] * W[N,K]^T, float32 accumulation in tensor
-// memory. One block computes a 128 x BN tile of C:
+// memory. Blocks are persistent and compute 128 x BN tiles of C, with two accumulators in tensor memory so that one
+// tile's epilogue overlaps the next tile's products:
 //   warp 0   one lane issues TMA loads (cp.async.bulk.tensor.2d, 128-byte swizzle) of 128x64 tiles of A and BNx64
 //            tiles of W into a ring of shared-memory stages, signalled by mbarriers (expect_tx / complete_tx);
 //   warp 1   allocates tensor memory; one lane issues tcgen05.mma (cta_group::1, kind::f16, M=128, N=BN, K=16) four
@@ -80,33 +81,47 @@ __device__ __forceinline__ void tmem_load16(unsigned taddr, unsigned* v) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+
 template <int BN> struct Shape {
-  static constexpr int STAGES = BN >= 128 ? 3 : 4;  // about 96 KB a block: two blocks share an SM
   static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
-  static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;  // a power of two, at least 32
+  static constexpr int ACC_COLS = BN < 32 ? 32 : BN;   // columns of one accumulator
+  static constexpr int TMEM_COLS = 2 * ACC_COLS;       // two accumulators: a power of two, at least 32
+  // about 96 KB a block where that is enough (two blocks share an SM, 2 x TMEM_COLS <= 512 columns); the 256-wide
+  // tile takes four 48 KB stages and all of the tensor memory, so one block owns the SM
+  static constexpr int STAGES = BN >= 256 ? 4 : (BN >= 128 ? 3 : 4);
   static constexpr size_t SMEM = (size_t)STAGES * (A_BYTES + B_BYTES) + 1024;
+  static constexpr int BLOCKS_PER_SM = BN >= 256 ? 1 : 2;
 };
 
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// A persistent block: it takes tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... of the m_tiles x n_tiles grid
+// (neighbouring blocks share a tile of W and read different rows of A). The producer's ring of stages runs on across
+// tiles; the accumulator alternates between two halves of the block's tensor memory, so the epilogue of one tile
+// overlaps the products of the next.
 template <int BN, int EPI>
 __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                const __grid_constant__ CUtensorMap map_w,
                                                                void* __restrict__ c, int M, int N, int K,
-                                                               int* __restrict__ status, RopeArgs rope) {
+                                                               int* __restrict__ status, RopeArgs rope, int m_tiles,
+                                                               int n_tiles) {
   typedef Shape<BN> S;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);  // swizzle atoms: 1 KB
-  __shared__ uint64_t full_bar[S::STAGES], empty_bar[S::STAGES], acc_bar;
+  __shared__ uint64_t full_bar[S::STAGES], empty_bar[S::STAGES], acc_full[2], acc_empty[2];
   __shared__ unsigned tmem_base_s;
   int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   int k_tiles = (K + BK - 1) / BK;
+  int total = m_tiles * n_tiles;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    mbar_init(&acc_bar, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }  // 4 epilogue warps
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) {  // tensor memory for the accumulator: BN columns of 128 lanes
+  if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                  ::"r"(smem_u32(&tmem_base_s)), "r"((unsigned)S::TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -120,93 +135,125 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
     if (lane == 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
-      for (int kt = 0; kt < k_tiles; ++kt) {
-        int s = kt % S::STAGES;
-        if (kt >= S::STAGES && !mbar_wait(&empty_bar[s], ((kt / S::STAGES) - 1) & 1)) { *(volatile int*)status = 2; break; }
-        mbar_expect_tx(&full_bar[s], S::A_BYTES + S::B_BYTES);
-        unsigned char* a_dst = tiles + (size_t)s * (S::A_BYTES + S::B_BYTES);
-        tma_load_2d(a_dst, &map_a, &full_bar[s], kt * BK, m0);
-        tma_load_2d(a_dst + S::A_BYTES, &map_w, &full_bar[s], kt * BK, n0);
+      int it = 0;  // k tiles issued so far, over all of this block's tiles
+      bool ok = true;
+      for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+        int m0 = (t % m_tiles) * BM, n0 = (t / m_tiles) * BN;
+        for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+          int s = it % S::STAGES;
+          if (it >= S::STAGES && !mbar_wait(&empty_bar[s], ((it / S::STAGES) - 1) & 1)) {
+            *(volatile int*)status = 2;
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(&full_bar[s], S::A_BYTES + S::B_BYTES);
+          unsigned char* a_dst = tiles + (size_t)s * (S::A_BYTES + S::B_BYTES);
+          tma_load_2d(a_dst, &map_a, &full_bar[s], kt * BK, m0);
+          tma_load_2d(a_dst + S::A_BYTES, &map_w, &full_bar[s], kt * BK, n0);
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr unsigned idesc = instr_desc(BN);
+      int it = 0, lt = 0;  // k tiles consumed, tiles started
       bool ok = true;
-      for (int kt = 0; kt < k_tiles && ok; ++kt) {
-        int s = kt % S::STAGES;
-        if (!mbar_wait(&full_bar[s], (kt / S::STAGES) & 1)) { *(volatile int*)status = 3; ok = false; break; }
+      for (int t = blockIdx.x; t < total && ok; t += gridDim.x, ++lt) {
+        int buf = lt & 1;
+        if (lt >= 2 && !mbar_wait(&acc_empty[buf], ((lt >> 1) - 1) & 1)) { *(volatile int*)status = 5; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        unsigned a_addr = smem_u32(tiles + (size_t)s * (S::A_BYTES + S::B_BYTES));
-        unsigned b_addr = a_addr + S::A_BYTES;
+        unsigned acc = tmem_base + (unsigned)(buf * S::ACC_COLS);
+        for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+          int s = it % S::STAGES;
+          if (!mbar_wait(&full_bar[s], (it / S::STAGES) & 1)) { *(volatile int*)status = 3; ok = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          unsigned a_addr = smem_u32(tiles + (size_t)s * (S::A_BYTES + S::B_BYTES));
+          unsigned b_addr = a_addr + S::A_BYTES;
 #pragma unroll
-        for (int k = 0; k < BK / UMMA_K; ++k) {
-          uint64_t adesc = smem_desc(a_addr + k * UMMA_K * 2), bdesc = smem_desc(b_addr + k * UMMA_K * 2);
-          umma(tmem_base, adesc, bdesc, idesc, (kt > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            uint64_t adesc = smem_desc(a_addr + k * UMMA_K * 2), bdesc = smem_desc(b_addr + k * UMMA_K * 2);
+            umma(acc, adesc, bdesc, idesc, (kt > 0 || k > 0) ? 1u : 0u);
+          }
+          tcgen05_commit(&empty_bar[s]);  // the stage is free once these products have read it
         }
-        tcgen05_commit(&empty_bar[s]);  // the stage is free once these products have read it
+        tcgen05_commit(&acc_full[buf]);   // this accumulator is complete once every product so far has finished
       }
-      tcgen05_commit(&acc_bar);         // the accumulator is complete once every product has finished
     }
   } else {
     // epilogue warps 2..5: warp w may read tensor-memory lanes 32 * (w % 4) .. + 31
     int quarter = warp & 3;
-    int m = m0 + quarter * 32 + lane;
-    bool ready = mbar_wait(&acc_bar, 0);
-    if (!ready && lane == 0) *(volatile int*)status = 4;
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (ready && EPI == EPI_QKV_ROPE) {
-      // the tile is one head (BN == head_dim): the thread holds its token's whole head, rotates the pairs
-      // (i, i + rotary_dim / 2) and writes the query, or the key / value into the token's cache row
-      float f[BN];
-#pragma unroll
-      for (int col = 0; col < BN; col += 16) {
-        unsigned v[16];
-        tmem_load16(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)col, v);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) f[col + i] = __uint_as_float(v[i]);
+    int lt = 0;
+    for (int t = blockIdx.x; t < total; t += gridDim.x, ++lt) {
+      int buf = lt & 1;
+      int m0 = (t % m_tiles) * BM, n_tile = t / m_tiles, n0 = n_tile * BN;
+      int m = m0 + quarter * 32 + lane;
+      if (!mbar_wait(&acc_full[buf], (lt >> 1) & 1)) {
+        if (lane == 0) *(volatile int*)status = 4;
+        break;
       }
-      int head = blockIdx.x, heads = rope.heads, nkv = rope.cache.kv_heads;
-      if (m < M && (head < heads || rope.write_cache)) {
-        int pos = rope.tok_pos[m];
-        if (rope.table != nullptr && head < heads + nkv) {
-          const float2* cs = rope.table + (size_t)pos * (rope.rotary_dim / 2);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      unsigned acc = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(buf * S::ACC_COLS);
+      if (EPI == EPI_QKV_ROPE) {
+        // the tile is one head (BN == head_dim): the thread holds its token's whole head, rotates the pairs
+        // (i, i + rotary_dim / 2) and writes the query, or the key / value into the token's cache row
+        float f[BN];
 #pragma unroll
-          for (int i = 0; i < BN / 2; ++i) {  // rotary_dim == head_dim here: the partner sits half a head away
-            float2 t = cs[i];
-            float x = f[i], y = f[i + BN / 2];
-            f[i] = fmaf(x, t.x, -(y * t.y));
-            f[i + BN / 2] = fmaf(x, t.y, y * t.x);
+        for (int col = 0; col < BN; col += 16) {
+          unsigned v[16];
+          tmem_load16(acc + (unsigned)col, v);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) f[col + i] = __uint_as_float(v[i]);
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[buf]);  // the values are in registers: the accumulator may be reused
+        int head = n_tile, heads = rope.heads, nkv = rope.cache.kv_heads;
+        if (m < M && (head < heads || rope.write_cache)) {
+          int pos = rope.tok_pos[m];
+          if (rope.table != nullptr && head < heads + nkv) {
+            const float2* cs = rope.table + (size_t)pos * (rope.rotary_dim / 2);
+#pragma unroll
+            for (int i = 0; i < BN / 2; ++i) {  // rotary_dim == head_dim here: the partner sits half a head away
+              float2 tc = cs[i];
+              float x = f[i], y = f[i + BN / 2];
+              f[i] = fmaf(x, tc.x, -(y * tc.y));
+              f[i + BN / 2] = fmaf(x, tc.y, y * tc.x);
+            }
+          }
+          bf16* dst;
+          if (head < heads) {
+            dst = rope.q_out + ((size_t)m * heads + head) * BN;
+          } else {
+            int which = head < heads + nkv ? 0 : 1;
+            int kvh = head - heads - which * nkv;
+            int slot = rope.slots[rope.tok_seq[m]];
+            int page = rope.cache.page_table[(size_t)slot * rope.cache.max_pages + pos / rope.cache.page_size];
+            dst = (bf16*)rope.cache.base + kv_offset(rope.cache, page, which, kvh, pos % rope.cache.page_size);
+          }
+#pragma unroll
+          for (int i = 0; i < BN; i += 8) {
+            uint4 o;
+            __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) po[j] = __floats2bfloat162_rn(f[i + 2 * j], f[i + 2 * j + 1]);
+            *reinterpret_cast<uint4*>(dst + i) = o;
           }
         }
-        bf16* dst;
-        if (head < heads) {
-          dst = rope.q_out + ((size_t)m * heads + head) * BN;
-        } else {
-          int which = head < heads + nkv ? 0 : 1;
-          int kvh = head - heads - which * nkv;
-          int slot = rope.slots[rope.tok_seq[m]];
-          int page = rope.cache.page_table[(size_t)slot * rope.cache.max_pages + pos / rope.cache.page_size];
-          dst = (bf16*)rope.cache.base + kv_offset(rope.cache, page, which, kvh, pos % rope.cache.page_size);
+      } else {
+#pragma unroll
+        for (int col = 0; col < BN; col += 16) {
+          unsigned v[16];
+          tmem_load16(acc + (unsigned)col, v);
+          if (col + 16 >= BN) {  // the last columns are in registers: the accumulator may be reused
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+          }
+          float f[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) f[i] = __uint_as_float(v[i]);
+          epilogue_row16<EPI, bf16>(c, m, n0 + col, M, N, f);
         }
-#pragma unroll
-        for (int i = 0; i < BN; i += 8) {
-          uint4 o;
-          __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) po[j] = __floats2bfloat162_rn(f[i + 2 * j], f[i + 2 * j + 1]);
-          *reinterpret_cast<uint4*>(dst + i) = o;
-        }
-      }
-    } else if (ready) {
-#pragma unroll
-      for (int col = 0; col < BN; col += 16) {
-        unsigned v[16];
-        tmem_load16(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)col, v);
-        float f[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) f[i] = __uint_as_float(v[i]);
-        epilogue_row16<EPI, bf16>(c, m, n0 + col, M, N, f);
       }
     }
   }
@@ -260,8 +307,20 @@ int launch(void* c, const void* a, const void* w, int M, int N, int K, int* stat
       return DLLM_LAUNCH_FAILED;
     configured = true;
   }
-  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-  gemm_tcgen05_kernel<BN, EPI><<<grid, THREADS, Shape<BN>::SMEM, stream>>>(map_a, map_w, c, M, N, K, status, rope);
+  int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
+  long long total = (long long)m_tiles * n_tiles;
+  if (total > 0x7fffffff) return DLLM_UNSUPPORTED_SIZE;
+  static int sms = 0;
+  if (sms == 0) {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0)
+      return DLLM_LAUNCH_FAILED;
+  }
+  int blocks = sms * Shape<BN>::BLOCKS_PER_SM;
+  if (blocks > total) blocks = (int)total;
+  gemm_tcgen05_kernel<BN, EPI><<<blocks, THREADS, Shape<BN>::SMEM, stream>>>(map_a, map_w, c, M, N, K, status, rope,
+                                                                            m_tiles, n_tiles);
   return dllm_launch_status();
 }
 
@@ -287,12 +346,18 @@ DLLM_EXPORT int dllm_gemm_tcgen05(void* c, const void* a, const void* w, int M, 
   if (M <= 0 || N <= 0) return DLLM_OK;
   if (K <= 0 || (K & 7) || (N & 1) || ((uintptr_t)a & 15) || ((uintptr_t)w & 15) || status == nullptr)
     return DLLM_UNSUPPORTED_SIZE;
-  if ((M + BM - 1) / BM > 65535) return DLLM_UNSUPPORTED_SIZE;
-  if (tile_n == 0) tile_n = M <= 256 ? 32 : ((N % 128 == 0 && N >= 2048) ? 128 : 64);
+  if (tile_n == 0) {
+    long long tiles128 = (long long)((M + BM - 1) / BM) * ((N + 127) / 128);
+    if (M <= 256) tile_n = 32;                                   // few rows: many narrow tiles
+    else if (N % 256 == 0 && tiles128 >= 8 * 148) tile_n = 256;  // plenty of work: the widest tile reuses A most
+    else if (N % 128 == 0 && N >= 2048) tile_n = 128;
+    else tile_n = 64;
+  }
   switch (tile_n) {
     case 32: return dispatch<32>(c, a, w, M, N, K, epilogue, status, stream);
     case 64: return dispatch<64>(c, a, w, M, N, K, epilogue, status, stream);
     case 128: return dispatch<128>(c, a, w, M, N, K, epilogue, status, stream);
+    case 256: return dispatch<256>(c, a, w, M, N, K, epilogue, status, stream);
     default: return DLLM_BAD_ARGUMENT;
   }
 }
@@ -311,7 +376,6 @@ DLLM_EXPORT int dllm_gemm_tcgen05_qkv_rope(const void* a, const void* w, int M, 
     return DLLM_UNSUPPORTED_SIZE;
   if ((head_dim != 32 && head_dim != 64 && head_dim != 128) || (table != nullptr && rotary_dim != head_dim))
     return DLLM_UNSUPPORTED_SIZE;
-  if ((M + BM - 1) / BM > 65535) return DLLM_UNSUPPORTED_SIZE;
   RopeArgs rope{(bf16*)q_out, KvLayout{cache_base, page_table, max_pages, page_size, kv_heads, head_dim},
                 (const float2*)table, table ? rotary_dim : 0, heads, tok_seq, tok_pos, slots, write_cache};
   int N = (heads + 2 * kv_heads) * head_dim;

@@ -405,9 +405,10 @@ def test_gemv_qkv_rope_refuses_head_sizes_it_cannot_pair():
                             device=DEV), view, None, 0, 6, batch)
 
 
-@pytest.mark.parametrize("m,n,k", GEMM_SHAPES + [(2048, 576, 576), (1000, 960, 1536), (64, 3072, 576), (129, 192, 72)])
+@pytest.mark.parametrize("m,n,k", GEMM_SHAPES + [(2048, 576, 576), (1000, 960, 1536), (64, 3072, 576), (129, 192, 72),
+                                                 (5000, 1024, 264), (300, 4608, 136)])
 @pytest.mark.parametrize("epilogue", [0, 1, 2, 3])
-@pytest.mark.parametrize("tile_n", [32, 64, 128])
+@pytest.mark.parametrize("tile_n", [32, 64, 128, 256])
 def test_gemm_tcgen05(m, n, k, epilogue, tile_n):
     a, w = _randn((m, k), torch.bfloat16, 3), _randn((n, k), torch.bfloat16, 4, 0.2)
     cols = n // 2 if epilogue == 3 else n
