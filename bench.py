@@ -147,6 +147,50 @@ def prefill_run(engine, vocab, warmup, repeats=5):
     return sorted(times)[len(times) // 2]  # the median: the step is launched from Python, host jitter shows in the mean
 
 
+def gemm_table() -> int:
+    """Times the tile products alone (CUDA events, 20 launches after 3) at layer shapes of the three model sizes:
+    the tcgen05 kernel at each tile width and the mma.sync kernel, in TFLOP/s."""
+    import torch
+
+    from etalii.dllm_b200.kernels import ops
+
+    def run(m, n, k, epilogue, tile_n, kernel):
+        a = torch.randn(m, k, device="cuda:0").bfloat16()
+        w = (torch.randn(n, k, device="cuda:0") * 0.05).bfloat16()
+        cols = n // 2 if epilogue == ops.EPI_SWIGLU else n
+        dtype = torch.float32 if epilogue in (ops.EPI_STORE_F32, ops.EPI_RESIDUAL) else torch.bfloat16
+        c = torch.zeros(m, cols, device="cuda:0", dtype=dtype)
+        for _ in range(3):
+            ops.gemm(c, a, w, epilogue, kernel=kernel, tile_n=tile_n)
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        for _ in range(20):
+            ops.gemm(c, a, w, epilogue, kernel=kernel, tile_n=tile_n)
+        end.record()
+        torch.cuda.synchronize()
+        ops.raise_if_failed()
+        ms = begin.elapsed_time(end) / 20
+        return ms * 1e3, 2 * m * n * k / ms / 1e9
+
+    shapes = [(2048, 576, 576, ops.EPI_RESIDUAL), (2048, 576, 1536, ops.EPI_RESIDUAL), (2048, 3072, 576, ops.EPI_SWIGLU),
+              (2048, 2048, 8192, ops.EPI_RESIDUAL), (2048, 16384, 2048, ops.EPI_SWIGLU),
+              (2048, 4096, 4096, ops.EPI_RESIDUAL), (2048, 28672, 4096, ops.EPI_SWIGLU),
+              (2048, 4096, 14336, ops.EPI_RESIDUAL), (8192, 4096, 4096, ops.EPI_STORE_T)]
+    print("M N K epilogue | tcgen05 tile 64 | 128 | 256 | chosen | mma.sync   (microseconds, TFLOP/s)")
+    for m, n, k, epilogue in shapes:
+        cells = []
+        for tile_n in (64, 128, 256, 0):
+            if tile_n and n % tile_n:
+                cells.append("-")
+                continue
+            us, tf = run(m, n, k, epilogue, tile_n, 3)
+            cells.append(f"{us:.1f} us {tf:.0f}")
+        us, tf = run(m, n, k, epilogue, 0, 1)
+        print(f"{m} {n} {k} {epilogue} | " + " | ".join(cells) + f" | {us:.1f} us {tf:.0f}")
+    return 0
+
+
 def model_numbers(config, layers):
     h, i, v = config["hidden_size"], config["intermediate_size"], config["vocab_size"]
     nh, nkv, hd = config["num_attention_heads"], config["num_key_value_heads"], config["head_dim"]
@@ -169,7 +213,7 @@ def main() -> int:
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
     parser.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 decode points")
-    parser.add_argument("--profile", choices=("decode", "prefill"),
+    parser.add_argument("--profile", choices=("decode", "prefill", "gemm"),
                         help="run only a few decode steps (or one prefill) and print no JSON: a small case for ncu")
     args = parser.parse_args()
     if args.impl == "reference":
@@ -177,6 +221,8 @@ def main() -> int:
                           "the reference does not install offline: pip finds no numpy in the wheelhouse, and with "
                           "--no-deps its wheel build fails in CMake because nanobind is not installed"}))
         return 0
+    if args.profile == "gemm":
+        return gemm_table()
     if args.gpus != 1:
         print(f"bench.py measures one GPU: --gpus {args.gpus} is not supported (this library runs on a single device)")
         return 2
