@@ -7,7 +7,7 @@ import torch
 
 from ..cache.paged import CacheNeed
 from ..kernels import ops
-from .norm import NormedInput, project
+from .norm import NormedInput, fuses_norm, project
 from .registry import build_part, register_part
 from .spec import ParamSpec
 
@@ -63,6 +63,8 @@ class Attention:
         rotary_dim = self.position.rotary_dim if self.position is not None else 0
         if rt.dtype == torch.bfloat16 and n <= ops.GEMV_MAX_ROWS and self.head_dim % 16 == 0 and rotary_dim % 16 == 0:
             # decode-sized: norm, projection, rotation and cache write in one kernel
+            if isinstance(h, NormedInput) and not fuses_norm(self.w_qkv):
+                h = h.tensor()
             pending = isinstance(h, NormedInput)
             ops.gemv_qkv_rope(h.x if pending else h, self.w_qkv, q, cache, table, rotary_dim, self.num_heads, batch,
                               write_cache, norm_weight=h.weight if pending else None, eps=h.eps if pending else 0.0)

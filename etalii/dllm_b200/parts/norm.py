@@ -52,11 +52,20 @@ class RMSNorm:
         return NormedInput(self, x, rt)
 
 
+FUSE_NORM_LIMIT = 16 << 20
+"""Weights up to this many bytes take the norm inside their decode-sized product (one kernel less); with larger
+weights every block of the product would redo the norm of all rows, and a separate norm kernel is cheaper."""
+
+
+def fuses_norm(w: torch.Tensor) -> bool:
+    return w.numel() * w.element_size() <= FUSE_NORM_LIMIT
+
+
 def project(out: torch.Tensor, h, w: torch.Tensor, epilogue: int) -> None:
     """out = epilogue(h @ w^T). `h` is a tensor of activations or a `NormedInput`; a decode-sized bfloat16 product
     applies the pending norm inside the kernel, anything else computes the normed activations first."""
     if isinstance(h, NormedInput):
-        if w.dtype == torch.bfloat16 and ops.streams(h.shape[0], w.shape[0]):
+        if w.dtype == torch.bfloat16 and ops.streams(h.shape[0], w.shape[0]) and fuses_norm(w):
             ops.gemm(out, h.x, w, epilogue, norm_weight=h.weight, eps=h.eps)
             return
         h = h.tensor()
