@@ -4,10 +4,10 @@
 //   double; candidates in the total order (p descending, id ascending); top-k keeps the first k, top-p the shortest
 //   prefix whose mass reaches it, min-p drops candidates below min_p * p_max; one double in [0,1) from the row's own
 //   xoshiro256** state, scaled by the kept mass, picks the first candidate whose running sum exceeds it.
-// The order is never materialised: a prefix of it is found by descending the 32 bits of p eight bits at a time
-// with counting histograms; masses are summed as 64-bit fixed point (2^-62 units), so every sum is exact integer
-// arithmetic, independent of the order of the atomic adds, and a row's choice is reproducible.
-// Scratch: one float per logit (the probabilities), given by the caller.
+// The order is never materialised: a prefix of it is found by descending the bits of p four at a time with counting
+// histograms (private to each thread, then summed in a fixed order); masses are summed as 64-bit fixed point (2^-62
+// units), so every sum is exact integer arithmetic and a row's choice is reproducible.
+// Scratch, given by the caller: per logit one float (the probability) and one double (the exponential).
 #include "common.cuh"
 
 namespace {
@@ -23,11 +23,13 @@ struct Found {
   int ok;
 };
 
+constexpr int BINS = 16;  // four bits of the key per pass
+
 struct Shared {
-  unsigned count[256];
-  unsigned long long mass[256];
-  unsigned long long scan_count[256];
-  unsigned long long scan_mass[256];
+  unsigned long long count[BINS];
+  unsigned long long mass[BINS];
+  unsigned long long part_count[BINS][THREADS / BINS];
+  unsigned long long part_mass[BINS][THREADS / BINS];
   Found found;
   double reduce_d[32];
   float reduce_f[32];
@@ -35,51 +37,89 @@ struct Shared {
   unsigned tie_counts[THREADS];
 };
 
-__device__ __forceinline__ unsigned long long to_fx(float p) { return (unsigned long long)((double)p * FX_ONE); }
+// p * 2^62 truncated, for 0 <= p <= 1, by integer shifts of the mantissa (the same value as the double product).
+__device__ __forceinline__ unsigned long long to_fx(float p) {
+  unsigned bits = __float_as_uint(p);
+  int exponent = (int)(bits >> 23) & 255;
+  if (exponent == 0) return 0ull;  // zero and subnormals are below 2^-62
+  unsigned long long mantissa = (unsigned long long)((bits & 0x7FFFFFu) | 0x800000u);
+  int shift = exponent - 88;       // value = mantissa * 2^(exponent - 150); times 2^62
+  return shift >= 0 ? mantissa << shift : (shift > -24 ? mantissa >> (-shift) : 0ull);
+}
 
 // Finds the boundary element of the prefix of the order (p descending, id ascending) at which the count reaches
 // `target` (FIND_COUNT), the mass reaches it (FIND_MASS_GE) or exceeds it (FIND_MASS_GT).
-__device__ void find_prefix(const float* __restrict__ p, int vocab, int kind, unsigned long long target, Shared& sh) {
+// Probabilities are not negative, so the key is their bits shifted left by one (the sign gone), taken four bits at a
+// time from the top. Every thread counts into 16 bins of its own in shared memory (hist_count[bin][thread],
+// hist_mass[bin][thread]: no atomics, no bank conflicts: most probabilities share their leading bits and would queue
+// on a handful of shared counters), then the bins are summed over the threads in two fixed stages.
+__device__ void find_prefix(const float* __restrict__ p, int vocab, int kind, unsigned long long target, Shared& sh,
+                            unsigned* __restrict__ hist_count, unsigned long long* __restrict__ hist_mass) {
   unsigned prefix = 0;
   unsigned long long above_count = 0, above_mass = 0;
   int tid = threadIdx.x;
-  for (int shift = 24; shift >= 0; shift -= 8) {
-    if (tid < 256) { sh.count[tid] = 0; sh.mass[tid] = 0; }
+  for (int shift = 28; shift >= 0; shift -= 4) {
+#pragma unroll
+    for (int bin = 0; bin < BINS; ++bin) {
+      hist_count[bin * THREADS + tid] = 0u;
+      hist_mass[bin * THREADS + tid] = 0ull;
+    }
     if (tid == 0) sh.found.ok = 0;
-    __syncthreads();
-    for (int i = tid; i < vocab; i += THREADS) {
-      unsigned bits = __float_as_uint(p[i]);
-      if (shift == 24 || (bits >> (shift + 8)) == prefix) {
-        unsigned bin = (bits >> shift) & 255u;
-        atomicAdd(&sh.count[bin], 1u);
-        atomicAdd(&sh.mass[bin], to_fx(p[i]));
+    for (int i0 = tid; i0 < vocab; i0 += 8 * THREADS) {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = i0 + u * THREADS < vocab ? p[i0 + u * THREADS] : -1.f;  // loads first
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        unsigned key = __float_as_uint(v[u]) << 1;
+        if (v[u] >= 0.f && (shift == 28 || (key >> (shift + 4)) == prefix)) {
+          unsigned bin = (key >> shift) & 15u;
+          hist_count[bin * THREADS + tid] += 1u;
+          hist_mass[bin * THREADS + tid] += to_fx(v[u]);
+        }
       }
     }
     __syncthreads();
-    // exclusive suffix sums over the bins (higher bins come first in the order)
-    if (tid < 256) { sh.scan_count[tid] = sh.count[tid]; sh.scan_mass[tid] = sh.mass[tid]; }
-    __syncthreads();
-    for (int step = 1; step < 256; step <<= 1) {
+    {  // stage 1: thread t adds 16 threads' counters of bin t / 64
+      int bin = tid / (THREADS / BINS), strip = tid % (THREADS / BINS);
       unsigned long long c = 0, m = 0;
-      if (tid < 256 && tid + step < 256) { c = sh.scan_count[tid + step]; m = sh.scan_mass[tid + step]; }
-      __syncthreads();
-      if (tid < 256) { sh.scan_count[tid] += c; sh.scan_mass[tid] += m; }
-      __syncthreads();
+#pragma unroll
+      for (int j = 0; j < BINS; ++j) {
+        c += hist_count[bin * THREADS + strip * BINS + j];
+        m += hist_mass[bin * THREADS + strip * BINS + j];
+      }
+      sh.part_count[bin][strip] = c;
+      sh.part_mass[bin][strip] = m;
     }
-    if (tid < 256 && sh.count[tid] > 0) {
-      unsigned long long ac = above_count + sh.scan_count[tid] - sh.count[tid];
-      unsigned long long am = above_mass + sh.scan_mass[tid] - sh.mass[tid];
-      bool hit;
-      if (kind == FIND_COUNT) hit = ac < target && target <= ac + sh.count[tid];
-      else if (kind == FIND_MASS_GE) hit = am < target && target <= am + sh.mass[tid];
-      else hit = am <= target && target < am + sh.mass[tid];
-      if (hit) {
-        sh.found.ok = 1;
-        sh.found.bits = (prefix << 8) | (unsigned)tid;
-        sh.found.above_count = ac;
-        sh.found.above_mass = am;
-        sh.found.tie_count = sh.count[tid];
-        sh.found.tie_mass = sh.mass[tid];
+    __syncthreads();
+    if (tid < BINS) {  // stage 2: one thread per bin adds the 64 partial sums
+      unsigned long long c = 0, m = 0;
+      for (int j = 0; j < THREADS / BINS; ++j) { c += sh.part_count[tid][j]; m += sh.part_mass[tid][j]; }
+      sh.count[tid] = c;
+      sh.mass[tid] = m;
+    }
+    __syncthreads();
+    if (tid == 0) {  // walk the bins from the top of the order
+      unsigned long long ac = above_count, am = above_mass;
+      for (int bin = BINS - 1; bin >= 0; --bin) {
+        unsigned long long c = sh.count[bin], m = sh.mass[bin];
+        if (c > 0) {
+          bool hit;
+          if (kind == FIND_COUNT) hit = ac < target && target <= ac + c;
+          else if (kind == FIND_MASS_GE) hit = am < target && target <= am + m;
+          else hit = am <= target && target < am + m;
+          if (hit) {
+            sh.found.ok = 1;
+            sh.found.bits = (prefix << 4) | (unsigned)bin;
+            sh.found.above_count = ac;
+            sh.found.above_mass = am;
+            sh.found.tie_count = c;
+            sh.found.tie_mass = m;
+            break;
+          }
+        }
+        ac += c;
+        am += m;
       }
     }
     __syncthreads();
@@ -91,6 +131,7 @@ __device__ void find_prefix(const float* __restrict__ p, int vocab, int kind, un
   }
   if (tid == 0) {
     Found& f = sh.found;
+    f.bits >>= 1;  // from the key back to the bits of the probability
     unsigned long long each = f.tie_count ? f.tie_mass / f.tie_count : 0;
     unsigned long long rank;
     if (kind == FIND_COUNT) rank = target - f.above_count;
@@ -126,6 +167,18 @@ __device__ double block_sum_d(double v, Shared& sh) {
   return total;
 }
 
+__device__ unsigned long long block_sum_u64(unsigned long long v, Shared& sh) {
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  unsigned long long* slots = reinterpret_cast<unsigned long long*>(sh.reduce_d);
+  __syncthreads();
+  if (lane == 0) slots[warp] = v;
+  __syncthreads();
+  unsigned long long total = 0;
+  for (int i = 0; i < THREADS / 32; ++i) total += slots[i];
+  return total;
+}
+
 // (value, index) maximum; ties go to the lower index
 __device__ void block_argmax(float& v, int& idx, Shared& sh) {
   for (int o = 16; o > 0; o >>= 1) {
@@ -150,6 +203,9 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(
     float* __restrict__ scratch, unsigned long long* __restrict__ rng, const int* __restrict__ rng_rows,
     float temperature, int top_k, double top_p, double min_p) {
   __shared__ Shared sh;
+  extern __shared__ __align__(16) unsigned char hist_raw[];  // hist_mass[BINS][THREADS], then hist_count[BINS][THREADS]
+  unsigned long long* hist_mass = reinterpret_cast<unsigned long long*>(hist_raw);
+  unsigned* hist_count = reinterpret_cast<unsigned*>(hist_mass + BINS * THREADS);
   int row = blockIdx.x, tid = threadIdx.x;
   pdl_launch_dependents();
   pdl_wait();
@@ -172,16 +228,27 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(
     if (z > best) { best = z; best_i = i; }
   }
   block_argmax(best, best_i, sh);
+  size_t floats = (((size_t)gridDim.x * vocab) + 1) & ~(size_t)1;  // the doubles start 8-byte aligned behind the floats
+  double* e = reinterpret_cast<double*>(scratch + floats) + (size_t)row * vocab;
   double partial = 0.0;
-  for (int i = tid; i < vocab; i += THREADS) partial += exp((double)p[i] - (double)best);
+  for (int i = tid; i < vocab; i += THREADS) {
+    double ex = exp((double)p[i] - (double)best);  // once per logit, kept in double for the division below
+    e[i] = ex;
+    partial += ex;
+  }
   double inverse = 1.0 / block_sum_d(partial, sh);
-  for (int i = tid; i < vocab; i += THREADS) p[i] = (float)(exp((double)p[i] - (double)best) * inverse);
+  unsigned long long all_mass = 0;  // this thread's share of the total mass, in fixed point (exact integer sums)
+  for (int i = tid; i < vocab; i += THREADS) {
+    float v = (float)(e[i] * inverse);
+    p[i] = v;
+    all_mass += to_fx(v);
+  }
   __syncthreads();
 
   unsigned long long keep = (unsigned long long)vocab;
   if (top_k > 0 && (unsigned long long)top_k < keep) keep = (unsigned long long)top_k;
   if (top_p < 1.0) {
-    find_prefix(p, vocab, FIND_MASS_GE, (unsigned long long)(top_p * FX_ONE), sh);
+    find_prefix(p, vocab, FIND_MASS_GE, (unsigned long long)(top_p * FX_ONE), sh, hist_count, hist_mass);
     if (sh.found.ok) {
       unsigned long long n = sh.found.above_count + sh.found.rank;
       if (n < keep) keep = n;
@@ -195,9 +262,14 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(
     unsigned long long n = (unsigned long long)block_sum_d((double)local, sh);
     if (n >= 1 && n < keep) keep = n;
   }
-  find_prefix(p, vocab, FIND_COUNT, keep, sh);
-  unsigned long long each = sh.found.tie_count ? sh.found.tie_mass / sh.found.tie_count : 0;
-  unsigned long long total = sh.found.above_mass + sh.found.rank * each;
+  unsigned long long total;
+  if (keep >= (unsigned long long)vocab) {  // everything is kept: the total is a plain sum, no search needed
+    total = block_sum_u64(all_mass, sh);
+  } else {
+    find_prefix(p, vocab, FIND_COUNT, keep, sh, hist_count, hist_mass);
+    unsigned long long each = sh.found.tie_count ? sh.found.tie_mass / sh.found.tie_count : 0;
+    total = sh.found.above_mass + sh.found.rank * each;
+  }
   __syncthreads();
   unsigned long long* state = rng + (size_t)rng_rows[row] * 4;
   double u;
@@ -212,7 +284,7 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(
   unsigned long long target = (unsigned long long)(u * (double)total);
   if (total > 0 && target >= total) target = total - 1;
   __syncthreads();
-  find_prefix(p, vocab, FIND_MASS_GT, target, sh);
+  find_prefix(p, vocab, FIND_MASS_GT, target, sh, hist_count, hist_mass);
   unsigned want_bits;
   unsigned long long want_rank;
   if (sh.found.ok) {
@@ -223,7 +295,7 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(
     if (position > keep) want_rank = keep > sh.found.above_count ? keep - sh.found.above_count : 1;
   } else {  // nothing exceeds the target (all mass is zero): the reference takes the last kept candidate
     __syncthreads();
-    find_prefix(p, vocab, FIND_COUNT, keep, sh);
+    find_prefix(p, vocab, FIND_COUNT, keep, sh, hist_count, hist_mass);
     want_bits = sh.found.bits;
     want_rank = sh.found.rank;
   }
@@ -271,7 +343,8 @@ __global__ void seed_kernel(unsigned long long* rng, const int* rows, const unsi
 }
 }  // namespace
 
-// Chooses one token per row of logits[rows, vocab] (row stride given). `scratch` holds rows * vocab floats.
+// Chooses one token per row of logits[rows, vocab] (row stride given). `scratch` holds 3 * rows * vocab + 2 floats
+// (8-byte aligned): the probabilities, then the exponentials as doubles.
 // `rng` holds 4 words of state per sequence; row r uses and advances rng[rng_rows[r]].
 DLLM_EXPORT int dllm_sample(int* out_tokens, const float* logits, long long row_stride, int rows, int vocab,
                             float* scratch, unsigned long long* rng, const int* rng_rows, float temperature,
@@ -279,8 +352,15 @@ DLLM_EXPORT int dllm_sample(int* out_tokens, const float* logits, long long row_
   if (rows <= 0) return DLLM_OK;
   if (vocab <= 0 || temperature < 0.f || !(top_p > 0.0) || min_p < 0.0 || top_k < 0) return DLLM_BAD_ARGUMENT;
   if (temperature > 0.f && (scratch == nullptr || rng == nullptr || rng_rows == nullptr)) return DLLM_BAD_ARGUMENT;
-  return dllm_launch_pdl(sample_kernel, dim3(rows), dim3(THREADS), 0, stream, out_tokens, logits, row_stride, vocab,
-                         scratch, rng, rng_rows, temperature, top_k, top_p, min_p);
+  size_t smem = temperature > 0.f ? (size_t)BINS * THREADS * (sizeof(unsigned long long) + sizeof(unsigned)) : 0;
+  static bool configured = false;
+  if (smem && !configured) {
+    if (cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return DLLM_LAUNCH_FAILED;
+    configured = true;
+  }
+  return dllm_launch_pdl(sample_kernel, dim3(rows), dim3(THREADS), smem, stream, out_tokens, logits, row_stride,
+                         vocab, scratch, rng, rng_rows, temperature, top_k, top_p, min_p);
 }
 
 // rng[rows[i]] = xoshiro256** state from SplitMix64(seeds[i]).

@@ -301,6 +301,11 @@ def add_residual(residual: torch.Tensor, update: torch.Tensor) -> None:
                                                    _code(update.dtype), _stream()), "add_residual")
 
 
+def sample_scratch(rows: int, vocab: int) -> int:
+    """Floats of scratch that temperature sampling needs: a float and a double per logit."""
+    return 3 * rows * vocab + 2
+
+
 def sample(out_tokens: torch.Tensor, logits: torch.Tensor, scratch: torch.Tensor | None, rng: torch.Tensor | None,
            rng_rows: torch.Tensor | None, temperature: float, top_k: int = 0, top_p: float = 1.0,
            min_p: float = 0.0) -> None:
@@ -309,7 +314,8 @@ def sample(out_tokens: torch.Tensor, logits: torch.Tensor, scratch: torch.Tensor
     rows, vocab = logits.shape
     assert logits.dtype == torch.float32 and out_tokens.dtype == torch.int32 and out_tokens.numel() >= rows
     if temperature > 0:
-        assert scratch is not None and scratch.dtype == torch.float32 and scratch.numel() >= rows * vocab
+        assert scratch is not None and scratch.dtype == torch.float32 and scratch.numel() >= sample_scratch(rows, vocab)
+        assert scratch.data_ptr() % 8 == 0
         assert rng is not None and rng.dtype == torch.int64 and rng_rows.dtype == torch.int32
     _check(_fn("sampling", "dllm_sample")(
         out_tokens.data_ptr(), logits.data_ptr(), logits.stride(0), rows, vocab,

@@ -28,7 +28,7 @@ class Sampler:
             out = torch.empty(rows, dtype=torch.int32, device=self.device)
         scratch = None
         if options.temperature > 0:
-            need = rows * logits.shape[1]
+            need = ops.sample_scratch(rows, logits.shape[1])
             if self._scratch is None or self._scratch.numel() < need:
                 self._scratch = torch.empty(need, dtype=torch.float32, device=self.device)
             scratch = self._scratch

@@ -178,3 +178,7 @@ def attention_decode_cluster_supported(cache):
 
 def streams(rows, outputs):
     return rows <= 16 or (rows <= 64 and outputs <= 4096)
+
+
+def sample_scratch(rows, vocab):
+    return 3 * rows * vocab + 2

@@ -212,7 +212,7 @@ def _sample_both(logits, options, seeds):
     stream_rows = torch.arange(rows, dtype=torch.int32, device=DEV) + 2
     wrapped = torch.tensor([((s % 2**64) + 2**63) % 2**64 - 2**63 for s in seeds], dtype=torch.int64, device=DEV)
     ops().seed_rng(rng, stream_rows, wrapped)
-    scratch = torch.empty(rows * logits.shape[1], dtype=torch.float32, device=DEV)
+    scratch = torch.empty(ops().sample_scratch(rows, logits.shape[1]), dtype=torch.float32, device=DEV)
     got, want = [], []
     randoms = [P.Random(s) for s in seeds]
     for _ in range(3):
