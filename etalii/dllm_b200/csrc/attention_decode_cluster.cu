@@ -1,10 +1,11 @@
 // Decode attention (one new token per sequence, bfloat16 cache) with the split over the keys held inside a
-// thread-block cluster: the eight blocks of a cluster serve one (sequence, kv head); each of a block's four warps
-// takes pages of 64 keys (tile t of the sequence goes to block (t / 4) % 8, warp t % 4), computes scores and
-// output on the tensor cores (mma.sync m16n8k16; the 16 rows are the query heads of the kv group) with a running
-// maximum and sum over its pages. The warps meet in shared memory, the blocks through distributed shared memory
-// (mapa + ld.shared::cluster between two cluster barriers): no scratch in global memory, no atomics, and a launch
-// shape (blocks per pair, kv heads, sequences) that does not depend on the context length. head_dim: a multiple of 16 up to 128.
+// thread-block cluster: the 1, 2, 4 or 8 blocks of a cluster serve one (sequence, kv head); each warp of a block
+// takes pages of 64 keys (tile t of the sequence goes to block (t / WARPS) % CLUSTER, warp t % WARPS), computes
+// scores and output on the tensor cores (mma.sync m16n8k16; the 16 rows are the query heads of the kv group) with a
+// running maximum and sum over its pages. The warps meet in shared memory, the blocks through distributed shared
+// memory (mapa + ld.shared::cluster between two cluster barriers): no scratch in global memory, no atomics, and a
+// launch shape (blocks per pair, kv heads, sequences) that does not depend on the context length; the number of
+// blocks per pair follows from how many pairs there are. head_dim: a multiple of 16 up to 128.
 #include "common.cuh"
 
 namespace {
@@ -49,8 +50,7 @@ __device__ __forceinline__ float remote_float(const float* local, unsigned rank)
 }
 
 // CLUSTER blocks of WARPS warps serve one (sequence, kv head). Few (sequence, kv head) pairs: many blocks per pair
-// (8 x 4 warps) to fill the device and shorten every chain of pages; many pairs: one block of 8 warps per pair,
-// no exchange between blocks at all.
+// to fill the device and shorten every chain of pages; many pairs: one block per pair, no exchange between blocks.
 template <int HD, int CLUSTER, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32) decode_attention_cluster_kernel(
     bf16* __restrict__ out, const bf16* __restrict__ q, KvLayout cache, const int* __restrict__ tok_pos,
@@ -135,9 +135,10 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attention_cluster_kernel(
         q_frag[ks][3] = (gq + 8 < nh && col + 8 < hd) ? *reinterpret_cast<const unsigned*>(q_hi + col + 8) : 0u;
       }
     }
+    // (the very first page is already on its way; a later pass over the heads starts again at the first page)
+    int page = page0;
+    if (h0 != 0 && my_first < end) page = copy_page(my_first);
     for (int key0 = my_first; key0 < end; key0 += ROUND) {
-      int page = page0;
-      if (key0 != my_first || h0 != 0) page = copy_page(key0);  // (the very first page is already on its way)
       asm volatile("cp.async.wait_group 0;\n" ::);
       __syncwarp();
       if (newest >= key0 && newest < key0 + TILE_KEYS) {  // the row the projection kernel has just written
@@ -220,6 +221,7 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attention_cluster_kernel(
         }
       }
       __syncwarp();  // the page's space is free for the next copy
+      if (key0 + ROUND < end) page = copy_page(key0 + ROUND);
     }
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
@@ -275,16 +277,21 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attention_cluster_kernel(
   }
 }
 
+template <int HD, int WARPS>
+constexpr size_t block_smem() {
+  size_t kv_bytes = (size_t)WARPS * 2 * TILE_KEYS * (HD + 8) * sizeof(bf16);
+  size_t red_bytes = (size_t)(WARPS + 1) * 16 * HD * sizeof(float);
+  return kv_bytes > red_bytes ? kv_bytes : red_bytes;
+}
+
 template <int HD, int CLUSTER, int WARPS>
 int launch(void* out, const void* q, const KvLayout& cache, const int* tok_pos, const int* slots, int heads,
            int sequences, float scale, int window, cudaStream_t stream) {
-  size_t kv_bytes = (size_t)WARPS * 2 * TILE_KEYS * (HD + 8) * sizeof(bf16);
-  size_t red_bytes = (size_t)(WARPS + 1) * 16 * HD * sizeof(float);
-  size_t smem = kv_bytes > red_bytes ? kv_bytes : red_bytes;
+  constexpr size_t smem = block_smem<HD, WARPS>();
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(decode_attention_cluster_kernel<HD, CLUSTER, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)smem) != cudaSuccess)
+    if (cudaFuncSetAttribute(decode_attention_cluster_kernel<HD, CLUSTER, WARPS>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       return DLLM_LAUNCH_FAILED;
     configured = true;
   }
@@ -302,30 +309,66 @@ int launch(void* out, const void* q, const KvLayout& cache, const int* tok_pos, 
   attributes[1].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attributes;
   config.numAttrs = dllm_pdl_enabled() ? 2 : 1;
-  return cudaLaunchKernelEx(&config, decode_attention_cluster_kernel<HD, CLUSTER, WARPS>, (bf16*)out, (const bf16*)q, cache, tok_pos,
-                            slots, heads, scale * 1.4426950408889634f, window) == cudaSuccess
+  return cudaLaunchKernelEx(&config, decode_attention_cluster_kernel<HD, CLUSTER, WARPS>, (bf16*)out, (const bf16*)q,
+                            cache, tok_pos, slots, heads, scale * 1.4426950408889634f, window) == cudaSuccess
              ? DLLM_OK
              : DLLM_LAUNCH_FAILED;
+}
+
+// What bounds this kernel is how many pages are on their way into shared memory at once: blocks are kept small
+// (4 warps, 2 where a page of head_dim above 64 is twice as large) so that three of them share a multiprocessor,
+// and the number of blocks per (sequence, kv head) pair is the smallest power of two that fills those places.
+// Launch shapes 0..3: 1, 2, 4, 8 blocks per pair; shape 4: 8 blocks of 4 warps at any head_dim (for very few pairs,
+// where every block has a multiprocessor of its own anyway).
+constexpr int SHAPES = 5;
+constexpr size_t SMEM_PER_SM = 227 * 1024;
+
+template <int HD>
+int launch_shape(int shape, void* out, const void* q, const KvLayout& cache, const int* tok_pos, const int* slots,
+                 int heads, int sequences, float scale, int window, cudaStream_t stream) {
+  constexpr int NW = HD > 64 ? 2 : 4;
+  if (shape < 0) {
+    static int sms = 0;
+    if (sms == 0) {
+      int device = 0;
+      if (cudaGetDevice(&device) != cudaSuccess ||
+          cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0)
+        sms = 148;
+    }
+    long long pairs = (long long)sequences * cache.kv_heads;
+    size_t per_sm = SMEM_PER_SM / (block_smem<HD, NW>() + 1024);
+    long long places = (long long)sms * (long long)(per_sm > 8 ? 8 : per_sm);
+    if (pairs * 8 <= sms) shape = 4;
+    else for (shape = 0; shape < 3 && (pairs << shape) * 20 < places * 17; ++shape) {}
+  }
+#define DLLM_GO(CL, WARPS) \
+  return launch<HD, CL, WARPS>(out, q, cache, tok_pos, slots, heads, sequences, scale, window, stream)
+  switch (shape) {
+    case 0: DLLM_GO(1, NW);
+    case 1: DLLM_GO(2, NW);
+    case 2: DLLM_GO(4, NW);
+    case 3: DLLM_GO(8, NW);
+    case 4: DLLM_GO(8, 4);
+  }
+#undef DLLM_GO
+  return DLLM_BAD_ARGUMENT;
 }
 }  // namespace
 
 // out, q: [sequences, heads * head_dim] bfloat16; sequence b's query is the token at tok_pos[b], whose key and value
 // are already in the cache. head_dim a multiple of 16 up to 128, pages of 64 positions, at most 65,535 sequences.
+// shape: -1 chooses by the number of (sequence, kv head) pairs; 0..4 name a launch shape (see above).
 DLLM_EXPORT int dllm_attention_decode_cluster(void* out, const void* q, void* cache_base, const int* page_table,
                                               int max_pages, int page_size, int heads, int kv_heads, int head_dim,
                                               const int* tok_pos, const int* slots, int sequences, float scale,
-                                              int window, cudaStream_t stream) {
+                                              int window, int shape, cudaStream_t stream) {
   if (sequences <= 0) return DLLM_OK;
-  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads) return DLLM_BAD_ARGUMENT;
+  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || shape < -1 || shape >= SHAPES) return DLLM_BAD_ARGUMENT;
   if (head_dim <= 0 || head_dim > 128 || (head_dim & 15) || page_size != TILE_KEYS || sequences > 65535 ||
       kv_heads > 65535)
     return DLLM_UNSUPPORTED_SIZE;
   KvLayout cache{cache_base, page_table, max_pages, page_size, kv_heads, head_dim};
-  bool many = (long long)sequences * kv_heads >= 128;  // enough pairs to fill the device without splitting the keys
-#define DLLM_GO(HD, CL, NW) \
-  return launch<HD, CL, NW>(out, q, cache, tok_pos, slots, heads, sequences, scale, window, stream)
-  if (head_dim <= 32) { if (many) DLLM_GO(32, 1, 8); else DLLM_GO(32, 8, 4); }
-  if (head_dim <= 64) { if (many) DLLM_GO(64, 1, 8); else DLLM_GO(64, 8, 4); }
-  if (many) DLLM_GO(128, 1, 4); else DLLM_GO(128, 8, 4);
-#undef DLLM_GO
+  if (head_dim <= 32) return launch_shape<32>(shape, out, q, cache, tok_pos, slots, heads, sequences, scale, window, stream);
+  if (head_dim <= 64) return launch_shape<64>(shape, out, q, cache, tok_pos, slots, heads, sequences, scale, window, stream);
+  return launch_shape<128>(shape, out, q, cache, tok_pos, slots, heads, sequences, scale, window, stream);
 }

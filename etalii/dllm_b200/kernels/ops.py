@@ -48,7 +48,7 @@ _prototypes = {
                                                     c_void_p, c_void_p, c_void_p],
     ("attention_decode_cluster", "dllm_attention_decode_cluster"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                                                     c_int, c_int, c_int, c_int, c_void_p, c_void_p,
-                                                                    c_int, c_float, c_int, c_void_p],
+                                                                    c_int, c_float, c_int, c_int, c_void_p],
     ("attention_prefill", "dllm_attention_prefill"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                                       c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                       c_int, c_float, c_int, c_void_p],
@@ -389,16 +389,22 @@ def attention_decode_cluster_supported(cache) -> bool:
         and cache.page_size == 64
 
 
+DECODE_CLUSTER_SHAPES = 5
+"""Launch shapes of the cluster decode kernel: 0 eight blocks of four warps per (sequence, kv head); 1 one block of
+eight warps; 2 one block of four warps with two page buffers each; 3 two blocks of four warps with two buffers."""
+
+
 def attention_decode_cluster(out: torch.Tensor, q: torch.Tensor, cache, heads: int, scale: float, window: int,
-                             batch) -> None:
+                             batch, shape: int = -1) -> None:
     """Attention for a batch in which every sequence brings one token (bfloat16, head_dim a multiple of 16 up to
-    128): a cluster of eight blocks per (sequence, kv head) splits the keys and combines through distributed shared
-    memory; no scratch, and a launch shape that does not depend on the context length."""
+    128): the blocks of a cluster split the keys of a (sequence, kv head) pair and combine through distributed
+    shared memory; no scratch, and a launch shape that does not depend on the context length. shape -1 lets the
+    kernel choose by the number of pairs; 0..3 name one of DECODE_CLUSTER_SHAPES."""
     _cuda(out, q)
     assert attention_decode_cluster_supported(cache) and q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
     assert batch.n_tokens == batch.n_seqs
     _check(_fn("attention_decode_cluster", "dllm_attention_decode_cluster")(
         out.data_ptr(), q.data_ptr(), cache.base_ptr, cache.page_table.data_ptr(), cache.max_pages, cache.page_size,
         heads, cache.kv_heads, cache.head_dim, batch.tok_pos.data_ptr(), batch.slots.data_ptr(), batch.n_seqs,
-        float(scale), int(window or 0), _stream()), "attention_decode_cluster",
+        float(scale), int(window or 0), int(shape), _stream()), "attention_decode_cluster",
         f"head_dim={cache.head_dim} must be a multiple of 16, at most 128; pages of 64")

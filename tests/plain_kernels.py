@@ -168,7 +168,10 @@ def gemm_qkv_rope_supported(cache, rotary_dim, has_table):
     return False
 
 
-def attention_decode_cluster(out, q, cache, heads, scale, window, batch):
+DECODE_CLUSTER_SHAPES = 5
+
+
+def attention_decode_cluster(out, q, cache, heads, scale, window, batch, shape=-1):
     attention_general(out, q, cache, heads, scale, window, batch)
 
 

@@ -475,15 +475,17 @@ def test_attention_decode_cluster(heads, kv_heads, head_dim, window, lengths):
     n = batch.n_tokens
     q = _randn((n, heads * head_dim), torch.bfloat16, 9)
     out = torch.zeros((n, heads * head_dim), dtype=torch.bfloat16, device=DEV)
-    ops().attention_decode_cluster(out, q, view, heads, 0.3, window or 0, batch)
     general = torch.zeros_like(out)
     ops().attention_general(general, q, view, heads, 0.3, window or 0, batch)  # itself checked against the plain one
-    assert rel_error(out.float().cpu(), general.float().cpu()) <= 8e-3
-    worst = (out.float() - general.float()).abs().max(dim=1).values
-    assert float(worst.max()) <= 8e-3 * float(general.float().abs().max()), int(worst.argmax())
-    again = torch.zeros_like(out)
-    ops().attention_decode_cluster(again, q, view, heads, 0.3, window or 0, batch)
-    assert torch.equal(again, out)
+    for shape in range(-1, ops().DECODE_CLUSTER_SHAPES):  # the kernel's own choice, then every launch shape by name
+        out.zero_()
+        ops().attention_decode_cluster(out, q, view, heads, 0.3, window or 0, batch, shape)
+        assert rel_error(out.float().cpu(), general.float().cpu()) <= 8e-3, shape
+        worst = (out.float() - general.float()).abs().max(dim=1).values
+        assert float(worst.max()) <= 8e-3 * float(general.float().abs().max()), (shape, int(worst.argmax()))
+        again = torch.zeros_like(out)
+        ops().attention_decode_cluster(again, q, view, heads, 0.3, window or 0, batch, shape)
+        assert torch.equal(again, out), shape
 
 
 def test_attention_decode_cluster_finds_a_far_key():
@@ -497,7 +499,8 @@ def test_attention_decode_cluster_finds_a_far_key():
         view.storage[page, 0, :, target % 64, :] = 4.0
         view.storage[page, 1, :, target % 64, :] = 7.0
         q = torch.full((1, heads * hd), 4.0, dtype=torch.bfloat16, device=DEV)
-        out = torch.zeros_like(q)
-        ops().attention_decode_cluster(out, q, view, heads, 1.0, 0, batch)
-        assert torch.allclose(out.float(), torch.full_like(out, 7.0).float(), atol=0.05), target
+        for shape in range(-1, ops().DECODE_CLUSTER_SHAPES):
+            out = torch.zeros_like(q)
+            ops().attention_decode_cluster(out, q, view, heads, 1.0, 0, batch, shape)
+            assert torch.allclose(out.float(), torch.full_like(out, 7.0).float(), atol=0.05), (target, shape)
         view.storage[page] = saved
