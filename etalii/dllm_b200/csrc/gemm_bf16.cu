@@ -1,6 +1,6 @@
 // bfloat16 matrix product with float32 accumulation on the tensor cores (mma.sync m16n8k16, cp.async 3-stage
 // pipeline), for any M, ending in the shared epilogues (store, residual add in float32, SwiGLU). K must be a
-// multiple of 8 (16-byte rows) and N even; anything else is refused. (Decode-sized products run in gemv.cu.)
+// multiple of 8 (16-byte rows), and N even for the SwiGLU epilogue; anything else is refused. (Decode-sized products run in gemv.cu.)
 #include "gemm_common.cuh"
 
 namespace {
@@ -128,7 +128,7 @@ int launch_mma(void* c, const bf16* a, const bf16* w, int M, int N, int K, cudaS
 DLLM_EXPORT int dllm_gemm_bf16(void* c, const void* a, const void* w, int M, int N, int K, int epilogue,
                                cudaStream_t stream) {
   if (M <= 0 || N <= 0) return DLLM_OK;
-  if (K <= 0 || (K & 7) || (N & 1)) return DLLM_UNSUPPORTED_SIZE;
+  if (K <= 0 || (K & 7) || ((N & 1) && epilogue == EPI_SWIGLU)) return DLLM_UNSUPPORTED_SIZE;
   const bf16 *ap = (const bf16*)a, *wp = (const bf16*)w;
   switch (epilogue) {
     case EPI_STORE_F32: return launch_mma<EPI_STORE_F32>(c, ap, wp, M, N, K, stream);

@@ -49,11 +49,11 @@ __global__ void __launch_bounds__(THREADS) gemm_f32_kernel(void* __restrict__ c,
 }
 }  // namespace
 
-// C = A[M,K] * W[N,K]^T in float32; K a multiple of 4 and N even (16-byte rows, column pairs).
+// C = A[M,K] * W[N,K]^T in float32; K a multiple of 4 (16-byte rows); N even for the SwiGLU epilogue (column pairs).
 DLLM_EXPORT int dllm_gemm_f32(void* c, const float* a, const float* w, int M, int N, int K, int epilogue,
                               cudaStream_t stream) {
   if (M <= 0 || N <= 0) return DLLM_OK;
-  if (K <= 0 || (K & 3) || (N & 1)) return DLLM_UNSUPPORTED_SIZE;
+  if (K <= 0 || (K & 3) || ((N & 1) && epilogue == EPI_SWIGLU)) return DLLM_UNSUPPORTED_SIZE;
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   if (grid.y > 65535) return DLLM_UNSUPPORTED_SIZE;
   switch (epilogue) {

@@ -11,76 +11,14 @@
 // Rows of A beyond M and columns of K beyond the matrix are zero-filled by TMA; rows of W beyond N give columns
 // that are never stored. No multicast, no clusters. Every wait on an mbarrier is bounded: after the limit the role
 // records a status word and leaves, the block still frees its tensor memory, and the host raises.
-#include <cuda.h>
-
 #include "gemm_common.cuh"
+#include "tcgen05.cuh"
 
 namespace {
+using namespace tc5;
 typedef __nv_bfloat16 bf16;
 constexpr int BM = 128, BK = 64, UMMA_K = 16;
 constexpr int THREADS = 192;
-constexpr long long WAIT_LIMIT_CYCLES = 2000000000ll;  // about a second
-
-__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-// Bounded wait: false if the phase did not complete within the limit.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity) {
-  unsigned addr = smem_u32(bar);
-  long long begin = clock64();
-  for (unsigned i = 0;; ++i) {
-    unsigned done;
-    asm volatile(
-        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-    if (done) return true;
-    if (clock64() - begin > WAIT_LIMIT_CYCLES) return false;  // try_wait itself pauses between looks
-  }
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void tcgen05_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-               : "memory");
-}
-// Shared-memory matrix descriptor of a K-major tile with 128-byte rows and 128-byte swizzle: start address / 16,
-// stride between 8-row groups 1024 bytes, descriptor version 1, swizzle mode 2 (128 bytes).
-__device__ __forceinline__ uint64_t smem_desc(unsigned addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((addr & 0x3FFFF) >> 4);
-  d |= (uint64_t)1 << 16;                 // leading byte offset (unused for swizzled K-major), 16 bytes
-  d |= (uint64_t)(1024 >> 4) << 32;       // stride byte offset
-  d |= (uint64_t)1 << 46;                 // descriptor version
-  d |= (uint64_t)2 << 61;                 // 128-byte swizzle
-  return d;
-}
-// Instruction descriptor, kind::f16: D float32, A and B bfloat16, both K-major, N / 8 at bit 17, M / 16 at bit 24.
-__host__ __device__ constexpr unsigned instr_desc(int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(BM >> 4) << 24);
-}
-__device__ __forceinline__ void umma(unsigned tmem_d, uint64_t adesc, uint64_t bdesc, unsigned idesc, unsigned acc) {
-  asm volatile(
-      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-      " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc) : "memory");
-}
-__device__ __forceinline__ void tmem_load16(unsigned taddr, unsigned* v) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-      : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
 
 template <int BN> struct Shape {
   static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
@@ -92,10 +30,6 @@ template <int BN> struct Shape {
   static constexpr size_t SMEM = (size_t)STAGES * (A_BYTES + B_BYTES) + 1024;
   static constexpr int BLOCKS_PER_SM = BN >= 256 ? 1 : 2;
 };
-
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
 
 // A persistent block: it takes tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... of the m_tiles x n_tiles grid
 // (neighbouring blocks share a tile of W and read different rows of A). The producer's ring of stages runs on across
@@ -122,9 +56,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                 ::"r"(smem_u32(&tmem_base_s)), "r"((unsigned)S::TMEM_COLS) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    tmem_alloc(&tmem_base_s, (unsigned)S::TMEM_COLS);
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -155,7 +87,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr unsigned idesc = instr_desc(BN);
+      constexpr unsigned idesc = instr_desc(BM, BN);
       int it = 0, lt = 0;  // k tiles consumed, tiles started
       bool ok = true;
       for (int t = blockIdx.x; t < total && ok; t += gridDim.x, ++lt) {
@@ -260,39 +192,8 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 1) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((unsigned)S::TMEM_COLS)
-                 : "memory");
+    tmem_dealloc(tmem_base, (unsigned)S::TMEM_COLS);
   }
-}
-
-// ---- host side: tensor maps through the driver entry point (no link against libcuda) ---------------------------
-typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiled encoder() {
-  static EncodeTiled fn = nullptr;
-  if (fn == nullptr) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult result;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &result) == cudaSuccess &&
-        result == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiled)p;
-  }
-  return fn;
-}
-
-// A [rows, cols] bfloat16 row-major matrix, boxes of box_rows x 64 columns, 128-byte swizzle, zero fill outside.
-bool make_map(CUtensorMap* map, const void* base, int rows, int cols, int box_rows) {
-  EncodeTiled encode = encoder();
-  if (encode == nullptr) return false;
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-  cuuint32_t elem[2] = {1, 1};
-  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 template <int BN, int EPI>
@@ -338,13 +239,13 @@ int dispatch(void* c, const void* a, const void* w, int M, int N, int K, int epi
 }  // namespace
 
 // C = A[M,K] * W[N,K]^T (bfloat16, float32 accumulation in tensor memory). K must be a multiple of 8 (16-byte row
-// pitch for TMA), N even, and A and W 16-byte aligned. `tile_n`: 32, 64 or 128 columns of C per block (0 chooses).
+// pitch for TMA), N even for the SwiGLU epilogue, and A and W 16-byte aligned. `tile_n`: 32, 64 or 128 columns of C per block (0 chooses).
 // `status` is a word the device can write (device or pinned host memory); the kernel sets it non-zero if one of its
 // bounded waits ran out (2: producer, 3: product issuer, 4: epilogue).
 DLLM_EXPORT int dllm_gemm_tcgen05(void* c, const void* a, const void* w, int M, int N, int K, int epilogue, int tile_n,
                                   int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return DLLM_OK;
-  if (K <= 0 || (K & 7) || (N & 1) || ((uintptr_t)a & 15) || ((uintptr_t)w & 15) || status == nullptr)
+  if (K <= 0 || (K & 7) || ((N & 1) && epilogue == EPI_SWIGLU) || ((uintptr_t)a & 15) || ((uintptr_t)w & 15) || status == nullptr)
     return DLLM_UNSUPPORTED_SIZE;
   if (tile_n == 0) {
     long long tiles256 = (long long)((M + BM - 1) / BM) * ((N + 255) / 256);

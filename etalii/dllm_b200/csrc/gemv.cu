@@ -357,13 +357,13 @@ int dispatch(void* c, const void* a, const float* norm_w, float eps, const bf16*
 }  // namespace
 
 // C = X[M,K] * W[N,K]^T for M <= 64. With norm_w != null, X is the float32 residual stream and is RMS-normed on
-// the way in; else X is bfloat16. Epilogues 0..3 as the tile kernels; K a multiple of 8, N even.
+// the way in; else X is bfloat16. Epilogues 0..3 as the tile kernels; K a multiple of 8, N even for SwiGLU.
 // prefetch_ptr / prefetch_bytes: optional memory (weights a later kernel reads) to bring into L2 meanwhile.
 DLLM_EXPORT int dllm_gemv_bf16(void* c, const void* a, const float* norm_w, float eps, const void* w, int M, int N,
                                int K, int epilogue, const void* prefetch_ptr, long long prefetch_bytes,
                                cudaStream_t stream) {
   if (M <= 0 || N <= 0) return DLLM_OK;
-  if (M > 64 || K <= 0 || (K & 7) || (N & 1) || epilogue < 0 || epilogue > EPI_SWIGLU) return DLLM_UNSUPPORTED_SIZE;
+  if (M > 64 || K <= 0 || (K & 7) || ((N & 1) && epilogue == EPI_SWIGLU) || epilogue < 0 || epilogue > EPI_SWIGLU) return DLLM_UNSUPPORTED_SIZE;
   RopeArgs rope{};
   Prefetch pf{(const char*)prefetch_ptr, prefetch_ptr ? (size_t)prefetch_bytes : 0};
   return norm_w ? dispatch<true>(c, a, norm_w, eps, (const bf16*)w, M, N, K, epilogue, rope, pf, stream)

@@ -30,6 +30,7 @@ SOURCES = {
     "attention_decode": "attention_decode.cu",
     "attention_decode_cluster": "attention_decode_cluster.cu",
     "attention_prefill": "attention_prefill.cu",
+    "attention_prefill_tcgen05": "attention_prefill_tcgen05.cu",
     "attention_decode_static": "attention_decode_static.cu",
     "sampling": "sampling.cu",
 }

@@ -52,6 +52,9 @@ _prototypes = {
     ("attention_prefill", "dllm_attention_prefill"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                                       c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                       c_int, c_float, c_int, c_void_p],
+    ("attention_prefill_tcgen05", "dllm_attention_prefill_tcgen05"): [
+        c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
+        c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_int, c_void_p, c_void_p],
     ("sampling", "dllm_sample"): [c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                   c_float, c_int, c_double, c_double, c_void_p],
     ("sampling", "dllm_seed_rng"): [c_void_p, c_void_p, c_void_p, c_int, c_void_p],
@@ -184,7 +187,7 @@ def gemm(c: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int = EPI_
     want_cols = n // 2 if epilogue == EPI_SWIGLU else n
     want_dtype = torch.float32 if epilogue in (EPI_STORE_F32, EPI_RESIDUAL) else w.dtype
     assert tuple(c.shape) == (m, want_cols) and c.dtype == want_dtype, (c.shape, c.dtype, m, want_cols, want_dtype)
-    detail = f"M={m} N={n} K={k}: K must be a multiple of {4 if w.dtype == torch.float32 else 8}, N even"
+    detail = f"M={m} N={n} K={k}: K must be a multiple of {4 if w.dtype == torch.float32 else 8}; N even for the SwiGLU epilogue"
     if w.dtype == torch.float32:
         assert a.dtype == torch.float32 and norm_weight is None
         status = _fn("gemm_simt", "dllm_gemm_f32")(c.data_ptr(), a.data_ptr(), w.data_ptr(), m, n, k, epilogue,
@@ -384,14 +387,33 @@ def attention_prefill(out: torch.Tensor, q: torch.Tensor, cache, heads: int, sca
         f"head_dim={cache.head_dim} must be a multiple of 16, at most 128; pages of 64")
 
 
+def attention_prefill_tcgen05_supported(cache) -> bool:
+    return cache.dtype == torch.bfloat16 and cache.head_dim == 64 and cache.page_size == 64
+
+
+def attention_prefill_tcgen05(out: torch.Tensor, q: torch.Tensor, cache, heads: int, scale: float, window: int,
+                              batch) -> None:
+    """Blockwise causal attention of the batch's new tokens over their sequences' caches on the 5th-generation
+    tensor cores (bfloat16, head_dim 64, pages of 64 positions): tiles of 128 queries, scores and outputs in tensor
+    memory, pages of keys and values by TMA."""
+    _cuda(out, q)
+    assert attention_prefill_tcgen05_supported(cache) and q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+    _check(_fn("attention_prefill_tcgen05", "dllm_attention_prefill_tcgen05")(
+        out.data_ptr(), q.data_ptr(), q.shape[0], cache.base_ptr, cache.storage.shape[0],
+        cache.page_table.data_ptr(), cache.max_pages, cache.page_size, heads, cache.kv_heads, cache.head_dim,
+        batch.tile_seq.data_ptr(), batch.tile_first.data_ptr(), batch.cu_seqlens.data_ptr(), batch.start.data_ptr(),
+        batch.slots.data_ptr(), batch.n_tiles, float(scale), int(window or 0), _status_word().data_ptr(),
+        _stream()), "attention_prefill_tcgen05", f"head_dim={cache.head_dim} must be 64; pages of 64")
+
+
 def attention_decode_cluster_supported(cache) -> bool:
     return cache.dtype == torch.bfloat16 and cache.head_dim % 16 == 0 and cache.head_dim <= 128 \
         and cache.page_size == 64
 
 
 DECODE_CLUSTER_SHAPES = 5
-"""Launch shapes of the cluster decode kernel: 0 eight blocks of four warps per (sequence, kv head); 1 one block of
-eight warps; 2 one block of four warps with two page buffers each; 3 two blocks of four warps with two buffers."""
+"""Launch shapes of the cluster decode kernel: 0..3 are 1, 2, 4, 8 blocks per (sequence, kv head) pair, of four warps
+(two when head_dim is above 64); 4 is eight blocks of four warps at any head_dim."""
 
 
 def attention_decode_cluster(out: torch.Tensor, q: torch.Tensor, cache, heads: int, scale: float, window: int,
@@ -399,7 +421,7 @@ def attention_decode_cluster(out: torch.Tensor, q: torch.Tensor, cache, heads: i
     """Attention for a batch in which every sequence brings one token (bfloat16, head_dim a multiple of 16 up to
     128): the blocks of a cluster split the keys of a (sequence, kv head) pair and combine through distributed
     shared memory; no scratch, and a launch shape that does not depend on the context length. shape -1 lets the
-    kernel choose by the number of pairs; 0..3 name one of DECODE_CLUSTER_SHAPES."""
+    kernel choose by the number of pairs; 0..4 name one of DECODE_CLUSTER_SHAPES."""
     _cuda(out, q)
     assert attention_decode_cluster_supported(cache) and q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
     assert batch.n_tokens == batch.n_seqs

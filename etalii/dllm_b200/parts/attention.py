@@ -86,6 +86,8 @@ class Attention:
             tickets = rt.ws.zeros("attention_tickets", batch.n_seqs * self.num_kv_heads, torch.int32)
             ops.attention_decode(attended, q, cache, self.num_heads, self.scale, self.window or 0, batch, chunk,
                                  scratch, tickets)
+        elif not batch.is_decode and ops.attention_prefill_tcgen05_supported(cache):
+            ops.attention_prefill_tcgen05(attended, q, cache, self.num_heads, self.scale, self.window or 0, batch)
         elif not batch.is_decode and ops.attention_prefill_supported(cache):
             ops.attention_prefill(attended, q, cache, self.num_heads, self.scale, self.window or 0, batch)
         else:

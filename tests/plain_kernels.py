@@ -175,6 +175,14 @@ def attention_decode_cluster(out, q, cache, heads, scale, window, batch, shape=-
     attention_general(out, q, cache, heads, scale, window, batch)
 
 
+def attention_prefill_tcgen05(out, q, cache, heads, scale, window, batch):
+    attention_general(out, q, cache, heads, scale, window, batch)
+
+
+def attention_prefill_tcgen05_supported(cache):
+    return False
+
+
 def attention_decode_cluster_supported(cache):
     return False
 

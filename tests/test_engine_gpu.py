@@ -214,12 +214,32 @@ def test_other_sizes(sizes, dtype):
 def test_sizes_the_kernels_refuse_are_clear_errors():
     from etalii.dllm_b200.kernels.ops import KernelError
 
-    config = dict(P.TINY_A, num_hidden_layers=1, vocab_size=131, tie_word_embeddings=False)  # an odd vocabulary
+    config = dict(P.TINY_A, num_hidden_layers=1, intermediate_size=100)  # rows of 100 bfloat16 are not 16-byte pieces
     weights = P.random_weights(config, seed=1)
     engine = make_engine(config, weights, "bfloat16", max_tokens=128)
     slot = engine.open(1)
-    with pytest.raises(KernelError, match="N even"):
+    with pytest.raises(KernelError, match="multiple of 8"):
         engine.step(slot, [[1, 2, 3]])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_an_odd_vocabulary(dtype):
+    config = dict(P.TINY_A, num_hidden_layers=2, vocab_size=131, tie_word_embeddings=False)
+    weights = P.random_weights(config, seed=1)
+    engine = make_engine(config, weights, dtype, max_tokens=256)
+    prompt = [5, 130, 17, 0, 99, 64, 3]
+    want = P.forward(config, weights, prompt)
+    slot = engine.open(1)
+    got = host(engine.step(slot, [prompt[:5]], [list(range(5))]))
+    assert rel_error(got, want[:5]) <= TOL[dtype]
+    for index in (5, 6):  # decode-sized products with an odd number of outputs
+        assert rel_error(host(engine.step(slot, [[prompt[index]]]))[0], want[index]) <= TOL[dtype]
+    engine.close(slot)
+    if dtype == "float32":  # the sampler over 131 logits
+        tokens = list(prompt)
+        for _ in range(4):
+            tokens.append(P.argmax(P.forward(config, weights, tokens)[-1]))
+        assert list(engine.generate([prompt], 4, ignore_eos=True)[0].tokens) == tokens[len(prompt):]
 
 
 def test_long_generation_through_the_graph_path(setup):

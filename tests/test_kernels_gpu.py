@@ -92,6 +92,36 @@ def test_gemm_bf16(m, n, k, epilogue, kernel):
     assert rel_error(c.float().cpu(), ref.float().cpu()) <= (2e-5 if epilogue in (0, 2) else 8e-3)
 
 
+ODD_SHAPES = [(5, 131, 72), (16, 61, 40), (70, 61, 40), (200, 257, 136), (64, 1001, 64)]
+
+
+@pytest.mark.parametrize("m,n,k", ODD_SHAPES)
+@pytest.mark.parametrize("epilogue", [0, 1, 2])
+@pytest.mark.parametrize("kernel", ["f32", 1, 2, 3])
+def test_gemm_with_an_odd_number_of_outputs(m, n, k, epilogue, kernel):
+    if kernel == 2 and m > 64:
+        pytest.skip("the weight-streaming kernel takes at most 64 rows")
+    dtype = torch.float32 if kernel == "f32" else torch.bfloat16
+    a, w = _randn((m, k), dtype, 3), _randn((n, k), dtype, 4, 0.2)
+    c = _randn((m, n), torch.float32 if epilogue in (0, 2) else dtype, 5)
+    ref = c.clone()
+    ops().gemm(c, a, w, epilogue, 0 if kernel == "f32" else kernel)
+    torch.cuda.synchronize()
+    ops().raise_if_failed()
+    PK.gemm(ref, a, w, epilogue)
+    tol = 2e-6 if kernel == "f32" else (2e-5 if epilogue in (0, 2) else 8e-3)
+    assert rel_error(c.float().cpu(), ref.float().cpu()) <= tol
+
+
+def test_swiglu_refuses_an_odd_number_of_rows():
+    from etalii.dllm_b200.kernels.ops import KernelError
+
+    for dtype, kernel in ((torch.float32, 0), (torch.bfloat16, 1), (torch.bfloat16, 2), (torch.bfloat16, 3)):
+        a, w = _randn((4, 64), dtype, 1), _randn((9, 64), dtype, 2)
+        with pytest.raises(KernelError, match="N even"):
+            ops().gemm(torch.empty((4, 4), dtype=dtype, device=DEV), a, w, 3, kernel)
+
+
 def test_gemm_refuses_sizes_it_cannot_run():
     from etalii.dllm_b200.kernels.ops import KernelError
 
@@ -108,8 +138,9 @@ def _cache_and_batch(dtype, kv_heads, head_dim, lengths, new, window=None, seed=
     from etalii.dllm_b200.cache.paged import CacheNeed, PagedCache
     from etalii.dllm_b200.engine.batch import BatchBuffers
 
-    cache = PagedCache([CacheNeed("kv", kv_heads, head_dim, window)], max_tokens=64 * 40, max_length=1024,
-                       dtype=dtype, device=DEV)
+    room = max(64 * 40, sum((n + 63) // 64 * 64 for n in lengths) + 128)
+    cache = PagedCache([CacheNeed("kv", kv_heads, head_dim, window)], max_tokens=room,
+                       max_length=max(1024, max(lengths)), dtype=dtype, device=DEV)
     slots = cache.acquire(len(lengths) + 1)[1:]  # slot 0 stays unused: slots are not sequence indices
     grown = [0] * len(lengths)
     while any(g < n for g, n in zip(grown, lengths)):  # grow round-robin so pages interleave
@@ -393,6 +424,76 @@ def test_attention_prefill_finds_a_far_key_and_ignores_what_lies_beyond():
         ops().attention_prefill(out, q, view, heads, 1.0, 0, batch)
         assert torch.allclose(out.float(), torch.full_like(out, 7.0).float(), atol=0.05), target
         view.storage[page] = saved
+
+
+@pytest.mark.parametrize("heads,kv_heads,window", [(9, 3, None), (4, 4, 70), (8, 1, 33), (6, 2, 200), (1, 1, None)])
+def test_attention_prefill_tcgen05(heads, kv_heads, window):
+    """Whole prompts, prompts that go on from a cached prefix, single tokens and tile edges, in one batch."""
+    head_dim = 64
+    lengths, new = [130, 200, 1, 64, 65, 300, 77, 128, 129, 390], [130, 9, 1, 64, 65, 128, 1, 128, 129, 257]
+    cache, view, batch = _cache_and_batch(torch.bfloat16, kv_heads, head_dim, lengths, new, window)
+    n = batch.n_tokens
+    q = _randn((n, heads * head_dim), torch.bfloat16, 9)
+    out = torch.zeros((n, heads * head_dim), dtype=torch.bfloat16, device=DEV)
+    ref = torch.zeros((n, heads * head_dim), dtype=torch.bfloat16)
+    ops().attention_prefill_tcgen05(out, q, view, heads, 0.3, window or 0, batch)
+    torch.cuda.synchronize()
+    ops().raise_if_failed()
+    view_cpu = type(view)(view.storage.cpu(), view.page_table.cpu(), view.page_size, kv_heads, head_dim, window)
+    cpu_batch = type("B", (), {"n_tokens": n, "tok_pos": batch.tok_pos.cpu(), "tok_seq": batch.tok_seq.cpu(),
+                               "slots": batch.slots.cpu()})
+    PK.attention_general(ref, q.cpu(), view_cpu, heads, 0.3, window or 0, cpu_batch)
+    worst = (out.float().cpu() - ref.float()).abs().max(dim=1).values
+    assert worst.max() <= 8e-3 * ref.float().abs().max(), int(worst.argmax())
+    assert rel_error(out.float().cpu(), ref.float()) <= 8e-3
+    again = torch.zeros_like(out)
+    ops().attention_prefill_tcgen05(again, q, view, heads, 0.3, window or 0, batch)
+    assert torch.equal(again, out)
+
+
+@pytest.mark.parametrize("window", [None, 1000])
+def test_attention_prefill_tcgen05_long(window):
+    """Thousands of keys per query (many trips round the rings of stages and buffers), against the mma.sync kernel."""
+    heads, kv_heads, head_dim = 6, 2, 64
+    lengths, new = [2500, 4100, 700], [2500, 1030, 700]
+    cache, view, batch = _cache_and_batch(torch.bfloat16, kv_heads, head_dim, lengths, new, window)
+    n = batch.n_tokens
+    q = _randn((n, heads * head_dim), torch.bfloat16, 9)
+    out, ref = (torch.zeros((n, heads * head_dim), dtype=torch.bfloat16, device=DEV) for _ in range(2))
+    ops().attention_prefill_tcgen05(out, q, view, heads, 0.3, window or 0, batch)
+    ops().attention_prefill(ref, q, view, heads, 0.3, window or 0, batch)
+    torch.cuda.synchronize()
+    ops().raise_if_failed()
+    worst = (out.float() - ref.float()).abs().max(dim=1).values
+    assert float(worst.max()) <= 8e-3 * float(ref.float().abs().max()), int(worst.argmax())
+
+
+def test_attention_prefill_tcgen05_finds_a_far_key_and_ignores_what_lies_beyond():
+    heads, kv_heads, hd = 4, 2, 64
+    cache, view, batch = _cache_and_batch(torch.bfloat16, kv_heads, hd, [700], [200])
+    view.storage.mul_(0.05)
+    slot = batch.h_slots[0]
+    last_page = int(view.page_table[slot, 699 // 64])
+    view.storage[last_page, :, :, 700 % 64:, :] = 1e4  # rows of the last page beyond the sequence's length
+    for target in (0, 63, 64, 333, 499):
+        page = int(view.page_table[slot, target // 64])
+        saved = view.storage[page].clone()
+        view.storage[page, 0, :, target % 64, :] = 4.0
+        view.storage[page, 1, :, target % 64, :] = 7.0
+        q = torch.full((200, heads * hd), 4.0, dtype=torch.bfloat16, device=DEV)
+        out = torch.zeros_like(q)
+        ops().attention_prefill_tcgen05(out, q, view, heads, 1.0, 0, batch)
+        assert torch.allclose(out.float(), torch.full_like(out, 7.0).float(), atol=0.05), target
+        view.storage[page] = saved
+
+
+def test_attention_prefill_tcgen05_refuses_other_head_sizes():
+    from etalii.dllm_b200.kernels.ops import KernelError
+
+    cache, view, batch = _cache_and_batch(torch.bfloat16, 2, 32, [70], [70])
+    q = _randn((70, 4 * 32), torch.bfloat16, 9)
+    with pytest.raises((KernelError, AssertionError)):
+        ops().attention_prefill_tcgen05(torch.zeros_like(q), q, view, 4, 0.3, 0, batch)
 
 
 def test_gemv_qkv_rope_refuses_head_sizes_it_cannot_pair():
