@@ -191,6 +191,75 @@ def gemm_table() -> int:
     return 0
 
 
+def attention_table() -> int:
+    """Times the attention kernels alone (CUDA events; several caches in turn, larger than L2 together for the decode
+    rows): the two prefill kernels on whole prompts, and the cluster decode kernel at every launch shape."""
+    import torch
+
+    from etalii.dllm_b200.cache.paged import CacheNeed, PagedCache
+    from etalii.dllm_b200.engine.batch import BatchBuffers
+    from etalii.dllm_b200.kernels import ops
+
+    device = torch.device("cuda:0")
+
+    def setup(heads, kv_heads, head_dim, lengths, new, layers):
+        total = sum((n + 63) // 64 * 64 for n in lengths)
+        cache = PagedCache([CacheNeed("kv", kv_heads, head_dim, None)] * layers, max_tokens=total + 64,
+                           max_length=max(lengths) + 64, dtype=torch.bfloat16, device=device)
+        slots = cache.acquire(len(lengths))
+        for slot, n in zip(slots, lengths):
+            cache.reserve(slot, n)
+            cache.advance(slot, n)
+        cache.sync_tables()
+        views = [cache.kv_view(i) for i in range(layers)]
+        for view in views:
+            view.storage.normal_()
+        batch = BatchBuffers(device).fill(slots, [[1] * k for k in new], [n - k for n, k in zip(lengths, new)],
+                                          [[] for _ in lengths])
+        q = torch.randn((batch.n_tokens, heads * head_dim), device=device).to(torch.bfloat16)
+        return views, batch, q, torch.zeros_like(q)
+
+    def time_us(call, views, reps=5):
+        for _ in range(2):
+            for view in views:
+                call(view)
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        for _ in range(reps):
+            for view in views:
+                call(view)
+        end.record()
+        torch.cuda.synchronize()
+        ops.raise_if_failed()
+        return begin.elapsed_time(end) * 1e3 / (reps * len(views))
+
+    print("prefill: heads kv_heads head_dim prompts | mma.sync us | tcgen05 us, TFLOP/s")
+    for heads, kv_heads, lengths in ((9, 3, [2048]), (9, 3, [512]), (9, 3, [8192]), (32, 8, [2048]),
+                                     (32, 8, [4096, 4096]), (9, 3, [300] * 16)):
+        views, batch, q, out = setup(heads, kv_heads, 64, lengths, lengths, 8)
+        old = time_us(lambda v: ops.attention_prefill(out, q, v, heads, 0.125, 0, batch), views)
+        new = time_us(lambda v: ops.attention_prefill_tcgen05(out, q, v, heads, 0.125, 0, batch), views)
+        flops = sum(4 * heads * 64 * n * (n + 1) / 2 for n in lengths)
+        shown = lengths if len(lengths) < 4 else f"{len(lengths)} x {lengths[0]}"
+        print(f"{heads} {kv_heads} 64 {shown} | {old:.1f} | {new:.1f}, {flops / new / 1e6:.0f}")
+    print("decode: heads kv_heads head_dim batch, MB of keys and values, us at the measured HBM rate | "
+          "chosen shape us | shapes 0..4 us")
+    bandwidth = peaks()["hbm_gbs"]
+    for heads, kv_heads, head_dim in ((9, 3, 64), (32, 8, 128), (32, 32, 64)):
+        for size in (1, 8, 64, 128):
+            g = torch.Generator().manual_seed(size)
+            lengths = [int(x) for x in torch.randint(128, 2304, (size,), generator=g)]
+            layers = max(2, min(16, int(300e6 / (size * 1200 * 4 * kv_heads * head_dim)) + 1))
+            views, batch, q, out = setup(heads, kv_heads, head_dim, lengths, [1] * size, layers)
+            kv_bytes = sum(lengths) * 4 * kv_heads * head_dim
+            cells = [time_us(lambda v: ops.attention_decode_cluster(out, q, v, heads, 0.125, 0, batch, shape), views)
+                     for shape in range(-1, ops.DECODE_CLUSTER_SHAPES)]
+            print(f"{heads} {kv_heads} {head_dim} {size}, {kv_bytes / 1e6:.1f} MB, {kv_bytes / bandwidth / 1e3:.1f} us | "
+                  f"{cells[0]:.1f} | " + " ".join(f"{c:.1f}" for c in cells[1:]))
+    return 0
+
+
 def model_numbers(config, layers):
     h, i, v = config["hidden_size"], config["intermediate_size"], config["vocab_size"]
     nh, nkv, hd = config["num_attention_heads"], config["num_key_value_heads"], config["head_dim"]
@@ -213,7 +282,7 @@ def main() -> int:
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
     parser.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 decode points")
-    parser.add_argument("--profile", choices=("decode", "prefill", "gemm"),
+    parser.add_argument("--profile", choices=("decode", "prefill", "gemm", "attention"),
                         help="run only a few decode steps (or one prefill) and print no JSON: a small case for ncu")
     args = parser.parse_args()
     if args.impl == "reference":
@@ -223,6 +292,8 @@ def main() -> int:
         return 0
     if args.profile == "gemm":
         return gemm_table()
+    if args.profile == "attention":
+        return attention_table()
     if args.gpus != 1:
         print(f"bench.py measures one GPU: --gpus {args.gpus} is not supported (this library runs on a single device)")
         return 2

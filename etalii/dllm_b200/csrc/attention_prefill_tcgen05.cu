@@ -39,6 +39,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tcgen05_kernel(
   int tile = blockIdx.x, h = blockIdx.y;
   int q0 = tile_first[tile];
   if (q0 % BQ) return;  // the host lists tiles of 64 tokens; every second one starts a tile of 128
+  pdl_launch_dependents();
   extern __shared__ unsigned char smem_raw[];
   unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);  // swizzle atoms: 1 KB
   unsigned char* q_s = tiles;
@@ -80,6 +81,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tcgen05_kernel(
   fence_after_sync();
   unsigned tmem_base = tmem_base_s;
   unsigned tmem_s = tmem_base, tmem_o = tmem_base + 2 * BKV;
+  pdl_wait();  // the queries and the newest keys and values come from the kernel before; so does `out`'s last reader
 
   if (warp == 8) {
     if (lane == 0) {
@@ -322,8 +324,7 @@ DLLM_EXPORT int dllm_attention_prefill_tcgen05(void* out, const void* q, int tok
     configured = true;
   }
   KvLayout cache{cache_base, page_table, max_pages, page_size, kv_heads, head_dim};
-  prefill_tcgen05_kernel<<<dim3(tiles, heads), THREADS, SMEM, stream>>>(
-      map_q, map_kv, (bf16*)out, cache, tile_seq, tile_first, cu_seqlens, start, slots, heads,
-      scale * 1.4426950408889634f, window, status);
-  return dllm_launch_status();
+  return dllm_launch_pdl(prefill_tcgen05_kernel, dim3(tiles, heads), dim3(THREADS), SMEM, stream, map_q, map_kv,
+                         (bf16*)out, cache, tile_seq, tile_first, cu_seqlens, start, slots, heads,
+                         scale * 1.4426950408889634f, window, status);
 }

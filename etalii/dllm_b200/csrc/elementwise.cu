@@ -79,6 +79,8 @@ __global__ void __launch_bounds__(256) rmsnorm_warp_kernel(T* __restrict__ out, 
                                                            const float* __restrict__ weight,
                                                            const int* __restrict__ rows, int n_rows, int hidden,
                                                            float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   int lane = threadIdx.x & 31;
   int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (r >= n_rows) return;
@@ -116,13 +118,12 @@ DLLM_EXPORT int dllm_rmsnorm(void* out, const float* x, const float* weight, con
   if ((hidden & 3) == 0 && hidden <= 4096) {  // whatever the number of rows, so a row has the same bits everywhere
     int blocks = (n_rows + 7) / 8;
     if (out_dtype == DLLM_F32)
-      rmsnorm_warp_kernel<float><<<blocks, 256, 0, stream>>>((float*)out, x, weight, rows, n_rows, hidden, eps);
-    else if (out_dtype == DLLM_BF16)
-      rmsnorm_warp_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((__nv_bfloat16*)out, x, weight, rows, n_rows,
-                                                                     hidden, eps);
-    else
-      return DLLM_BAD_ARGUMENT;
-    return dllm_launch_status();
+      return dllm_launch_pdl(rmsnorm_warp_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)out, x, weight, rows,
+                             n_rows, hidden, eps);
+    if (out_dtype == DLLM_BF16)
+      return dllm_launch_pdl(rmsnorm_warp_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream,
+                             (__nv_bfloat16*)out, x, weight, rows, n_rows, hidden, eps);
+    return DLLM_BAD_ARGUMENT;
   }
   int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
   if (out_dtype == DLLM_F32)

@@ -49,6 +49,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
   int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int k_tiles = (K + BK - 1) / BK;
   int total = m_tiles * n_tiles;
+  pdl_launch_dependents();  // the next kernel may set itself up (barriers, tensor memory) while this one runs
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -62,11 +63,14 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   unsigned tmem_base = tmem_base_s;
+  if (warp == 0 && lane == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+  }
+  pdl_wait();  // everything above touched nothing an earlier kernel writes; from here on this kernel reads and writes
 
   if (warp == 0) {
     if (lane == 0) {
-      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
-      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
       int it = 0;  // k tiles issued so far, over all of this block's tiles
       bool ok = true;
       for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
@@ -220,9 +224,8 @@ int launch(void* c, const void* a, const void* w, int M, int N, int K, int* stat
   }
   int blocks = sms * Shape<BN>::BLOCKS_PER_SM;
   if (blocks > total) blocks = (int)total;
-  gemm_tcgen05_kernel<BN, EPI><<<blocks, THREADS, Shape<BN>::SMEM, stream>>>(map_a, map_w, c, M, N, K, status, rope,
-                                                                            m_tiles, n_tiles);
-  return dllm_launch_status();
+  return dllm_launch_pdl(gemm_tcgen05_kernel<BN, EPI>, dim3(blocks), dim3(THREADS), Shape<BN>::SMEM, stream, map_a,
+                         map_w, c, M, N, K, status, rope, m_tiles, n_tiles);
 }
 
 template <int BN>

@@ -5,6 +5,9 @@
 #pragma once
 #include <cuda.h>
 
+#include <mutex>
+#include <unordered_map>
+
 #include "common.cuh"
 
 namespace tc5 {
@@ -118,15 +121,42 @@ static inline EncodeTiled encoder() {
 }
 
 // A [rows, cols] bfloat16 row-major matrix, boxes of box_rows x 64 columns, 128-byte swizzle, zero fill outside.
+// Encoded maps are kept (a map depends only on these five numbers, and the same weights and workspace buffers come
+// again every step): a launch then costs a table lookup instead of two driver calls.
 static inline bool make_map(CUtensorMap* map, const void* base, long long rows, long long cols, int box_rows) {
+  struct Key {
+    const void* base; long long rows, cols; int box_rows;
+    bool operator==(const Key& o) const { return base == o.base && rows == o.rows && cols == o.cols && box_rows == o.box_rows; }
+  };
+  struct Hash {
+    size_t operator()(const Key& k) const {
+      size_t h = (size_t)(uintptr_t)k.base * 0x9E3779B97F4A7C15ull;
+      h ^= (size_t)k.rows * 0xC2B2AE3D27D4EB4Full + (h << 6) + (h >> 2);
+      h ^= (size_t)k.cols * 0x165667B19E3779F9ull + (h << 6) + (h >> 2);
+      return h ^ (size_t)k.box_rows;
+    }
+  };
+  static std::unordered_map<Key, CUtensorMap, Hash> cache;
+  static std::mutex lock;
+  Key key{base, rows, cols, box_rows};
+  {
+    std::lock_guard<std::mutex> guard(lock);
+    auto found = cache.find(key);
+    if (found != cache.end()) { *map = found->second; return true; }
+  }
   EncodeTiled encode = encoder();
   if (encode == nullptr) return false;
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
   cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
   cuuint32_t elem[2] = {1, 1};
-  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  if (encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  std::lock_guard<std::mutex> guard(lock);
+  if (cache.size() >= 8192) cache.clear();
+  cache.emplace(key, *map);
+  return true;
 }
 }  // namespace tc5

@@ -16,8 +16,13 @@ class Workspace:
         self.device = device
         self.generation = 0
         self._buffers: dict[str, torch.Tensor] = {}
+        self._views: dict[tuple, torch.Tensor] = {}
 
     def buffer(self, name: str, shape, dtype) -> torch.Tensor:
+        key = (name, tuple(shape), dtype)
+        view = self._views.get(key)  # the same step shapes come again and again: the view object is kept
+        if view is not None:
+            return view
         count = 1
         for d in shape:
             count *= int(d)
@@ -27,7 +32,12 @@ class Workspace:
             have = torch.empty(capacity, dtype=dtype, device=self.device)
             self._buffers[name] = have
             self.generation += 1
-        return have[:count].view(*shape)
+            self._views = {k: v for k, v in self._views.items() if k[0] != name}
+        if len(self._views) > 4096:
+            self._views.clear()
+        view = have[:count].view(*shape)
+        self._views[key] = view
+        return view
 
     def zeros(self, name: str, count: int, dtype) -> torch.Tensor:
         """A buffer that starts as zeros and is kept between steps (kernels that use it leave it zero)."""
