@@ -77,10 +77,14 @@ def _fn(lib: str, name: str):
     return found
 
 
-def _check(status: int, what: str, detail: str = "") -> None:
+def _check(status: int, what: str, detail="") -> None:
+    """Counts the launch; a refusal raises. `detail` may be a callable that makes the text (only then is it made:
+    formatting a message costs a launch's worth of host time)."""
     global launches
     launches += 1
     if status != 0:
+        if callable(detail):
+            detail = detail()
         raise KernelError(f"{what}: {_STATUS.get(status, status)}{(' (' + detail + ')') if detail else ''}")
 
 
@@ -194,7 +198,9 @@ def gemm(c: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int = EPI_
     want_cols = n // 2 if epilogue == EPI_SWIGLU else n
     want_dtype = torch.float32 if epilogue in (EPI_STORE_F32, EPI_RESIDUAL) else w.dtype
     assert tuple(c.shape) == (m, want_cols) and c.dtype == want_dtype, (c.shape, c.dtype, m, want_cols, want_dtype)
-    detail = f"M={m} N={n} K={k}: K must be a multiple of {4 if w.dtype == torch.float32 else 8}; N even for the SwiGLU epilogue"
+    def detail() -> str:
+        return (f"M={m} N={n} K={k}: K must be a multiple of {4 if w.dtype == torch.float32 else 8}; N even for the "
+                f"SwiGLU epilogue; the weight-streaming kernel takes M up to {GEMV_MAX_ROWS}")
     if w.dtype == torch.float32:
         assert a.dtype == torch.float32 and norm_weight is None
         status = _fn("gemm_simt", "dllm_gemm_f32")(c.data_ptr(), a.data_ptr(), w.data_ptr(), m, n, k, epilogue,
@@ -209,7 +215,6 @@ def gemm(c: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int = EPI_
             status = _fn("gemv", "dllm_gemv_bf16")(
                 c.data_ptr(), a.data_ptr(), norm_weight.data_ptr() if norm_weight is not None else None, float(eps),
                 w.data_ptr(), m, n, k, epilogue, *_prefetch_of(w), _stream())
-            detail += f", M at most {GEMV_MAX_ROWS}"
         elif kernel == 1:
             assert a.dtype == torch.bfloat16 and norm_weight is None
             status = _fn("gemm_bf16", "dllm_gemm_bf16")(c.data_ptr(), a.data_ptr(), w.data_ptr(), m, n, k, epilogue,
@@ -247,7 +252,7 @@ def gemm_qkv_rope(a: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, cache, 
         cache.max_pages, cache.page_size, heads, cache.kv_heads, cache.head_dim,
         table.data_ptr() if table is not None else None, rotary_dim if table is not None else 0,
         batch.tok_seq.data_ptr(), batch.tok_pos.data_ptr(), batch.slots.data_ptr(), 1 if write_cache else 0,
-        _status_word().data_ptr(), _stream()), "gemm_qkv_rope", f"M={m} K={k} head_dim={cache.head_dim}")
+        _status_word().data_ptr(), _stream()), "gemm_qkv_rope", lambda: f"M={m} K={k} head_dim={cache.head_dim}")
 
 
 def gemv_qkv_rope(a: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, cache, table: torch.Tensor | None,
@@ -269,7 +274,7 @@ def gemv_qkv_rope(a: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, cache, 
         cache.kv_heads, cache.head_dim, table.data_ptr() if table is not None else None,
         rotary_dim if table is not None else 0, batch.tok_seq.data_ptr(), batch.tok_pos.data_ptr(),
         batch.slots.data_ptr(), 1 if write_cache else 0, *_prefetch_of(w), _stream()),
-        "gemv_qkv_rope", f"M={m} (at most 64), K={k} (multiple of 8), head_dim and rotary_dim multiples of 16")
+        "gemv_qkv_rope", lambda: f"M={m} (at most 64), K={k} (multiple of 8), head_dim and rotary_dim multiples of 16")
 
 
 def rope_cache_write(qkv: torch.Tensor, q_out: torch.Tensor, cache, table: torch.Tensor | None, rotary_dim: int,
@@ -300,7 +305,7 @@ def attention_general(out: torch.Tensor, q: torch.Tensor, cache, heads: int, sca
         out.data_ptr(), q.data_ptr(), cache.base_ptr, cache.page_table.data_ptr(), cache.max_pages, cache.page_size,
         heads, cache.kv_heads, cache.head_dim, batch.tok_seq.data_ptr(), batch.tok_pos.data_ptr(),
         batch.slots.data_ptr(), batch.n_tokens, float(scale), int(window or 0), _code(cache.dtype), _stream()),
-        "attention", f"head_dim={cache.head_dim} must be a multiple of 8, at most 256")
+        "attention", lambda: f"head_dim={cache.head_dim} must be a multiple of 8, at most 256")
 
 
 def add_residual(residual: torch.Tensor, update: torch.Tensor) -> None:
@@ -372,7 +377,7 @@ def attention_decode(out: torch.Tensor, q: torch.Tensor, cache, heads: int, scal
         heads, cache.kv_heads, cache.head_dim, batch.tok_pos.data_ptr(), batch.slots.data_ptr(), batch.n_seqs,
         float(scale), int(window or 0), int(chunk), int(batch.max_context), scratch.data_ptr(),
         tickets.data_ptr(), _stream()),
-        "attention_decode", f"head_dim={cache.head_dim} must be a multiple of 8, at most 256")
+        "attention_decode", lambda: f"head_dim={cache.head_dim} must be a multiple of 8, at most 256")
 
 
 def attention_prefill_supported(cache) -> bool:
@@ -391,7 +396,7 @@ def attention_prefill(out: torch.Tensor, q: torch.Tensor, cache, heads: int, sca
         heads, cache.kv_heads, cache.head_dim, batch.tile_seq.data_ptr(), batch.tile_first.data_ptr(),
         batch.cu_seqlens.data_ptr(), batch.start.data_ptr(), batch.slots.data_ptr(), batch.n_tiles, float(scale),
         int(window or 0), _stream()), "attention_prefill",
-        f"head_dim={cache.head_dim} must be a multiple of 16, at most 128; pages of 64")
+        lambda: f"head_dim={cache.head_dim} must be a multiple of 16, at most 128; pages of 64")
 
 
 def attention_prefill_tcgen05_supported(cache) -> bool:
@@ -410,7 +415,7 @@ def attention_prefill_tcgen05(out: torch.Tensor, q: torch.Tensor, cache, heads: 
         cache.page_table.data_ptr(), cache.max_pages, cache.page_size, heads, cache.kv_heads, cache.head_dim,
         batch.tile_seq.data_ptr(), batch.tile_first.data_ptr(), batch.cu_seqlens.data_ptr(), batch.start.data_ptr(),
         batch.slots.data_ptr(), batch.n_tiles, float(scale), int(window or 0), _status_word().data_ptr(),
-        _stream()), "attention_prefill_tcgen05", f"head_dim={cache.head_dim} must be 64; pages of 64")
+        _stream()), "attention_prefill_tcgen05", lambda: f"head_dim={cache.head_dim} must be 64; pages of 64")
 
 
 def attention_decode_cluster_supported(cache) -> bool:
@@ -436,4 +441,4 @@ def attention_decode_cluster(out: torch.Tensor, q: torch.Tensor, cache, heads: i
         out.data_ptr(), q.data_ptr(), cache.base_ptr, cache.page_table.data_ptr(), cache.max_pages, cache.page_size,
         heads, cache.kv_heads, cache.head_dim, batch.tok_pos.data_ptr(), batch.slots.data_ptr(), batch.n_seqs,
         float(scale), int(window or 0), int(shape), _stream()), "attention_decode_cluster",
-        f"head_dim={cache.head_dim} must be a multiple of 16, at most 128; pages of 64")
+        lambda: f"head_dim={cache.head_dim} must be a multiple of 16, at most 128; pages of 64")
