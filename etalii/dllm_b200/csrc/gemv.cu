@@ -99,7 +99,7 @@ template <int WARPS, int NT, int EPI, bool NORM, bool PIPE>
 __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(void* __restrict__ c, const void* __restrict__ a,
                                                           const float* __restrict__ norm_w, float eps,
                                                           const bf16* __restrict__ w, int M, int N, int K,
-                                                          RopeArgs rope, Prefetch pf) {
+                                                          RopeArgs rope, Prefetch pf, int items) {
   // 32-value k steps whose loads a warp issues before the first product (fewer when more tokens need registers)
   constexpr int MAX_STEPS = NORM ? (NT == 1 ? 6 : (NT == 2 ? 3 : 1)) : (NT == 1 ? 8 : (NT == 2 ? 4 : 2));
   // exchange space of the warps: [WARPS][TILE][NT * 8 + 1] partial tiles, then [WARPS][NT * 8] sums of squares
@@ -108,10 +108,13 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(void* __restrict__ c, 
   float (*red_ss)[NT * 8] = reinterpret_cast<float (*)[NT * 8]>(exchange + WARPS * TILE * (NT * 8 + 1));
   int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   int g = lane >> 2, t = lane & 3;
+  // A block takes the tiles blockIdx.x, blockIdx.x + gridDim.x, ... of the `items` tiles of 16 rows of W. (Launched
+  // with one block per tile, the loop below runs once.)
+  int item = blockIdx.x;
   int head, dim0;
   bool paired;
-  int row_lo = tile_row<EPI>(blockIdx.x, g, N, rope, head, dim0, paired);
-  int row_hi = tile_row<EPI>(blockIdx.x, g + 8, N, rope, head, dim0, paired);
+  int row_lo = tile_row<EPI>(item, g, N, rope, head, dim0, paired);
+  int row_hi = tile_row<EPI>(item, g + 8, N, rope, head, dim0, paired);
   const uint4* w_lo = (const uint4*)(w + (size_t)row_lo * K);
   const uint4* w_hi = (const uint4*)(w + (size_t)row_hi * K);
   int chunks = K >> 3;                   // 16-byte pieces of a row
@@ -144,158 +147,191 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(void* __restrict__ c, 
     }
   };
   if (s_begin < s_end) load_weights(s_begin, wl, wh);
-  for (int s0 = s_begin; s0 < s_end; s0 += MAX_STEPS) {
-    uint4 xb[MAX_STEPS][NT];
-    if (s0 == s_begin) {
-      prefetch_share(pf);
-      pdl_wait();  // the weights above are nobody's output; everything below may be the previous kernel's
-      early.load(c, tid, M, N, blockIdx.x, rope, paired, dim0);
-    }
-    if (NORM) {
-      // all loads of the stretch first (activations and norm weights), then the arithmetic: a step's loads must
-      // not wait behind the previous step's sums
-      float4 xr[MAX_STEPS][NT][2], nr[MAX_STEPS][2];
+  bool waited = false;
+  for (;;) {
+    for (int s0 = s_begin; s0 < s_end; s0 += MAX_STEPS) {
+      uint4 xb[MAX_STEPS][NT];
+      if (s0 == s_begin) {
+        if (!PIPE || !waited) {
+          prefetch_share(pf);
+          pdl_wait();  // the weights above are nobody's output; everything below may be the previous kernel's
+          waited = true;
+        }
+        early.load(c, tid, M, N, item, rope, paired, dim0);
+      }
+      if (NORM) {
+        // all loads of the stretch first (activations and norm weights), then the arithmetic: a step's loads must
+        // not wait behind the previous step's sums
+        float4 xr[MAX_STEPS][NT][2], nr[MAX_STEPS][2];
 #pragma unroll
-      for (int i = 0; i < MAX_STEPS; ++i) {
-        int ch = (s0 + i) * 4 + t;
-        bool ok = s0 + i < s_end && ch < chunks;
-        nr[i][0] = nr[i][1] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (ok) {
-          nr[i][0] = __ldg((const float4*)norm_w + 2 * ch);
-          nr[i][1] = __ldg((const float4*)norm_w + 2 * ch + 1);
+        for (int i = 0; i < MAX_STEPS; ++i) {
+          int ch = (s0 + i) * 4 + t;
+          bool ok = s0 + i < s_end && ch < chunks;
+          nr[i][0] = nr[i][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (ok) {
+            nr[i][0] = __ldg((const float4*)norm_w + 2 * ch);
+            nr[i][1] = __ldg((const float4*)norm_w + 2 * ch + 1);
+          }
+#pragma unroll
+          for (int n = 0; n < NT; ++n) {
+            int m = n * 8 + g;
+            xr[i][n][0] = xr[i][n][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (ok && m < M) {
+              const float4* xp = (const float4*)((const float*)a + (size_t)m * K) + 2 * ch;
+              xr[i][n][0] = xp[0];
+              xr[i][n][1] = xp[1];
+            }
+          }
         }
 #pragma unroll
-        for (int n = 0; n < NT; ++n) {
-          int m = n * 8 + g;
-          xr[i][n][0] = xr[i][n][1] = make_float4(0.f, 0.f, 0.f, 0.f);
-          if (ok && m < M) {
-            const float4* xp = (const float4*)((const float*)a + (size_t)m * K) + 2 * ch;
-            xr[i][n][0] = xp[0];
-            xr[i][n][1] = xp[1];
+        for (int i = 0; i < MAX_STEPS; ++i) {
+#pragma unroll
+          for (int n = 0; n < NT; ++n) {
+            float4 x0 = xr[i][n][0], x1 = xr[i][n][1], n0 = nr[i][0], n1 = nr[i][1];
+            ss[n] = fmaf(x0.x, x0.x, ss[n]); ss[n] = fmaf(x0.y, x0.y, ss[n]);
+            ss[n] = fmaf(x0.z, x0.z, ss[n]); ss[n] = fmaf(x0.w, x0.w, ss[n]);
+            ss[n] = fmaf(x1.x, x1.x, ss[n]); ss[n] = fmaf(x1.y, x1.y, ss[n]);
+            ss[n] = fmaf(x1.z, x1.z, ss[n]); ss[n] = fmaf(x1.w, x1.w, ss[n]);
+            xb[i][n] = make_uint4(pack_bf16(x0.x * n0.x, x0.y * n0.y), pack_bf16(x0.z * n0.z, x0.w * n0.w),
+                                  pack_bf16(x1.x * n1.x, x1.y * n1.y), pack_bf16(x1.z * n1.z, x1.w * n1.w));
+          }
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < MAX_STEPS; ++i) {
+          int ch = (s0 + i) * 4 + t;
+          bool ok = s0 + i < s_end && ch < chunks;
+#pragma unroll
+          for (int n = 0; n < NT; ++n) {
+            int m = n * 8 + g;
+            xb[i][n] = (ok && m < M) ? *((const uint4*)((const bf16*)a + (size_t)m * K) + ch) : zero;
           }
         }
       }
+      uint4 wl_next[PIPE ? MAX_STEPS : 1], wh_next[PIPE ? MAX_STEPS : 1];
+      bool more = PIPE && s0 + MAX_STEPS < s_end;
+      if (PIPE && more) load_weights(s0 + MAX_STEPS, wl_next, wh_next);
 #pragma unroll
       for (int i = 0; i < MAX_STEPS; ++i) {
+        unsigned a0[4] = {wl[i].x, wh[i].x, wl[i].y, wh[i].y};
+        unsigned a1[4] = {wl[i].z, wh[i].z, wl[i].w, wh[i].w};
 #pragma unroll
         for (int n = 0; n < NT; ++n) {
-          float4 x0 = xr[i][n][0], x1 = xr[i][n][1], n0 = nr[i][0], n1 = nr[i][1];
-          ss[n] = fmaf(x0.x, x0.x, ss[n]); ss[n] = fmaf(x0.y, x0.y, ss[n]);
-          ss[n] = fmaf(x0.z, x0.z, ss[n]); ss[n] = fmaf(x0.w, x0.w, ss[n]);
-          ss[n] = fmaf(x1.x, x1.x, ss[n]); ss[n] = fmaf(x1.y, x1.y, ss[n]);
-          ss[n] = fmaf(x1.z, x1.z, ss[n]); ss[n] = fmaf(x1.w, x1.w, ss[n]);
-          xb[i][n] = make_uint4(pack_bf16(x0.x * n0.x, x0.y * n0.y), pack_bf16(x0.z * n0.z, x0.w * n0.w),
-                                pack_bf16(x1.x * n1.x, x1.y * n1.y), pack_bf16(x1.z * n1.z, x1.w * n1.w));
+          mma_bf16(acc[n], a0, xb[i][n].x, xb[i][n].y);
+          mma_bf16(acc[n], a1, xb[i][n].z, xb[i][n].w);
         }
       }
-    } else {
+      if (PIPE) {
+        if (more) {
 #pragma unroll
-      for (int i = 0; i < MAX_STEPS; ++i) {
-        int ch = (s0 + i) * 4 + t;
-        bool ok = s0 + i < s_end && ch < chunks;
-#pragma unroll
-        for (int n = 0; n < NT; ++n) {
-          int m = n * 8 + g;
-          xb[i][n] = (ok && m < M) ? *((const uint4*)((const bf16*)a + (size_t)m * K) + ch) : zero;
+          for (int i = 0; i < MAX_STEPS; ++i) { wl[i] = wl_next[PIPE ? i : 0]; wh[i] = wh_next[PIPE ? i : 0]; }
         }
+      } else if (s0 + MAX_STEPS < s_end) {
+        load_weights(s0 + MAX_STEPS, wl, wh);
       }
     }
-    uint4 wl_next[PIPE ? MAX_STEPS : 1], wh_next[PIPE ? MAX_STEPS : 1];
-    bool more = PIPE && s0 + MAX_STEPS < s_end;
-    if (PIPE && more) load_weights(s0 + MAX_STEPS, wl_next, wh_next);
+    if (s_begin >= s_end) {  // a warp without work has not waited yet
+      if (!PIPE || !waited) {
+        pdl_wait();
+        waited = true;
+      }
+      early.load(c, tid, M, N, item, rope, paired, dim0);
+    }
+    // the block's next tile: its first weights are requested now and travel while this tile is summed and stored
+    // (only the variants for long rows walk over several tiles; the others are launched with a block per tile)
+    int next = PIPE ? item + (int)gridDim.x : items, next_head = 0, next_dim0 = 0;
+    bool next_paired = false;
+    if (PIPE && next < items) {
+      row_lo = tile_row<EPI>(next, g, N, rope, next_head, next_dim0, next_paired);
+      row_hi = tile_row<EPI>(next, g + 8, N, rope, next_head, next_dim0, next_paired);
+      w_lo = (const uint4*)(w + (size_t)row_lo * K);
+      w_hi = (const uint4*)(w + (size_t)row_hi * K);
+      if (s_begin < s_end) load_weights(s_begin, wl, wh);
+    }
+    // partial tiles and partial sums of squares to shared memory
 #pragma unroll
-    for (int i = 0; i < MAX_STEPS; ++i) {
-      unsigned a0[4] = {wl[i].x, wh[i].x, wl[i].y, wh[i].y};
-      unsigned a1[4] = {wl[i].z, wh[i].z, wl[i].w, wh[i].w};
-#pragma unroll
-      for (int n = 0; n < NT; ++n) {
-        mma_bf16(acc[n], a0, xb[i][n].x, xb[i][n].y);
-        mma_bf16(acc[n], a1, xb[i][n].z, xb[i][n].w);
+    for (int n = 0; n < NT; ++n) {
+      red[warp][g][n * 8 + 2 * t] = acc[n][0];
+      red[warp][g][n * 8 + 2 * t + 1] = acc[n][1];
+      red[warp][g + 8][n * 8 + 2 * t] = acc[n][2];
+      red[warp][g + 8][n * 8 + 2 * t + 1] = acc[n][3];
+      if (NORM) {
+        float v = ss[n];
+        v += __shfl_xor_sync(0xffffffffu, v, 1);
+        v += __shfl_xor_sync(0xffffffffu, v, 2);
+        if (t == 0) red_ss[warp][n * 8 + g] = v;
       }
     }
-    if (PIPE) {
-      if (more) {
-#pragma unroll
-        for (int i = 0; i < MAX_STEPS; ++i) { wl[i] = wl_next[PIPE ? i : 0]; wh[i] = wh_next[PIPE ? i : 0]; }
-      }
-    } else if (s0 + MAX_STEPS < s_end) {
-      load_weights(s0 + MAX_STEPS, wl, wh);
-    }
-  }
-  if (s_begin >= s_end) {  // a warp without work has not waited yet
-    pdl_wait();
-    early.load(c, tid, M, N, blockIdx.x, rope, paired, dim0);
-  }
-  // partial tiles and partial sums of squares to shared memory
-#pragma unroll
-  for (int n = 0; n < NT; ++n) {
-    red[warp][g][n * 8 + 2 * t] = acc[n][0];
-    red[warp][g][n * 8 + 2 * t + 1] = acc[n][1];
-    red[warp][g + 8][n * 8 + 2 * t] = acc[n][2];
-    red[warp][g + 8][n * 8 + 2 * t + 1] = acc[n][3];
-    if (NORM) {
-      float v = ss[n];
-      v += __shfl_xor_sync(0xffffffffu, v, 1);
-      v += __shfl_xor_sync(0xffffffffu, v, 2);
-      if (t == 0) red_ss[warp][n * 8 + g] = v;
-    }
-  }
-  __syncthreads();
+    __syncthreads();
 
-  // one thread per (pair of tile rows, token): rows (2p, 2p+1), or (p, p + 8) for rotary pairs
-  for (int idx = tid; idx < 8 * NT * 8; idx += WARPS * 32) {
-    int p = idx / (NT * 8), m = idx % (NT * 8);
-    if (m >= M) continue;
-    int r0 = (EPI == EPI_QKV_ROPE) ? p : 2 * p, r1 = (EPI == EPI_QKV_ROPE) ? p + 8 : 2 * p + 1;
-    float v0 = 0.f, v1 = 0.f, sumsq = 0.f;
+    // one thread per (pair of tile rows, token): rows (2p, 2p+1), or (p, p + 8) for rotary pairs
+    for (int idx = tid; idx < 8 * NT * 8; idx += WARPS * 32) {
+      int p = idx / (NT * 8), m = idx % (NT * 8);
+      if (m >= M) continue;
+      int r0 = (EPI == EPI_QKV_ROPE) ? p : 2 * p, r1 = (EPI == EPI_QKV_ROPE) ? p + 8 : 2 * p + 1;
+      float v0 = 0.f, v1 = 0.f, sumsq = 0.f;
 #pragma unroll
-    for (int wi = 0; wi < WARPS; ++wi) {
-      v0 += red[wi][r0][m];
-      v1 += red[wi][r1][m];
-      if (NORM) sumsq += red_ss[wi][m];
-    }
-    if (NORM) {
-      float inv = 1.0f / sqrtf(sumsq / (float)K + eps);
-      v0 *= inv;
-      v1 *= inv;
-    }
-    bool first_item = idx == tid;  // what `early` fetched belongs to each thread's first item
-    if (EPI == EPI_QKV_ROPE) {
-      int hd = rope.cache.head_dim, nkv = rope.cache.kv_heads, heads = rope.heads;
-      int pos = first_item ? early.pos : rope.tok_pos[m];
-      int d0, d1;
-      if (paired) {
-        int half = rope.rotary_dim / 2;
-        d0 = dim0 + p;
-        d1 = d0 + half;
-        float2 cs = first_item ? early.cs : rope.table[(size_t)pos * half + d0];
-        float x = v0, y = v1;
-        v0 = fmaf(x, cs.x, -(y * cs.y));
-        v1 = fmaf(x, cs.y, y * cs.x);
-      } else {
-        d0 = dim0 + p;
-        d1 = d0 + 8;
+      for (int wi = 0; wi < WARPS; ++wi) {
+        v0 += red[wi][r0][m];
+        v1 += red[wi][r1][m];
+        if (NORM) sumsq += red_ss[wi][m];
       }
-      bf16* dst;
-      if (head < heads) {
-        dst = rope.q_out + ((size_t)m * heads + head) * hd;
-      } else {
-        if (!rope.write_cache) continue;
-        int which = head < heads + nkv ? 0 : 1;
-        int kvh = head - heads - which * nkv;
-        int page = first_item ? early.page
-                              : rope.cache.page_table[(size_t)rope.slots[rope.tok_seq[m]] * rope.cache.max_pages +
-                                                      pos / rope.cache.page_size];
-        dst = (bf16*)rope.cache.base + kv_offset(rope.cache, page, which, kvh, pos % rope.cache.page_size);
+      if (NORM) {
+        float inv = 1.0f / sqrtf(sumsq / (float)K + eps);
+        v0 *= inv;
+        v1 *= inv;
       }
-      dst[d0] = __float2bfloat16_rn(v0);
-      dst[d1] = __float2bfloat16_rn(v1);
-    } else if (EPI == EPI_RESIDUAL && first_item && early.have) {
-      float* dst = (float*)c + (size_t)m * N + blockIdx.x * TILE + 2 * p;
-      dst[0] = early.r0 + v0;
-      if (early.have > 1) dst[1] = early.r1 + v1;
-    } else {
-      epilogue_pair<EPI, bf16>(c, m, blockIdx.x * TILE + 2 * p, M, N, v0, v1);
+      bool first_item = idx == tid;  // what `early` fetched belongs to each thread's first item
+      if (EPI == EPI_QKV_ROPE) {
+        int hd = rope.cache.head_dim, nkv = rope.cache.kv_heads, heads = rope.heads;
+        int pos = first_item ? early.pos : rope.tok_pos[m];
+        int d0, d1;
+        if (paired) {
+          int half = rope.rotary_dim / 2;
+          d0 = dim0 + p;
+          d1 = d0 + half;
+          float2 cs = first_item ? early.cs : rope.table[(size_t)pos * half + d0];
+          float x = v0, y = v1;
+          v0 = fmaf(x, cs.x, -(y * cs.y));
+          v1 = fmaf(x, cs.y, y * cs.x);
+        } else {
+          d0 = dim0 + p;
+          d1 = d0 + 8;
+        }
+        bf16* dst;
+        if (head < heads) {
+          dst = rope.q_out + ((size_t)m * heads + head) * hd;
+        } else {
+          if (!rope.write_cache) continue;
+          int which = head < heads + nkv ? 0 : 1;
+          int kvh = head - heads - which * nkv;
+          int page = first_item ? early.page
+                                : rope.cache.page_table[(size_t)rope.slots[rope.tok_seq[m]] * rope.cache.max_pages +
+                                                        pos / rope.cache.page_size];
+          dst = (bf16*)rope.cache.base + kv_offset(rope.cache, page, which, kvh, pos % rope.cache.page_size);
+        }
+        dst[d0] = __float2bfloat16_rn(v0);
+        dst[d1] = __float2bfloat16_rn(v1);
+      } else if (EPI == EPI_RESIDUAL && first_item && early.have) {
+        float* dst = (float*)c + (size_t)m * N + item * TILE + 2 * p;
+        dst[0] = early.r0 + v0;
+        if (early.have > 1) dst[1] = early.r1 + v1;
+      } else {
+        epilogue_pair<EPI, bf16>(c, m, item * TILE + 2 * p, M, N, v0, v1);
+      }
+    }
+    if (!PIPE || next >= items) break;
+    __syncthreads();  // the exchange space is written again by the next tile
+    item = next;
+    head = next_head;
+    dim0 = next_dim0;
+    paired = next_paired;
+    early = Early<EPI, NT>();
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+      ss[n] = 0.f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
     }
   }
 }
@@ -304,17 +340,27 @@ template <int WARPS, int NT, int EPI, bool NORM, bool PIPE>
 int launch_one(int items, void* c, const void* a, const float* norm_w, float eps, const bf16* w, int M, int N, int K,
                const RopeArgs& rope, const Prefetch& pf, cudaStream_t stream) {
   size_t smem = (size_t)(WARPS * TILE * (NT * 8 + 1) + WARPS * NT * 8) * sizeof(float);
-  if (smem > 48 * 1024) {
-    static bool configured = false;
-    if (!configured) {
-      if (cudaFuncSetAttribute(gemv_kernel<WARPS, NT, EPI, NORM, PIPE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               (int)smem) != cudaSuccess)
-        return DLLM_LAUNCH_FAILED;
-      configured = true;
-    }
+  static int resident = 0;  // blocks of this kernel that fit on the device at once
+  if (resident == 0) {
+    if (smem > 48 * 1024 &&
+        cudaFuncSetAttribute(gemv_kernel<WARPS, NT, EPI, NORM, PIPE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem) != cudaSuccess)
+      return DLLM_LAUNCH_FAILED;
+    int device = 0, sms = 0, per_sm = 0;
+    if (cudaGetDevice(&device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemv_kernel<WARPS, NT, EPI, NORM, PIPE>, WARPS * 32,
+                                                      smem) != cudaSuccess ||
+        sms <= 0 || per_sm <= 0)
+      return DLLM_LAUNCH_FAILED;
+    resident = sms * per_sm;
   }
-  return dllm_launch_pdl(gemv_kernel<WARPS, NT, EPI, NORM, PIPE>, dim3(items), dim3(WARPS * 32), smem, stream, c, a,
-                         norm_w, eps, w, M, N, K, rope, pf);
+  // long rows (measured: from K = 4096 on): as many blocks as fit at once, each walking over its tiles with the next
+  // tile's weights on their way during the sum and store of this one; shorter rows: a block a tile (there the loop
+  // costs more than the overlap brings)
+  int blocks = (PIPE && items > resident) ? resident : items;
+  return dllm_launch_pdl(gemv_kernel<WARPS, NT, EPI, NORM, PIPE>, dim3(blocks), dim3(WARPS * 32), smem, stream, c, a,
+                         norm_w, eps, w, M, N, K, rope, pf, items);
 }
 
 template <int EPI, bool NORM>
@@ -363,7 +409,8 @@ DLLM_EXPORT int dllm_gemv_bf16(void* c, const void* a, const float* norm_w, floa
                                int K, int epilogue, const void* prefetch_ptr, long long prefetch_bytes,
                                cudaStream_t stream) {
   if (M <= 0 || N <= 0) return DLLM_OK;
-  if (M > 64 || K <= 0 || (K & 7) || ((N & 1) && epilogue == EPI_SWIGLU) || epilogue < 0 || epilogue > EPI_SWIGLU) return DLLM_UNSUPPORTED_SIZE;
+  if (M > 64 || K <= 0 || (K & 7) || ((N & 1) && epilogue == EPI_SWIGLU) || epilogue < 0 || epilogue > EPI_SWIGLU)
+    return DLLM_UNSUPPORTED_SIZE;
   RopeArgs rope{};
   Prefetch pf{(const char*)prefetch_ptr, prefetch_ptr ? (size_t)prefetch_bytes : 0};
   return norm_w ? dispatch<true>(c, a, norm_w, eps, (const bf16*)w, M, N, K, epilogue, rope, pf, stream)

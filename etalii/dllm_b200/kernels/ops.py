@@ -37,6 +37,7 @@ _prototypes = {
                                                      c_void_p, c_void_p, c_int, c_void_p, c_void_p],
     ("gemv", "dllm_gemv_bf16"): [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int,
                                  c_void_p, c_longlong, c_void_p],
+    ("gemv_tma", "dllm_gemv_tma"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     ("gemv", "dllm_gemv_qkv_rope"): [c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_void_p, c_void_p,
                                      c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p,
                                      c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_void_p],
@@ -183,13 +184,25 @@ def streams(rows: int, outputs: int) -> bool:
     return rows <= 16 or (rows <= GEMV_MAX_ROWS and outputs <= 4096)
 
 
+TMA_STREAM_BYTES = 48 << 20
+
+
+def streams_through_shared_memory(rows: int, outputs: int, inner: int) -> bool:
+    """Whether a decode-sized product takes the kernel that streams W through a ring of shared-memory stages.
+    Measured against the kernel that streams through registers: it wins (0.71 to 0.97 of the HBM rate against 0.65 to
+    0.89) for one or two rows of activations, long rows of W (its copies are 2 KB pieces of a row) and matrices of
+    tens of megabytes; with more rows the copies of the activations cost it the lead."""
+    return rows <= 2 and inner >= 4096 and inner % 64 == 0 and 2 * outputs * inner >= TMA_STREAM_BYTES
+
+
 def gemm(c: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int = EPI_STORE_T, kernel: int = 0,
          norm_weight: torch.Tensor | None = None, eps: float = 0.0, tile_n: int = 0) -> None:
     """c = a[M,K] @ w[N,K]^T with float32 accumulation, then the epilogue: EPI_STORE_F32 (c float32), EPI_STORE_T
     (c in the weights' dtype), EPI_RESIDUAL (c float32 += product), EPI_SWIGLU (w interleaves gate and up rows;
     c[M,N/2] = silu(gate) * up). float32 weights run the true 32-bit kernel; bfloat16 the tcgen05/TMA tile kernel
-    or, for M <= 64, the weight-streaming kernel (`kernel`: 0 chooses by M, 1 forces the mma.sync tile kernel, 2
-    forces streaming, 3 forces tcgen05; `tile_n` picks the tcgen05 tile width).
+    or, for M <= 64, a weight-streaming kernel (`kernel`: 0 chooses by the sizes, 1 forces the mma.sync tile kernel,
+    2 forces streaming through registers, 3 forces tcgen05, 4 forces streaming through shared memory; `tile_n`
+    picks the tcgen05 tile width).
     With `norm_weight` (streaming kernel only), `a` is the float32 residual stream and is RMS-normed on the way in."""
     _cuda(c, a, w, norm_weight)
     m, k = a.shape
@@ -207,7 +220,11 @@ def gemm(c: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int = EPI_
                                                    _stream())
     elif w.dtype == torch.bfloat16:
         streaming = (kernel == 2 and m <= GEMV_MAX_ROWS) or (kernel == 0 and streams(m, n))
-        if streaming:
+        if kernel == 4 or (kernel == 0 and norm_weight is None and streams_through_shared_memory(m, n, k)):
+            assert a.dtype == torch.bfloat16 and norm_weight is None
+            status = _fn("gemv_tma", "dllm_gemv_tma")(c.data_ptr(), a.data_ptr(), w.data_ptr(), m, n, k, epilogue,
+                                                      _status_word().data_ptr(), _stream())
+        elif streaming:
             if norm_weight is not None:
                 assert a.dtype == torch.float32 and norm_weight.dtype == torch.float32 and norm_weight.numel() == k
             else:

@@ -191,5 +191,9 @@ def streams(rows, outputs):
     return rows <= 16 or (rows <= 64 and outputs <= 4096)
 
 
+def streams_through_shared_memory(rows, outputs, inner):
+    return False
+
+
 def sample_scratch(rows, vocab):
     return 3 * rows * vocab + 2

@@ -113,6 +113,38 @@ def test_gemm_with_an_odd_number_of_outputs(m, n, k, epilogue, kernel):
     assert rel_error(c.float().cpu(), ref.float().cpu()) <= tol
 
 
+@pytest.mark.parametrize("m", [1, 5, 8, 9, 16])
+@pytest.mark.parametrize("n,k", [(64, 64), (130, 576), (1001, 1088), (4100, 512), (9500, 192), (96, 2624)])
+@pytest.mark.parametrize("epilogue", [0, 1, 2, 3])
+def test_gemm_streaming_through_shared_memory(m, n, k, epilogue):
+    """The bulk-copy ring kernel: tiles of 16 and 32 rows, several trips round the ring, a short last stage, rows of
+    W beyond N, fewer tokens than the fragment holds."""
+    if epilogue == 3 and n % 2:
+        n += 1
+    a, w = _randn((m, k), torch.bfloat16, 3), _randn((n, k), torch.bfloat16, 4, 0.2)
+    cols = n // 2 if epilogue == 3 else n
+    c = _randn((m, cols), torch.float32 if epilogue in (0, 2) else torch.bfloat16, 5)
+    ref = c.clone()
+    ops().gemm(c, a, w, epilogue, kernel=4)
+    torch.cuda.synchronize()
+    ops().raise_if_failed()
+    PK.gemm(ref, a, w, epilogue)
+    assert rel_error(c.float().cpu(), ref.float().cpu()) <= (2e-5 if epilogue in (0, 2) else 8e-3)
+    again = ref.clone()  # the same starting values as c had
+    again.copy_(_randn((m, cols), c.dtype, 5))
+    ops().gemm(again, a, w, epilogue, kernel=4)
+    assert torch.equal(again, c)
+
+
+def test_gemm_streaming_through_shared_memory_refuses_what_it_cannot_run():
+    from etalii.dllm_b200.kernels.ops import KernelError
+
+    for m, k in ((17, 64), (4, 72)):
+        a, w = _randn((m, k), torch.bfloat16, 1), _randn((32, k), torch.bfloat16, 2)
+        with pytest.raises(KernelError):
+            ops().gemm(torch.empty((m, 32), dtype=torch.bfloat16, device=DEV), a, w, 1, kernel=4)
+
+
 def test_swiglu_refuses_an_odd_number_of_rows():
     from etalii.dllm_b200.kernels.ops import KernelError
 
