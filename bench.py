@@ -1,6 +1,8 @@
 """Measures decode and prefill throughput of the engine on one B200 and prints ONE JSON line.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
+                    [--shape smollm2-135m|smollm2-1.7b|llama-3.1-8b] [--batch B] [--no-points]
+                    [--profile decode|prefill|gemm|attention]
 
 Default workload: the SmolLM2-135M shape (30 layers, hidden 576, 9 heads, 3 kv heads, head_dim 64, intermediate 1536,
 vocabulary 49152, tied head) with seeded random bfloat16 weights; a batch of 8 sequences with unequal prompt lengths
@@ -26,6 +28,18 @@ SMOLLM2_135M = {
     "num_key_value_heads": 3, "head_dim": 64, "intermediate_size": 1536, "vocab_size": 49152,
     "rope_theta": 100000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "max_position_embeddings": 8192,
     "hidden_act": "silu", "bos_token_id": 1, "eos_token_id": 2,
+}
+SHAPES = {
+    "smollm2-135m": ("SmolLM2-135M", SMOLLM2_135M),
+    # the two larger shapes of the same architecture (not the default run; `--layers` keeps a slice of them small)
+    "smollm2-1.7b": ("SmolLM2-1.7B", dict(
+        SMOLLM2_135M, num_hidden_layers=24, hidden_size=2048, num_attention_heads=32, num_key_value_heads=32,
+        head_dim=64, intermediate_size=8192, rope_theta=130000.0)),
+    "llama-3.1-8b": ("Llama-3.1-8B", dict(
+        SMOLLM2_135M, num_hidden_layers=32, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8,
+        head_dim=128, intermediate_size=14336, vocab_size=128256, rope_theta=500000.0, tie_word_embeddings=False,
+        rope_scaling={"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                      "original_max_position_embeddings": 8192})),
 }
 FULL_LAYERS = SMOLLM2_135M["num_hidden_layers"]
 PREFILL_TOKENS = 2048
@@ -278,7 +292,9 @@ def main() -> int:
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=256)
     parser.add_argument("--warmup", type=int, default=8)
-    parser.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the full model (named in config)")
+    parser.add_argument("--shape", default="smollm2-135m", choices=sorted(SHAPES),
+                        help="layer sizes: the default is the benchmark's; the others are larger shapes of the family")
+    parser.add_argument("--layers", type=int, default=0, help="fewer layers than the full model (named in config)")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
     parser.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 decode points")
@@ -306,7 +322,10 @@ def main() -> int:
     from etalii.dllm_b200.engine.engine import Engine
     from etalii.dllm_b200.kernels import ops
 
-    config_dict = dict(SMOLLM2_135M, num_hidden_layers=args.layers)
+    shape_name, shape = SHAPES[args.shape]
+    full_layers = shape["num_hidden_layers"]
+    args.layers = args.layers or full_layers
+    config_dict = dict(shape, num_hidden_layers=args.layers)
     config = config_from_dict(config_dict)
     numbers = model_numbers(config_dict, args.layers)
     cache_tokens = 64 * (PREFILL_TOKENS + 64 * ((warmup + args.steps) // 64 + 3))
@@ -357,18 +376,21 @@ def main() -> int:
             points[name] = round(batch * args.steps / (point_ms / 1e3), 1)
 
     line = {
-        "metric": "decode tokens/s (SmolLM2-135M shape, batch 8, bf16, random weights)", "value": round(value, 1),
+        "metric": f"decode tokens/s ({shape_name} shape, batch {args.batch}, bf16, random weights)",
+        "value": round(value, 1),
         "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
         "ms_per_step": round(ms_per_step, 5), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: seeded random token ids, seeded random weights N(0, 0.02)",
         "config": {
-            "model": "SmolLM2-135M shape (llama)", "global_batch": args.batch, "seq_len": config_dict["max_position_embeddings"],
-            "parallelism": "single GPU", "layers": args.layers, "layers_full_model": FULL_LAYERS,
+            "model": f"{shape_name} shape (llama)", "global_batch": args.batch,
+            "seq_len": config_dict["max_position_embeddings"],
+            "parallelism": "single GPU", "layers": args.layers, "layers_full_model": full_layers,
             "hidden": config_dict["hidden_size"], "heads": config_dict["num_attention_heads"],
             "kv_heads": config_dict["num_key_value_heads"], "head_dim": config_dict["head_dim"],
             "intermediate": config_dict["intermediate_size"], "vocab": vocab,
             "prompt_lengths": "128-2048 unequal", "mean_cached_tokens_per_seq": round(mean_cached / args.batch, 1),
-            "l2": "inputs larger than L2 (weights 269 MB + cache per step)", "sampling": "greedy, on device",
+            "l2": f"inputs larger than L2 (weights {weight_bytes / 1e6:.0f} MB + cache per step)",
+            "sampling": "greedy, on device",
             "decode": "CUDA graph per batch size", "peaks": peak["source"],
         },
         "clocks": clocks.summary(),
