@@ -154,6 +154,22 @@ def test_swiglu_refuses_an_odd_number_of_rows():
             ops().gemm(torch.empty((4, 4), dtype=dtype, device=DEV), a, w, 3, kernel)
 
 
+@pytest.mark.parametrize("m,n,k", [(3, 5008, 2112), (16, 4800, 4160), (40, 9552, 2240), (1, 300, 6400)])
+@pytest.mark.parametrize("epilogue", [0, 1, 2, 3])
+def test_streaming_products_with_long_rows(m, n, k, epilogue):
+    """Rows of more than 2,048 values: the variants that ask for the next stretch early, and whose blocks walk over
+    several tiles when there are more tiles than blocks fit on the device."""
+    a, w = _randn((m, k), torch.bfloat16, 3), _randn((n, k), torch.bfloat16, 4, 0.05)
+    cols = n // 2 if epilogue == 3 else n
+    c = _randn((m, cols), torch.float32 if epilogue in (0, 2) else torch.bfloat16, 5)
+    ref = c.clone()
+    ops().gemm(c, a, w, epilogue, kernel=2)
+    PK.gemm(ref, a, w, epilogue)
+    assert rel_error(c.float().cpu(), ref.float().cpu()) <= (2e-5 if epilogue in (0, 2) else 8e-3)
+    worst = (c.float().cpu() - ref.float().cpu()).abs().max(dim=0).values  # per output column: no tile left out
+    assert float(worst.max()) <= 2e-2 * float(ref.float().abs().max()), int(worst.argmax())
+
+
 def test_gemm_refuses_sizes_it_cannot_run():
     from etalii.dllm_b200.kernels.ops import KernelError
 
@@ -386,14 +402,24 @@ def test_gemv_with_the_norm_in_front(m, n, k, epilogue):
 @pytest.mark.parametrize("normed", [False, True])
 @pytest.mark.parametrize("rows_extra", [1, 40])
 def test_gemv_qkv_rope(heads, kv_heads, head_dim, rotary, normed, rows_extra):
-    lengths, new, k = [70, 5, 129, 64, 200, 33], [1, 1, 3, 2, rows_extra, 1], 136
+    _check_gemv_qkv_rope(heads, kv_heads, head_dim, rotary, normed, rows_extra, 136)
+
+
+@pytest.mark.parametrize("normed", [False, True])
+def test_gemv_qkv_rope_long_rows_and_more_tiles_than_blocks(normed):
+    """Rows of W of more than 2,048 values and 448 tiles: the variant whose blocks walk over several tiles."""
+    _check_gemv_qkv_rope(40, 8, 128, 128, normed, 3, 2240)
+
+
+def _check_gemv_qkv_rope(heads, kv_heads, head_dim, rotary, normed, rows_extra, k):
+    lengths, new = [70, 5, 129, 64, 200, 33], [1, 1, 3, 2, rows_extra, 1]
     cache, view, batch = _cache_and_batch(torch.bfloat16, kv_heads, head_dim, lengths, new)
     n = batch.n_tokens
     table = None
     if rotary:
         angles = torch.arange(256, dtype=torch.float64)[:, None] * torch.rand(rotary // 2, dtype=torch.float64)[None]
         table = torch.stack([angles.cos(), angles.sin()], -1).float().to(DEV)
-    w = _randn(((heads + 2 * kv_heads) * head_dim, k), torch.bfloat16, 4, 0.2)
+    w = _randn(((heads + 2 * kv_heads) * head_dim, k), torch.bfloat16, 4, 0.2 if k < 1000 else 0.05)
     x = _randn((n, k), torch.float32 if normed else torch.bfloat16, 6)
     nw = _randn((k,), torch.float32, 8) * 0.1 + 1
     q = torch.zeros((n, heads * head_dim), dtype=torch.bfloat16, device=DEV)
