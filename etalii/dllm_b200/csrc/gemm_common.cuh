@@ -12,6 +12,12 @@
 #define EPI_RESIDUAL 2
 #define EPI_SWIGLU 3
 #define EPI_QKV_ROPE 4  // q/k/v projection: rotate q and k, q to its buffer, k and v into the paged cache
+// The same four for a product computed the other way round (the accumulator tile is C^T: its rows are output
+// features, its columns tokens), used when the tokens are few and W is the 128-row operand of the tensor cores:
+#define EPI_T_STORE_F32 5
+#define EPI_T_STORE_T 6
+#define EPI_T_RESIDUAL 7
+#define EPI_T_SWIGLU 8
 
 // What the q/k/v epilogue needs: where queries go, where the cache is, the rotation table, who the tokens are.
 struct RopeArgs {
@@ -116,4 +122,40 @@ __device__ __forceinline__ void epilogue_row16(void* __restrict__ c, int m, int 
   }
 #pragma unroll
   for (int i = 0; i < 16; i += 2) epilogue_pair<EPI, T>(c, m, n + i, M, N, v[i], v[i + 1]);
+}
+
+// Sixteen consecutive tokens token0 .. token0+15 of one output feature held by one thread, the lanes of the warp
+// holding consecutive features (the accumulator is C^T). C is [tokens, features] as always, so a warp's stores for
+// one token are contiguous. Every lane of the warp must call this (the SwiGLU pairs sit in neighbouring lanes).
+template <int EPI, typename T>
+__device__ __forceinline__ void epilogue_col16(void* __restrict__ c, int feature, int token0, int features, int tokens,
+                                               const float* v) {
+  if (EPI == EPI_T_SWIGLU) {
+    T* out = (T*)c;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float up = __shfl_xor_sync(0xffffffffu, v[i], 1);  // the odd lane's value: up_i beside gate_i
+      if (!(feature & 1) && feature + 1 < features && token0 + i < tokens)
+        out[(size_t)(token0 + i) * (features / 2) + (feature >> 1)] = from_float<T>(silu_for<T>(v[i]) * up);
+    }
+    return;
+  }
+  if (feature >= features) return;
+  if (EPI == EPI_T_RESIDUAL) {  // all sixteen loads first: one round trip, not sixteen
+    float old[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      old[i] = token0 + i < tokens ? ((const float*)c)[(size_t)(token0 + i) * features + feature] : 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      if (token0 + i < tokens) ((float*)c)[(size_t)(token0 + i) * features + feature] = old[i] + v[i];
+    return;
+  }
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    if (token0 + i >= tokens) break;
+    size_t at = (size_t)(token0 + i) * features + feature;
+    if (EPI == EPI_T_STORE_F32) ((float*)c)[at] = v[i];
+    else ((T*)c)[at] = from_float<T>(v[i]);
+  }
 }

@@ -188,7 +188,8 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
           float f[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) f[i] = __uint_as_float(v[i]);
-          epilogue_row16<EPI, bf16>(c, m, n0 + col, M, N, f);
+          if (EPI >= EPI_T_STORE_F32) epilogue_col16<EPI, bf16>(c, m, n0 + col, M, N, f);  // the tile is C^T
+          else epilogue_row16<EPI, bf16>(c, m, n0 + col, M, N, f);
         }
       }
     }
@@ -236,6 +237,10 @@ int dispatch(void* c, const void* a, const void* w, int M, int N, int K, int epi
     case EPI_STORE_T: return launch<BN, EPI_STORE_T>(c, a, w, M, N, K, status, stream);
     case EPI_RESIDUAL: return launch<BN, EPI_RESIDUAL>(c, a, w, M, N, K, status, stream);
     case EPI_SWIGLU: return launch<BN, EPI_SWIGLU>(c, a, w, M, N, K, status, stream);
+    case EPI_T_STORE_F32: return launch<BN, EPI_T_STORE_F32>(c, a, w, M, N, K, status, stream);
+    case EPI_T_STORE_T: return launch<BN, EPI_T_STORE_T>(c, a, w, M, N, K, status, stream);
+    case EPI_T_RESIDUAL: return launch<BN, EPI_T_RESIDUAL>(c, a, w, M, N, K, status, stream);
+    case EPI_T_SWIGLU: return launch<BN, EPI_T_SWIGLU>(c, a, w, M, N, K, status, stream);
     default: return DLLM_BAD_ARGUMENT;
   }
 }
@@ -245,10 +250,14 @@ int dispatch(void* c, const void* a, const void* w, int M, int N, int K, int epi
 // pitch for TMA), N even for the SwiGLU epilogue, and A and W 16-byte aligned. `tile_n`: 32, 64 or 128 columns of C per block (0 chooses).
 // `status` is a word the device can write (device or pinned host memory); the kernel sets it non-zero if one of its
 // bounded waits ran out (2: producer, 3: product issuer, 4: epilogue).
+// Epilogues 5..8 are 0..3 for a product taken the other way round: the caller passes W as A (M = output features)
+// and the activations as W (N = tokens), and C is still [tokens, features]; for a few tokens and a large W this
+// streams W through 128-row tiles once instead of re-reading it for every 128 rows of a mostly empty tile of tokens.
 DLLM_EXPORT int dllm_gemm_tcgen05(void* c, const void* a, const void* w, int M, int N, int K, int epilogue, int tile_n,
                                   int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return DLLM_OK;
-  if (K <= 0 || (K & 7) || ((N & 1) && epilogue == EPI_SWIGLU) || ((uintptr_t)a & 15) || ((uintptr_t)w & 15) || status == nullptr)
+  if (K <= 0 || (K & 7) || ((N & 1) && epilogue == EPI_SWIGLU) || ((M & 1) && epilogue == EPI_T_SWIGLU) ||
+      ((uintptr_t)a & 15) || ((uintptr_t)w & 15) || status == nullptr)
     return DLLM_UNSUPPORTED_SIZE;
   if (tile_n == 0) {
     long long tiles256 = (long long)((M + BM - 1) / BM) * ((N + 255) / 256);

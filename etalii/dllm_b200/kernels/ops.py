@@ -195,14 +195,22 @@ def streams_through_shared_memory(rows: int, outputs: int, inner: int) -> bool:
     return rows <= 2 and inner >= 4096 and inner % 64 == 0 and 2 * outputs * inner >= TMA_STREAM_BYTES
 
 
+def takes_weights_as_rows(rows: int, outputs: int, inner: int) -> bool:
+    """Whether a product with 17 to 64 rows of activations runs the other way round on the tile kernel (W as the
+    128-row operand, read once). Measured: it wins where W has at least as many 128-row tiles as the device has
+    multiprocessors (28672 x 4096 with 64 rows: 49 µs against 89 µs for the tile kernel and 187 µs for the streaming
+    one; 16384 x 2048: 17 against 25); with fewer tiles a block's rate is bound by its one lane issuing products."""
+    return 16 < rows <= 64 and outputs >= 16384 and 2 * outputs * inner >= (32 << 20)
+
+
 def gemm(c: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int = EPI_STORE_T, kernel: int = 0,
          norm_weight: torch.Tensor | None = None, eps: float = 0.0, tile_n: int = 0) -> None:
     """c = a[M,K] @ w[N,K]^T with float32 accumulation, then the epilogue: EPI_STORE_F32 (c float32), EPI_STORE_T
     (c in the weights' dtype), EPI_RESIDUAL (c float32 += product), EPI_SWIGLU (w interleaves gate and up rows;
     c[M,N/2] = silu(gate) * up). float32 weights run the true 32-bit kernel; bfloat16 the tcgen05/TMA tile kernel
     or, for M <= 64, a weight-streaming kernel (`kernel`: 0 chooses by the sizes, 1 forces the mma.sync tile kernel,
-    2 forces streaming through registers, 3 forces tcgen05, 4 forces streaming through shared memory; `tile_n`
-    picks the tcgen05 tile width).
+    2 forces streaming through registers, 3 forces tcgen05, 4 forces streaming through shared memory, 5 forces
+    tcgen05 with W as the 128-row operand (for at most 256 rows of `a`); `tile_n` picks the tcgen05 tile width).
     With `norm_weight` (streaming kernel only), `a` is the float32 residual stream and is RMS-normed on the way in."""
     _cuda(c, a, w, norm_weight)
     m, k = a.shape
@@ -220,7 +228,14 @@ def gemm(c: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int = EPI_
                                                    _stream())
     elif w.dtype == torch.bfloat16:
         streaming = (kernel == 2 and m <= GEMV_MAX_ROWS) or (kernel == 0 and streams(m, n))
-        if kernel == 4 or (kernel == 0 and norm_weight is None and streams_through_shared_memory(m, n, k)):
+        if kernel == 5 or (kernel == 0 and norm_weight is None and takes_weights_as_rows(m, n, k)):
+            # the product the other way round: W is the 128-row operand, the tokens are the tile's columns
+            assert a.dtype == torch.bfloat16 and norm_weight is None and m <= 256
+            width = 32 if m <= 32 else (64 if m <= 64 else (128 if m <= 128 else 256))
+            status = _fn("gemm_tcgen05", "dllm_gemm_tcgen05")(
+                c.data_ptr(), w.data_ptr(), a.data_ptr(), n, m, k, epilogue + 5, width, _status_word().data_ptr(),
+                _stream())
+        elif kernel == 4 or (kernel == 0 and norm_weight is None and streams_through_shared_memory(m, n, k)):
             assert a.dtype == torch.bfloat16 and norm_weight is None
             status = _fn("gemv_tma", "dllm_gemv_tma")(c.data_ptr(), a.data_ptr(), w.data_ptr(), m, n, k, epilogue,
                                                       _status_word().data_ptr(), _stream())

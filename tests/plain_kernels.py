@@ -191,6 +191,10 @@ def streams(rows, outputs):
     return rows <= 16 or (rows <= 64 and outputs <= 4096)
 
 
+def takes_weights_as_rows(rows, outputs, inner):
+    return False
+
+
 def streams_through_shared_memory(rows, outputs, inner):
     return False
 

@@ -136,6 +136,25 @@ def test_gemm_streaming_through_shared_memory(m, n, k, epilogue):
     assert torch.equal(again, c)
 
 
+@pytest.mark.parametrize("m", [1, 17, 33, 64, 100, 256])
+@pytest.mark.parametrize("n,k", [(128, 64), (130, 576), (1001, 1088), (4100, 512), (300, 2240), (19000, 128)])
+@pytest.mark.parametrize("epilogue", [0, 1, 2, 3])
+def test_gemm_with_weights_as_rows(m, n, k, epilogue):
+    """The tile kernel the other way round (W as the 128-row operand, the accumulator tile is C^T): every width of
+    the token tile, features beyond the last tile of W, tokens beyond the tile, fewer and more tiles than blocks."""
+    if epilogue == 3 and n % 2:
+        n += 1
+    a, w = _randn((m, k), torch.bfloat16, 3), _randn((n, k), torch.bfloat16, 4, 0.2)
+    cols = n // 2 if epilogue == 3 else n
+    c = _randn((m, cols), torch.float32 if epilogue in (0, 2) else torch.bfloat16, 5)
+    ref = c.clone()
+    ops().gemm(c, a, w, epilogue, kernel=5)
+    torch.cuda.synchronize()
+    ops().raise_if_failed()
+    PK.gemm(ref, a, w, epilogue)
+    assert rel_error(c.float().cpu(), ref.float().cpu()) <= (2e-5 if epilogue in (0, 2) else 8e-3)
+
+
 def test_gemm_streaming_through_shared_memory_refuses_what_it_cannot_run():
     from etalii.dllm_b200.kernels.ops import KernelError
 
