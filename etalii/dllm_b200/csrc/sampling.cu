@@ -1,4 +1,7 @@
-// Token choice on the device, one block per row of logits.
+// Token choice on the device. A row of logits is the work of a thread-block cluster of 1, 2, 4 or 8 blocks (the fewer
+// rows, the more blocks a row gets): the blocks take interleaved stripes of the vocabulary, and every sum or maximum
+// over the row goes through distributed shared memory (each block publishes its part, one cluster barrier, every
+// block adds the parts in rank order: all blocks hold the same totals and take the same decisions).
 //   temperature 0: the first index of the largest logit.
 //   temperature > 0: z = float(logit / float(T)); p = float(exp(z - max) / sum) with the exponentials and the sum in
 //   double; candidates in the total order (p descending, id ascending); top-k keeps the first k, top-p the shortest
@@ -25,16 +28,49 @@ struct Found {
 
 constexpr int BINS = 16;  // four bits of the key per pass
 
+
 struct Shared {
+  unsigned long long out_u64[2][2 * BINS];  // what this block publishes to its cluster: two sets, used in turn
+  double out_d[2];
+  float out_f[2];
+  int out_i[2];
+  unsigned out_u32[2];
   unsigned long long count[BINS];
   unsigned long long mass[BINS];
-  unsigned long long part_count[BINS][THREADS / BINS];
-  unsigned long long part_mass[BINS][THREADS / BINS];
+  unsigned long long part_count[BINS][2];
+  unsigned long long part_mass[BINS][2];
   Found found;
   double reduce_d[32];
   float reduce_f[32];
   int reduce_i[32];
   unsigned tie_counts[THREADS];
+};
+
+// ---- the cluster: barrier and reads of the same variable in another block's shared memory
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n"
+               "barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ unsigned remote_addr(const void* local, unsigned rank) {
+  unsigned addr = (unsigned)__cvta_generic_to_shared(local), remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+  return remote;
+}
+__device__ __forceinline__ unsigned long long remote_u64(const unsigned long long* local, unsigned rank) {
+  unsigned long long v;
+  asm volatile("ld.shared::cluster.u64 %0, [%1];" : "=l"(v) : "r"(remote_addr(local, rank)) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned remote_u32(const void* local, unsigned rank) {
+  unsigned v;
+  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(remote_addr(local, rank)) : "memory");
+  return v;
+}
+// Which of the two sets of published values the next exchange uses. A block may publish into a set again only
+// after every block has read it: between two uses of the same set lies the barrier of the exchange in between.
+struct Turn {
+  int set = 0;
+  __device__ __forceinline__ int next() { int s = set; set ^= 1; return s; }
 };
 
 // p * 2^62 truncated, for 0 <= p <= 1, by integer shifts of the mantissa (the same value as the double product).
@@ -52,9 +88,12 @@ __device__ __forceinline__ unsigned long long to_fx(float p) {
 // Probabilities are not negative, so the key is their bits shifted left by one (the sign gone), taken four bits at a
 // time from the top. Every thread counts into 16 bins of its own in shared memory (hist_count[bin][thread],
 // hist_mass[bin][thread]: no atomics, no bank conflicts: most probabilities share their leading bits and would queue
-// on a handful of shared counters), then the bins are summed over the threads in two fixed stages.
+// on a handful of shared counters), then the bins are summed over the threads (a fixed tree) and over the blocks of
+// the cluster in rank order. Every block walks the same totals and finds the same boundary.
+template <int CL>
 __device__ void find_prefix(const float* __restrict__ p, int vocab, int kind, unsigned long long target, Shared& sh,
-                            unsigned* __restrict__ hist_count, unsigned long long* __restrict__ hist_mass) {
+                            unsigned* __restrict__ hist_count, unsigned long long* __restrict__ hist_mass,
+                            unsigned rank, Turn& turn) {
   unsigned prefix = 0;
   unsigned long long above_count = 0, above_mass = 0;
   int tid = threadIdx.x;
@@ -65,10 +104,11 @@ __device__ void find_prefix(const float* __restrict__ p, int vocab, int kind, un
       hist_mass[bin * THREADS + tid] = 0ull;
     }
     if (tid == 0) sh.found.ok = 0;
-    for (int i0 = tid; i0 < vocab; i0 += 8 * THREADS) {
+    for (int i0 = (int)rank * THREADS + tid; i0 < vocab; i0 += 8 * CL * THREADS) {
       float v[8];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) v[u] = i0 + u * THREADS < vocab ? p[i0 + u * THREADS] : -1.f;  // loads first
+      for (int u = 0; u < 8; ++u)  // loads first
+        v[u] = i0 + u * CL * THREADS < vocab ? p[i0 + u * CL * THREADS] : -1.f;
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
         unsigned key = __float_as_uint(v[u]) << 1;
@@ -80,21 +120,36 @@ __device__ void find_prefix(const float* __restrict__ p, int vocab, int kind, un
       }
     }
     __syncthreads();
-    {  // stage 1: thread t adds 16 threads' counters of bin t / 64
-      int bin = tid / (THREADS / BINS), strip = tid % (THREADS / BINS);
+    {  // stage 1: warps 2b and 2b + 1 add bin b over the two halves of the block's threads (lanes stride through
+       // the threads, then the warp adds up by shuffles: a fixed tree)
+      int warp = tid >> 5, lane = tid & 31;
+      int bin = warp >> 1, half = warp & 1;
       unsigned long long c = 0, m = 0;
 #pragma unroll
-      for (int j = 0; j < BINS; ++j) {
-        c += hist_count[bin * THREADS + strip * BINS + j];
-        m += hist_mass[bin * THREADS + strip * BINS + j];
+      for (int j = 0; j < THREADS / 64; ++j) {
+        c += hist_count[bin * THREADS + half * (THREADS / 2) + j * 32 + lane];
+        m += hist_mass[bin * THREADS + half * (THREADS / 2) + j * 32 + lane];
       }
-      sh.part_count[bin][strip] = c;
-      sh.part_mass[bin][strip] = m;
+      for (int o = 16; o > 0; o >>= 1) {
+        c += __shfl_xor_sync(0xffffffffu, c, o);
+        m += __shfl_xor_sync(0xffffffffu, m, o);
+      }
+      if (lane == 0) { sh.part_count[bin][half] = c; sh.part_mass[bin][half] = m; }
     }
     __syncthreads();
-    if (tid < BINS) {  // stage 2: one thread per bin adds the 64 partial sums
+    int set = turn.next();
+    if (tid < BINS) {  // stage 2: the block's bins, published to the cluster
+      sh.out_u64[set][tid] = sh.part_count[tid][0] + sh.part_count[tid][1];
+      sh.out_u64[set][BINS + tid] = sh.part_mass[tid][0] + sh.part_mass[tid][1];
+    }
+    cluster_sync();
+    if (tid < BINS) {  // stage 3: the cluster's bins, blocks in rank order
       unsigned long long c = 0, m = 0;
-      for (int j = 0; j < THREADS / BINS; ++j) { c += sh.part_count[tid][j]; m += sh.part_mass[tid][j]; }
+#pragma unroll
+      for (unsigned r = 0; r < CL; ++r) {
+        c += remote_u64(&sh.out_u64[set][tid], r);
+        m += remote_u64(&sh.out_u64[set][BINS + tid], r);
+      }
       sh.count[tid] = c;
       sh.mass[tid] = m;
     }
@@ -123,7 +178,7 @@ __device__ void find_prefix(const float* __restrict__ p, int vocab, int kind, un
       }
     }
     __syncthreads();
-    if (!sh.found.ok) return;  // the whole vocabulary does not reach the target
+    if (!sh.found.ok) return;  // the whole vocabulary does not reach the target (every block sees the same)
     prefix = sh.found.bits;
     above_count = sh.found.above_count;
     above_mass = sh.found.above_mass;
@@ -133,14 +188,14 @@ __device__ void find_prefix(const float* __restrict__ p, int vocab, int kind, un
     Found& f = sh.found;
     f.bits >>= 1;  // from the key back to the bits of the probability
     unsigned long long each = f.tie_count ? f.tie_mass / f.tie_count : 0;
-    unsigned long long rank;
-    if (kind == FIND_COUNT) rank = target - f.above_count;
-    else if (each == 0) rank = 1;
-    else if (kind == FIND_MASS_GE) rank = (target - f.above_mass + each - 1) / each;
-    else rank = (target - f.above_mass) / each + 1;
-    if (rank < 1) rank = 1;
-    if (rank > f.tie_count) rank = f.tie_count;
-    f.rank = rank;
+    unsigned long long rank_in_ties;
+    if (kind == FIND_COUNT) rank_in_ties = target - f.above_count;
+    else if (each == 0) rank_in_ties = 1;
+    else if (kind == FIND_MASS_GE) rank_in_ties = (target - f.above_mass + each - 1) / each;
+    else rank_in_ties = (target - f.above_mass) / each + 1;
+    if (rank_in_ties < 1) rank_in_ties = 1;
+    if (rank_in_ties > f.tie_count) rank_in_ties = f.tie_count;
+    f.rank = rank_in_ties;
   }
   __syncthreads();
 }
@@ -156,31 +211,53 @@ __device__ double next_double(unsigned long long* s) {  // xoshiro256**, top 53 
   return (double)(result >> 11) * (1.0 / 9007199254740992.0);
 }
 
-__device__ double block_sum_d(double v, Shared& sh) {
-  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  __syncthreads();
-  if (lane == 0) sh.reduce_d[warp] = v;
-  __syncthreads();
-  double total = 0.0;
-  for (int i = 0; i < THREADS / 32; ++i) total += sh.reduce_d[i];  // same order in every thread
-  return total;
-}
-
-__device__ unsigned long long block_sum_u64(unsigned long long v, Shared& sh) {
+// Sums over the cluster: the block's sum first (warps by shuffles, then the warps' sums in warp order), published,
+// then the blocks' sums in rank order. Every thread of every block returns the same value.
+template <int CL>
+__device__ unsigned long long cluster_sum_u64(unsigned long long v, Shared& sh, Turn& turn) {
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   unsigned long long* slots = reinterpret_cast<unsigned long long*>(sh.reduce_d);
   __syncthreads();
   if (lane == 0) slots[warp] = v;
   __syncthreads();
+  int set = turn.next();
+  if (threadIdx.x == 0) {
+    unsigned long long block = 0;
+    for (int i = 0; i < THREADS / 32; ++i) block += slots[i];
+    sh.out_u64[set][0] = block;
+  }
+  cluster_sync();
   unsigned long long total = 0;
-  for (int i = 0; i < THREADS / 32; ++i) total += slots[i];
+#pragma unroll
+  for (unsigned r = 0; r < CL; ++r) total += remote_u64(&sh.out_u64[set][0], r);
   return total;
 }
 
-// (value, index) maximum; ties go to the lower index
-__device__ void block_argmax(float& v, int& idx, Shared& sh) {
+template <int CL>
+__device__ double cluster_sum_d(double v, Shared& sh, Turn& turn) {
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();
+  if (lane == 0) sh.reduce_d[warp] = v;
+  __syncthreads();
+  int set = turn.next();
+  if (threadIdx.x == 0) {
+    double block = 0.0;
+    for (int i = 0; i < THREADS / 32; ++i) block += sh.reduce_d[i];
+    sh.out_d[set] = block;
+  }
+  cluster_sync();
+  double total = 0.0;
+#pragma unroll
+  for (unsigned r = 0; r < CL; ++r)
+    total += __longlong_as_double((long long)remote_u64(reinterpret_cast<unsigned long long*>(&sh.out_d[set]), r));
+  return total;
+}
+
+// (value, index) maximum over the cluster; ties go to the lower index
+template <int CL>
+__device__ void cluster_argmax(float& v, int& idx, Shared& sh, Turn& turn) {
   for (int o = 16; o > 0; o >>= 1) {
     float ov = __shfl_xor_sync(0xffffffffu, v, o);
     int oi = __shfl_xor_sync(0xffffffffu, idx, o);
@@ -190,14 +267,30 @@ __device__ void block_argmax(float& v, int& idx, Shared& sh) {
   __syncthreads();
   if (lane == 0) { sh.reduce_f[warp] = v; sh.reduce_i[warp] = idx; }
   __syncthreads();
-  v = sh.reduce_f[0]; idx = sh.reduce_i[0];
-  for (int i = 1; i < THREADS / 32; ++i) {
-    float ov = sh.reduce_f[i];
-    int oi = sh.reduce_i[i];
+  int set = turn.next();
+  if (threadIdx.x == 0) {
+    float bv = sh.reduce_f[0];
+    int bi = sh.reduce_i[0];
+    for (int i = 1; i < THREADS / 32; ++i) {
+      float ov = sh.reduce_f[i];
+      int oi = sh.reduce_i[i];
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    sh.out_f[set] = bv;
+    sh.out_i[set] = bi;
+  }
+  cluster_sync();
+  v = __uint_as_float(remote_u32(&sh.out_f[set], 0));
+  idx = (int)remote_u32(&sh.out_i[set], 0);
+#pragma unroll
+  for (unsigned r = 1; r < CL; ++r) {
+    float ov = __uint_as_float(remote_u32(&sh.out_f[set], r));
+    int oi = (int)remote_u32(&sh.out_i[set], r);
     if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
   }
 }
 
+template <int CL>
 __global__ void __launch_bounds__(THREADS) sample_kernel(
     int* __restrict__ out_tokens, const float* __restrict__ logits, long long row_stride, int vocab,
     float* __restrict__ scratch, unsigned long long* __restrict__ rng, const int* __restrict__ rng_rows,
@@ -206,39 +299,43 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(
   extern __shared__ __align__(16) unsigned char hist_raw[];  // hist_mass[BINS][THREADS], then hist_count[BINS][THREADS]
   unsigned long long* hist_mass = reinterpret_cast<unsigned long long*>(hist_raw);
   unsigned* hist_count = reinterpret_cast<unsigned*>(hist_mass + BINS * THREADS);
-  int row = blockIdx.x, tid = threadIdx.x;
+  unsigned rank = blockIdx.x;  // cluster dims are (CL, 1, 1) and gridDim.x == CL
+  int row = blockIdx.y, rows = gridDim.y, tid = threadIdx.x;
+  const int first = (int)rank * THREADS + tid, stride = CL * THREADS;  // this thread's stripe of the vocabulary
+  Turn turn;
   pdl_launch_dependents();
   pdl_wait();
   const float* l = logits + (size_t)row * row_stride;
   float best = -INFINITY;
   int best_i = 0x7fffffff;
   if (temperature == 0.f) {
-    for (int i = tid; i < vocab; i += THREADS) {
+    for (int i = first; i < vocab; i += stride) {
       float v = l[i];
       if (v > best) { best = v; best_i = i; }
     }
-    block_argmax(best, best_i, sh);
-    if (tid == 0) out_tokens[row] = best_i == 0x7fffffff ? 0 : best_i;
+    cluster_argmax<CL>(best, best_i, sh, turn);
+    if (rank == 0 && tid == 0) out_tokens[row] = best_i == 0x7fffffff ? 0 : best_i;
+    cluster_sync();  // nobody leaves while its published values may still be read
     return;
   }
   float* p = scratch + (size_t)row * vocab;
-  for (int i = tid; i < vocab; i += THREADS) {
+  for (int i = first; i < vocab; i += stride) {
     float z = __fdiv_rn(l[i], temperature);
     p[i] = z;
     if (z > best) { best = z; best_i = i; }
   }
-  block_argmax(best, best_i, sh);
-  size_t floats = (((size_t)gridDim.x * vocab) + 1) & ~(size_t)1;  // the doubles start 8-byte aligned behind the floats
+  cluster_argmax<CL>(best, best_i, sh, turn);
+  size_t floats = (((size_t)rows * vocab) + 1) & ~(size_t)1;  // the doubles start 8-byte aligned behind the floats
   double* e = reinterpret_cast<double*>(scratch + floats) + (size_t)row * vocab;
   double partial = 0.0;
-  for (int i = tid; i < vocab; i += THREADS) {
+  for (int i = first; i < vocab; i += stride) {
     double ex = exp((double)p[i] - (double)best);  // once per logit, kept in double for the division below
     e[i] = ex;
     partial += ex;
   }
-  double inverse = 1.0 / block_sum_d(partial, sh);
+  double inverse = 1.0 / cluster_sum_d<CL>(partial, sh, turn);
   unsigned long long all_mass = 0;  // this thread's share of the total mass, in fixed point (exact integer sums)
-  for (int i = tid; i < vocab; i += THREADS) {
+  for (int i = first; i < vocab; i += stride) {
     float v = (float)(e[i] * inverse);
     p[i] = v;
     all_mass += to_fx(v);
@@ -248,7 +345,7 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(
   unsigned long long keep = (unsigned long long)vocab;
   if (top_k > 0 && (unsigned long long)top_k < keep) keep = (unsigned long long)top_k;
   if (top_p < 1.0) {
-    find_prefix(p, vocab, FIND_MASS_GE, (unsigned long long)(top_p * FX_ONE), sh, hist_count, hist_mass);
+    find_prefix<CL>(p, vocab, FIND_MASS_GE, (unsigned long long)(top_p * FX_ONE), sh, hist_count, hist_mass, rank, turn);
     if (sh.found.ok) {
       unsigned long long n = sh.found.above_count + sh.found.rank;
       if (n < keep) keep = n;
@@ -256,35 +353,36 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(
     __syncthreads();
   }
   if (min_p > 0.0) {
-    double floor_p = min_p * (double)p[best_i];
-    unsigned local = 0;
-    for (int i = tid; i < vocab; i += THREADS) local += ((double)p[i] >= floor_p) ? 1u : 0u;
-    unsigned long long n = (unsigned long long)block_sum_d((double)local, sh);
+    cluster_sync();  // the largest probability may have been written by another block of the cluster
+    double floor_p = min_p * (double)__ldcg(p + best_i);
+    unsigned long long local = 0;
+    for (int i = first; i < vocab; i += stride) local += ((double)p[i] >= floor_p) ? 1ull : 0ull;
+    unsigned long long n = cluster_sum_u64<CL>(local, sh, turn);
     if (n >= 1 && n < keep) keep = n;
   }
   unsigned long long total;
   if (keep >= (unsigned long long)vocab) {  // everything is kept: the total is a plain sum, no search needed
-    total = block_sum_u64(all_mass, sh);
+    total = cluster_sum_u64<CL>(all_mass, sh, turn);
   } else {
-    find_prefix(p, vocab, FIND_COUNT, keep, sh, hist_count, hist_mass);
+    find_prefix<CL>(p, vocab, FIND_COUNT, keep, sh, hist_count, hist_mass, rank, turn);
     unsigned long long each = sh.found.tie_count ? sh.found.tie_mass / sh.found.tie_count : 0;
     total = sh.found.above_mass + sh.found.rank * each;
   }
   __syncthreads();
-  unsigned long long* state = rng + (size_t)rng_rows[row] * 4;
-  double u;
-  if (tid == 0) {
+  // one draw per row: the first block of the cluster advances the row's generator and passes the number on
+  // (the others contribute an exact zero to the sum)
+  double u = 0.0;
+  if (rank == 0 && tid == 0) {
+    unsigned long long* state = rng + (size_t)rng_rows[row] * 4;
     unsigned long long s[4] = {state[0], state[1], state[2], state[3]};
     u = next_double(s);
     state[0] = s[0]; state[1] = s[1]; state[2] = s[2]; state[3] = s[3];
-    sh.reduce_d[0] = u;
   }
-  __syncthreads();
-  u = sh.reduce_d[0];
+  u = cluster_sum_d<CL>(u, sh, turn);
   unsigned long long target = (unsigned long long)(u * (double)total);
   if (total > 0 && target >= total) target = total - 1;
   __syncthreads();
-  find_prefix(p, vocab, FIND_MASS_GT, target, sh, hist_count, hist_mass);
+  find_prefix<CL>(p, vocab, FIND_MASS_GT, target, sh, hist_count, hist_mass, rank, turn);
   unsigned want_bits;
   unsigned long long want_rank;
   if (sh.found.ok) {
@@ -295,20 +393,34 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(
     if (position > keep) want_rank = keep > sh.found.above_count ? keep - sh.found.above_count : 1;
   } else {  // nothing exceeds the target (all mass is zero): the reference takes the last kept candidate
     __syncthreads();
-    find_prefix(p, vocab, FIND_COUNT, keep, sh, hist_count, hist_mass);
+    find_prefix<CL>(p, vocab, FIND_COUNT, keep, sh, hist_count, hist_mass, rank, turn);
     want_bits = sh.found.bits;
     want_rank = sh.found.rank;
   }
-  __syncthreads();
-  // the want_rank-th id, ascending, among the elements whose probability has exactly want_bits
-  int chunk = (vocab + THREADS - 1) / THREADS;
-  int lo = min(tid * chunk, vocab), hi = min(lo + chunk, vocab);
+  // the want_rank-th id, ascending, among the elements whose probability has exactly want_bits: ids in contiguous
+  // pieces now, a piece per thread of the cluster (the probabilities of other blocks' stripes are read here)
+  cluster_sync();
+  int chunk = (vocab + stride - 1) / stride;
+  int lo = min(first * chunk, vocab), hi = min(lo + chunk, vocab);
   unsigned mine = 0;
-  for (int i = lo; i < hi; ++i) mine += __float_as_uint(p[i]) == want_bits ? 1u : 0u;
+  for (int i = lo; i < hi; ++i) mine += __float_as_uint(__ldcg(p + i)) == want_bits ? 1u : 0u;
   sh.tie_counts[tid] = mine;
   __syncthreads();
+  int set = turn.next();
   if (tid == 0) {
-    unsigned long long seen = 0;
+    unsigned block_ties = 0;
+    for (int i = 0; i < THREADS; ++i) block_ties += sh.tie_counts[i];
+    sh.out_u32[set] = block_ties;
+  }
+  cluster_sync();
+  unsigned long long before_block = 0;  // ties in the blocks of lower rank (their ids are lower)
+#pragma unroll
+  for (unsigned r = 0; r < CL; ++r)
+    if (r < rank) before_block += remote_u32(&sh.out_u32[set], r);
+  unsigned my_ties = remote_u32(&sh.out_u32[set], rank);
+  bool here = before_block < want_rank && want_rank <= before_block + my_ties;  // true in exactly one block
+  if (here && tid == 0) {
+    unsigned long long seen = before_block;
     int owner = THREADS - 1;
     for (int i = 0; i < THREADS; ++i) {
       if (seen + sh.tie_counts[i] >= want_rank) { owner = i; break; }
@@ -318,14 +430,15 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(
     sh.found.above_count = seen;
   }
   __syncthreads();
-  if (tid == sh.reduce_i[0]) {
+  if (here && tid == sh.reduce_i[0]) {
     unsigned long long seen = sh.found.above_count;
     int chosen = best_i;
     for (int i = lo; i < hi; ++i) {
-      if (__float_as_uint(p[i]) == want_bits && ++seen == want_rank) { chosen = i; break; }
+      if (__float_as_uint(__ldcg(p + i)) == want_bits && ++seen == want_rank) { chosen = i; break; }
     }
     out_tokens[row] = chosen;
   }
+  cluster_sync();  // nobody leaves while its published values may still be read
 }
 
 __global__ void seed_kernel(unsigned long long* rng, const int* rows, const unsigned long long* seeds, int count) {
@@ -341,6 +454,35 @@ __global__ void seed_kernel(unsigned long long* rng, const int* rows, const unsi
     s[w] = z ^ (z >> 31);
   }
 }
+template <int CL>
+int launch(size_t smem, int* out_tokens, const float* logits, long long row_stride, int rows, int vocab, float* scratch,
+           unsigned long long* rng, const int* rng_rows, float temperature, int top_k, double top_p, double min_p,
+           cudaStream_t stream) {
+  static bool configured = false;
+  if (smem && !configured) {
+    if (cudaFuncSetAttribute(sample_kernel<CL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return DLLM_LAUNCH_FAILED;
+    configured = true;
+  }
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(CL, rows);
+  config.blockDim = dim3(THREADS);
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attributes[2];
+  attributes[0].id = cudaLaunchAttributeClusterDimension;
+  attributes[0].val.clusterDim.x = CL;
+  attributes[0].val.clusterDim.y = 1;
+  attributes[0].val.clusterDim.z = 1;
+  attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attributes[1].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attributes;
+  config.numAttrs = dllm_pdl_enabled() ? 2 : 1;
+  return cudaLaunchKernelEx(&config, sample_kernel<CL>, out_tokens, logits, row_stride, vocab, scratch, rng, rng_rows,
+                            temperature, top_k, top_p, min_p) == cudaSuccess
+             ? DLLM_OK
+             : DLLM_LAUNCH_FAILED;
+}
 }  // namespace
 
 // Chooses one token per row of logits[rows, vocab] (row stride given). `scratch` holds 3 * rows * vocab + 2 floats
@@ -352,15 +494,13 @@ DLLM_EXPORT int dllm_sample(int* out_tokens, const float* logits, long long row_
   if (rows <= 0) return DLLM_OK;
   if (vocab <= 0 || temperature < 0.f || !(top_p > 0.0) || min_p < 0.0 || top_k < 0) return DLLM_BAD_ARGUMENT;
   if (temperature > 0.f && (scratch == nullptr || rng == nullptr || rng_rows == nullptr)) return DLLM_BAD_ARGUMENT;
+  if (rows > 65535) return DLLM_UNSUPPORTED_SIZE;
   size_t smem = temperature > 0.f ? (size_t)BINS * THREADS * (sizeof(unsigned long long) + sizeof(unsigned)) : 0;
-  static bool configured = false;
-  if (smem && !configured) {
-    if (cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-      return DLLM_LAUNCH_FAILED;
-    configured = true;
-  }
-  return dllm_launch_pdl(sample_kernel, dim3(rows), dim3(THREADS), smem, stream, out_tokens, logits, row_stride,
-                         vocab, scratch, rng, rng_rows, temperature, top_k, top_p, min_p);
+  // blocks per row: as many as keep the whole launch within one wave of the device
+  if (rows <= 18) return launch<8>(smem, out_tokens, logits, row_stride, rows, vocab, scratch, rng, rng_rows, temperature, top_k, top_p, min_p, stream);
+  if (rows <= 37) return launch<4>(smem, out_tokens, logits, row_stride, rows, vocab, scratch, rng, rng_rows, temperature, top_k, top_p, min_p, stream);
+  if (rows <= 74) return launch<2>(smem, out_tokens, logits, row_stride, rows, vocab, scratch, rng, rng_rows, temperature, top_k, top_p, min_p, stream);
+  return launch<1>(smem, out_tokens, logits, row_stride, rows, vocab, scratch, rng, rng_rows, temperature, top_k, top_p, min_p, stream);
 }
 
 // rng[rows[i]] = xoshiro256** state from SplitMix64(seeds[i]).
