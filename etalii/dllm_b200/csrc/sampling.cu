@@ -143,38 +143,41 @@ __device__ void find_prefix(const float* __restrict__ p, int vocab, int kind, un
       sh.out_u64[set][BINS + tid] = sh.part_mass[tid][0] + sh.part_mass[tid][1];
     }
     cluster_sync();
-    if (tid < BINS) {  // stage 3: the cluster's bins, blocks in rank order
+    if (tid < 32) {
+      // stage 3 (the first warp): lane b < 16 adds bin b over the cluster, blocks in rank order; then the lanes
+      // walk the bins from the top of the order together: lane b needs what lies in the bins above it
       unsigned long long c = 0, m = 0;
+      if (tid < BINS) {
 #pragma unroll
-      for (unsigned r = 0; r < CL; ++r) {
-        c += remote_u64(&sh.out_u64[set][tid], r);
-        m += remote_u64(&sh.out_u64[set][BINS + tid], r);
-      }
-      sh.count[tid] = c;
-      sh.mass[tid] = m;
-    }
-    __syncthreads();
-    if (tid == 0) {  // walk the bins from the top of the order
-      unsigned long long ac = above_count, am = above_mass;
-      for (int bin = BINS - 1; bin >= 0; --bin) {
-        unsigned long long c = sh.count[bin], m = sh.mass[bin];
-        if (c > 0) {
-          bool hit;
-          if (kind == FIND_COUNT) hit = ac < target && target <= ac + c;
-          else if (kind == FIND_MASS_GE) hit = am < target && target <= am + m;
-          else hit = am <= target && target < am + m;
-          if (hit) {
-            sh.found.ok = 1;
-            sh.found.bits = (prefix << 4) | (unsigned)bin;
-            sh.found.above_count = ac;
-            sh.found.above_mass = am;
-            sh.found.tie_count = c;
-            sh.found.tie_mass = m;
-            break;
-          }
+        for (unsigned r = 0; r < CL; ++r) {
+          c += remote_u64(&sh.out_u64[set][tid], r);
+          m += remote_u64(&sh.out_u64[set][BINS + tid], r);
         }
-        ac += c;
-        am += m;
+      }
+      unsigned long long ac = c, am = m;  // inclusive sums over the lanes above and this one
+#pragma unroll
+      for (int o = 1; o < BINS; o <<= 1) {
+        unsigned long long oc = __shfl_down_sync(0xffffffffu, ac, o), om = __shfl_down_sync(0xffffffffu, am, o);
+        if (tid + o < BINS) { ac += oc; am += om; }
+      }
+      ac = above_count + ac - c;  // what lies above this bin
+      am = above_mass + am - m;
+      bool hit = false;
+      if (tid < BINS && c > 0) {
+        if (kind == FIND_COUNT) hit = ac < target && target <= ac + c;
+        else if (kind == FIND_MASS_GE) hit = am < target && target <= am + m;
+        else hit = am <= target && target < am + m;
+      }
+      // (the ranges of the bins do not overlap: at most one lane hits; with several empty-mass bins tied on a
+      // boundary the highest bin is the reference's choice)
+      unsigned hits = __ballot_sync(0xffffffffu, hit);
+      if (hit && tid == 31 - __clz((int)hits)) {
+        sh.found.ok = 1;
+        sh.found.bits = (prefix << 4) | (unsigned)tid;
+        sh.found.above_count = ac;
+        sh.found.above_mass = am;
+        sh.found.tie_count = c;
+        sh.found.tie_mass = m;
       }
     }
     __syncthreads();
@@ -182,7 +185,27 @@ __device__ void find_prefix(const float* __restrict__ p, int vocab, int kind, un
     prefix = sh.found.bits;
     above_count = sh.found.above_count;
     above_mass = sh.found.above_mass;
+    bool single = sh.found.tie_count == 1 && shift > 0;
     __syncthreads();
+    if (single) {
+      // one candidate is left under this prefix: no need to descend bit by bit; whoever holds it tells its bits
+      int set2 = turn.next();
+      if (tid == 0) sh.out_u32[set2] = 0u;
+      __syncthreads();
+      for (int i = (int)rank * THREADS + tid; i < vocab; i += CL * THREADS) {
+        float v = p[i];
+        unsigned key = __float_as_uint(v) << 1;
+        if (v >= 0.f && (key >> shift) == prefix) sh.out_u32[set2] = key;  // exactly one thread of the cluster
+      }
+      cluster_sync();
+      unsigned key = 0;
+#pragma unroll
+      for (unsigned r = 0; r < CL; ++r) key |= remote_u32(&sh.out_u32[set2], r);
+      __syncthreads();
+      if (tid == 0) sh.found.bits = key;
+      __syncthreads();
+      break;
+    }
   }
   if (tid == 0) {
     Found& f = sh.found;

@@ -336,6 +336,19 @@ def test_sample_matches_plain_sampler(options, vocab):
     assert got == want
 
 
+@pytest.mark.parametrize("rows", [19, 40, 80])
+@pytest.mark.parametrize("spread", [0.5, 3.0, 12.0])
+def test_sample_with_many_rows_and_flat_or_peaked_distributions(rows, spread):
+    """More rows mean fewer blocks per row (clusters of 4, 2 and 1); a peaked distribution leaves single candidates
+    early in the descent, a flat one crowds the bins to the last bits."""
+    g = torch.Generator().manual_seed(rows)
+    logits = torch.randn((rows, 1500), generator=g) * spread
+    seeds = [11 * r + 3 for r in range(rows)]
+    for options in ({"temperature": 0.9}, {"temperature": 1.1, "top_k": 50, "top_p": 0.8, "min_p": 0.01}):
+        got, want = _sample_both(logits, options, seeds)
+        assert got == want, options
+
+
 def test_sample_ties_go_to_the_lower_id():
     logits = torch.zeros((4, 1000))
     logits[0, [5, 700]] = 3.0      # two equal maxima
