@@ -10,7 +10,7 @@ vocabulary 49152, tied head) with seeded random bfloat16 weights; a batch of 8 s
 (model, greedy token choice, feedback), replayed as a CUDA graph; `value` is decoded tokens per second over exactly K
 steps timed with CUDA events. `e2e` is the same through `Engine.generate` with host token lists in and out.
 `prefill` is one 2,048-token prompt in one step. `roofline` relates the decode step to HBM bandwidth: every weight
-read once plus the cache of the live sequences, over the step's time. `points` repeats the decode at batch 1 and 64.
+read once plus the cache of the live sequences, over the step's time. `points` repeats the decode at batch 1 and 64, and the end-to-end run with temperature sampling.
 """
 import argparse
 import json
@@ -369,6 +369,11 @@ def main() -> int:
 
     points = {}
     if not args.no_points:
+        # the same end-to-end run with sampling on the device instead of greedy choice
+        sampled = SamplingOptions(temperature=0.8, seed=1)
+        engine.generate(prompts, 20, sampled, ignore_eos=True)
+        engine.generate(prompts, args.steps + 1, sampled, ignore_eos=True)
+        points["e2e_temperature_0.8"] = round(engine.stats["decode_tokens"] / engine.stats["decode_s"], 1)
         for name, batch in (("decode_b1", 1), ("decode_b64", 64)):
             batch_prompts = make_prompts(batch, vocab, seed=2 + batch)
             decode_run(engine, batch_prompts, 4, 3)
