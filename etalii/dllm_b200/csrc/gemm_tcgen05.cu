@@ -20,28 +20,31 @@ typedef __nv_bfloat16 bf16;
 constexpr int BM = 128, BK = 64, UMMA_K = 16;
 constexpr int THREADS = 192;
 
-template <int BN> struct Shape {
+// DEEP: a ring of nine or ten stages (about 215 KB) for a block that has its multiprocessor to itself: a product
+// with no more tiles than the device has multiprocessors and a short reduction then brings a tile's whole operand
+// panels in one round trip instead of three.
+template <int BN, bool DEEP = false> struct Shape {
   static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
   static constexpr int ACC_COLS = BN < 32 ? 32 : BN;   // columns of one accumulator
   static constexpr int TMEM_COLS = 2 * ACC_COLS;       // two accumulators: a power of two, at least 32
   // about 96 KB a block where that is enough (two blocks share an SM, 2 x TMEM_COLS <= 512 columns); the 256-wide
   // tile takes four 48 KB stages and all of the tensor memory, so one block owns the SM
-  static constexpr int STAGES = BN >= 256 ? 4 : (BN >= 128 ? 3 : 4);
+  static constexpr int STAGES = DEEP ? (220 * 1024) / (A_BYTES + B_BYTES) : (BN >= 256 ? 4 : (BN >= 128 ? 3 : 4));
   static constexpr size_t SMEM = (size_t)STAGES * (A_BYTES + B_BYTES) + 1024;
-  static constexpr int BLOCKS_PER_SM = BN >= 256 ? 1 : 2;
+  static constexpr int BLOCKS_PER_SM = (DEEP || BN >= 256) ? 1 : 2;
 };
 
 // A persistent block: it takes tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... of the m_tiles x n_tiles grid
 // (neighbouring blocks share a tile of W and read different rows of A). The producer's ring of stages runs on across
 // tiles; the accumulator alternates between two halves of the block's tensor memory, so the epilogue of one tile
 // overlaps the products of the next.
-template <int BN, int EPI>
+template <int BN, int EPI, bool DEEP>
 __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                const __grid_constant__ CUtensorMap map_w,
                                                                void* __restrict__ c, int M, int N, int K,
                                                                int* __restrict__ status, RopeArgs rope, int m_tiles,
                                                                int n_tiles) {
-  typedef Shape<BN> S;
+  typedef Shape<BN, DEEP> S;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);  // swizzle atoms: 1 KB
   __shared__ uint64_t full_bar[S::STAGES], empty_bar[S::STAGES], acc_full[2], acc_empty[2];
@@ -201,18 +204,29 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
   }
 }
 
+template <int BN, int EPI, bool DEEP>
+int launch_shape(void* c, const CUtensorMap& map_a, const CUtensorMap& map_w, int M, int N, int K, int* status,
+                 cudaStream_t stream, const RopeArgs& rope, int m_tiles, int n_tiles, int sms) {
+  typedef Shape<BN, DEEP> S;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, EPI, DEEP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)S::SMEM) != cudaSuccess)
+      return DLLM_LAUNCH_FAILED;
+    configured = true;
+  }
+  long long total = (long long)m_tiles * n_tiles;
+  int blocks = sms * S::BLOCKS_PER_SM;
+  if (blocks > total) blocks = (int)total;
+  return dllm_launch_pdl(gemm_tcgen05_kernel<BN, EPI, DEEP>, dim3(blocks), dim3(THREADS), S::SMEM, stream, map_a, map_w,
+                         c, M, N, K, status, rope, m_tiles, n_tiles);
+}
+
 template <int BN, int EPI>
 int launch(void* c, const void* a, const void* w, int M, int N, int K, int* status, cudaStream_t stream,
            const RopeArgs& rope = RopeArgs{}) {
   alignas(64) CUtensorMap map_a, map_w;
   if (!make_map(&map_a, a, M, K, BM) || !make_map(&map_w, w, N, K, BN)) return DLLM_LAUNCH_FAILED;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)Shape<BN>::SMEM) != cudaSuccess)
-      return DLLM_LAUNCH_FAILED;
-    configured = true;
-  }
   int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
   long long total = (long long)m_tiles * n_tiles;
   if (total > 0x7fffffff) return DLLM_UNSUPPORTED_SIZE;
@@ -223,10 +237,10 @@ int launch(void* c, const void* a, const void* w, int M, int N, int K, int* stat
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0)
       return DLLM_LAUNCH_FAILED;
   }
-  int blocks = sms * Shape<BN>::BLOCKS_PER_SM;
-  if (blocks > total) blocks = (int)total;
-  return dllm_launch_pdl(gemm_tcgen05_kernel<BN, EPI>, dim3(blocks), dim3(THREADS), Shape<BN>::SMEM, stream, map_a,
-                         map_w, c, M, N, K, status, rope, m_tiles, n_tiles);
+  constexpr bool CAN_DEEP = BN == 64 && EPI <= EPI_QKV_ROPE;  // (the shapes where it was measured to pay)
+  if (CAN_DEEP && total <= sms && K > 4 * BK)
+    return launch_shape<BN, EPI, CAN_DEEP>(c, map_a, map_w, M, N, K, status, stream, rope, m_tiles, n_tiles, sms);
+  return launch_shape<BN, EPI, false>(c, map_a, map_w, M, N, K, status, stream, rope, m_tiles, n_tiles, sms);
 }
 
 template <int BN>
