@@ -188,7 +188,7 @@ def attention_decode_cluster_supported(cache):
 
 
 def streams(rows, outputs):
-    return rows <= 16 or (rows <= 64 and outputs <= 4096)
+    return rows <= 16 or (rows <= 32 and outputs <= 4096) or (rows <= 64 and outputs < 2048)
 
 
 def takes_weights_as_rows(rows, outputs, inner):
