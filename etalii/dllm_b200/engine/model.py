@@ -32,6 +32,15 @@ class Model:
         self.final_norm = bound("norm", spec.final_norm)
         self.head = bound("head", spec.head)
         rt.done_loading()
+        if torch.device(rt.device).type == "cuda":  # what the parts say they call, compiled side by side
+            from ..kernels.build import prebuild
+
+            names = {"elementwise", "gemm_simt" if rt.dtype == torch.float32 else "gemv"}
+            for block in self.blocks:
+                for part in (block.mixer, block.feed_forward):
+                    if hasattr(part, "kernel_libraries"):
+                        names |= set(part.kernel_libraries(rt))
+            prebuild(sorted(names))
 
         self.order = spec.run_order()
         n_entries = max((e.cache for e in self.order), default=-1) + 1

@@ -144,5 +144,25 @@ def library(name: str) -> ctypes.CDLL:
         return _loaded[name]
 
 
-def build_all(verbose: bool = True) -> list[str]:
-    return [compile_library(name, verbose) for name in SOURCES]
+def prebuild(names, verbose: bool = True) -> None:
+    """Compiles the named libraries that are not built yet, side by side (a model knows which ones its parts use;
+    building them together at load time takes as long as the slowest, not as their sum)."""
+    from concurrent.futures import ThreadPoolExecutor
+
+    missing = [n for n in dict.fromkeys(names) if n in SOURCES and n not in _loaded and
+               not os.path.isfile(library_path(n))]
+    if len(missing) <= 1:
+        for name in missing:
+            compile_library(name, verbose)
+        return
+    with ThreadPoolExecutor(max_workers=min(len(missing), os.cpu_count() or 1)) as pool:
+        list(pool.map(lambda name: compile_library(name, verbose), missing))
+
+
+def build_all(verbose: bool = True, jobs: int | None = None) -> list[str]:
+    """Builds every library (those that are missing), several nvcc processes at a time; returns the paths."""
+    from concurrent.futures import ThreadPoolExecutor
+
+    workers = max(1, min(jobs or (os.cpu_count() or 1), len(SOURCES)))
+    with ThreadPoolExecutor(max_workers=workers) as pool:
+        return list(pool.map(lambda name: compile_library(name, verbose), SOURCES))

@@ -95,4 +95,20 @@ class Attention:
         ops.gemm(residual, attended, self.w_o, ops.EPI_RESIDUAL)
 
 
+    def kernel_libraries(self, rt) -> set[str]:
+        """The kernel libraries this part's steps call (built together when the model loads)."""
+        if rt.dtype != torch.bfloat16:
+            return {"gemm_simt", "elementwise", "attention"}
+        hd = self.head_dim
+        names = {"gemv", "gemm_tcgen05", "elementwise"}
+        names.add("attention_decode_cluster" if hd % 16 == 0 and hd <= 128 else "attention_decode")
+        if hd == 64:
+            names.add("attention_prefill_tcgen05")
+        elif hd % 16 == 0 and hd <= 128:
+            names.add("attention_prefill")
+        else:
+            names.add("attention")
+        return names
+
+
 register_part("mixer", "attention", Attention)

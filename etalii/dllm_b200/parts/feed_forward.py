@@ -36,4 +36,13 @@ class SwiGLU:
         ops.gemm(residual, act, self.w_down, ops.EPI_RESIDUAL)
 
 
+    def kernel_libraries(self, rt) -> set[str]:
+        if rt.dtype != torch.bfloat16:
+            return {"gemm_simt"}
+        names = {"gemv", "gemm_tcgen05"}
+        if any(ops.streams_through_shared_memory(1, w.shape[0], w.shape[1]) for w in (self.w_gate_up, self.w_down)):
+            names.add("gemv_tma")
+        return names
+
+
 register_part("feed_forward", "swiglu", SwiGLU)
