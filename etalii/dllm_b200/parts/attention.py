@@ -24,6 +24,12 @@ def decode_chunk(sequences: int, kv_heads: int, max_context: int, head_dim: int 
     return 1024
 
 
+TCGEN05_ATTENTION_FROM = 512
+"""Prefill steps whose longest context is above this take the tcgen05 attention kernel (measured: it leads from about
+a thousand keys per query on, 1.3 to 1.6 times at 2,048 and more; a block's fixed costs weigh more on short prompts,
+where the mma.sync kernel with its tiles of 64 queries is as fast or a little faster)."""
+
+
 class Attention:
     accepts_pending_norm = True
 
@@ -86,7 +92,8 @@ class Attention:
             tickets = rt.ws.zeros("attention_tickets", batch.n_seqs * self.num_kv_heads, torch.int32)
             ops.attention_decode(attended, q, cache, self.num_heads, self.scale, self.window or 0, batch, chunk,
                                  scratch, tickets)
-        elif not batch.is_decode and ops.attention_prefill_tcgen05_supported(cache):
+        elif not batch.is_decode and ops.attention_prefill_tcgen05_supported(cache) and \
+                batch.max_context > TCGEN05_ATTENTION_FROM:
             ops.attention_prefill_tcgen05(attended, q, cache, self.num_heads, self.scale, self.window or 0, batch)
         elif not batch.is_decode and ops.attention_prefill_supported(cache):
             ops.attention_prefill(attended, q, cache, self.num_heads, self.scale, self.window or 0, batch)
@@ -103,8 +110,8 @@ class Attention:
         names = {"gemv", "gemm_tcgen05", "elementwise"}
         names.add("attention_decode_cluster" if hd % 16 == 0 and hd <= 128 else "attention_decode")
         if hd == 64:
-            names.add("attention_prefill_tcgen05")
-        elif hd % 16 == 0 and hd <= 128:
+            names.add("attention_prefill_tcgen05")  # (long prompts; short ones take the mma.sync kernel)
+        if hd % 16 == 0 and hd <= 128:
             names.add("attention_prefill")
         else:
             names.add("attention")

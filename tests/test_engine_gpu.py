@@ -266,6 +266,38 @@ def test_long_generation_through_the_graph_path(setup):
     engine.cache.check()
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_head_dim_64_with_long_and_short_prompts(dtype):
+    """The benchmark's head size at engine level: in bfloat16 a prompt of 700 tokens takes the tcgen05 attention and
+    the tile product that ends in rotation and cache write, prompts below 512 the mma.sync attention, single tokens
+    the cluster kernel; a prompt that goes on from a cached prefix crosses tile and page edges."""
+    config = dict(P.TINY_A, num_hidden_layers=2, tie_word_embeddings=False, max_position_embeddings=1024,
+                  num_attention_heads=3, num_key_value_heads=1, head_dim=64, hidden_size=72, intermediate_size=120,
+                  vocab_size=203)
+    weights = P.random_weights(config, seed=21, std=0.08)
+    engine = make_engine(config, weights, dtype, max_tokens=64 * 40, max_length=1024)
+    plain = PlainLogits(config, weights)
+    long_prompt, short_a, short_b = prompts_for(config, (700, 130, 5), seed=22)
+    slots = engine.open(3)
+    rows = [0, 63, 64, 127, 128, 511, 512, 640, 699]
+    got = host(engine.step([slots[0]], [long_prompt], [rows]))
+    assert rel_error(got, plain(long_prompt)[rows]) <= TOL[dtype]
+    got = host(engine.step(slots[1:], [short_a, short_b], [[129], [4]]))
+    assert rel_error(got[0], plain(short_a)[-1]) <= TOL[dtype] and rel_error(got[1], plain(short_b)[-1]) <= TOL[dtype]
+    more = prompts_for(config, (190,), seed=23)[0]  # goes on from position 700: a long context again
+    got = host(engine.step([slots[0]], [more], [[0, 100, 189]]))
+    assert rel_error(got, plain(long_prompt + more)[[700, 800, 889]]) <= TOL[dtype]
+    contexts = [long_prompt + more, short_a, short_b]
+    for step in range(3):
+        tokens = [[(7 * step + i) % config["vocab_size"]] for i in range(3)]
+        got = host(engine.step(slots, tokens))
+        for i in range(3):
+            contexts[i] = contexts[i] + tokens[i]
+            assert rel_error(got[i], plain(contexts[i])[-1]) <= TOL[dtype], (step, i)
+    engine.close(slots)
+    engine.cache.check()
+
+
 @pytest.fixture(scope="module")
 def long_case():
     config = dict(P.TINY_B, num_hidden_layers=1, max_position_embeddings=8192, vocab_size=128, num_attention_heads=4,
