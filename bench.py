@@ -249,14 +249,15 @@ def attention_table() -> int:
         return begin.elapsed_time(end) * 1e3 / (reps * len(views))
 
     print("prefill: heads kv_heads head_dim prompts | mma.sync us | tcgen05 us, TFLOP/s")
-    for heads, kv_heads, lengths in ((9, 3, [2048]), (9, 3, [512]), (9, 3, [8192]), (32, 8, [2048]),
-                                     (32, 8, [4096, 4096]), (9, 3, [300] * 16)):
-        views, batch, q, out = setup(heads, kv_heads, 64, lengths, lengths, 8)
+    for heads, kv_heads, head_dim, lengths in (
+            (9, 3, 64, [2048]), (9, 3, 64, [512]), (9, 3, 64, [8192]), (32, 8, 64, [2048]), (32, 8, 64, [4096, 4096]),
+            (9, 3, 64, [300] * 16), (32, 8, 128, [512]), (32, 8, 128, [2048]), (32, 8, 128, [8192])):
+        views, batch, q, out = setup(heads, kv_heads, head_dim, lengths, lengths, 4 if head_dim > 64 else 8)
         old = time_us(lambda v: ops.attention_prefill(out, q, v, heads, 0.125, 0, batch), views)
         new = time_us(lambda v: ops.attention_prefill_tcgen05(out, q, v, heads, 0.125, 0, batch), views)
-        flops = sum(4 * heads * 64 * n * (n + 1) / 2 for n in lengths)
+        flops = sum(4 * heads * head_dim * n * (n + 1) / 2 for n in lengths)
         shown = lengths if len(lengths) < 4 else f"{len(lengths)} x {lengths[0]}"
-        print(f"{heads} {kv_heads} 64 {shown} | {old:.1f} | {new:.1f}, {flops / new / 1e6:.0f}")
+        print(f"{heads} {kv_heads} {head_dim} {shown} | {old:.1f} | {new:.1f}, {flops / new / 1e6:.0f}")
     print("decode: heads kv_heads head_dim batch, MB of keys and values, us at the measured HBM rate | "
           "chosen shape us | shapes 0..4 us")
     bandwidth = peaks()["hbm_gbs"]

@@ -438,13 +438,13 @@ def attention_prefill(out: torch.Tensor, q: torch.Tensor, cache, heads: int, sca
 
 
 def attention_prefill_tcgen05_supported(cache) -> bool:
-    return cache.dtype == torch.bfloat16 and cache.head_dim == 64 and cache.page_size == 64
+    return cache.dtype == torch.bfloat16 and cache.head_dim in (64, 128) and cache.page_size == 64
 
 
 def attention_prefill_tcgen05(out: torch.Tensor, q: torch.Tensor, cache, heads: int, scale: float, window: int,
                               batch) -> None:
     """Blockwise causal attention of the batch's new tokens over their sequences' caches on the 5th-generation
-    tensor cores (bfloat16, head_dim 64, pages of 64 positions): tiles of 128 queries, scores and outputs in tensor
+    tensor cores (bfloat16, head_dim 64 or 128, pages of 64 positions): tiles of 128 queries, scores and outputs in tensor
     memory, pages of keys and values by TMA."""
     _cuda(out, q)
     assert attention_prefill_tcgen05_supported(cache) and q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
@@ -453,7 +453,7 @@ def attention_prefill_tcgen05(out: torch.Tensor, q: torch.Tensor, cache, heads: 
         cache.page_table.data_ptr(), cache.max_pages, cache.page_size, heads, cache.kv_heads, cache.head_dim,
         batch.tile_seq.data_ptr(), batch.tile_first.data_ptr(), batch.cu_seqlens.data_ptr(), batch.start.data_ptr(),
         batch.slots.data_ptr(), batch.n_tiles, float(scale), int(window or 0), _status_word().data_ptr(),
-        _stream()), "attention_prefill_tcgen05", lambda: f"head_dim={cache.head_dim} must be 64; pages of 64")
+        _stream()), "attention_prefill_tcgen05", lambda: f"head_dim={cache.head_dim} must be 64 or 128; pages of 64")
 
 
 def attention_decode_cluster_supported(cache) -> bool:

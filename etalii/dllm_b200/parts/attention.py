@@ -109,7 +109,7 @@ class Attention:
         hd = self.head_dim
         names = {"gemv", "gemm_tcgen05", "elementwise"}
         names.add("attention_decode_cluster" if hd % 16 == 0 and hd <= 128 else "attention_decode")
-        if hd == 64:
+        if hd in (64, 128):
             names.add("attention_prefill_tcgen05")  # (long prompts; short ones take the mma.sync kernel)
         if hd % 16 == 0 and hd <= 128:
             names.add("attention_prefill")

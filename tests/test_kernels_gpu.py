@@ -517,9 +517,9 @@ def test_attention_prefill_finds_a_far_key_and_ignores_what_lies_beyond():
 
 
 @pytest.mark.parametrize("heads,kv_heads,window", [(9, 3, None), (4, 4, 70), (8, 1, 33), (6, 2, 200), (1, 1, None)])
-def test_attention_prefill_tcgen05(heads, kv_heads, window):
+@pytest.mark.parametrize("head_dim", [64, 128])
+def test_attention_prefill_tcgen05(heads, kv_heads, window, head_dim):
     """Whole prompts, prompts that go on from a cached prefix, single tokens and tile edges, in one batch."""
-    head_dim = 64
     lengths, new = [130, 200, 1, 64, 65, 300, 77, 128, 129, 390], [130, 9, 1, 64, 65, 128, 1, 128, 129, 257]
     cache, view, batch = _cache_and_batch(torch.bfloat16, kv_heads, head_dim, lengths, new, window)
     n = batch.n_tokens
@@ -542,9 +542,10 @@ def test_attention_prefill_tcgen05(heads, kv_heads, window):
 
 
 @pytest.mark.parametrize("window", [None, 1000])
-def test_attention_prefill_tcgen05_long(window):
+@pytest.mark.parametrize("head_dim", [64, 128])
+def test_attention_prefill_tcgen05_long(window, head_dim):
     """Thousands of keys per query (many trips round the rings of stages and buffers), against the mma.sync kernel."""
-    heads, kv_heads, head_dim = 6, 2, 64
+    heads, kv_heads = 6, 2
     lengths, new = [2500, 4100, 700], [2500, 1030, 700]
     cache, view, batch = _cache_and_batch(torch.bfloat16, kv_heads, head_dim, lengths, new, window)
     n = batch.n_tokens
@@ -558,8 +559,9 @@ def test_attention_prefill_tcgen05_long(window):
     assert float(worst.max()) <= 8e-3 * float(ref.float().abs().max()), int(worst.argmax())
 
 
-def test_attention_prefill_tcgen05_finds_a_far_key_and_ignores_what_lies_beyond():
-    heads, kv_heads, hd = 4, 2, 64
+@pytest.mark.parametrize("hd", [64, 128])
+def test_attention_prefill_tcgen05_finds_a_far_key_and_ignores_what_lies_beyond(hd):
+    heads, kv_heads = 4, 2
     cache, view, batch = _cache_and_batch(torch.bfloat16, kv_heads, hd, [700], [200])
     view.storage.mul_(0.05)
     slot = batch.h_slots[0]
