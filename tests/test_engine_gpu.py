@@ -267,13 +267,14 @@ def test_long_generation_through_the_graph_path(setup):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_head_dim_64_with_long_and_short_prompts(dtype):
-    """The benchmark's head size at engine level: in bfloat16 a prompt of 700 tokens takes the tcgen05 attention and
+@pytest.mark.parametrize("head_dim", [64, 128])
+def test_head_dims_of_the_tcgen05_attention_with_long_and_short_prompts(dtype, head_dim):
+    """The head sizes of the tcgen05 attention at engine level: in bfloat16 a prompt of 700 tokens takes it and
     the tile product that ends in rotation and cache write, prompts below 512 the mma.sync attention, single tokens
     the cluster kernel; a prompt that goes on from a cached prefix crosses tile and page edges."""
     config = dict(P.TINY_A, num_hidden_layers=2, tie_word_embeddings=False, max_position_embeddings=1024,
-                  num_attention_heads=3, num_key_value_heads=1, head_dim=64, hidden_size=72, intermediate_size=120,
-                  vocab_size=203)
+                  num_attention_heads=3, num_key_value_heads=1, head_dim=head_dim, hidden_size=72,
+                  intermediate_size=120, vocab_size=203)
     weights = P.random_weights(config, seed=21, std=0.08)
     engine = make_engine(config, weights, dtype, max_tokens=64 * 40, max_length=1024)
     plain = PlainLogits(config, weights)
