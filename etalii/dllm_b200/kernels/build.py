@@ -53,22 +53,32 @@ def _nvcc() -> str:
     raise KernelBuildError("nvcc was not found: the sm_100a kernels cannot be built (there is no fallback path)")
 
 
+_build_dir_found: str | None = None
+_build_dir_lock = threading.Lock()
+
+
 def _build_dir() -> str:
-    override = os.environ.get("DLLM_B200_BUILD_DIR")
-    candidates = [override] if override else []
-    candidates.append(os.path.join(CSRC, "_build"))
-    candidates.append(os.path.join(tempfile.gettempdir(), f"dllm_b200_build_{os.getuid()}"))
-    for path in candidates:
-        try:
-            os.makedirs(path, exist_ok=True)
-            probe = os.path.join(path, f".write_{os.getpid()}")
-            with open(probe, "w"):
-                pass
-            os.remove(probe)
-            return path
-        except OSError:
-            continue
-    raise KernelBuildError(f"no writable build directory among {candidates}")
+    """Where libraries are kept: found once (libraries may be built from several threads at a time)."""
+    global _build_dir_found
+    with _build_dir_lock:
+        if _build_dir_found is not None and os.path.isdir(_build_dir_found):
+            return _build_dir_found
+        override = os.environ.get("DLLM_B200_BUILD_DIR")
+        candidates = [override] if override else []
+        candidates.append(os.path.join(CSRC, "_build"))
+        candidates.append(os.path.join(tempfile.gettempdir(), f"dllm_b200_build_{os.getuid()}"))
+        for path in candidates:
+            try:
+                os.makedirs(path, exist_ok=True)
+                probe = os.path.join(path, f".write_{os.getpid()}_{threading.get_ident()}")
+                with open(probe, "w"):
+                    pass
+                os.remove(probe)
+                _build_dir_found = path
+                return path
+            except OSError:
+                continue
+        raise KernelBuildError(f"no writable build directory among {candidates}")
 
 
 def _digest(source: str) -> str:
