@@ -114,3 +114,18 @@ def test_run_batches_gives_back_on_error():
         run_batches([[1], [2]], [[0, 1]], lambda ix: BatchRun([1, 1], 2, frozenset(), 10), fake.start, failing,
                     fake.decode, fake.finish)
     assert all(not left for left in fake.open.values())
+
+
+def test_kernel_choice_rules_for_products():
+    """Which kernel a bfloat16 product takes, as plain functions of its sizes (no device needed)."""
+    from etalii.dllm_b200.kernels import ops
+
+    assert ops.streams(1, 128256) and ops.streams(16, 49152)          # up to 16 rows: always streamed
+    assert ops.streams(32, 3072) and not ops.streams(32, 49152)       # 17 to 32 rows: unless the matrix is wide
+    assert ops.streams(64, 576) and not ops.streams(64, 3072)         # 33 to 64 rows: only narrow matrices
+    assert not ops.streams(65, 576)
+    assert ops.streams_through_shared_memory(1, 28672, 4096) and not ops.streams_through_shared_memory(8, 28672, 4096)
+    assert not ops.streams_through_shared_memory(1, 16384, 2048)      # short rows of W
+    assert not ops.streams_through_shared_memory(1, 4096, 4096 + 8)   # a reduction that is no multiple of 64
+    assert ops.takes_weights_as_rows(64, 28672, 4096) and not ops.takes_weights_as_rows(64, 4096, 14336)
+    assert not ops.takes_weights_as_rows(16, 28672, 4096) and not ops.takes_weights_as_rows(65, 28672, 4096)
