@@ -2,7 +2,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
                     [--shape smollm2-135m|smollm2-1.7b|llama-3.1-8b] [--batch B] [--no-points]
-                    [--profile decode|prefill|gemm|attention]
+                    [--profile decode|prefill|gemm|attention|stream]
 
 Default workload: the SmolLM2-135M shape (30 layers, hidden 576, 9 heads, 3 kv heads, head_dim 64, intermediate 1536,
 vocabulary 49152, tied head) with seeded random bfloat16 weights; a batch of 8 sequences with unequal prompt lengths
@@ -275,6 +275,54 @@ def attention_table() -> int:
     return 0
 
 
+def stream_table() -> int:
+    """Times the decode products alone at layer shapes of the larger models: the kernel that streams W through
+    registers against the one that streams it through shared memory, as fractions of the measured HBM rate (a CUDA
+    graph of 20 launches over several copies of W, so that W comes from HBM)."""
+    import torch
+
+    from etalii.dllm_b200.kernels import ops
+
+    device = "cuda:0"
+    rate = peaks()["hbm_gbs"]
+
+    def run(m, n, k, epilogue, kernel):
+        copies = max(2, int(300e6 // (n * k * 2)) + 1)
+        ws = [(torch.randn(n, k, device=device) * 0.05).bfloat16() for _ in range(copies)]
+        x = torch.randn(m, k, device=device).bfloat16()
+        cols = n // 2 if epilogue == ops.EPI_SWIGLU else n
+        dtype = torch.float32 if epilogue in (ops.EPI_STORE_F32, ops.EPI_RESIDUAL) else torch.bfloat16
+        c = torch.zeros(m, cols, device=device, dtype=dtype)
+        for i in range(3):
+            ops.gemm(c, x, ws[i % copies], epilogue, kernel=kernel)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(20):
+                ops.gemm(c, x, ws[i % copies], epilogue, kernel=kernel)
+        graph.replay()
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        graph.replay()
+        end.record()
+        torch.cuda.synchronize()
+        ops.raise_if_failed()
+        us = begin.elapsed_time(end) / 20 * 1e3
+        return us, n * k * 2 / us / 1e3 / rate
+
+    shapes = [(6144, 4096, ops.EPI_STORE_T), (4096, 4096, ops.EPI_RESIDUAL), (28672, 4096, ops.EPI_SWIGLU),
+              (4096, 14336, ops.EPI_RESIDUAL), (128256, 4096, ops.EPI_STORE_F32), (6144, 2048, ops.EPI_STORE_T),
+              (16384, 2048, ops.EPI_SWIGLU), (2048, 8192, ops.EPI_RESIDUAL), (49152, 2048, ops.EPI_STORE_F32),
+              (49152, 576, ops.EPI_STORE_F32)]
+    print("rows of activations, W rows x row length, epilogue | registers: us, of HBM | shared memory: us, of HBM")
+    for m in (1, 8, 16):
+        for n, k, epilogue in shapes:
+            a, b = run(m, n, k, epilogue, 2), run(m, n, k, epilogue, 4)
+            print(f"{m} {n} x {k} {epilogue} | {a[0]:.1f} {a[1]:.2f} | {b[0]:.1f} {b[1]:.2f}")
+    return 0
+
+
 def model_numbers(config, layers):
     h, i, v = config["hidden_size"], config["intermediate_size"], config["vocab_size"]
     nh, nkv, hd = config["num_attention_heads"], config["num_key_value_heads"], config["head_dim"]
@@ -299,7 +347,7 @@ def main() -> int:
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
     parser.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 decode points")
-    parser.add_argument("--profile", choices=("decode", "prefill", "gemm", "attention"),
+    parser.add_argument("--profile", choices=("decode", "prefill", "gemm", "attention", "stream"),
                         help="run only a few decode steps (or one prefill) and print no JSON: a small case for ncu")
     args = parser.parse_args()
     if args.impl == "reference":
@@ -311,6 +359,8 @@ def main() -> int:
         return gemm_table()
     if args.profile == "attention":
         return attention_table()
+    if args.profile == "stream":
+        return stream_table()
     if args.gpus != 1:
         print(f"bench.py measures one GPU: --gpus {args.gpus} is not supported (this library runs on a single device)")
         return 2
