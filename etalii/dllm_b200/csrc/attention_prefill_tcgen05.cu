@@ -3,8 +3,9 @@
 // each):
 //   softmax warps (0-7): two groups of four warps that take alternate steps (group j % 2 takes step j, with the
 //            score, P and output buffers number j % 2), one thread per query: read its row of scores from tensor
-//            memory (tcgen05.ld 32x32b), mask, running maximum and sum in float32 (no shuffles: the row is the
-//            thread's own), write the probabilities as bfloat16 into the swizzled P tile, then fetch the group's
+//            memory (tcgen05.ld 32x32b), mask, maximum and sum in float32 (no shuffles: the row is the thread's
+//            own; the maximum a row subtracts is renewed only when a score exceeds it by 2^8, so most steps read
+//            their scores once), write the probabilities as bfloat16 into the swizzled P tile, fetch the group's
 //            previous P V and fold it into the float32 output kept in registers: O = O * 2^(m_old - m_new) + P V.
 //            At the end the second group hands its maximum, sum and output to the first through shared memory.
 //   next warp: one lane issues TMA loads: the query tile once, then a page of keys and a page of values per step
@@ -35,7 +36,10 @@ template <int HD> struct Shape {
   static constexpr int BOXES = HD / 64;                       // 64-column boxes per row of an operand
   static constexpr int Q_BOX = BQ * 128, KV_BOX = BKV * 128;  // bytes of a box: rows of 128 bytes
   static constexpr int Q_BYTES = BOXES * Q_BOX, KV_BYTES = BOXES * KV_BOX;
-  static constexpr size_t SMEM = Q_BYTES + 2 * STAGES * KV_BYTES + 2 * P_BYTES + 1024;
+  // P tiles: with two groups a group would write its next P while its previous product may still read the last
+  // one, so each group has two; a single group alternates between the two buffers anyway
+  static constexpr int P_TILES = 2 * GROUPS;
+  static constexpr size_t SMEM = Q_BYTES + 2 * STAGES * KV_BYTES + P_TILES * P_BYTES + 1024;
   static constexpr unsigned TMEM_COLS = 2 * BKV + 2 * HD <= 256 ? 256 : 512;  // scores 2 x 64, outputs 2 x HD
   static constexpr int EX_LD = HD + 2;  // floats per row of the exchange between the two softmax groups
 };
@@ -156,7 +160,7 @@ __global__ void __launch_bounds__(Shape<HD>::THREADS, 1) prefill_tcgen05_kernel(
         if (!mbar_wait(&bar.v_full[s], (i / STAGES) & 1)) { *(volatile int*)status = 16; break; }
         if (i >= 2 && !mbar_wait(&bar.o_empty[pb], ((i >> 1) - 1) & 1)) { *(volatile int*)status = 17; break; }
         fence_after_sync();
-        unsigned p_addr = smem_u32(p_s + pb * P_BYTES), v_addr = smem_u32(v_s + s * KV_BYTES);
+        unsigned p_addr = smem_u32(p_s + (i % S::P_TILES) * P_BYTES), v_addr = smem_u32(v_s + s * KV_BYTES);
 #pragma unroll
         for (int k = 0; k < BKV / 16; ++k)
 #pragma unroll
@@ -207,7 +211,7 @@ __global__ void __launch_bounds__(Shape<HD>::THREADS, 1) prefill_tcgen05_kernel(
     for (int j = wg; j < steps; j += GROUPS, ++taken) {
       const int sb = j & 1;
       unsigned s_addr = tmem_s + lane_base + (unsigned)(sb * BKV);
-      unsigned char* p_tile = p_s + sb * P_BYTES;
+      unsigned char* p_tile = p_s + (j % S::P_TILES) * P_BYTES;
       if (!mbar_wait(&bar.s_full[sb], (j >> 1) & 1)) {
         if (lane == 0) *(volatile int*)status = 21;
         ok = false;
@@ -218,73 +222,72 @@ __global__ void __launch_bounds__(Shape<HD>::THREADS, 1) prefill_tcgen05_kernel(
       // a tile with an edge for some row of the block: keys beyond the query, or before its window
       bool edge = key0 + BKV - 1 > pos0 || (window > 0 && key0 < pos0 + BQ - window);
       int key_hi = qp - key0, key_lo = window > 0 ? qp + 1 - window - key0 : -1;  // columns key_lo .. key_hi count
-      // first pass over the scores: the row's maximum (four chains: the thread has no one to hide behind)
-      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-      unsigned v[2][16];  // two pieces of 16 columns: one in flight from tensor memory while the other is used
-      tmem_load16_nowait(s_addr, v[0]);
-#pragma unroll
-      for (int c = 0; c < BKV; c += 16) {
-        const int cur = (c >> 4) & 1;
-        tmem_wait_ld();
-        if (c + 16 < BKV) tmem_load16_nowait(s_addr + (unsigned)(c + 16), v[cur ^ 1]);
-        if (edge) {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            float x = (c + i > key_hi || c + i < key_lo) ? -INFINITY : __uint_as_float(v[cur][i]);
-            mx[i & 3] = fmaxf(mx[i & 3], x);
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(v[cur][i]));
-        }
-      }
-      // the group's previous product, before this step's P: its output buffer is free early for the next product
-      if (taken >= 1 && !consume(j - GROUPS, corr_saved)) { ok = false; break; }
-      tmem_load16_nowait(s_addr, v[0]);  // the second pass's first piece, under the arithmetic in between
-      float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-      float m_new = fmaxf(m_run, tile_max * scale_log2);  // maxima live in the scaled log2 domain
-      float m_use = m_new == -INFINITY ? 0.f : m_new;     // a row that has seen nothing so far
-      float corr = fast_exp2(m_run - m_use);
-      m_run = m_new;
-      corr_saved = corr;
-      // (the product consumed above had read the group's previous P: the P tile is free)
-      // second pass (tensor memory is read again rather than 64 scores kept in registers): probabilities
-      float sum[4] = {0.f, 0.f, 0.f, 0.f};
+      // (the P tile of this step is free: the product that read it last, P_TILES steps ago, has been consumed)
+      // One sweep over the scores gives the probabilities relative to the maximum the row has used so far, and the
+      // tile's own maximum on the way. The used maximum need not be the true one: any constant cancels in the
+      // quotient, and as long as no score lies more than 8 (in the log2 domain) above it the probabilities stay
+      // below 256, which bfloat16 and the float32 sums carry as well as values below 1. Only when a row of the warp
+      // exceeds that (mostly in a row's first steps) the warp sweeps again with the new maximum.
       unsigned char* p_row = p_tile + r * 128;  // K-major tile, 128-byte rows, 128-byte swizzle
+      auto sweep = [&](float m_use, float& tile_max, float& row_sum) {
+        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains each: the thread has no one to
+        float sum[4] = {0.f, 0.f, 0.f, 0.f};                         // hide behind
+        unsigned v[2][16];  // two pieces of 16 columns: one in flight from tensor memory while the other is used
+        tmem_load16_nowait(s_addr, v[0]);
 #pragma unroll
-      for (int c = 0; c < BKV; c += 16) {
-        const int cur = (c >> 4) & 1;
-        tmem_wait_ld();
-        if (c + 16 < BKV) {
-          tmem_load16_nowait(s_addr + (unsigned)(c + 16), v[cur ^ 1]);
-        } else {  // the last scores are in registers: the buffer may be written again
-          fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&bar.s_empty[sb]);
-        }
-        float p[16];
-        if (edge) {
+        for (int c = 0; c < BKV; c += 16) {
+          const int cur = (c >> 4) & 1;
+          tmem_wait_ld();
+          if (c + 16 < BKV) tmem_load16_nowait(s_addr + (unsigned)(c + 16), v[cur ^ 1]);
+          float p[16];
+          if (edge) {  // (two copies of the loop: the compares cost as much as the rest of an element)
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            float x = (c + i > key_hi || c + i < key_lo) ? -INFINITY : __uint_as_float(v[cur][i]);
-            p[i] = fast_exp2(fmaf(x, scale_log2, -m_use));
+            for (int i = 0; i < 16; ++i) {
+              float x = (c + i > key_hi || c + i < key_lo) ? -INFINITY : __uint_as_float(v[cur][i]);
+              mx[i & 3] = fmaxf(mx[i & 3], x);
+              p[i] = fast_exp2(fmaf(x, scale_log2, -m_use));
+              sum[i & 3] += p[i];
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              float x = __uint_as_float(v[cur][i]);
+              mx[i & 3] = fmaxf(mx[i & 3], x);
+              p[i] = fast_exp2(fmaf(x, scale_log2, -m_use));
+              sum[i & 3] += p[i];
+            }
           }
-        } else {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) p[i] = fast_exp2(fmaf(__uint_as_float(v[cur][i]), scale_log2, -m_use));
+          for (int half = 0; half < 2; ++half) {
+            uint4 packed;
+            __nv_bfloat162* pk = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) pk[i] = __floats2bfloat162_rn(p[half * 8 + 2 * i], p[half * 8 + 2 * i + 1]);
+            *reinterpret_cast<uint4*>(p_row + ((((c >> 3) + half) ^ (r & 7)) << 4)) = packed;
+          }
         }
-#pragma unroll
-        for (int i = 0; i < 16; ++i) sum[i & 3] += p[i];
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint4 packed;
-          __nv_bfloat162* pk = reinterpret_cast<__nv_bfloat162*>(&packed);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) pk[i] = __floats2bfloat162_rn(p[half * 8 + 2 * i], p[half * 8 + 2 * i + 1]);
-          *reinterpret_cast<uint4*>(p_row + ((((c >> 3) + half) ^ (r & 7)) << 4)) = packed;
-        }
+        tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2;  // in the scaled log2 domain
+        row_sum = (sum[0] + sum[1]) + (sum[2] + sum[3]);
+      };
+      float tile_max, row_sum, corr = 1.f;
+      sweep(m_run == -INFINITY ? 0.f : m_run, tile_max, row_sum);
+      bool over = tile_max > m_run + 8.f;  // (also: the row's first scores, while its maximum is still -inf)
+      if (__any_sync(0xffffffffu, over)) {
+        // the sweep is a warp's affair (tensor memory is read by whole warps): rows that are not over sweep again
+        // with their old maximum and get the same values
+        float m_new = over ? fmaxf(m_run, tile_max) : m_run;
+        float m_use = m_new == -INFINITY ? 0.f : m_new;  // a row that has seen nothing so far
+        corr = fast_exp2(m_run - m_use);
+        m_run = m_new;
+        sweep(m_use, tile_max, row_sum);
       }
-      l_run = l_run * corr + ((sum[0] + sum[1]) + (sum[2] + sum[3]));
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar.s_empty[sb]);  // the scores are not needed again: the buffer may be rewritten
+      // the group's previous product: it had the time of the sweep to finish
+      if (taken >= 1 && !consume(j - GROUPS, corr_saved)) { ok = false; break; }
+      corr_saved = corr;
+      l_run = l_run * corr + row_sum;
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes, read by the tensor cores
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar.p_full[sb]);
