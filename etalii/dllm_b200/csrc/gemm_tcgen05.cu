@@ -38,7 +38,7 @@ template <int BN, bool DEEP = false> struct Shape {
 // (neighbouring blocks share a tile of W and read different rows of A). The producer's ring of stages runs on across
 // tiles; the accumulator alternates between two halves of the block's tensor memory, so the epilogue of one tile
 // overlaps the products of the next.
-template <int BN, int EPI, bool DEEP>
+template <int BN, int EPI, bool DEEP, int HD>
 __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                const __grid_constant__ CUtensorMap map_w,
                                                                void* __restrict__ c, int M, int N, int K,
@@ -133,35 +133,41 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       unsigned acc = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(buf * S::ACC_COLS);
       if (EPI == EPI_QKV_ROPE) {
-        // the tile is one head (BN == head_dim): the thread holds its token's whole head, rotates the pairs
+        // the tile is BN / HD whole heads: the thread holds its token's head, one after the other, rotates the pairs
         // (i, i + rotary_dim / 2) and writes the query, or the key / value into the token's cache row
-        float f[BN];
+        constexpr int HEAD = HD > 0 ? HD : BN;  // (HD is 0 only in instantiations that never take this branch)
+        int heads = rope.heads, nkv = rope.cache.kv_heads;
+        int pos = m < M ? rope.tok_pos[m] : 0;
+#pragma unroll 1
+        for (int seg = 0; seg < BN / HEAD; ++seg) {
+          float f[HEAD];
 #pragma unroll
-        for (int col = 0; col < BN; col += 16) {
-          unsigned v[16];
-          tmem_load16(acc + (unsigned)col, v);
+          for (int col = 0; col < HEAD; col += 16) {
+            unsigned v[16];
+            tmem_load16(acc + (unsigned)(seg * HEAD + col), v);
 #pragma unroll
-          for (int i = 0; i < 16; ++i) f[col + i] = __uint_as_float(v[i]);
-        }
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&acc_empty[buf]);  // the values are in registers: the accumulator may be reused
-        int head = n_tile, heads = rope.heads, nkv = rope.cache.kv_heads;
-        if (m < M && (head < heads || rope.write_cache)) {
-          int pos = rope.tok_pos[m];
+            for (int i = 0; i < 16; ++i) f[col + i] = __uint_as_float(v[i]);
+          }
+          if (seg == BN / HEAD - 1) {  // the last values are in registers: the accumulator may be reused
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+          }
+          int head = n_tile * (BN / HEAD) + seg;
+          if (m >= M || head >= heads + 2 * nkv || !(head < heads || rope.write_cache)) continue;
           if (rope.table != nullptr && head < heads + nkv) {
             const float2* cs = rope.table + (size_t)pos * (rope.rotary_dim / 2);
 #pragma unroll
-            for (int i = 0; i < BN / 2; ++i) {  // rotary_dim == head_dim here: the partner sits half a head away
+            for (int i = 0; i < HEAD / 2; ++i) {  // rotary_dim == head_dim here: the partner sits half a head away
               float2 tc = cs[i];
-              float x = f[i], y = f[i + BN / 2];
+              float x = f[i], y = f[i + HEAD / 2];
               f[i] = fmaf(x, tc.x, -(y * tc.y));
-              f[i + BN / 2] = fmaf(x, tc.y, y * tc.x);
+              f[i + HEAD / 2] = fmaf(x, tc.y, y * tc.x);
             }
           }
           bf16* dst;
           if (head < heads) {
-            dst = rope.q_out + ((size_t)m * heads + head) * BN;
+            dst = rope.q_out + ((size_t)m * heads + head) * HEAD;
           } else {
             int which = head < heads + nkv ? 0 : 1;
             int kvh = head - heads - which * nkv;
@@ -170,7 +176,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
             dst = (bf16*)rope.cache.base + kv_offset(rope.cache, page, which, kvh, pos % rope.cache.page_size);
           }
 #pragma unroll
-          for (int i = 0; i < BN; i += 8) {
+          for (int i = 0; i < HEAD; i += 8) {
             uint4 o;
             __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
@@ -204,13 +210,13 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
   }
 }
 
-template <int BN, int EPI, bool DEEP>
+template <int BN, int EPI, bool DEEP, int HD>
 int launch_shape(void* c, const CUtensorMap& map_a, const CUtensorMap& map_w, int M, int N, int K, int* status,
                  cudaStream_t stream, const RopeArgs& rope, int m_tiles, int n_tiles, int sms) {
   typedef Shape<BN, DEEP> S;
   static bool configured = false;
   if (!configured) {
-    if (cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, EPI, DEEP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, EPI, DEEP, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)S::SMEM) != cudaSuccess)
       return DLLM_LAUNCH_FAILED;
     configured = true;
@@ -218,11 +224,11 @@ int launch_shape(void* c, const CUtensorMap& map_a, const CUtensorMap& map_w, in
   long long total = (long long)m_tiles * n_tiles;
   int blocks = sms * S::BLOCKS_PER_SM;
   if (blocks > total) blocks = (int)total;
-  return dllm_launch_pdl(gemm_tcgen05_kernel<BN, EPI, DEEP>, dim3(blocks), dim3(THREADS), S::SMEM, stream, map_a, map_w,
+  return dllm_launch_pdl(gemm_tcgen05_kernel<BN, EPI, DEEP, HD>, dim3(blocks), dim3(THREADS), S::SMEM, stream, map_a, map_w,
                          c, M, N, K, status, rope, m_tiles, n_tiles);
 }
 
-template <int BN, int EPI>
+template <int BN, int EPI, int HD = 0>
 int launch(void* c, const void* a, const void* w, int M, int N, int K, int* status, cudaStream_t stream,
            const RopeArgs& rope = RopeArgs{}) {
   alignas(64) CUtensorMap map_a, map_w;
@@ -239,8 +245,8 @@ int launch(void* c, const void* a, const void* w, int M, int N, int K, int* stat
   }
   constexpr bool CAN_DEEP = BN == 64 && EPI <= EPI_QKV_ROPE;  // (the shapes where it was measured to pay)
   if (CAN_DEEP && total <= sms && K > 4 * BK)
-    return launch_shape<BN, EPI, CAN_DEEP>(c, map_a, map_w, M, N, K, status, stream, rope, m_tiles, n_tiles, sms);
-  return launch_shape<BN, EPI, false>(c, map_a, map_w, M, N, K, status, stream, rope, m_tiles, n_tiles, sms);
+    return launch_shape<BN, EPI, CAN_DEEP, HD>(c, map_a, map_w, M, N, K, status, stream, rope, m_tiles, n_tiles, sms);
+  return launch_shape<BN, EPI, false, HD>(c, map_a, map_w, M, N, K, status, stream, rope, m_tiles, n_tiles, sms);
 }
 
 template <int BN>
@@ -292,7 +298,7 @@ DLLM_EXPORT int dllm_gemm_tcgen05(void* c, const void* a, const void* w, int M, 
 }
 
 // The q/k/v projection of a prefill-sized step in one kernel: W is [(heads + 2 kv_heads) * head_dim, K], every tile
-// of the product is one head (head_dim 32, 64 or 128; rotary_dim equal to head_dim, or no table), its epilogue
+// of the product is one or several whole heads (head_dim 32, 64 or 128; rotary_dim equal to head_dim, or no table), its epilogue
 // rotates q and k by the table's angle for each token's position and writes q to q_out and k, v into the paged cache.
 DLLM_EXPORT int dllm_gemm_tcgen05_qkv_rope(const void* a, const void* w, int M, int K, void* q_out, void* cache_base,
                                            const int* page_table, int max_pages, int page_size, int heads,
@@ -308,9 +314,16 @@ DLLM_EXPORT int dllm_gemm_tcgen05_qkv_rope(const void* a, const void* w, int M, 
   RopeArgs rope{(bf16*)q_out, KvLayout{cache_base, page_table, max_pages, page_size, kv_heads, head_dim},
                 (const float2*)table, table ? rotary_dim : 0, heads, tok_seq, tok_pos, slots, write_cache};
   int N = (heads + 2 * kv_heads) * head_dim;
+  // a tile is one head, or four heads of 64 / two of 128 where the product is large enough to fill the device with
+  // the wide tiles (which reuse A four times as often: 1.0 to 1.2 PFLOP/s against 0.6)
+  bool wide = M >= 1024 && K >= 1024 && (long long)((M + BM - 1) / BM) * ((N + 255) / 256) >= 64;
   switch (head_dim) {
-    case 32: return launch<32, EPI_QKV_ROPE>(nullptr, a, w, M, N, K, status, stream, rope);
-    case 64: return launch<64, EPI_QKV_ROPE>(nullptr, a, w, M, N, K, status, stream, rope);
-    default: return launch<128, EPI_QKV_ROPE>(nullptr, a, w, M, N, K, status, stream, rope);
+    case 32: return launch<32, EPI_QKV_ROPE, 32>(nullptr, a, w, M, N, K, status, stream, rope);
+    case 64:
+      if (wide) return launch<256, EPI_QKV_ROPE, 64>(nullptr, a, w, M, N, K, status, stream, rope);
+      return launch<64, EPI_QKV_ROPE, 64>(nullptr, a, w, M, N, K, status, stream, rope);
+    default:
+      if (wide) return launch<256, EPI_QKV_ROPE, 128>(nullptr, a, w, M, N, K, status, stream, rope);
+      return launch<128, EPI_QKV_ROPE, 128>(nullptr, a, w, M, N, K, status, stream, rope);
   }
 }

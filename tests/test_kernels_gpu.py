@@ -614,17 +614,20 @@ def test_gemm_tcgen05(m, n, k, epilogue, tile_n):
     assert rel_error(c.float().cpu(), ref.float().cpu()) <= (2e-5 if epilogue in (0, 2) else 8e-3)
 
 
-@pytest.mark.parametrize("heads,kv_heads,head_dim,rotary", [(9, 3, 64, 64), (4, 2, 32, 32), (5, 1, 128, 128),
-                                                           (3, 3, 64, 0)])
-def test_gemm_qkv_rope(heads, kv_heads, head_dim, rotary):
-    lengths, new, k = [300, 70, 5, 129], [300, 70, 1, 9], 136
+@pytest.mark.parametrize("heads,kv_heads,head_dim,rotary,wide", [
+    (9, 3, 64, 64, False), (4, 2, 32, 32, False), (5, 1, 128, 128, False), (3, 3, 64, 0, False),
+    (21, 6, 64, 64, True), (13, 2, 128, 128, True), (29, 3, 64, 0, True)])
+def test_gemm_qkv_rope(heads, kv_heads, head_dim, rotary, wide):
+    """`wide`: enough rows, columns and a long enough reduction that a tile holds four heads of 64 or two of 128
+    (head counts that are no multiples of that: the last tile ends beyond the last head, tiles straddle q, k and v)."""
+    lengths, new, k = ([900, 70, 5, 129], [900, 70, 1, 129], 1032) if wide else ([300, 70, 5, 129], [300, 70, 1, 9], 136)
     cache, view, batch = _cache_and_batch(torch.bfloat16, kv_heads, head_dim, lengths, new)
     n = batch.n_tokens
     table = None
     if rotary:
-        angles = torch.arange(400, dtype=torch.float64)[:, None] * torch.rand(rotary // 2, dtype=torch.float64)[None]
+        angles = torch.arange(1024, dtype=torch.float64)[:, None] * torch.rand(rotary // 2, dtype=torch.float64)[None]
         table = torch.stack([angles.cos(), angles.sin()], -1).float().to(DEV)
-    w = _randn(((heads + 2 * kv_heads) * head_dim, k), torch.bfloat16, 4, 0.2)
+    w = _randn(((heads + 2 * kv_heads) * head_dim, k), torch.bfloat16, 4, 0.05 if wide else 0.2)
     x = _randn((n, k), torch.bfloat16, 6)
     q = torch.zeros((n, heads * head_dim), dtype=torch.bfloat16, device=DEV)
     before = view.storage.clone()
