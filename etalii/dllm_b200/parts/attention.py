@@ -24,10 +24,11 @@ def decode_chunk(sequences: int, kv_heads: int, max_context: int, head_dim: int 
     return 1024
 
 
-TCGEN05_ATTENTION_FROM = 512
-"""Prefill steps whose longest context is above this take the tcgen05 attention kernel (measured: it leads from about
-a thousand keys per query on, 1.3 to 1.6 times at 2,048 and more; a block's fixed costs weigh more on short prompts,
-where the mma.sync kernel with its tiles of 64 queries is as fast or a little faster)."""
+TCGEN05_ATTENTION_FROM = {64: 512, 128: 192}
+"""Prefill steps whose longest context is above this (by head size) take the tcgen05 attention kernel. Measured: with
+heads of 128 it leads from 256 keys on (1.4 to 1.8 times from 384 on, one prompt or eight); with heads of 64 it leads
+from about 768 keys per query on, 1.3 to 1.6 times at 2,048 and more, while on shorter prompts a block's fixed costs
+weigh more and the mma.sync kernel with its tiles of 64 queries is as fast or a little faster."""
 
 
 class Attention:
@@ -93,7 +94,7 @@ class Attention:
             ops.attention_decode(attended, q, cache, self.num_heads, self.scale, self.window or 0, batch, chunk,
                                  scratch, tickets)
         elif not batch.is_decode and ops.attention_prefill_tcgen05_supported(cache) and \
-                batch.max_context > TCGEN05_ATTENTION_FROM:
+                batch.max_context > TCGEN05_ATTENTION_FROM.get(self.head_dim, 512):
             ops.attention_prefill_tcgen05(attended, q, cache, self.num_heads, self.scale, self.window or 0, batch)
         elif not batch.is_decode and ops.attention_prefill_supported(cache):
             ops.attention_prefill(attended, q, cache, self.num_heads, self.scale, self.window or 0, batch)

@@ -270,8 +270,9 @@ def test_long_generation_through_the_graph_path(setup):
 @pytest.mark.parametrize("head_dim", [64, 128])
 def test_head_dims_of_the_tcgen05_attention_with_long_and_short_prompts(dtype, head_dim):
     """The head sizes of the tcgen05 attention at engine level: in bfloat16 a prompt of 700 tokens takes it and
-    the tile product that ends in rotation and cache write, prompts below 512 the mma.sync attention, single tokens
-    the cluster kernel; a prompt that goes on from a cached prefix crosses tile and page edges."""
+    the tile product that ends in rotation and cache write, short prompts the mma.sync attention (a batch of 300 and
+    40 tokens lies on either side of the change, by head size), single tokens the cluster kernel; a prompt that goes
+    on from a cached prefix crosses tile and page edges."""
     config = dict(P.TINY_A, num_hidden_layers=2, tie_word_embeddings=False, max_position_embeddings=1024,
                   num_attention_heads=3, num_key_value_heads=1, head_dim=head_dim, hidden_size=72,
                   intermediate_size=120, vocab_size=203)
@@ -295,6 +296,12 @@ def test_head_dims_of_the_tcgen05_attention_with_long_and_short_prompts(dtype, h
         for i in range(3):
             contexts[i] = contexts[i] + tokens[i]
             assert rel_error(got[i], plain(contexts[i])[-1]) <= TOL[dtype], (step, i)
+    engine.close(slots)
+    middle, little = prompts_for(config, (300, 40), seed=24)
+    slots = engine.open(2)
+    got = host(engine.step(slots, [middle, little], [[0, 191, 192, 299], [39]]))
+    assert rel_error(got[:4], plain(middle)[[0, 191, 192, 299]]) <= TOL[dtype]
+    assert rel_error(got[4], plain(little)[-1]) <= TOL[dtype]
     engine.close(slots)
     engine.cache.check()
 
