@@ -113,7 +113,7 @@ def test_gemm_with_an_odd_number_of_outputs(m, n, k, epilogue, kernel):
     assert rel_error(c.float().cpu(), ref.float().cpu()) <= tol
 
 
-@pytest.mark.parametrize("m", [1, 5, 8, 9, 16])
+@pytest.mark.parametrize("m", [1, 2, 3, 5, 8, 9, 16])
 @pytest.mark.parametrize("n,k", [(64, 64), (130, 576), (1001, 1088), (4100, 512), (9500, 192), (96, 2624)])
 @pytest.mark.parametrize("epilogue", [0, 1, 2, 3])
 def test_gemm_streaming_through_shared_memory(m, n, k, epilogue):
