@@ -56,7 +56,7 @@ class BatchBuffers:
         cu = np.zeros(b + 1, dtype=np.int32)
         np.cumsum(counts, out=cu[1:])
         o = 0
-        host[o:o + n] = np.fromiter((t for seq in new_tokens for t in seq), dtype=np.int32, count=n); o += n
+        host[o:o + n] = np.concatenate([np.asarray(seq) for seq in new_tokens]) if n else np.zeros(0, np.int32); o += n
         host[o:o + n] = np.repeat(np.arange(b, dtype=np.int32), counts); o += n
         pos = np.concatenate([np.arange(s, s + c, dtype=np.int32) for s, c in zip(starts, counts)]) if n else \
             np.zeros(0, np.int32)

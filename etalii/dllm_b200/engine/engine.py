@@ -8,6 +8,7 @@ from __future__ import annotations
 import time
 from typing import Sequence
 
+import numpy as np
 import torch
 
 from .. import architectures  # noqa: F401  (registers the built-in architectures)
@@ -102,10 +103,11 @@ class Engine:
             raise CacheError("a sequence appears twice in one step")  # src/etalii_dllm/transformer.py:405-406
         if want is None:
             want = [[len(t) - 1] for t in new_tokens]
+        new_tokens = [np.asarray(tokens, dtype=np.int64) for tokens in new_tokens]  # one pass over each list
         for tokens, rows in zip(new_tokens, want):
-            if len(tokens) == 0:
+            if tokens.ndim != 1 or tokens.size == 0:
                 raise ValueError("a sequence in a step needs at least one token")
-            if min(tokens) < 0 or max(tokens) >= self.vocab_size:
+            if tokens.min() < 0 or tokens.max() >= self.vocab_size:
                 raise ValueError(f"a token is outside the vocabulary of {self.vocab_size}")
             if any(not 0 <= r < len(tokens) for r in rows):
                 raise ValueError("a wanted position is outside the sequence's new tokens")

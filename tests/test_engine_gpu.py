@@ -223,6 +223,42 @@ def test_sizes_the_kernels_refuse_are_clear_errors():
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_a_step_shape_that_comes_again_with_other_tokens_slots_and_pages(dtype, name):
+    """The same step shape (two prompts of unequal lengths, the same wanted rows) with other tokens each time, in
+    other slots and pages, and a different shape in between: every time the logits are those of the plain
+    implementation for THAT time's tokens (anything kept from an earlier step of the same shape, a buffer view, a
+    tensor map or a table, would show if it were stale)."""
+    config = P.TINY_A if name == "A" else P.TINY_B
+    weights = P.random_weights(config, seed=31)
+    engine = make_engine(config, weights, dtype, max_tokens=64 * 12)
+    plain = PlainLogits(config, weights)
+    want = [[0, 17, 69], [4]]
+    held = engine.open(1)  # a slot that stays taken, so the prompts' slots change between rounds
+    engine.step(held, [[1, 2, 3]])
+    for turn in range(5):
+        a, b = prompts_for(config, (70, 5), seed=40 + turn)
+        extra = engine.open(turn % 2)  # shifts which slots and pages the prompts get
+        slots = engine.open(2)
+        got = host(engine.step(slots, [a, b], want))
+        assert rel_error(got[:3], plain(a)[[0, 17, 69]]) <= TOL[dtype], turn
+        assert rel_error(got[3], plain(b)[4]) <= TOL[dtype], turn
+        if turn == 2:  # another shape in between
+            other = prompts_for(config, (33,), seed=50)[0]
+            slot = engine.open(1)
+            assert rel_error(host(engine.step(slot, [other]))[0], plain(other)[-1]) <= TOL[dtype]
+            engine.close(slot)
+        # the prompts go on by a token each: a step from the cache that the replayed step wrote
+        nxt = [[7], [9]]
+        got = host(engine.step(slots, nxt))
+        assert rel_error(got[0], plain(a + nxt[0])[-1]) <= TOL[dtype], turn
+        assert rel_error(got[1], plain(b + nxt[1])[-1]) <= TOL[dtype], turn
+        engine.close(slots + extra)
+    engine.close(held)
+    engine.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_an_odd_vocabulary(dtype):
     config = dict(P.TINY_A, num_hidden_layers=2, vocab_size=131, tie_word_embeddings=False)
     weights = P.random_weights(config, seed=1)
