@@ -258,6 +258,39 @@ def test_a_step_shape_that_comes_again_with_other_tokens_slots_and_pages(dtype, 
     engine.cache.check()
 
 
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_a_neighbour_in_decode_changes_no_bit_in_float32_and_a_repetition_none_in_bfloat16(name):
+    """Two sequences decoded side by side in 32-bit give the bits each gives as a whole prompt alone (the
+    reference's character, README.md:9-15: bits independent of batch and of how a sequence is split). In bfloat16
+    the kernels differ with the number of rows, so only the repetition of a run gives the same bits there: no
+    kernel sums in an order that depends on which block arrives first."""
+    config = P.TINY_A if name == "A" else P.TINY_B
+    weights = P.random_weights(config, seed=3, std=0.08)
+    engine = make_engine(config, weights, "float32", max_tokens=64 * 16)
+    a, b = prompts_for(config, (90, 33), seed=4)
+    alone = []
+    for prompt in (a, b):
+        slot = engine.open(1)
+        alone.append(host(engine.step(slot, [prompt], [list(range(len(prompt)))])))
+        engine.close(slot)
+    slots = engine.open(2)
+    engine.step(slots, [a[:70], b[:13]], [[], []])
+    for i in range(20):
+        got = host(engine.step(slots, [[a[70 + i]], [b[13 + i]]]))
+        assert np.array_equal(got[0], alone[0][70 + i]) and np.array_equal(got[1], alone[1][13 + i]), i
+    engine.close(slots)
+    engine.cache.check()
+    bf16 = make_engine(config, weights, "bfloat16", max_tokens=64 * 16)
+    runs = []
+    for _ in range(2):
+        slots = bf16.open(2)
+        rows = [host(bf16.step(slots, [a, b], [[0, 89], [32]]))]
+        rows += [host(bf16.step(slots, [[5 + i], [6 + i]])) for i in range(3)]
+        bf16.close(slots)
+        runs.append(np.concatenate(rows))
+    assert np.array_equal(runs[0], runs[1])
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_an_odd_vocabulary(dtype):
     config = dict(P.TINY_A, num_hidden_layers=2, vocab_size=131, tie_word_embeddings=False)
