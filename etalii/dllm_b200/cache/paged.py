@@ -90,6 +90,8 @@ class PagedCache:
         self.device, self.dtype = device, dtype
         self.slots = FreeList(self.n_slots, "slot")
         self.lengths = [0] * self.n_slots
+        self._stage_ring = [[None, None, None] for _ in range(self.STAGING_RING)]  # table rows, indices, event
+        self._stage_at = 0
         self.needs = list(needs)
         self._groups: list[_KvGroup] = []
         self._state: dict[int, torch.Tensor | None] = {}
@@ -171,14 +173,42 @@ class PagedCache:
         self.lengths[slot] += new_tokens
 
     def sync_tables(self) -> None:
-        """Copies the page-table rows that changed to the device."""
+        """Copies the page-table rows that changed to the device: staged in pinned memory (a small ring, each
+        buffer waited for before it is written again), then copied on the current stream without a host wait; a
+        few rows go row by row, many through one copy and a scatter."""
         for group in self._groups:
             if group.dirty and group.table is not None:
                 rows = sorted(group.dirty)
-                index = torch.tensor(rows, dtype=torch.int64)
-                update = torch.from_numpy(group.table_host[rows])
-                group.table.index_copy_(0, index.to(self.device), update.to(self.device))
+                stage, index = self._staging(len(rows), group.table.shape[1])
+                stage.numpy()[:] = group.table_host[rows]
+                if len(rows) <= 4:
+                    for i, row in enumerate(rows):
+                        group.table[row].copy_(stage[i], non_blocking=True)
+                else:
+                    index.numpy()[:] = rows
+                    group.table.index_copy_(0, index.to(self.device, non_blocking=True),
+                                            stage.to(self.device, non_blocking=True))
+                self._staged()
             group.dirty.clear()
+
+    STAGING_RING = 4
+
+    def _staging(self, rows: int, width: int) -> tuple[torch.Tensor, torch.Tensor]:
+        entry = self._stage_ring[self._stage_at]
+        if entry[2] is not None:
+            entry[2].synchronize()
+        if entry[0] is None or entry[0].numel() < rows * width:
+            entry[0] = torch.empty(max(rows * width, 1024), dtype=torch.int32).pin_memory()
+            entry[1] = torch.empty(max(rows, 64), dtype=torch.int64).pin_memory()
+        if entry[1].numel() < rows:
+            entry[1] = torch.empty(rows, dtype=torch.int64).pin_memory()
+        return entry[0][: rows * width].view(rows, width), entry[1][:rows]
+
+    def _staged(self) -> None:
+        event = torch.cuda.Event()
+        event.record()
+        self._stage_ring[self._stage_at][2] = event
+        self._stage_at = (self._stage_at + 1) % self.STAGING_RING
 
     # ---- views ----
     def kv_view(self, entry: int) -> KvView:

@@ -3,6 +3,9 @@ token into the next step's input, captured once per batch size as a CUDA graph a
 batch's fixed buffers before a run of steps and reads the chosen tokens after it."""
 from __future__ import annotations
 
+import gc
+import weakref
+
 import numpy as np
 import torch
 
@@ -15,7 +18,9 @@ class DecodeGraph:
     """Most steps one run may take before the host reads the tokens."""
 
     def __init__(self, engine, batch_size: int, options, use_graph: bool = True, max_context: int | None = None) -> None:
-        self.engine, self.b, self.options, self.use_graph = engine, batch_size, options, use_graph
+        # (a weak reference: the engine owns its graphs, and an engine that is dropped should die at once, with
+        # its device and pinned memory, not wait for the cycle collector)
+        self.engine, self.b, self.options, self.use_graph = weakref.proxy(engine), batch_size, options, use_graph
         b = batch_size
         device = engine.rt.device
         self.host = torch.empty(7 * b + 2, dtype=torch.int32).pin_memory()
@@ -76,9 +81,19 @@ class DecodeGraph:
             steps -= 1
             torch.cuda.synchronize()
             if steps > 0:
-                graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph):
-                    self._body()
+                # No garbage collection while the stream captures: an object that dies then and owns pinned host
+                # memory (an engine that is no longer used, say) makes the allocator record an event on the
+                # default stream, which is not permitted during a capture and invalidates it. Dead cycles go first.
+                gc.collect()
+                collecting = gc.isenabled()
+                gc.disable()
+                try:
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph):
+                        self._body()
+                finally:
+                    if collecting:
+                        gc.enable()
                 self.graph, self.generation = graph, ws.generation
         for _ in range(steps):
             if self.use_graph:
