@@ -63,9 +63,13 @@ def main(argv: list[str] | None = None) -> int:
     if args.command == "random":
         from .weights.random_init import write_random_model
 
-        with open(args.config, encoding="utf-8") as handle:
-            config = config_from_dict(json.load(handle))
-        print(write_random_model(args.out, config, args.seed, std=args.std))
+        try:
+            with open(args.config, encoding="utf-8") as handle:
+                config = config_from_dict(json.load(handle))
+            print(write_random_model(args.out, config, args.seed, std=args.std))
+        except (ValueError, OSError) as error:  # an unreadable file, bad JSON, a configuration that is refused
+            print(f"error: {error}", file=sys.stderr)
+            return 2
         return 0
     if not args.model:
         print("error: --model is required", file=sys.stderr)
@@ -80,10 +84,14 @@ def main(argv: list[str] | None = None) -> int:
                          indent=1))
         return 0
 
-    prompts = [_ids(text) for text in args.prompt_ids]
-    if args.prompt_file:
-        with open(args.prompt_file, encoding="utf-8") as handle:
-            prompts += [_ids(line) for line in handle if line.strip()]
+    try:
+        prompts = [_ids(text) for text in args.prompt_ids]
+        if args.prompt_file:
+            with open(args.prompt_file, encoding="utf-8") as handle:
+                prompts += [_ids(line) for line in handle if line.strip()]
+    except (ValueError, OSError) as error:
+        print(f"error: a prompt is a list of token ids: {error}", file=sys.stderr)
+        return 2
     if not prompts:
         print("error: give --prompt-ids or --prompt-file", file=sys.stderr)
         return 2
@@ -98,7 +106,11 @@ def main(argv: list[str] | None = None) -> int:
         return 2
     from .engine.engine import Engine
 
-    engine = Engine.from_folder(args.model, dtype=args.dtype, device=args.device, max_tokens=args.cache_tokens)
+    try:
+        engine = Engine.from_folder(args.model, dtype=args.dtype, device=args.device, max_tokens=args.cache_tokens)
+    except (ValueError, OSError, RuntimeError) as error:  # weights that do not fit, no CUDA device, a failed build
+        print(f"error: {error}", file=sys.stderr)
+        return 2
     try:
         for index, prompt in enumerate(prompts):
             # the N choices of one prompt run as one batch; choice i draws from the stream of seed + i
@@ -110,7 +122,7 @@ def main(argv: list[str] | None = None) -> int:
                 print(" ".join(str(t) for t in result.tokens))
                 print(f"fingerprint: {result.fingerprint}  tokens: {len(result.tokens)}  "
                       f"finish: {result.finish_reason}", file=sys.stderr)
-    except ValueError as error:
+    except (ValueError, RuntimeError) as error:  # a prompt that is refused, a cache that is too small, a kernel error
         print(f"error: {error}", file=sys.stderr)
         return 2
     return 0
