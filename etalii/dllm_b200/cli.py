@@ -40,6 +40,7 @@ def build_parser() -> argparse.ArgumentParser:
     generate.add_argument("--top-p", type=float, default=1.0)
     generate.add_argument("--seed", type=int, default=0)
     generate.add_argument("--min-p", type=float, default=0.0, help="drop tokens below MIN_P times the top one")
+    generate.add_argument("--min-tokens", type=int, default=0, help="no stop token before this many tokens")
     generate.add_argument("--ignore-eos", action="store_true", help="write past the model's end-of-sequence")
     generate.add_argument("--stop-token-id", type=int, action="append", default=[],
                           help="also end at this token id (repeatable)")
@@ -115,7 +116,7 @@ def main(argv: list[str] | None = None) -> int:
         for index, prompt in enumerate(prompts):
             # the N choices of one prompt run as one batch; choice i draws from the stream of seed + i
             results = engine.generate([prompt] * args.n, args.max_tokens, options, ignore_eos=args.ignore_eos,
-                                      stop_token_ids=args.stop_token_id)
+                                      stop_token_ids=args.stop_token_id, min_tokens=args.min_tokens)
             for choice, result in enumerate(results):
                 if args.n > 1:
                     print(f"--- choice {choice} (seed {options.for_choice(choice).seed})", file=sys.stderr)

@@ -243,3 +243,27 @@ DLLM_EXPORT int dllm_decode_advance(int* tokens, int* tok_pos, int* start, const
   return dllm_launch_pdl(decode_advance_kernel, dim3(1), dim3(256), 0, stream, tokens, tok_pos, start, chosen,
                          history, counter, batch, capacity);
 }
+
+// Takes token ids out of the choice while an output is shorter than it has to be: logits[row, ids[i]] = -inf for
+// every row, if *produced + *steps < min_tokens (`produced`: tokens every sequence of the batch has so far when a run
+// of steps begins; `steps`: the steps of that run so far, or null). A probability of exactly zero is never drawn and
+// never the largest, so what is chosen is what a choice among the other tokens alone would choose.
+__global__ void mask_tokens_kernel(float* __restrict__ logits, int rows, int vocab, const int* __restrict__ ids,
+                                   int n_ids, const int* __restrict__ produced, const int* __restrict__ steps,
+                                   int min_tokens) {
+  pdl_wait();
+  int have = *produced + (steps != nullptr ? *steps : 0);
+  if (have >= min_tokens) return;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < rows * n_ids; i += gridDim.x * blockDim.x) {
+    int id = ids[i % n_ids];
+    if (id >= 0 && id < vocab) logits[(size_t)(i / n_ids) * vocab + id] = -INFINITY;
+  }
+}
+
+DLLM_EXPORT int dllm_mask_tokens(float* logits, int rows, int vocab, const int* ids, int n_ids, const int* produced,
+                                 const int* steps, int min_tokens, cudaStream_t stream) {
+  if (rows <= 0 || n_ids <= 0 || min_tokens <= 0) return DLLM_OK;
+  if (vocab <= 0 || logits == nullptr || ids == nullptr || produced == nullptr) return DLLM_BAD_ARGUMENT;
+  return dllm_launch_pdl(mask_tokens_kernel, dim3(1), dim3(256), 0, stream, logits, rows, vocab, ids, n_ids, produced,
+                         steps, min_tokens);
+}

@@ -17,14 +17,17 @@ class DecodeGraph:
     CAPACITY = 64
     """Most steps one run may take before the host reads the tokens."""
 
-    def __init__(self, engine, batch_size: int, options, use_graph: bool = True, max_context: int | None = None) -> None:
+    def __init__(self, engine, batch_size: int, options, use_graph: bool = True, max_context: int | None = None,
+                 min_tokens: int = 0, blocked: tuple = ()) -> None:
+        """`min_tokens`, `blocked`: while the sequences have fewer than `min_tokens` tokens of output, the token ids in
+        `blocked` (the stop tokens) are taken out of the choice (src/etalii_dllm/generation.py:316, 373-381)."""
         # (a weak reference: the engine owns its graphs, and an engine that is dropped should die at once, with
         # its device and pinned memory, not wait for the cycle collector)
         self.engine, self.b, self.options, self.use_graph = weakref.proxy(engine), batch_size, options, use_graph
         b = batch_size
         device = engine.rt.device
-        self.host = torch.empty(7 * b + 2, dtype=torch.int32).pin_memory()
-        self.meta = torch.zeros(7 * b + 2, dtype=torch.int32, device=device)
+        self.host = torch.empty(7 * b + 3, dtype=torch.int32).pin_memory()
+        self.meta = torch.zeros(7 * b + 3, dtype=torch.int32, device=device)
         self.history = torch.zeros(self.CAPACITY * b, dtype=torch.int32, device=device)
         self.chosen = torch.zeros(b, dtype=torch.int32, device=device)
         batch = StepBatch()
@@ -36,7 +39,10 @@ class DecodeGraph:
         batch.slots = self.meta[o:o + b]; o += b
         batch.start = self.meta[o:o + b]; o += b
         batch.want_rows = self.meta[o:o + b]; o += b
-        self.counter = self.meta[o:o + 1]
+        self.counter = self.meta[o:o + 1]; o += 1
+        self.produced = self.meta[o:o + 1]  # tokens of output every sequence has when a run of steps begins
+        self.min_tokens = int(min_tokens) if blocked else 0
+        self.blocked = torch.tensor(sorted(blocked), dtype=torch.int32, device=device) if self.min_tokens > 0 else None
         batch.n_seqs = batch.n_tokens = batch.n_want = b
         batch.h_new = [1] * b
         batch.max_new = 1
@@ -51,12 +57,15 @@ class DecodeGraph:
 
     def _body(self) -> None:
         logits = self.engine.model.forward(self.batch)
+        if self.blocked is not None:
+            ops.mask_tokens(logits, self.blocked, self.produced, self.counter, self.min_tokens)
         self.engine.sampler.choose(logits, self.batch.slots, self.options, out=self.chosen)
         ops.decode_advance(self.batch.tokens, self.batch.tok_pos, self.batch.start, self.chosen, self.history,
                            self.counter, self.b)
 
-    def load(self, slots, tokens, starts) -> None:
-        """Fills the fixed buffers: each sequence's slot, next input token and cached length."""
+    def load(self, slots, tokens, starts, produced: int = 0) -> None:
+        """Fills the fixed buffers: each sequence's slot, next input token and cached length, and how many tokens of
+        output the sequences have so far."""
         b = self.b
         host = self.host.numpy()
         arange = np.arange(b, dtype=np.int32)
@@ -68,6 +77,7 @@ class DecodeGraph:
         host[5 * b + 1:6 * b + 1] = starts
         host[6 * b + 1:7 * b + 1] = arange
         host[7 * b + 1] = 0
+        host[7 * b + 2] = produced
         self.batch.h_slots, self.batch.h_start = list(slots), list(starts)
         self.meta.copy_(self.host, non_blocking=True)
 

@@ -14,6 +14,7 @@ import torch
 from .. import architectures  # noqa: F401  (registers the built-in architectures)
 from ..cache.allocators import CacheError
 from ..config.registry import architecture, load_config
+from ..kernels import ops
 from ..sampling.options import SamplingOptions
 from ..sampling.sampler import Sampler
 from ..weights.loader import load_weights
@@ -125,17 +126,23 @@ class Engine:
         return logits
 
     def decode(self, slots: Sequence[int], tokens: Sequence[int], steps: int,
-               options: SamplingOptions | None = None) -> list[list[int]]:
+               options: SamplingOptions | None = None, min_tokens: int = 0, blocked: Sequence[int] = (),
+               produced: int = 0) -> list[list[int]]:
         """Runs `steps` single-token steps for the sequences in `slots`, starting from `tokens` (each sequence's
         latest token, not yet in the cache); every step's chosen token is the next step's input, on the device.
-        Returns the chosen tokens [step][sequence]. Uses one CUDA graph per batch size and sampling options."""
+        Returns the chosen tokens [step][sequence]. Uses one CUDA graph per batch size and sampling options.
+        `blocked` token ids cannot be chosen while a sequence has fewer than `min_tokens` tokens of output, of which
+        it has `produced` now."""
+        if produced >= min_tokens or not blocked:
+            min_tokens, blocked = 0, ()  # nothing is held back any more: the graph without the masking kernel
         graph = self._decode_graph(len(slots), options or SamplingOptions(),
-                                   max(self.cache.length(s) for s in slots) + steps)
-        self.decode_start(graph, slots, tokens, steps)
+                                   max(self.cache.length(s) for s in slots) + steps, int(min_tokens),
+                                   tuple(sorted(set(int(t) for t in blocked))))
+        self.decode_start(graph, slots, tokens, steps, produced)
         graph.replay(steps)
         return graph.tokens(steps)
 
-    def decode_start(self, graph, slots, tokens, steps: int) -> None:
+    def decode_start(self, graph, slots, tokens, steps: int, produced: int = 0) -> None:
         """Makes cache room for `steps` more tokens of each sequence and loads the graph's fixed buffers."""
         if steps > graph.CAPACITY:
             raise ValueError(f"at most {graph.CAPACITY} steps per run")
@@ -148,7 +155,7 @@ class Engine:
             self.cache.reserve(slot, steps)
             starts.append(self.cache.length(slot))
         self.cache.sync_tables()
-        graph.load(slots, tokens, starts)
+        graph.load(slots, tokens, starts, produced)
         for slot in slots:
             self.cache.advance(slot, steps)
         self.steps_run += steps
@@ -157,24 +164,30 @@ class Engine:
     """Decode graphs are captured for contexts up to a multiple of this; a batch that outgrows its bucket moves to
     the next graph (so attention does not launch blocks for the whole cache when contexts are short)."""
 
-    def _decode_graph(self, batch_size: int, options: SamplingOptions, longest: int | None = None):
+    def _decode_graph(self, batch_size: int, options: SamplingOptions, longest: int | None = None,
+                      min_tokens: int = 0, blocked: tuple = ()):
         bound = self.max_length if longest is None else \
             min(self.max_length, -(-int(longest) // self.CONTEXT_BUCKET) * self.CONTEXT_BUCKET)
-        key = (batch_size, bound, options.temperature, options.top_k, options.top_p, options.min_p)
+        key = (batch_size, bound, options.temperature, options.top_k, options.top_p, options.min_p, min_tokens,
+               blocked)
         graph = self._graphs.get(key)
         if graph is None:
             graph = self._graphs[key] = DecodeGraph(self, batch_size, options, use_graph=self.cuda_graphs,
-                                                    max_context=bound)
+                                                    max_context=bound, min_tokens=min_tokens, blocked=blocked)
         return graph
 
     # ---- generation ----
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int = 64,
                  options: SamplingOptions | None = None, stop_token_ids: Sequence[int] | None = None,
-                 ignore_eos: bool = False, max_batch: int | None = None) -> list[GenerationResult]:
+                 ignore_eos: bool = False, max_batch: int | None = None, min_tokens: int = 0) -> list[GenerationResult]:
         """Generates for every prompt (lists of token ids), as many batches one after another as the cache needs.
         Stop ids default to the model's end-of-sequence ids; `stop_token_ids` adds more; `ignore_eos` drops the
-        model's own (src/etalii_dllm/cli.py:427-431). Sequence i draws from the stream of options.seed + i."""
+        model's own; until an output has `min_tokens` tokens no stop token can be chosen: they are taken out of the
+        choice (src/etalii_dllm/cli.py:427-431, src/etalii_dllm/generation.py:316, 373-381, 512-513).
+        Sequence i draws from the stream of options.seed + i."""
         options = options or SamplingOptions()
+        if min_tokens < 0:
+            raise ValueError("min_tokens must be non-negative")
         stats = self.stats = {"prefill_s": 0.0, "prefill_tokens": 0, "decode_s": 0.0, "decode_steps": 0,
                               "decode_tokens": 0}
         prompts = [list(map(int, p)) for p in prompts]
@@ -185,10 +198,14 @@ class Engine:
         batches = plan_batches([len(p) for p in prompts], max_new_tokens, window, self.cache.page_size,
                                self.cache.n_pages, self.cache.n_slots, max_batch)
 
+        held_back = tuple(sorted(stops)) if min_tokens > 0 else ()
+        produced = [0]  # tokens of output every running sequence of the batch has (they start together)
+
         def make_run(indices):
             return BatchRun([len(prompts[i]) for i in indices], max_new_tokens, frozenset(stops), window)
 
         def start(indices):
+            produced[0] = 0
             slots = self.open(len(indices))
             if options.temperature > 0:
                 self.sampler.seed(slots, [options.seed + i for i in indices])
@@ -197,14 +214,20 @@ class Engine:
         def prefill(slots, positions, tokens):
             began = time.perf_counter()
             logits = self.step([slots[p] for p in positions], tokens)
+            if held_back:
+                ops.mask_tokens(logits, torch.tensor(held_back, dtype=torch.int32, device=self.rt.device),
+                                torch.zeros(1, dtype=torch.int32, device=self.rt.device), None, min_tokens)
             chosen = self.sampler.choose(logits, self.last_batch.slots, options).tolist()
+            produced[0] = 1
             stats["prefill_s"] += time.perf_counter() - began
             stats["prefill_tokens"] += sum(len(t) for t in tokens)
             return chosen
 
         def decode(slots, positions, last_tokens, steps):
             began = time.perf_counter()
-            out = self.decode([slots[p] for p in positions], last_tokens, steps, options)
+            out = self.decode([slots[p] for p in positions], last_tokens, steps, options, min_tokens, held_back,
+                              produced[0])
+            produced[0] += steps
             stats["decode_s"] += time.perf_counter() - began
             stats["decode_steps"] += steps
             stats["decode_tokens"] += steps * len(positions)

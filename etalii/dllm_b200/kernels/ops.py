@@ -28,6 +28,7 @@ _prototypes = {
     ("elementwise", "dllm_add_residual"): [c_void_p, c_void_p, c_longlong, c_int, c_void_p],
     ("elementwise", "dllm_decode_advance"): [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                              c_void_p],
+    ("elementwise", "dllm_mask_tokens"): [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p],
     ("gemm_simt", "dllm_gemm_f32"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     ("gemm_bf16", "dllm_gemm_bf16"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     ("gemm_tcgen05", "dllm_gemm_tcgen05"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
@@ -392,6 +393,19 @@ def decode_advance(tokens: torch.Tensor, tok_pos: torch.Tensor, start: torch.Ten
     _check(_fn("elementwise", "dllm_decode_advance")(
         tokens.data_ptr(), tok_pos.data_ptr(), start.data_ptr(), chosen.data_ptr(), history.data_ptr(),
         counter.data_ptr(), batch, history.numel() // batch, _stream()), "decode_advance")
+
+
+def mask_tokens(logits: torch.Tensor, ids: torch.Tensor, produced: torch.Tensor, steps: torch.Tensor | None,
+                min_tokens: int) -> None:
+    """logits[:, ids] = -inf in every row while produced[0] + steps[0] < min_tokens (float32 logits [rows, vocab];
+    ids, produced and steps int32 on the device; `steps` may be None). Ids outside the vocabulary are skipped."""
+    _cuda(logits, ids, produced)
+    assert logits.dtype == torch.float32 and logits.dim() == 2 and logits.is_contiguous()
+    assert ids.dtype == torch.int32 and produced.dtype == torch.int32
+    assert steps is None or (steps.is_cuda and steps.dtype == torch.int32)
+    _check(_fn("elementwise", "dllm_mask_tokens")(
+        logits.data_ptr(), logits.shape[0], logits.shape[1], ids.data_ptr(), ids.numel(), produced.data_ptr(),
+        steps.data_ptr() if steps is not None else None, int(min_tokens), _stream()), "mask_tokens")
 
 
 def attention_decode_scratch(sequences: int, heads: int, head_dim: int, chunk: int, max_context: int) -> int:

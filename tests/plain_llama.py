@@ -226,11 +226,17 @@ def softmax(logits: np.ndarray) -> np.ndarray:
 
 
 def sample(logits: np.ndarray, random: Random, temperature: float = 0.0, top_k: int = 0, top_p: float = 1.0,
-           min_p: float = 0.0) -> int:
+           min_p: float = 0.0, allowed: Sequence[int] | None = None) -> int:
     """Greedy at temperature 0; else float32 logits / float32 temperature, softmax, candidates ordered by
     (probability descending, id ascending), top-k, top-p (shortest prefix reaching it), min-p, then one
     next_double() scaled by the kept mass picks the first candidate whose running sum exceeds it
-    (src/etalii_dllm/reference.py:909-982, src/etalii_dllm/sampling.py:441-500)."""
+    (src/etalii_dllm/reference.py:909-982, src/etalii_dllm/sampling.py:441-500). With `allowed` (ascending ids) the
+    choice is made among those tokens only: the same rule on the logits of the subset
+    (src/etalii_dllm/sampling.py:400-409)."""
+    if allowed is not None:
+        ids = [int(i) for i in allowed]
+        subset = np.asarray(logits, F32)[ids]
+        return ids[sample(subset, random, temperature, top_k, top_p, min_p)]
     if temperature == 0:
         return argmax(logits)
     scaled = np.asarray(logits, F32) / F32(temperature)
@@ -266,10 +272,11 @@ def sample(logits: np.ndarray, random: Random, temperature: float = 0.0, top_k: 
 
 def generate(config: Mapping, weights: Mapping[str, np.ndarray], prompt: Sequence[int], max_tokens: int,
              temperature: float = 0.0, top_k: int = 0, top_p: float = 1.0, min_p: float = 0.0, seed: int = 0,
-             stop_tokens: Sequence[int] = ()) -> tuple[list[int], str]:
+             stop_tokens: Sequence[int] = (), min_tokens: int = 0) -> tuple[list[int], str]:
     """One sequence: forward over the whole context each time (no cache), choose, stop on a stop token (which is not
     part of the output), else append; ends at max_tokens or a full context window
-    (src/etalii_dllm/generation.py:277-330, src/etalii_dllm/reference.py:1372-1396)."""
+    (src/etalii_dllm/generation.py:277-330, src/etalii_dllm/reference.py:1372-1396). While the output is shorter
+    than `min_tokens` the stop tokens are taken out of the choice (src/etalii_dllm/generation.py:316, 373-381)."""
     window = int(config.get("max_position_embeddings", 2048))
     if len(prompt) >= window:
         raise ValueError(f"the prompt has {len(prompt)} tokens; the context window holds {window}")
@@ -281,7 +288,10 @@ def generate(config: Mapping, weights: Mapping[str, np.ndarray], prompt: Sequenc
         if len(context) >= window:
             break
         logits = forward(config, weights, context)[-1]
-        token = sample(logits, random, temperature, top_k, top_p, min_p)
+        allowed = None
+        if len(out) < min_tokens and stop_tokens:
+            allowed = [t for t in range(len(logits)) if t not in stop_tokens]
+        token = sample(logits, random, temperature, top_k, top_p, min_p, allowed)
         if token in stop_tokens:
             finish = "stop"
             break

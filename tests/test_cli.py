@@ -56,3 +56,16 @@ def test_prompts_that_are_not_ids_and_missing_prompts(config_file, tmp_path, cap
     if not torch.cuda.is_available():
         assert main(["--model", str(out), "generate", "--prompt-ids", "1,2"]) == 2
         assert "no CUDA device" in capsys.readouterr().err
+
+
+def test_generate_options_have_the_reference_names():
+    """src/etalii_dllm/cli.py:357-431: the length controls and sampling options of `generate`."""
+    from etalii.dllm_b200.cli import build_parser
+
+    args = build_parser().parse_args(
+        ["--model", "m", "--dtype", "float32", "generate", "--prompt-ids", "1,2", "--max-tokens", "9", "--temperature",
+         "0.7", "--top-k", "5", "--top-p", "0.9", "--min-p", "0.1", "--seed", "4", "--n", "2", "--min-tokens", "3",
+         "--ignore-eos", "--stop-token-id", "7", "--stop-token-id", "8"])
+    assert (args.max_tokens, args.temperature, args.top_k, args.top_p, args.min_p, args.seed, args.n) == \
+        (9, 0.7, 5, 0.9, 0.1, 4, 2)
+    assert args.min_tokens == 3 and args.ignore_eos and args.stop_token_id == [7, 8]

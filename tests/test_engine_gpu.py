@@ -291,6 +291,33 @@ def test_a_neighbour_in_decode_changes_no_bit_in_float32_and_a_repetition_none_i
     assert np.array_equal(runs[0], runs[1])
 
 
+def test_no_stop_token_before_min_tokens(setup):
+    """`min_tokens`: the stop tokens are taken out of the choice until an output is that long (greedy: the runner-up
+    is chosen where a stop token leads; sampled: the draw is made among the other tokens), in the prompt step, inside
+    a run of decode steps and across runs; after that a stop token ends the sequence as ever."""
+    from etalii.dllm_b200 import SamplingOptions
+
+    tag, dtype, config, weights, engine, _ = setup
+    if dtype != "float32":
+        pytest.skip("tokens are compared one for one in float32")
+    prompts = prompts_for(config, (6, 19, 2), seed=33)
+    for options, kwargs in ((SamplingOptions(), {}), (SamplingOptions(temperature=0.9, seed=3), {"temperature": 0.9})):
+        free = engine.generate(prompts, 24, options, ignore_eos=True)
+        # stop tokens that each sequence would choose early: its first token and one a few steps in
+        stops = sorted({free[0].tokens[0], free[1].tokens[2], free[2].tokens[5], free[0].tokens[9]})
+        for min_tokens in (0, 1, 4, 7, 30):
+            results = engine.generate(prompts, 24, options, ignore_eos=True, stop_token_ids=stops,
+                                      min_tokens=min_tokens)
+            for index, (prompt, result) in enumerate(zip(prompts, results)):
+                want, reason = P.generate(config, weights, prompt, 24, seed=options.seed + index, stop_tokens=stops,
+                                          min_tokens=min_tokens, **kwargs)
+                assert list(result.tokens) == want and result.finish_reason == reason, (min_tokens, index)
+                assert reason == "length" or len(want) >= min_tokens
+    with pytest.raises(ValueError, match="min_tokens"):
+        engine.generate(prompts, 4, min_tokens=-1)
+    engine.cache.check()
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_an_odd_vocabulary(dtype):
     config = dict(P.TINY_A, num_hidden_layers=2, vocab_size=131, tie_word_embeddings=False)

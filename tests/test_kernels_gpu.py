@@ -349,6 +349,37 @@ def test_sample_with_many_rows_and_flat_or_peaked_distributions(rows, spread):
         assert got == want, options
 
 
+def test_mask_tokens_holds_stop_tokens_back_until_the_output_is_long_enough():
+    """logits[:, ids] = -inf while produced + steps < min_tokens, nothing otherwise; ids outside the vocabulary are
+    skipped; and the sampler's choice on the masked rows is the plain sampler's choice among the other tokens."""
+    import plain_llama as P
+
+    g = torch.Generator().manual_seed(9)
+    logits = torch.randn((5, 777), generator=g) * 2
+    ids = [3, 776, 400, 5000, -1]
+    best = logits.argmax(dim=1).tolist()
+    ids[2] = best[1]  # one row's largest logit is held back
+    dev_ids = torch.tensor(ids, dtype=torch.int32, device=DEV)
+    for produced, steps, min_tokens, masked in ((0, None, 1, True), (2, 1, 4, True), (2, 2, 4, False),
+                                                (4, None, 4, False), (0, 0, 0, False)):
+        work = logits.to(DEV)
+        ops().mask_tokens(work, dev_ids, torch.tensor([produced], dtype=torch.int32, device=DEV),
+                          None if steps is None else torch.tensor([steps], dtype=torch.int32, device=DEV), min_tokens)
+        want = logits.clone()
+        if masked:
+            want[:, [3, 776, best[1]]] = float("-inf")
+        assert torch.equal(work.cpu(), want), (produced, steps, min_tokens)
+    masked_rows = logits.clone()
+    masked_rows[:, [3, 776, best[1]]] = float("-inf")
+    allowed = [t for t in range(777) if t not in (3, 776, best[1])]
+    for options in ({"temperature": 0.0}, {"temperature": 0.9}, {"temperature": 1.2, "top_k": 9, "top_p": 0.8}):
+        got, _ = _sample_both(masked_rows, options, [1, 2, 3, 4, 5])
+        randoms = [P.Random(s) for s in [1, 2, 3, 4, 5]]
+        want = [[P.sample(logits[r].numpy(), randoms[r], allowed=allowed, **options) for r in range(5)]
+                for _ in range(3)]
+        assert got == want, options
+
+
 def test_sample_ties_go_to_the_lower_id():
     logits = torch.zeros((4, 1000))
     logits[0, [5, 700]] = 3.0      # two equal maxima

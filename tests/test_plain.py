@@ -74,3 +74,22 @@ def test_window_attention_edges():
     run = P.attention(np.repeat(q[6:7], 3, 0), k[4:7], v[4:7], 0.35)
     np.testing.assert_allclose(run[2], windowed[6], rtol=1e-6)
     assert alone.shape == (1, 4, 8)
+
+
+def test_choosing_among_allowed_tokens_is_choosing_with_the_others_at_minus_infinity():
+    """What the engine does for `min_tokens` (stop tokens' logits set to -inf before the choice) gives the token that
+    the reference's rule gives (the same choice made on the logits of the allowed tokens alone,
+    src/etalii_dllm/sampling.py:400-409): a probability of exactly zero is never the largest and never drawn."""
+    rng = np.random.default_rng(3)
+    for trial in range(40):
+        logits = (rng.standard_normal(50) * 3).astype(np.float32)
+        held_back = sorted(set(int(t) for t in rng.integers(0, 50, 3)) | {int(np.argmax(logits))})
+        allowed = [t for t in range(50) if t not in held_back]
+        masked = logits.copy()
+        masked[held_back] = -np.inf
+        for options in (dict(temperature=0.0), dict(temperature=0.8), dict(temperature=1.3, top_k=5),
+                        dict(temperature=0.7, top_p=0.6), dict(temperature=1.0, min_p=0.2),
+                        dict(temperature=0.9, top_k=48, top_p=0.99, min_p=0.01)):
+            a = P.sample(logits, P.Random(trial), allowed=allowed, **options)
+            b = P.sample(masked, P.Random(trial), **options)
+            assert a == b and a not in held_back, (trial, options)
