@@ -12,7 +12,7 @@ __global__ void embed_kernel(float* __restrict__ out, const T* __restrict__ tabl
   pdl_wait();
   int token = tokens[row];
   if (token < 0 || token >= vocab) {  // refused, never read out of range
-    if (threadIdx.x == 0) atomicExch(status, 1);
+    if (threadIdx.x == 0) *(volatile int*)status = 64;  // (a word in device or pinned host memory)
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[(size_t)row * hidden + i] = 0.f;
     return;
   }

@@ -348,6 +348,14 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(
     if (z > best) { best = z; best_i = i; }
   }
   cluster_argmax<CL>(best, best_i, sh, turn);
+  if (best_i == 0x7fffffff) {
+    // no logit of the row is above -inf (all NaN, or every token masked): there is no largest probability to read,
+    // so the row gets token 0, as in the greedy path, and nothing below indexes with best_i. Every thread of the
+    // cluster holds the same best_i here, so all of them leave together.
+    if (rank == 0 && tid == 0) out_tokens[row] = 0;
+    cluster_sync();
+    return;
+  }
   size_t floats = (((size_t)rows * vocab) + 1) & ~(size_t)1;  // the doubles start 8-byte aligned behind the floats
   double* e = reinterpret_cast<double*>(scratch + floats) + (size_t)row * vocab;
   double partial = 0.0;

@@ -11,7 +11,10 @@
 #include "common.cuh"
 
 namespace tc5 {
-constexpr long long WAIT_LIMIT_CYCLES = 2000000000ll;  // about a second
+#ifndef DLLM_WAIT_LIMIT_CYCLES
+#define DLLM_WAIT_LIMIT_CYCLES 2000000000ll  // about a second; a test builds with a few microseconds instead
+#endif
+constexpr long long WAIT_LIMIT_CYCLES = DLLM_WAIT_LIMIT_CYCLES;
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
 

@@ -61,7 +61,7 @@ class Engine:
         self.cache = self.model.cache
         self.vocab_size = self.spec.vocab_size
         self.buffers = BatchBuffers(self.rt.device)
-        self.sampler = Sampler(self.cache.n_slots, self.vocab_size, self.rt.device)
+        self.sampler = Sampler(self.cache.n_slots, self.vocab_size, self.rt.device, self.rt.ws)
         self.steps_run = 0
         self.cuda_graphs = bool(cuda_graphs)
         self.decode_chunk = int(decode_chunk)
@@ -97,9 +97,14 @@ class Engine:
         """Runs the next tokens of each sequence (whole prompts or single tokens, unequal lengths) as one packed
         batch from the cache; returns float32 logits [wanted rows, vocab] on the device in the order of `slots` and
         of `want` (`want[b]` indexes sequence b's new tokens; default: each sequence's last token), or None if no
-        row is wanted. The returned tensor is a work buffer: it is overwritten by the next step."""
+        row is wanted. The returned tensor is a work buffer: it is overwritten by the next step.
+
+        The step is only launched when this returns. A kernel that could not finish (a bounded wait that ran out)
+        reports through a status word: call `check()` after waiting for the logits (a copy to the host, a
+        synchronize); `decode` and `generate` do so themselves, and the next `step` looks before it starts."""
         if len(slots) == 0:
             return None
+        ops.raise_if_failed()  # whatever an earlier step reported and nobody looked at
         if len(set(slots)) != len(slots):
             raise CacheError("a sequence appears twice in one step")  # src/etalii_dllm/transformer.py:405-406
         if want is None:
@@ -125,6 +130,10 @@ class Engine:
         self.last_batch = batch
         return logits
 
+    def check(self) -> None:
+        """Raises `KernelError` if a kernel of a step that has finished reported that its results are invalid."""
+        ops.raise_if_failed()
+
     def decode(self, slots: Sequence[int], tokens: Sequence[int], steps: int,
                options: SamplingOptions | None = None, min_tokens: int = 0, blocked: Sequence[int] = (),
                produced: int = 0) -> list[list[int]]:
@@ -140,7 +149,9 @@ class Engine:
                                    tuple(sorted(set(int(t) for t in blocked))))
         self.decode_start(graph, slots, tokens, steps, produced)
         graph.replay(steps)
-        return graph.tokens(steps)
+        chosen = graph.tokens(steps)  # (waits for the steps)
+        ops.raise_if_failed()
+        return chosen
 
     def decode_start(self, graph, slots, tokens, steps: int, produced: int = 0) -> None:
         """Makes cache room for `steps` more tokens of each sequence and loads the graph's fixed buffers."""
@@ -218,6 +229,7 @@ class Engine:
                 ops.mask_tokens(logits, torch.tensor(held_back, dtype=torch.int32, device=self.rt.device),
                                 torch.zeros(1, dtype=torch.int32, device=self.rt.device), None, min_tokens)
             chosen = self.sampler.choose(logits, self.last_batch.slots, options).tolist()
+            ops.raise_if_failed()
             produced[0] = 1
             stats["prefill_s"] += time.perf_counter() - began
             stats["prefill_tokens"] += sum(len(t) for t in tokens)

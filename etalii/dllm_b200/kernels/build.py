@@ -103,16 +103,14 @@ def library_path(name: str) -> str:
     return os.path.join(_build_dir(), f"libdllm_b200_{name}-{_digest(source)}.so")
 
 
-def compile_library(name: str, verbose: bool = True) -> str:
-    """Builds the library if its file is not there yet; returns the path."""
-    path = library_path(name)
-    if os.path.isfile(path):
-        return path
-    source = os.path.join(CSRC, SOURCES[name])
+def _run_nvcc(source: str, path: str, flags, verbose: bool) -> None:
+    """Compiles `source` into the shared library `path` (written under a temporary name first), printing a line now
+    and then while nvcc runs."""
+    label = os.path.basename(source)
     temporary = f"{path}.{os.getpid()}.tmp"
-    command = [_nvcc(), *ARCH_FLAGS, *NVCC_FLAGS, "-I", CSRC, source, "-o", temporary]
+    command = [_nvcc(), *ARCH_FLAGS, *NVCC_FLAGS, *flags, "-I", CSRC, source, "-o", temporary]
     if verbose:
-        print(f"[dllm_b200] compiling {SOURCES[name]} for sm_100a ...", file=sys.stderr, flush=True)
+        print(f"[dllm_b200] compiling {label} for sm_100a ...", file=sys.stderr, flush=True)
     start = time.time()
     process = subprocess.Popen(command, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     while True:
@@ -121,13 +119,23 @@ def compile_library(name: str, verbose: bool = True) -> str:
             break
         except subprocess.TimeoutExpired:
             if verbose:
-                print(f"[dllm_b200] ... still compiling {SOURCES[name]} ({time.time() - start:.0f} s)",
+                print(f"[dllm_b200] ... still compiling {label} ({time.time() - start:.0f} s)",
                       file=sys.stderr, flush=True)
     if process.returncode != 0:
         if os.path.exists(temporary):
             os.remove(temporary)
-        raise KernelBuildError(f"nvcc failed on {SOURCES[name]}:\n{output}")
+        raise KernelBuildError(f"nvcc failed on {label}:\n{output}")
     os.replace(temporary, path)
+    if verbose:
+        print(f"[dllm_b200] built {os.path.basename(path)} in {time.time() - start:.1f} s", file=sys.stderr, flush=True)
+
+
+def compile_library(name: str, verbose: bool = True) -> str:
+    """Builds the library if its file is not there yet; returns the path."""
+    path = library_path(name)
+    if os.path.isfile(path):
+        return path
+    _run_nvcc(os.path.join(CSRC, SOURCES[name]), path, (), verbose)
     prefix = f"libdllm_b200_{name}-"
     for stale in os.listdir(os.path.dirname(path)):  # older builds of the same source
         if stale.startswith(prefix) and stale.endswith(".so") and stale != os.path.basename(path):
@@ -135,9 +143,27 @@ def compile_library(name: str, verbose: bool = True) -> str:
                 os.remove(os.path.join(os.path.dirname(path), stale))
             except OSError:
                 pass
-    if verbose:
-        print(f"[dllm_b200] built {os.path.basename(path)} in {time.time() - start:.1f} s", file=sys.stderr, flush=True)
     return path
+
+
+def compile_extra(source: str, flags=(), verbose: bool = True) -> ctypes.CDLL:
+    """Builds and loads a CUDA source that is not part of the library (a test's own kernel, a user's part) with the
+    library's compiler flags plus `flags` and `csrc/` on the include path, so it can use the library's headers."""
+    with open(source, "rb") as handle:
+        sha = hashlib.sha256(handle.read())
+    sha.update(" ".join([*ARCH_FLAGS, *NVCC_FLAGS, *flags]).encode())
+    for name in sorted(f for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))):
+        with open(os.path.join(CSRC, name), "rb") as handle:
+            sha.update(handle.read())
+    stem = os.path.splitext(os.path.basename(source))[0]
+    path = os.path.join(_build_dir(), f"libextra_{stem}-{sha.hexdigest()[:16]}.so")
+    with _lock:
+        if not os.path.isfile(path):
+            _run_nvcc(source, path, tuple(flags), verbose)
+        try:
+            return ctypes.CDLL(path)
+        except OSError as error:
+            raise KernelBuildError(f"{path} does not load: {error}") from error
 
 
 def library(name: str) -> ctypes.CDLL:

@@ -114,9 +114,12 @@ def _code(dtype: torch.dtype) -> int:
         raise KernelError(f"dtype {dtype} is not supported (float32 and bfloat16 are)") from None
 
 
-def embed(out: torch.Tensor, table: torch.Tensor, tokens: torch.Tensor, status: torch.Tensor) -> None:
-    """out[r] = float32(table[tokens[r]]); a token outside the table sets status[0] and gives a zero row."""
-    _cuda(out, table, tokens, status)
+def embed(out: torch.Tensor, table: torch.Tensor, tokens: torch.Tensor, status: torch.Tensor | None = None) -> None:
+    """out[r] = float32(table[tokens[r]]); a token outside the table gives a zero row and sets the status word
+    (`status`: an int32 word the device can write; default: the pinned word that `raise_if_failed` reads)."""
+    _cuda(out, table, tokens)
+    if status is None:
+        status = _status_word()
     assert out.dtype == torch.float32 and tokens.dtype == torch.int32 and status.dtype == torch.int32
     rows, hidden = out.shape
     assert tokens.numel() >= rows and table.shape[1] == hidden
@@ -167,11 +170,17 @@ def _status_word() -> torch.Tensor:
 
 
 def raise_if_failed() -> None:
-    """Raises if a kernel reported that one of its bounded waits ran out (its results are then not valid)."""
+    """Raises if a kernel has set the status word since the last look: a bounded wait on an mbarrier ran out
+    (codes 2-5 the tile product, 12-21 the tcgen05 attention, 32-33 the product that streams through shared memory)
+    or the embedding met a token outside its table (64). Results computed since are not valid. The word lives in
+    pinned host memory, so the look costs no synchronisation; it is meaningful after the host has waited for the
+    kernels in question (a `.tolist()`, a copy to the host, a synchronize)."""
     if _async_status is not None and int(_async_status[0]) != 0:
         code = int(_async_status[0])
         _async_status[0] = 0
-        raise KernelError(f"a tcgen05 product gave up waiting on an mbarrier (role code {code}); results are invalid")
+        if code == 64:
+            raise KernelError("the embedding was given a token outside its table; the step's results are invalid")
+        raise KernelError(f"a kernel gave up waiting on an mbarrier (role code {code}); the step's results are invalid")
 
 
 GEMV_MAX_ROWS = 64

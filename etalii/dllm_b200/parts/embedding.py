@@ -22,11 +22,12 @@ class TokenEmbedding:
 
     def bind(self, tensors, rt) -> None:
         self.weight = rt.to_device(tensors["weight"], rt.dtype)
-        self.status = torch.zeros(1, dtype=torch.int32, device=rt.device)
 
     def forward(self, tokens: torch.Tensor, n_tokens: int, rt) -> torch.Tensor:
+        # a token outside the table sets the kernels' shared status word, which the engine looks at after each
+        # step it waits for (kernels/ops.py::raise_if_failed)
         x = rt.ws.buffer("residual", (n_tokens, self.hidden_size), torch.float32)
-        ops.embed(x, self.weight, tokens, self.status)
+        ops.embed(x, self.weight, tokens)
         return x
 
 

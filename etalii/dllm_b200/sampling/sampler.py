@@ -9,10 +9,13 @@ from .options import SamplingOptions
 
 
 class Sampler:
-    def __init__(self, n_slots: int, vocab_size: int, device) -> None:
+    def __init__(self, n_slots: int, vocab_size: int, device, workspace) -> None:
+        """`workspace`: the engine's work buffers. The scratch of temperature sampling is one of them, so that a
+        captured decode graph, which holds the scratch's address, is dropped like any other graph when the buffer
+        is replaced by a larger one (the workspace counts its reallocations and graphs compare the count)."""
         self.device, self.vocab_size = device, vocab_size
         self.rng = torch.zeros((n_slots, 4), dtype=torch.int64, device=device)
-        self._scratch = None
+        self.ws = workspace
 
     def seed(self, slots: list[int], seeds: list[int]) -> None:
         """Starts the stream of each slot from its seed (modulo 2^64)."""
@@ -28,10 +31,7 @@ class Sampler:
             out = torch.empty(rows, dtype=torch.int32, device=self.device)
         scratch = None
         if options.temperature > 0:
-            need = ops.sample_scratch(rows, logits.shape[1])
-            if self._scratch is None or self._scratch.numel() < need:
-                self._scratch = torch.empty(need, dtype=torch.float32, device=self.device)
-            scratch = self._scratch
+            scratch = self.ws.buffer("sample_scratch", (ops.sample_scratch(rows, logits.shape[1]),), torch.float32)
         ops.sample(out, logits, scratch, self.rng if scratch is not None else None,
                    slots if scratch is not None else None, options.temperature, options.top_k, options.top_p,
                    options.min_p)

@@ -14,7 +14,7 @@ def embed(out, table, tokens, status):
     ids = tokens[: out.shape[0]].long()
     bad = (ids < 0) | (ids >= table.shape[0])
     if bad.any():
-        status[0] = 1
+        status[0] = 64
     rows = table[ids.clamp(0, table.shape[0] - 1)].float()
     rows[bad] = 0
     out.copy_(rows)

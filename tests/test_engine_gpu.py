@@ -431,3 +431,34 @@ def test_long_context(long_case, dtype):
         assert rel_error(got[1], reference[index]) <= TOL[dtype], index
     engine.close(slots)
     engine.cache.check()
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_sampled_batches_that_grow_and_shrink_keep_their_graphs_valid(name):
+    """A captured decode graph holds the addresses of work buffers, the sampler's scratch among them. Batches of 8,
+    3, 8, 3 and 4, 5, 6, 5 sequences on one engine make those buffers grow after graphs of smaller batches were
+    captured; every run must still give the plain implementation's tokens (float32, seeded draws)."""
+    from etalii.dllm_b200 import SamplingOptions
+
+    config, weights = model_case(name.lower())
+    engine = make_engine(config, weights, "float32", max_tokens=64 * 24)
+    lengths = (5, 11, 17, 3, 9, 2, 14, 7)
+    prompts = prompts_for(config, lengths, seed=44)
+
+    memo = {}
+
+    def run(count, options, seed_of):
+        results = engine.generate(prompts[:count], 20, options, ignore_eos=True)
+        for index, (prompt, result) in enumerate(zip(prompts, results)):
+            key = (index, options.temperature, seed_of(index))
+            if key not in memo:
+                memo[key] = P.generate(config, weights, prompt, 20, temperature=options.temperature,
+                                       seed=seed_of(index))[0]
+            assert list(result.tokens) == memo[key], (count, index)
+
+    run(8, SamplingOptions(), lambda i: 0)
+    sampled = SamplingOptions(temperature=0.8, seed=5)
+    for count in (3, 8, 3, 4, 5, 6, 5, 3):
+        run(count, sampled, lambda i: 5 + i)
+    assert engine.cache.slots.held == 0
+    engine.cache.check()

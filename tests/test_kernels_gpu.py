@@ -32,8 +32,15 @@ def test_embed(dtype):
     bad = torch.tensor([3, 37, -1], dtype=torch.int32, device=DEV)
     out3 = torch.empty((3, 72), dtype=torch.float32, device=DEV)
     ops().embed(out3, table, bad, status)
-    assert int(status[0]) == 1 and torch.equal(out3[1], torch.zeros(72, device=DEV))
+    assert int(status[0]) == 64 and torch.equal(out3[1], torch.zeros(72, device=DEV))
     assert torch.equal(out3[0], table[3].float())
+    # without a status argument the kernels' shared pinned word is set, and the host raises when it looks
+    ops().raise_if_failed()
+    ops().embed(out3, table, bad)
+    torch.cuda.synchronize()
+    with pytest.raises(ops().KernelError, match="outside its table"):
+        ops().raise_if_failed()
+    ops().raise_if_failed()  # looked at once, the word is clear again
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-6), (torch.bfloat16, 8e-3)])
@@ -394,6 +401,38 @@ def test_sample_ties_go_to_the_lower_id():
         assert got == want, options
 
 
+@pytest.mark.parametrize("rows", [3, 40, 80])
+def test_sample_rows_without_a_largest_logit_get_token_zero(rows):
+    """A row whose logits are all NaN or all -inf has no largest probability. With min_p > 0 the kernel reads the
+    probability at the index of the maximum, so such a row must leave before that: it gets token 0 in the greedy
+    and in the sampling path, and its neighbours are chosen as always."""
+    import plain_llama as P
+
+    g = torch.Generator().manual_seed(rows)
+    vocab = 1000
+    logits = torch.randn((rows, vocab), generator=g) * 2
+    logits[0, :] = float("nan")
+    logits[2, :] = float("-inf")
+    seeds = list(range(rows))
+    dev = logits.to(DEV)
+    rng = torch.zeros((rows, 4), dtype=torch.int64, device=DEV)
+    stream_rows = torch.arange(rows, dtype=torch.int32, device=DEV)
+    ops().seed_rng(rng, stream_rows, torch.tensor(seeds, dtype=torch.int64, device=DEV))
+    scratch = torch.empty(ops().sample_scratch(rows, vocab), dtype=torch.float32, device=DEV)
+    for options in ({"temperature": 0.0}, {"temperature": 0.9, "min_p": 0.05},
+                    {"temperature": 1.2, "top_k": 5, "top_p": 0.7, "min_p": 0.5}):
+        out = torch.full((rows,), -7, dtype=torch.int32, device=DEV)
+        ops().sample(out, dev, scratch, rng, stream_rows, options["temperature"], options.get("top_k", 0),
+                     options.get("top_p", 1.0), options.get("min_p", 0.0))
+        got = out.tolist()
+        assert got[0] == 0 and got[2] == 0, options
+        want = P.sample(logits[1].numpy(), P.Random(1), **options)
+        assert got[1] == want, options
+        assert all(0 <= t < vocab for t in got)
+        if options["temperature"] > 0:  # the next draw of row 1 continues row 1's stream
+            ops().seed_rng(rng, stream_rows, torch.tensor(seeds, dtype=torch.int64, device=DEV))
+
+
 @pytest.mark.parametrize("heads,kv_heads,head_dim,window", [(4, 2, 16, None), (6, 3, 24, None), (9, 3, 64, None),
                                                            (8, 1, 128, 70), (5, 5, 40, 33), (12, 1, 256, None),
                                                            (20, 2, 96, 300)])
@@ -731,3 +770,38 @@ def test_attention_decode_cluster_finds_a_far_key():
             ops().attention_decode_cluster(out, q, view, heads, 1.0, 0, batch, shape)
             assert torch.allclose(out.float(), torch.full_like(out, 7.0).float(), atol=0.05), (target, shape)
         view.storage[page] = saved
+
+
+def test_a_bounded_wait_that_runs_out_is_reported_and_hangs_nothing():
+    """The tcgen05 kernels wait on mbarriers with a limit; when it runs out they set the pinned status word and
+    return. Here a one-thread kernel of the test, built from the same header with a limit of 100,000 cycles, waits
+    on a barrier nobody arrives at: it must come back within milliseconds, and the host must raise."""
+    import ctypes
+    import os
+    import time
+
+    from etalii.dllm_b200.kernels.build import compile_extra
+
+    source = os.path.join(os.path.dirname(os.path.abspath(__file__)), "csrc", "bounded_wait_probe.cu")
+    lib = compile_extra(source, flags=("-DDLLM_WAIT_LIMIT_CYCLES=100000ll",))
+    lib.probe_wait_limit.restype = ctypes.c_longlong
+    assert lib.probe_wait_limit() == 100000
+    lib.probe_wait_that_runs_out.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+    lib.probe_wait_that_runs_out.restype = ctypes.c_int
+    module = ops()
+    module.raise_if_failed()
+    word = module._status_word()
+    cycles = torch.zeros(1, dtype=torch.int64, device=DEV)
+    torch.cuda.synchronize()
+    began = time.perf_counter()
+    assert lib.probe_wait_that_runs_out(word.data_ptr(), cycles.data_ptr(), module._stream()) == 0
+    torch.cuda.synchronize()
+    elapsed = time.perf_counter() - began
+    assert elapsed < 0.5, f"the wait took {elapsed:.3f} s"
+    assert 100000 < int(cycles[0]) < 50_000_000
+    with pytest.raises(module.KernelError, match="gave up waiting"):
+        module.raise_if_failed()
+    module.raise_if_failed()  # reported once
+    # the context is as usable as before
+    x = torch.arange(8, device=DEV, dtype=torch.float32)
+    assert float((x * 2).sum()) == 56.0
