@@ -190,15 +190,19 @@ class Engine:
     # ---- generation ----
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int = 64,
                  options: SamplingOptions | None = None, stop_token_ids: Sequence[int] | None = None,
-                 ignore_eos: bool = False, max_batch: int | None = None, min_tokens: int = 0) -> list[GenerationResult]:
+                 ignore_eos: bool = False, max_batch: int | None = None, min_tokens: int = 0,
+                 seeds: Sequence[int] | None = None) -> list[GenerationResult]:
         """Generates for every prompt (lists of token ids), as many batches one after another as the cache needs.
         Stop ids default to the model's end-of-sequence ids; `stop_token_ids` adds more; `ignore_eos` drops the
         model's own; until an output has `min_tokens` tokens no stop token can be chosen: they are taken out of the
         choice (src/etalii_dllm/cli.py:427-431, src/etalii_dllm/generation.py:316, 373-381, 512-513).
-        Sequence i draws from the stream of options.seed + i."""
+        Sequence i draws from the stream of options.seed + i, or of seeds[i] where `seeds` is given (the command
+        line's N choices of each of several prompts: choice c of every prompt draws from seed + c)."""
         options = options or SamplingOptions()
         if min_tokens < 0:
             raise ValueError("min_tokens must be non-negative")
+        if seeds is not None and len(seeds) != len(prompts):
+            raise ValueError("seeds: one per prompt")
         stats = self.stats = {"prefill_s": 0.0, "prefill_tokens": 0, "decode_s": 0.0, "decode_steps": 0,
                               "decode_tokens": 0}
         prompts = [list(map(int, p)) for p in prompts]
@@ -219,7 +223,7 @@ class Engine:
             produced[0] = 0
             slots = self.open(len(indices))
             if options.temperature > 0:
-                self.sampler.seed(slots, [options.seed + i for i in indices])
+                self.sampler.seed(slots, [options.seed + i if seeds is None else int(seeds[i]) for i in indices])
             return slots
 
         def prefill(slots, positions, tokens):
