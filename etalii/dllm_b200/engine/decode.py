@@ -54,9 +54,12 @@ class DecodeGraph:
         self.graph = None
         self.generation = -1
         self.launches_per_step = 0
+        self.logits = None
+        """The work buffer the captured step writes its logits to, [batch, vocab] float32: after a run of steps it
+        holds the last step's logits (tests compare them with a plain implementation without a second forward)."""
 
     def _body(self) -> None:
-        logits = self.engine.model.forward(self.batch)
+        logits = self.logits = self.engine.model.forward(self.batch)
         if self.blocked is not None:
             ops.mask_tokens(logits, self.blocked, self.produced, self.counter, self.min_tokens)
         self.engine.sampler.choose(logits, self.batch.slots, self.options, out=self.chosen)

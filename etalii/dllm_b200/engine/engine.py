@@ -148,6 +148,7 @@ class Engine:
                                    max(self.cache.length(s) for s in slots) + steps, int(min_tokens),
                                    tuple(sorted(set(int(t) for t in blocked))))
         self.decode_start(graph, slots, tokens, steps, produced)
+        self.last_decode_graph = graph
         graph.replay(steps)
         chosen = graph.tokens(steps)  # (waits for the steps)
         ops.raise_if_failed()

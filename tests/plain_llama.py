@@ -34,10 +34,23 @@ def embedding(table: np.ndarray, tokens: Sequence[int]) -> np.ndarray:
     return np.asarray(table, dtype=F32)[ids]
 
 
+LINEAR_BLOCK = 1 << 25
+"""`linear` widens at most this many weights to double at a time (a head of 128,256 x 4,096 would otherwise need
+4 GB for its double copy); the blocks are whole rows of the weight, so every output is the same sum either way."""
+
+
 def linear(x: np.ndarray, weight: np.ndarray) -> np.ndarray:
     """out[r, n] = sum_k x[r, k] w[n, k] in double, rounded once (src/etalii_dllm/reference.py:322-335,
     cpp/include/dllm/nn.hpp:28-50)."""
-    return _round(np.asarray(x, F32).astype(F64) @ np.asarray(weight, F32).astype(F64).T)
+    xd = np.asarray(x, F32).astype(F64)
+    weight = np.asarray(weight, F32)
+    if weight.size <= LINEAR_BLOCK:
+        return _round(xd @ weight.astype(F64).T)
+    rows = max(1, LINEAR_BLOCK // weight.shape[1])
+    out = np.empty((xd.shape[0], weight.shape[0]), dtype=F32)
+    for begin in range(0, weight.shape[0], rows):
+        out[:, begin:begin + rows] = _round(xd @ weight[begin:begin + rows].astype(F64).T)
+    return out
 
 
 def rms_norm(x: np.ndarray, weight: np.ndarray, eps: float) -> np.ndarray:
@@ -113,6 +126,29 @@ def attention(q: np.ndarray, k: np.ndarray, v: np.ndarray, scale: float, window:
     return out
 
 
+def attention_by_matrices(q: np.ndarray, k: np.ndarray, v: np.ndarray, scale: float,
+                          window: int | None = None) -> np.ndarray:
+    """The same function as `attention`, a head at a time instead of a query at a time: all scores of a head as one
+    matrix in double, keys outside [t - window + 1, t] masked, row-wise exp(s - max), (p v) * (1 / sum p), rounded
+    once. For the tests at real sizes, where the loop over queries would take minutes; `tests/test_plain.py` holds
+    it to `attention` (same formulas: src/etalii_dllm/reference.py:518-569)."""
+    qv, kv, vv = (np.asarray(a, F32).astype(F64) for a in (q, k, v))
+    q_len, q_heads, _ = qv.shape
+    group = q_heads // kv.shape[1]
+    out = np.zeros((q_len, q_heads, vv.shape[2]), dtype=F32)
+    t = np.arange(q_len)
+    visible = t[None, :] <= t[:, None]
+    if window:
+        visible &= t[None, :] > t[:, None] - window
+    for h in range(q_heads):
+        g = h // group
+        scores = (qv[:, h, :] @ kv[:, g, :].T) * scale
+        scores[~visible] = -np.inf
+        p = np.exp(scores - scores.max(axis=1, keepdims=True))
+        out[:, h, :] = _round((p @ vv[:, g, :]) * (1.0 / p.sum(axis=1, keepdims=True)))
+    return out
+
+
 def sigmoid(x: np.ndarray) -> np.ndarray:
     """1/(1+e^-x) for x >= 0, else e^x/(1+e^x) (src/etalii_dllm/reference.py:218-225)."""
     x = np.asarray(x, F64)
@@ -137,12 +173,24 @@ def feed_forward(h: np.ndarray, gate_w: np.ndarray, up_w: np.ndarray, down_w: np
 
 # ---- whole model ----------------------------------------------------------------------------------------------------
 
-def forward(config: Mapping, weights: Mapping[str, np.ndarray], tokens: Sequence[int]) -> np.ndarray:
+def forward(config: Mapping, weights: Mapping[str, np.ndarray], tokens: Sequence[int],
+            rows: Sequence[int] | None = None) -> np.ndarray:
     """Logits [len(tokens), vocab] of one whole sequence from position 0: embedding, then per layer RMSNorm, q/k/v,
     RoPE, attention, o, float32 residual add, RMSNorm, SwiGLU feed-forward, float32 residual add; final RMSNorm and
     the (tied or own) head (src/etalii_dllm/reference.py:1231-1290, src/etalii_dllm/transformer.py:493-562).
+    With `rows`, only the logits at those positions, [len(rows), vocab].
 
     `config` is the model's config.json as a dict (Hugging Face keys)."""
+    return forward_many(config, weights, [tokens], None if rows is None else [rows], attention)[0]
+
+
+def forward_many(config: Mapping, weights: Mapping[str, np.ndarray], sequences: Sequence[Sequence[int]],
+                 rows: Sequence[Sequence[int]] | None = None, attend=attention_by_matrices) -> list[np.ndarray]:
+    """`forward` for several whole sequences at once, for the tests at real sizes: the tokens of all sequences are
+    stacked for everything that works on a token alone (embedding, norms, products, rotation by each token's own
+    position, SwiGLU, residual adds: a row's result does not depend on the other rows), attention runs sequence by
+    sequence. Every weight is widened to double once per call instead of once per sequence. Returns each
+    sequence's logits at its `rows` (default: all positions)."""
     heads = int(config["num_attention_heads"])
     kv_heads = int(config.get("num_key_value_heads") or heads)
     hidden = int(config["hidden_size"])
@@ -150,9 +198,11 @@ def forward(config: Mapping, weights: Mapping[str, np.ndarray], tokens: Sequence
     eps = float(config.get("rms_norm_eps", 1e-6))
     inv_freq = rope_inv_freq(head_dim, float(config.get("rope_theta", 10000.0)), config.get("rope_scaling"))
     scale = 1.0 / math.sqrt(head_dim)  # src/etalii_dllm/architecture.py:310-312
-    count = len(tokens)
-    positions = np.arange(count)
-    x = embedding(weights["model.embed_tokens.weight"], tokens)
+    counts = [len(tokens) for tokens in sequences]
+    bounds = np.concatenate([[0], np.cumsum(counts)])
+    count = int(bounds[-1])
+    positions = np.concatenate([np.arange(n) for n in counts])
+    x = embedding(weights["model.embed_tokens.weight"], [t for tokens in sequences for t in tokens])
     for layer in range(int(config["num_hidden_layers"])):
         p = f"model.layers.{layer}."
         h = rms_norm(x, weights[p + "input_layernorm.weight"], eps)
@@ -160,16 +210,21 @@ def forward(config: Mapping, weights: Mapping[str, np.ndarray], tokens: Sequence
         k = linear(h, weights[p + "self_attn.k_proj.weight"]).reshape(count, kv_heads, head_dim)
         v = linear(h, weights[p + "self_attn.v_proj.weight"]).reshape(count, kv_heads, head_dim)
         q, k = rope(q, positions, inv_freq), rope(k, positions, inv_freq)
-        attended = attention(q, k, v, scale)
+        attended = np.concatenate([attend(q[a:b], k[a:b], v[a:b], scale) for a, b in zip(bounds[:-1], bounds[1:])])
         x = x + linear(attended.reshape(count, heads * head_dim), weights[p + "self_attn.o_proj.weight"])
         h = rms_norm(x, weights[p + "post_attention_layernorm.weight"], eps)
         x = x + feed_forward(
             h, weights[p + "mlp.gate_proj.weight"], weights[p + "mlp.up_proj.weight"], weights[p + "mlp.down_proj.weight"]
         )
+    if rows is not None:
+        x = x[np.concatenate([bounds[i] + np.asarray(r, dtype=np.int64) for i, r in enumerate(rows)]).astype(np.int64)]
+        counts = [len(r) for r in rows]
+        bounds = np.concatenate([[0], np.cumsum(counts)])
     hidden_rows = rms_norm(x, weights["model.norm.weight"], eps)
     tied = bool(config.get("tie_word_embeddings", False))
     head = weights["model.embed_tokens.weight"] if tied else weights["lm_head.weight"]
-    return linear(hidden_rows, head)
+    logits = linear(hidden_rows, head)
+    return [logits[a:b] for a, b in zip(bounds[:-1], bounds[1:])]
 
 
 # ---- sampling -------------------------------------------------------------------------------------------------------
@@ -356,8 +411,8 @@ def random_weights(config: Mapping, seed: int, std: float = 0.02, bf16_exact: bo
         norm = name.endswith("norm.weight")
         values = (rng.standard_normal(shape) * (0.01 if norm else std) + (1.0 if norm else 0.0)).astype(F32)
         if bf16_exact:
-            bits = values.view(np.uint32).astype(np.uint64)
-            bits = ((bits + 0x7FFF + ((bits >> 16) & 1)) >> 16) << 16  # round to nearest even on the top 16 bits
-            values = bits.astype(np.uint32).view(F32).reshape(shape)
+            bits = values.view(np.uint32)  # (finite values: the additions below cannot carry out of 32 bits)
+            bits = ((bits + np.uint32(0x7FFF) + ((bits >> np.uint32(16)) & np.uint32(1))) >> np.uint32(16)) << np.uint32(16)
+            values = bits.view(F32).reshape(shape)  # rounded to nearest even on the top 16 bits
         out[name] = values
     return out

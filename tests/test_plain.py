@@ -93,3 +93,31 @@ def test_choosing_among_allowed_tokens_is_choosing_with_the_others_at_minus_infi
             a = P.sample(logits, P.Random(trial), allowed=allowed, **options)
             b = P.sample(masked, P.Random(trial), **options)
             assert a == b and a not in held_back, (trial, options)
+
+
+def test_attention_by_matrices_is_the_same_function_as_attention_by_queries():
+    """The head-at-a-time form used at real sizes against the query-at-a-time form that restates the reference."""
+    rng = np.random.default_rng(3)
+    for heads, kv_heads, dim, length, window in ((6, 3, 24, 70, None), (4, 1, 16, 33, 9), (5, 5, 40, 130, 64)):
+        q = rng.standard_normal((length, heads, dim)).astype(np.float32)
+        k = rng.standard_normal((length, kv_heads, dim)).astype(np.float32)
+        v = rng.standard_normal((length, kv_heads, dim)).astype(np.float32)
+        a = P.attention(q, k, v, 0.3, window)
+        b = P.attention_by_matrices(q, k, v, 0.3, window)
+        assert np.abs(a.astype(np.float64) - b).max() <= 1e-6 * np.abs(a).max()
+
+
+def test_forward_many_gives_each_sequence_the_logits_of_forward():
+    weights = P.random_weights(P.TINY_B, 1, std=0.08)
+    rng = np.random.default_rng(4)
+    sequences = [rng.integers(0, P.TINY_B["vocab_size"], n).tolist() for n in (40, 1, 17)]
+    rows = [[0, 39], [0], [3, 4, 16]]
+    many = P.forward_many(P.TINY_B, weights, sequences, rows)
+    for tokens, wanted, got in zip(sequences, rows, many):
+        want = P.forward(P.TINY_B, weights, tokens)[wanted]
+        assert got.shape == want.shape and np.abs(got.astype(np.float64) - want).max() <= 2e-6 * np.abs(want).max()
+    block, P.LINEAR_BLOCK = P.LINEAR_BLOCK, 1000  # the product in row blocks of the weight: the same sums
+    try:
+        assert all(np.array_equal(a, b) for a, b in zip(many, P.forward_many(P.TINY_B, weights, sequences, rows)))
+    finally:
+        P.LINEAR_BLOCK = block
