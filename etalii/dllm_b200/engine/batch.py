@@ -1,17 +1,123 @@
 """The tokens of one step, as the kernels see them: every sequence's new tokens packed one after another, with each
 token's sequence index and absolute position, each sequence's slot and cached length, and the rows whose logits are
-wanted. There is no padding: a step runs exactly the tokens it is given."""
+wanted. There is no padding: a step runs exactly the tokens it is given.
+
+`StepLayout` is the one place that says which fields a step's metadata has and where each lies in the step's int32
+buffer; `step_values` computes them on the host. The step function (`BatchBuffers.fill`) and the captured decode
+step (`DecodeGraph`) both lay their buffers out with it, so a part that needs one more field per token or per
+sequence registers it once (`register_step_field`) and finds it as `batch.<name>` on both paths."""
 from __future__ import annotations
 
-from typing import Sequence
+from typing import Callable, Sequence
 
 import numpy as np
 import torch
 
+TILE = 64
+"""New tokens of one sequence per tile of the prefill attention."""
+
+_PER = ("token", "sequence", "sequence+1", "want", "tile", "one")
+FIELDS: list[tuple[str, str]] = [
+    ("tokens", "token"), ("tok_seq", "token"), ("tok_pos", "token"), ("cu_seqlens", "sequence+1"),
+    ("slots", "sequence"), ("start", "sequence"), ("want_rows", "want"), ("tile_seq", "tile"), ("tile_first", "tile"),
+]
+"""(name, one value per ...) of the fields every step has, in buffer order."""
+_EXTRA: dict[str, tuple[str, Callable]] = {}
+
+
+def register_step_field(name: str, per: str, values: Callable[["StepInfo"], np.ndarray]) -> None:
+    """Adds an int32 field to every step's metadata: `per` is "token" or "sequence", `values(info)` returns the
+    field's values from the host-side description of the step (`info.slots`, `info.counts`, `info.starts`). The
+    field arrives on the device with the step's one copy and is found as `batch.<name>`. In a captured decode run
+    the field keeps the values it had when the run was loaded unless the part's own kernel advances it."""
+    if per not in ("token", "sequence"):
+        raise ValueError("a step field has one value per token or per sequence")
+    if name in _EXTRA or any(name == known for known, _ in FIELDS) or name in StepBatch.HOST_FIELDS:
+        raise ValueError(f"step field {name!r} exists already")
+    _EXTRA[name] = (per, values)
+
+
+def unregister_step_field(name: str) -> None:
+    _EXTRA.pop(name, None)
+
+
+class StepInfo:
+    """The host-side description of a step that field functions see."""
+
+    def __init__(self, slots, counts, starts) -> None:
+        self.slots, self.counts, self.starts = list(slots), list(counts), list(starts)
+
 
 class StepBatch:
-    __slots__ = ("n_seqs", "n_tokens", "n_want", "tokens", "tok_seq", "tok_pos", "cu_seqlens", "slots", "start",
-                 "want_rows", "tile_seq", "tile_first", "n_tiles", "h_slots", "h_new", "h_start", "max_new", "max_position", "max_context", "is_decode")
+    """A step as the parts see it: the device views of the layout's fields as attributes, and the host-side counts."""
+
+    HOST_FIELDS = ("n_seqs", "n_tokens", "n_want", "n_tiles", "h_slots", "h_new", "h_start", "max_new",
+                   "max_position", "max_context", "is_decode")
+
+
+class StepLayout:
+    """Where each field of a step with these counts lies in the step's int32 buffer. `extra` appends fields that
+    only one user of the layout has (the decode run's step counter)."""
+
+    def __init__(self, n_tokens: int, n_seqs: int, n_want: int, n_tiles: int, extra: Sequence[tuple[str, str]] = ()):
+        sizes = {"token": n_tokens, "sequence": n_seqs, "sequence+1": n_seqs + 1, "want": n_want, "tile": n_tiles,
+                 "one": 1}
+        self.counts = (n_tokens, n_seqs, n_want, n_tiles)
+        self.offsets: dict[str, tuple[int, int]] = {}
+        at = 0
+        for name, per in (*FIELDS, *((name, per) for name, (per, _) in _EXTRA.items()), *extra):
+            self.offsets[name] = (at, sizes[per])
+            at += sizes[per]
+        self.total = at
+
+    def view(self, buffer, name: str):
+        begin, count = self.offsets[name]
+        return buffer[begin:begin + count]
+
+    def write(self, host: np.ndarray, values: dict[str, np.ndarray]) -> None:
+        for name, value in values.items():
+            begin, count = self.offsets[name]
+            host[begin:begin + count] = value
+
+    def attach(self, batch: StepBatch, device_buffer: torch.Tensor) -> None:
+        """Sets every field's device view on `batch`."""
+        for name in self.offsets:
+            setattr(batch, name, self.view(device_buffer, name))
+
+
+def prefill_tiles(counts: Sequence[int], starts: Sequence[int]) -> list[tuple[int, int]]:
+    """Tiles of up to TILE new tokens of one sequence for the prefill attention, the longest contexts first."""
+    tiles = [(i, first) for i, c in enumerate(counts) for first in range(0, c, TILE)]
+    tiles.sort(key=lambda t: -(starts[t[0]] + t[1]))
+    return tiles
+
+
+def step_values(slots: Sequence[int], new_tokens: Sequence[Sequence[int]], starts: Sequence[int],
+                want: Sequence[Sequence[int]], tiles: Sequence[tuple[int, int]] = ()) -> dict[str, np.ndarray]:
+    """The values of every field of a step, by name."""
+    b = len(slots)
+    counts = [len(t) for t in new_tokens]
+    n = sum(counts)
+    cu = np.zeros(b + 1, dtype=np.int32)
+    np.cumsum(counts, out=cu[1:])
+    empty = np.zeros(0, np.int32)
+    values = {
+        "tokens": np.concatenate([np.asarray(seq, dtype=np.int32) for seq in new_tokens]) if n else empty,
+        "tok_seq": np.repeat(np.arange(b, dtype=np.int32), counts),
+        "tok_pos": np.concatenate([np.arange(s, s + c, dtype=np.int32) for s, c in zip(starts, counts)]) if n
+        else empty,
+        "cu_seqlens": cu,
+        "slots": np.asarray(slots, dtype=np.int32),
+        "start": np.asarray(starts, dtype=np.int32),
+        "want_rows": np.asarray([cu[i] + w for i, ws in enumerate(want) for w in ws], dtype=np.int32),
+        "tile_seq": np.asarray([t[0] for t in tiles], dtype=np.int32),
+        "tile_first": np.asarray([t[1] for t in tiles], dtype=np.int32),
+    }
+    if _EXTRA:
+        info = StepInfo(slots, counts, starts)
+        for name, (_, function) in _EXTRA.items():
+            values[name] = np.asarray(function(info), dtype=np.int32)
+    return values
 
 
 class BatchBuffers:
@@ -19,7 +125,7 @@ class BatchBuffers:
     staging buffers lets a step be prepared while the copy of the previous one may still be in flight."""
 
     RING = 4
-    TILE = 64
+    TILE = TILE
 
     def __init__(self, device, capacity: int = 4096) -> None:
         self.device = device
@@ -37,55 +143,24 @@ class BatchBuffers:
     def fill(self, slots: Sequence[int], new_tokens: Sequence[Sequence[int]], starts: Sequence[int],
              want: Sequence[Sequence[int]]) -> StepBatch:
         """`want[b]` lists indices into sequence b's new tokens. Returns the batch with its device views."""
-        b = len(slots)
         counts = [len(t) for t in new_tokens]
-        n = sum(counts)
-        r = sum(len(w) for w in want)
-        # tiles of up to TILE new tokens of one sequence for the prefill attention, the longest contexts first
-        tiles = [(i, first) for i, c in enumerate(counts) for first in range(0, c, self.TILE)]
-        tiles.sort(key=lambda t: -(starts[t[0]] + t[1]))
-        nt = len(tiles)
-        total = 3 * n + (b + 1) + 2 * b + r + 2 * nt
-        if total > self.capacity:
-            self._grow(max(total, 2 * self.capacity))
+        tiles = prefill_tiles(counts, starts)
+        layout = StepLayout(sum(counts), len(slots), sum(len(w) for w in want), len(tiles))
+        if layout.total > self.capacity:
+            self._grow(max(layout.total, 2 * self.capacity))
         ring = self._ring
         self._ring = (ring + 1) % self.RING
         if self.events[ring] is not None:
             self.events[ring].synchronize()
-        host = self.host[ring].numpy()
-        cu = np.zeros(b + 1, dtype=np.int32)
-        np.cumsum(counts, out=cu[1:])
-        o = 0
-        host[o:o + n] = np.concatenate([np.asarray(seq) for seq in new_tokens]) if n else np.zeros(0, np.int32); o += n
-        host[o:o + n] = np.repeat(np.arange(b, dtype=np.int32), counts); o += n
-        pos = np.concatenate([np.arange(s, s + c, dtype=np.int32) for s, c in zip(starts, counts)]) if n else \
-            np.zeros(0, np.int32)
-        host[o:o + n] = pos; o += n
-        host[o:o + b + 1] = cu; o += b + 1
-        host[o:o + b] = np.asarray(slots, dtype=np.int32); o += b
-        host[o:o + b] = np.asarray(starts, dtype=np.int32); o += b
-        rows = [cu[i] + w for i, ws in enumerate(want) for w in ws]
-        host[o:o + r] = np.asarray(rows, dtype=np.int32) if r else np.zeros(0, np.int32); o += r
-        host[o:o + nt] = [t[0] for t in tiles]; o += nt
-        host[o:o + nt] = [t[1] for t in tiles]; o += nt
-        self.dev[:total].copy_(self.host[ring][:total], non_blocking=True)
+        layout.write(self.host[ring].numpy(), step_values(slots, new_tokens, starts, want, tiles))
+        self.dev[:layout.total].copy_(self.host[ring][:layout.total], non_blocking=True)
         event = torch.cuda.Event()
         event.record()
         self.events[ring] = event
 
         batch = StepBatch()
-        batch.n_seqs, batch.n_tokens, batch.n_want = b, n, r
-        o = 0
-        batch.tokens = self.dev[o:o + n]; o += n
-        batch.tok_seq = self.dev[o:o + n]; o += n
-        batch.tok_pos = self.dev[o:o + n]; o += n
-        batch.cu_seqlens = self.dev[o:o + b + 1]; o += b + 1
-        batch.slots = self.dev[o:o + b]; o += b
-        batch.start = self.dev[o:o + b]; o += b
-        batch.want_rows = self.dev[o:o + r]; o += r
-        batch.tile_seq = self.dev[o:o + nt]; o += nt
-        batch.tile_first = self.dev[o:o + nt]; o += nt
-        batch.n_tiles = nt
+        layout.attach(batch, self.dev)
+        batch.n_tokens, batch.n_seqs, batch.n_want, batch.n_tiles = layout.counts
         batch.h_slots, batch.h_new, batch.h_start = list(slots), counts, list(starts)
         batch.max_new = max(counts) if counts else 0
         batch.max_context = max((s + c for s, c in zip(starts, counts)), default=0)

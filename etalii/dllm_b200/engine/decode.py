@@ -10,7 +10,7 @@ import numpy as np
 import torch
 
 from ..kernels import ops
-from .batch import StepBatch
+from .batch import StepBatch, StepLayout, step_values
 
 
 class DecodeGraph:
@@ -26,24 +26,20 @@ class DecodeGraph:
         self.engine, self.b, self.options, self.use_graph = weakref.proxy(engine), batch_size, options, use_graph
         b = batch_size
         device = engine.rt.device
-        self.host = torch.empty(7 * b + 3, dtype=torch.int32).pin_memory()
-        self.meta = torch.zeros(7 * b + 3, dtype=torch.int32, device=device)
+        # one token per sequence, every row wanted, no prefill tiles; behind the step's fields, the run's own two:
+        # how many steps it has taken, and how many tokens of output every sequence had when it began
+        self.layout = StepLayout(b, b, b, 0, extra=(("counter", "one"), ("produced", "one")))
+        self.host = torch.empty(self.layout.total, dtype=torch.int32).pin_memory()
+        self.meta = torch.zeros(self.layout.total, dtype=torch.int32, device=device)
         self.history = torch.zeros(self.CAPACITY * b, dtype=torch.int32, device=device)
         self.chosen = torch.zeros(b, dtype=torch.int32, device=device)
         batch = StepBatch()
-        o = 0
-        batch.tokens = self.meta[o:o + b]; o += b
-        batch.tok_seq = self.meta[o:o + b]; o += b
-        batch.tok_pos = self.meta[o:o + b]; o += b
-        batch.cu_seqlens = self.meta[o:o + b + 1]; o += b + 1
-        batch.slots = self.meta[o:o + b]; o += b
-        batch.start = self.meta[o:o + b]; o += b
-        batch.want_rows = self.meta[o:o + b]; o += b
-        self.counter = self.meta[o:o + 1]; o += 1
-        self.produced = self.meta[o:o + 1]  # tokens of output every sequence has when a run of steps begins
+        self.layout.attach(batch, self.meta)
+        self.counter, self.produced = batch.counter, batch.produced
         self.min_tokens = int(min_tokens) if blocked else 0
         self.blocked = torch.tensor(sorted(blocked), dtype=torch.int32, device=device) if self.min_tokens > 0 else None
         batch.n_seqs = batch.n_tokens = batch.n_want = b
+        batch.n_tiles = 0
         batch.h_new = [1] * b
         batch.max_new = 1
         batch.is_decode = True
@@ -69,18 +65,10 @@ class DecodeGraph:
     def load(self, slots, tokens, starts, produced: int = 0) -> None:
         """Fills the fixed buffers: each sequence's slot, next input token and cached length, and how many tokens of
         output the sequences have so far."""
-        b = self.b
-        host = self.host.numpy()
-        arange = np.arange(b, dtype=np.int32)
-        host[0:b] = tokens
-        host[b:2 * b] = arange
-        host[2 * b:3 * b] = starts
-        host[3 * b:4 * b + 1] = np.arange(b + 1, dtype=np.int32)
-        host[4 * b + 1:5 * b + 1] = slots
-        host[5 * b + 1:6 * b + 1] = starts
-        host[6 * b + 1:7 * b + 1] = arange
-        host[7 * b + 1] = 0
-        host[7 * b + 2] = produced
+        values = step_values(slots, [[int(t)] for t in tokens], starts, [[0]] * self.b)
+        values["counter"] = np.zeros(1, np.int32)
+        values["produced"] = np.asarray([produced], np.int32)
+        self.layout.write(self.host.numpy(), values)
         self.batch.h_slots, self.batch.h_start = list(slots), list(starts)
         self.meta.copy_(self.host, non_blocking=True)
 

@@ -12,34 +12,51 @@ from ..parts.spec import ModelSpec
 from .runtime import Runtime
 
 
+class UnsupportedConfiguration(ValueError):
+    """A configuration that loads but that the kernels of one of its parts cannot run; the message names the rule."""
+
+
 class Model:
     def __init__(self, spec: ModelSpec, tensors: Mapping[str, torch.Tensor], rt: Runtime, max_tokens: int,
                  max_slots: int | None = None, page_size: int = 64) -> None:
         self.spec, self.rt = spec, rt
         self.vocab_size, self.hidden_size = spec.vocab_size, spec.hidden_size
 
-        def bound(role, part_spec):
+        # every part is built first and asked whether it can run here (`supports(rt)`: None, or the reason why
+        # not); only then do weights go to the device
+        built: list[tuple[str, object, object]] = []
+
+        def build(path, role, part_spec):
             part = build_part(role, part_spec)
-            part.bind({local: tensors[name] for local, name in part_spec.names.items()}, rt)
+            built.append((path, part, part_spec))
             return part
 
-        self.embedding = bound("embedding", spec.embedding)
-        self.blocks = []
-        for layer in spec.layers:
-            self.blocks.append(part_factory("block", layer.block)(
-                mixer=bound("mixer", layer.mixer), feed_forward=bound("feed_forward", layer.feed_forward),
-                mixer_norm=bound("norm", layer.mixer_norm), feed_forward_norm=bound("norm", layer.feed_forward_norm)))
-        self.final_norm = bound("norm", spec.final_norm)
-        self.head = bound("head", spec.head)
+        self.embedding = build("embedding", "embedding", spec.embedding)
+        layer_parts = []
+        for index, layer in enumerate(spec.layers):
+            roles = layer.roles()
+            layer_parts.append({name: build(f"layers.{index}.{name}", roles[name], part_spec)
+                                for name, part_spec in layer.parts.items()})
+        self.final_norm = build("final_norm", "norm", spec.final_norm)
+        self.head = build("head", "head", spec.head)
+        refused = []
+        for path, part, _ in built:
+            reason = part.supports(rt) if hasattr(part, "supports") else None
+            if reason:
+                refused.append(f"{path}: {reason}")
+        if refused:
+            raise UnsupportedConfiguration("this configuration cannot run on the kernels:\n  " + "\n  ".join(refused))
+        for _, part, part_spec in built:
+            part.bind({local: tensors[name] for local, name in part_spec.names.items()}, rt)
+        self.blocks = [part_factory("block", layer.block)(**parts) for layer, parts in zip(spec.layers, layer_parts)]
         rt.done_loading()
         if torch.device(rt.device).type == "cuda":  # what the parts say they call, compiled side by side
             from ..kernels.build import prebuild
 
             names = {"elementwise", "gemm_simt" if rt.dtype == torch.float32 else "gemv"}
-            for block in self.blocks:
-                for part in (block.mixer, block.feed_forward):
-                    if hasattr(part, "kernel_libraries"):
-                        names |= set(part.kernel_libraries(rt))
+            for part in self._layer_parts():
+                if hasattr(part, "kernel_libraries"):
+                    names |= set(part.kernel_libraries(rt))
             prebuild(sorted(names))
 
         self.order = spec.run_order()
@@ -63,6 +80,15 @@ class Model:
 
         self._plan_prefetch()
 
+    def _layer_parts(self, block=None):
+        """The parts of one block, or of all blocks: a block's `parts` mapping where it has one, else what it holds
+        under the names its class declares."""
+        for b in (self.blocks if block is None else [block]):
+            parts = getattr(b, "parts", None)
+            if parts is None:
+                parts = {name: getattr(b, name) for name in getattr(type(b), "PARTS", {}) if hasattr(b, name)}
+            yield from parts.values()
+
     def _plan_prefetch(self, ahead: int = 4) -> None:
         """Tells the decode-sized products which weights come `ahead` products later in the run order, so that they
         can be brought into L2 before they are needed (kernels/ops.py::prefetch_hints)."""
@@ -70,8 +96,7 @@ class Model:
 
         order = []
         for entry in self.order:
-            block = self.blocks[entry.layer]
-            for part in (block.mixer, block.feed_forward):
+            for part in self._layer_parts(self.blocks[entry.layer]):
                 order += [v for v in vars(part).values()
                           if isinstance(v, torch.Tensor) and v.dim() == 2 and v.dtype == torch.bfloat16]
         order += [v for v in vars(self.head).values() if isinstance(v, torch.Tensor) and v.dim() == 2
@@ -100,12 +125,11 @@ class Model:
 
     def weight_bytes(self) -> int:
         seen, total = set(), 0
-        for block in self.blocks:
-            for part in (block.mixer, block.feed_forward, block.mixer_norm, block.feed_forward_norm):
-                for value in vars(part).values():
-                    if isinstance(value, torch.Tensor) and value.data_ptr() not in seen:
-                        seen.add(value.data_ptr())
-                        total += value.numel() * value.element_size()
+        for part in self._layer_parts():
+            for value in vars(part).values():
+                if isinstance(value, torch.Tensor) and value.data_ptr() not in seen:
+                    seen.add(value.data_ptr())
+                    total += value.numel() * value.element_size()
         for part in (self.embedding, self.final_norm, self.head):
             for value in vars(part).values():
                 if isinstance(value, torch.Tensor) and value.data_ptr() not in seen:

@@ -7,7 +7,7 @@ import torch
 
 from ..cache.paged import CacheNeed
 from ..kernels import ops
-from .norm import NormedInput, fuses_norm, project
+from .norm import NormedInput, fuses_norm, project, row_rule
 from .registry import build_part, register_part
 from .spec import ParamSpec
 
@@ -49,6 +49,16 @@ class Attention:
         q, kv = int(num_heads) * int(head_dim), int(num_kv_heads) * int(head_dim)
         return {"q": ParamSpec((q, hidden_size)), "k": ParamSpec((kv, hidden_size)),
                 "v": ParamSpec((kv, hidden_size)), "o": ParamSpec((hidden_size, q))}
+
+    def supports(self, rt) -> str | None:
+        """None, or why the attention kernels cannot run these sizes (asked before weights go to the device)."""
+        hd, group = self.head_dim, self.num_heads // self.num_kv_heads
+        if hd % 8 or hd > 256:
+            return f"head_dim {hd}: the attention kernels take multiples of 8 up to 256"
+        if rt.dtype == torch.bfloat16 and (hd % 16 or hd > 128) and group > 64:
+            return (f"{group} query heads per key/value head with head_dim {hd}: the decode kernel for head sizes "
+                    f"that are no multiple of 16 up to 128 takes at most 64")
+        return row_rule(rt, hidden_size=self.hidden_size, **{"heads x head_dim": self.num_heads * hd})
 
     def cache_need(self) -> CacheNeed:
         return CacheNeed("kv", kv_heads=self.num_kv_heads, head_dim=self.head_dim, window=self.window)

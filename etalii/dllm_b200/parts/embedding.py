@@ -6,7 +6,7 @@ from __future__ import annotations
 import torch
 
 from ..kernels import ops
-from .norm import project
+from .norm import project, row_rule
 from .registry import register_part
 from .spec import ParamSpec
 
@@ -44,6 +44,9 @@ class LinearHead:
 
     def bind(self, tensors, rt) -> None:
         self.weight = rt.to_device(tensors["weight"], rt.dtype)
+
+    def supports(self, rt) -> str | None:
+        return row_rule(rt, hidden_size=self.hidden_size)
 
     def forward(self, hidden, rt) -> torch.Tensor:
         """hidden: final-normed rows, or the norm still pending (`NormedInput`)."""

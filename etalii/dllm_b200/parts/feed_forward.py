@@ -7,7 +7,7 @@ from __future__ import annotations
 import torch
 
 from ..kernels import ops
-from .norm import project
+from .norm import project, row_rule
 from .registry import register_part
 from .spec import ParamSpec
 
@@ -23,6 +23,9 @@ class SwiGLU:
     def parameters(hidden_size, intermediate_size) -> dict[str, ParamSpec]:
         return {"gate": ParamSpec((intermediate_size, hidden_size)), "up": ParamSpec((intermediate_size, hidden_size)),
                 "down": ParamSpec((hidden_size, intermediate_size))}
+
+    def supports(self, rt) -> str | None:
+        return row_rule(rt, hidden_size=self.hidden_size, intermediate_size=self.intermediate_size)
 
     def bind(self, tensors, rt) -> None:
         gate, up = tensors["gate"].to(rt.dtype), tensors["up"].to(rt.dtype)

@@ -61,6 +61,17 @@ def fuses_norm(w: torch.Tensor) -> bool:
     return w.numel() * w.element_size() <= FUSE_NORM_LIMIT
 
 
+def row_rule(rt, **widths: int) -> str | None:
+    """The rule every product kernel has: rows are read in 16-byte pieces, so the reduced width of a product must be
+    a multiple of 8 values in bfloat16 and of 4 in float32. Returns the reason if one of `widths` breaks it."""
+    step = 4 if rt.dtype == torch.float32 else 8
+    bad = [f"{name} {value}" for name, value in widths.items() if int(value) % step]
+    if bad:
+        return (f"{', '.join(bad)}: the products read rows in 16-byte pieces, so this width must be a multiple of "
+                f"{step} in {'float32' if step == 4 else 'bfloat16'}")
+    return None
+
+
 def project(out: torch.Tensor, h, w: torch.Tensor, epilogue: int) -> None:
     """out = epilogue(h @ w^T). `h` is a tensor of activations or a `NormedInput`; a decode-sized bfloat16 product
     applies the pending norm inside the kernel, anything else computes the normed activations first."""

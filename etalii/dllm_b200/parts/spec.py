@@ -2,8 +2,9 @@
 
 An architecture's `build_spec(config)` returns a `ModelSpec`. Nothing below knows which model it describes: a
 `PartSpec` names a registered kind ("rmsnorm", "attention", "swiglu", ...) and carries that part's parameters; a
-`LayerSpec` puts a mixer, a feed-forward and their norms into a block arrangement; `schedule` lists which layer runs
-when and with which cache, so a layer may run twice or read the cache another layer wrote.
+`LayerSpec` names a block arrangement and gives it its parts by name (the arrangement says which names it wants and
+which role each plays); `schedule` lists which layer runs when and with which cache, so a layer may run twice or
+read the cache another layer wrote.
 """
 from __future__ import annotations
 
@@ -28,14 +29,38 @@ class PartSpec:
     """The part's own parameter name -> the tensor's name in the checkpoint."""
 
 
-@dataclass(frozen=True)
+@dataclass(frozen=True, init=False)
 class LayerSpec:
-    mixer: PartSpec
-    feed_forward: PartSpec
-    mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
-    block: str = "pre_norm"
-    """The arrangement: "pre_norm" is x += mixer(norm(x)); x += feed_forward(norm(x))."""
+    """One layer: `block` names a registered arrangement, `parts` maps the names that arrangement asks for (its
+    class attribute `PARTS`: name -> role) to the specs of the parts. The pre-norm arrangement asks for `mixer`,
+    `feed_forward`, `mixer_norm` and `feed_forward_norm`, which may also be given as the first four arguments;
+    another arrangement (norms behind the parts as well, one norm for both parts) names its own."""
+
+    block: str
+    parts: Mapping[str, PartSpec]
+
+    def __init__(self, mixer: PartSpec | None = None, feed_forward: PartSpec | None = None,
+                 mixer_norm: PartSpec | None = None, feed_forward_norm: PartSpec | None = None,
+                 block: str = "pre_norm", parts: Mapping[str, PartSpec] | None = None) -> None:
+        named = dict(parts or {})
+        for name, spec in (("mixer", mixer), ("feed_forward", feed_forward), ("mixer_norm", mixer_norm),
+                           ("feed_forward_norm", feed_forward_norm)):
+            if spec is not None:
+                if name in named:
+                    raise ValueError(f"the layer's part {name!r} is given twice")
+                named[name] = spec
+        object.__setattr__(self, "block", block)
+        object.__setattr__(self, "parts", named)
+
+    def roles(self) -> dict[str, str]:
+        """name -> role of this layer's parts, as its arrangement declares them; the names must match exactly."""
+        from .registry import part_factory
+
+        wanted = dict(getattr(part_factory("block", self.block), "PARTS"))
+        if set(wanted) != set(self.parts):
+            raise ValueError(f"block {self.block!r} takes the parts {sorted(wanted)}; the layer gives "
+                             f"{sorted(self.parts)}")
+        return wanted
 
 
 @dataclass(frozen=True)
@@ -75,11 +100,7 @@ class ModelSpec:
         """Every part as (path in the model, role, spec), e.g. ("layers.2.mixer", "mixer", ...)."""
         out = [("embedding", "embedding", self.embedding)]
         for index, layer in enumerate(self.layers):
-            out += [
-                (f"layers.{index}.mixer_norm", "norm", layer.mixer_norm),
-                (f"layers.{index}.mixer", "mixer", layer.mixer),
-                (f"layers.{index}.feed_forward_norm", "norm", layer.feed_forward_norm),
-                (f"layers.{index}.feed_forward", "feed_forward", layer.feed_forward),
-            ]
+            roles = layer.roles()
+            out += [(f"layers.{index}.{name}", roles[name], spec) for name, spec in layer.parts.items()]
         out += [("final_norm", "norm", self.final_norm), ("head", "head", self.head)]
         return out

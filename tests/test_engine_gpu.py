@@ -211,15 +211,29 @@ def test_other_sizes(sizes, dtype):
     assert all(len(r.tokens) == 4 for r in chosen)
 
 
-def test_sizes_the_kernels_refuse_are_clear_errors():
+def test_sizes_the_kernels_refuse_are_refused_when_the_engine_is_built():
+    """config.json allows widths and head sizes the kernels cannot run (rows are read in 16-byte pieces). Every
+    part is asked before weights go to the device, and the error names the part and the rule; the kernels keep
+    their own refusal for a caller that comes another way."""
+    from etalii.dllm_b200.engine.model import UnsupportedConfiguration
     from etalii.dllm_b200.kernels.ops import KernelError
+    from etalii.dllm_b200.kernels import ops
 
     config = dict(P.TINY_A, num_hidden_layers=1, intermediate_size=100)  # rows of 100 bfloat16 are not 16-byte pieces
     weights = P.random_weights(config, seed=1)
-    engine = make_engine(config, weights, "bfloat16", max_tokens=128)
-    slot = engine.open(1)
+    before = torch.cuda.memory_allocated()
+    with pytest.raises(UnsupportedConfiguration, match=r"layers\.0\.feed_forward: intermediate_size 100.*multiple of 8"):
+        make_engine(config, weights, "bfloat16", max_tokens=128)
+    assert torch.cuda.memory_allocated() == before  # nothing was uploaded
+    make_engine(config, weights, "float32", max_tokens=128)  # 100 is a multiple of 4: the 32-bit path takes it
+    odd = dict(P.TINY_A, num_hidden_layers=1, head_dim=20, num_attention_heads=4, num_key_value_heads=2)
+    with pytest.raises(UnsupportedConfiguration, match="head_dim 20"):
+        make_engine(odd, P.random_weights(odd, seed=1), "float32", max_tokens=128)
+    c = torch.zeros((3, 16), dtype=torch.float32, device="cuda:0")
+    a = torch.zeros((3, 100), dtype=torch.bfloat16, device="cuda:0")
+    w = torch.zeros((16, 100), dtype=torch.bfloat16, device="cuda:0")
     with pytest.raises(KernelError, match="multiple of 8"):
-        engine.step(slot, [[1, 2, 3]])
+        ops.gemm(c, a, w, ops.EPI_STORE_F32)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -182,6 +182,34 @@ class ToyConfig:
         return cls()
 
 
+def _toy_plain(w, tokens):
+    """The toy architecture as a plain whole-sequence computation: the decay layer is the recurrence
+    state_t = 0.5 state_(t-1) + h_t from a zero state, output state_t w^T; the schedule runs layer 0, layer 1,
+    layer 0 again (a second state) and layer 1 again with the keys and values of its first run."""
+    import plain_llama as P
+
+    n = len(tokens)
+    x = P.embedding(w["emb"], tokens)
+    kept = {}
+    for layer, reads_cache in ((0, False), (1, False), (0, False), (1, True)):
+        h = P.rms_norm(x, w[f"l{layer}.n1"], 1e-5)
+        if layer == 0:
+            state, rows = np.zeros(h.shape[1]), []
+            for t in range(n):
+                state = 0.5 * state + h[t].astype(np.float64)
+                rows.append(state.copy())
+            x = x + P.linear(np.asarray(rows, dtype=np.float32), w["l0.w"])
+        else:
+            q = P.linear(h, w["l1.q"]).reshape(n, 2, 16)
+            if not reads_cache:
+                kept["k"] = P.linear(h, w["l1.k"]).reshape(n, 1, 16)
+                kept["v"] = P.linear(h, w["l1.v"]).reshape(n, 1, 16)
+            x = x + P.linear(P.attention(q, kept["k"], kept["v"], 0.25, window=5).reshape(n, -1), w["l1.o"])
+        h = P.rms_norm(x, w[f"l{layer}.n2"], 1e-5)
+        x = x + P.feed_forward(h, w[f"l{layer}.gate"], w[f"l{layer}.up"], w[f"l{layer}.down"])
+    return P.linear(P.rms_norm(x, w["final"], 1e-5), w["emb"])
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_toy_architecture_with_a_stateful_mixer(dtype):
     from etalii.dllm_b200.config.registry import register_architecture, unregister_architecture
@@ -204,6 +232,11 @@ def test_toy_architecture_with_a_stateful_mixer(dtype):
         slots = engine.open(2)
         whole = host(engine.step(slots, tokens, [list(range(9)), list(range(3))]))
         engine.close(slots)
+        # against the plain recurrence, not only against itself
+        w = {k: v.float().numpy() for k, v in tensors.items()}
+        plain_tol = 5e-5 if dtype == "float32" else 3e-2
+        assert rel_error(whole[:9], _toy_plain(w, tokens[0])) <= plain_tol
+        assert rel_error(whole[9:], _toy_plain(w, tokens[1])) <= plain_tol
         slots = engine.open(2)  # the same slots again: the state must start from zero
         first = host(engine.step(slots, [tokens[0][:4], tokens[1][:1]], [list(range(4)), [0]]))
         rest = []

@@ -187,3 +187,114 @@ def test_routed_feed_forward_and_another_position_encoding(dtype, tol):
         unregister_part("feed_forward", "routed_experts")
         unregister_part("position", "quadratic_rotary")
         unregister_architecture("toy_routed")
+
+
+class SandwichBlock:
+    """Another arrangement, defined here: a third norm behind the mixer. x += post_norm(mixer(norm(x)));
+    x += feed_forward(norm(x)). It names the parts it takes (and their roles) itself; the layer's spec gives them by
+    those names, and no file of the library knows this arrangement."""
+
+    PARTS = {"mixer": "mixer", "feed_forward": "feed_forward", "mixer_norm": "norm", "mixer_post_norm": "norm",
+             "feed_forward_norm": "norm"}
+
+    def __init__(self, mixer, feed_forward, mixer_norm, mixer_post_norm, feed_forward_norm):
+        self.mixer, self.feed_forward = mixer, feed_forward
+        self.mixer_norm, self.mixer_post_norm, self.feed_forward_norm = mixer_norm, mixer_post_norm, feed_forward_norm
+        self.parts = dict(mixer=mixer, feed_forward=feed_forward, mixer_norm=mixer_norm,
+                          mixer_post_norm=mixer_post_norm, feed_forward_norm=feed_forward_norm)
+
+    def forward(self, x, batch, cache, rt, write_cache=True):
+        from etalii.dllm_b200.kernels import ops
+
+        mixed = torch.zeros_like(x)  # the mixer adds its output into what it is given as the residual
+        self.mixer.forward(self.mixer_norm.forward(x, rt), mixed, batch, cache, rt, write_cache)
+        ops.add_residual(x, self.mixer_post_norm.forward(mixed, rt, name="post_normed"))
+        self.feed_forward.forward(self.feed_forward_norm.forward(x, rt), x, batch, rt)
+
+
+class SandwichConfig:
+    model_type = "toy_sandwich"
+
+    @classmethod
+    def from_hf(cls, config, generation=None):
+        return cls()
+
+
+def sandwich_spec(config):
+    from etalii.dllm_b200.parts import LayerSpec, ModelSpec, PartSpec
+
+    norm = lambda name, eps=EPS: PartSpec("rmsnorm", {"hidden_size": HIDDEN, "eps": eps}, {"weight": name})  # noqa: E731
+    layers = []
+    for i in range(2):
+        parts = {
+            "mixer": PartSpec("attention", {"hidden_size": HIDDEN, "num_heads": HEADS, "num_kv_heads": KV_HEADS,
+                                            "head_dim": HEAD_DIM, "scale": 0.3, "window": None,
+                                            "position": PartSpec("rotary", {"head_dim": HEAD_DIM, "theta": 300.0,
+                                                                            "scaling": None})},
+                              {k: f"l{i}.{k}" for k in "qkvo"}),
+            "feed_forward": PartSpec("swiglu", {"hidden_size": HIDDEN, "intermediate_size": 56},
+                                     {k: f"l{i}.{k}" for k in ("gate", "up", "down")}),
+            "mixer_norm": norm(f"l{i}.n1"), "mixer_post_norm": norm(f"l{i}.n_post", 1e-3),
+            "feed_forward_norm": norm(f"l{i}.n2"),
+        }
+        # layer 1 is the library's own arrangement: the two kinds of block stand side by side in one model
+        if i == 1:
+            del parts["mixer_post_norm"]
+        layers.append(LayerSpec(block="sandwich" if i == 0 else "pre_norm", parts=parts))
+    return ModelSpec(VOCAB, HIDDEN, 128,
+                     PartSpec("token_embedding", {"vocab_size": VOCAB, "hidden_size": HIDDEN}, {"weight": "emb"}),
+                     tuple(layers), norm("final"),
+                     PartSpec("linear", {"vocab_size": VOCAB, "hidden_size": HIDDEN}, {"weight": "head"}))
+
+
+def sandwich_plain(w, tokens):
+    n = len(tokens)
+    freqs = P.rope_inv_freq(HEAD_DIM, 300.0)
+    x = P.embedding(w["emb"], tokens)
+    for i in range(2):
+        h = P.rms_norm(x, w[f"l{i}.n1"], EPS)
+        q = P.rope(P.linear(h, w[f"l{i}.q"]).reshape(n, HEADS, HEAD_DIM), np.arange(n), freqs)
+        k = P.rope(P.linear(h, w[f"l{i}.k"]).reshape(n, KV_HEADS, HEAD_DIM), np.arange(n), freqs)
+        v = P.linear(h, w[f"l{i}.v"]).reshape(n, KV_HEADS, HEAD_DIM)
+        mixed = P.linear(P.attention(q, k, v, 0.3).reshape(n, -1), w[f"l{i}.o"])
+        x = x + (P.rms_norm(mixed, w["l0.n_post"], 1e-3) if i == 0 else mixed)
+        x = x + P.feed_forward(P.rms_norm(x, w[f"l{i}.n2"], EPS), w[f"l{i}.gate"], w[f"l{i}.up"], w[f"l{i}.down"])
+    return P.linear(P.rms_norm(x, w["final"], EPS), w["head"])
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 5e-5), ("bfloat16", 3e-2)])
+def test_a_block_arrangement_with_a_third_norm_registered_from_outside(dtype, tol):
+    from etalii.dllm_b200.config.registry import register_architecture, unregister_architecture
+    from etalii.dllm_b200.engine.engine import Engine
+    from etalii.dllm_b200.parts import LayerSpec, register_part, unregister_part
+    from etalii.dllm_b200.weights.loader import expected_tensors
+
+    register_part("block", "sandwich", SandwichBlock)
+    register_architecture("toy_sandwich", SandwichConfig, sandwich_spec)
+    try:
+        spec = sandwich_spec(SandwichConfig())
+        assert [path for path, role, _ in spec.part_specs() if role == "norm" and path.startswith("layers.0")] == \
+            ["layers.0.mixer_norm", "layers.0.mixer_post_norm", "layers.0.feed_forward_norm"]
+        with pytest.raises(ValueError, match="takes the parts"):  # a layer must give exactly what its block names
+            LayerSpec(block="pre_norm", parts=spec.layers[0].parts).roles()
+        g = torch.Generator().manual_seed(17)
+        tensors = {name: (torch.randn(p.shape, generator=g) * 0.1 + (1 if p.init == "ones" else 0)).to(torch.bfloat16)
+                   for name, p in expected_tensors(spec).items()}
+        assert "l0.n_post" in tensors and "l1.n_post" not in tensors
+        w = {k: v.float().numpy() for k, v in tensors.items()}
+        engine = Engine(SandwichConfig(), tensors, dtype=dtype, max_tokens=64 * 4, cuda_graphs=False)
+        prompts = [[int(t) for t in torch.randint(0, VOCAB, (n,), generator=g)] for n in (19, 6)]
+        want = [sandwich_plain(w, p) for p in prompts]
+        slots = engine.open(2)
+        whole = host(engine.step(slots, prompts, [list(range(len(p))) for p in prompts]))
+        engine.close(slots)
+        assert rel_error(whole[:19], want[0]) <= tol and rel_error(whole[19:], want[1]) <= tol
+        slots = engine.open(2)  # cut: a few tokens, then one by one
+        engine.step(slots, [prompts[0][:4], prompts[1][:4]], [[], []])
+        for index in range(4, 6):
+            got = host(engine.step(slots, [[prompts[0][index]], [prompts[1][index]]]))
+            assert rel_error(got[0], want[0][index]) <= tol and rel_error(got[1], want[1][index]) <= tol
+        engine.close(slots)
+    finally:
+        unregister_part("block", "sandwich")
+        unregister_architecture("toy_sandwich")
