@@ -1,16 +1,23 @@
 """Measures decode and prefill throughput of the engine on one B200 and prints ONE JSON line.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--repeats R] [--layers L] [--impl ours|reference]
                     [--shape smollm2-135m|smollm2-1.7b|llama-3.1-8b] [--batch B] [--no-points]
-                    [--profile decode|prefill|gemm|attention|stream]
+                    [--profile decode|prefill|kernels|gemm|attention|stream]
 
 Default workload: the SmolLM2-135M shape (30 layers, hidden 576, 9 heads, 3 kv heads, head_dim 64, intermediate 1536,
 vocabulary 49152, tied head) with seeded random bfloat16 weights; a batch of 8 sequences with unequal prompt lengths
 (128 to 2,048 seeded random tokens) inside a context of 8,192. A "step" is one decode step of the whole batch
-(model, greedy token choice, feedback), replayed as a CUDA graph; `value` is decoded tokens per second over exactly K
-steps timed with CUDA events. `e2e` is the same through `Engine.generate` with host token lists in and out.
-`prefill` is one 2,048-token prompt in one step. `roofline` relates the decode step to HBM bandwidth: every weight
-read once plus the cache of the live sequences, over the step's time. `points` repeats the decode at batch 1 and 64, and the end-to-end run with temperature sampling.
+(model, greedy token choice, feedback), replayed as a CUDA graph. After one untimed run, R runs of exactly K steps are
+timed with CUDA events, each from a fresh cache; `value` is decoded tokens per second at the mean step time, `sd` the
+standard deviation over the runs (the reference's method: benchmarks/benchmark.py:209-216).
+`e2e` is generated tokens per second of whole `Engine.generate` calls (wall clock around the call: prompt step,
+decoding, host token lists in and out), mean and sd of R calls, with the call's prompt and decode parts.
+`prefill` is one 2,048-token prompt in one step: `ms` as a user calls it, `host_ms` until the last launch is issued,
+`device_ms` the same launches replayed as a CUDA graph. `roofline` relates the decode step to HBM bandwidth: every
+weight read once plus the cache of the live sequences, over the step's time. `points` repeats the decode at batch 1
+and 64, the end-to-end run with temperature sampling, and decode and prefill of the true 32-bit path (`fp32_*`, against
+twice the bytes). `kernels` lists where the decode step's time goes, kind of launch by kind of launch.
+`--impl reference` tries the reference's own pure-NumPy implementation on the same configuration (see `reference_arm`).
 """
 import argparse
 import json
@@ -329,11 +336,214 @@ def model_numbers(config, layers):
     per_layer = h * (nh + 2 * nkv) * hd + nh * hd * h + 3 * h * i
     matrix_params = layers * per_layer
     norm_params = (2 * layers + 1) * h
-    kv_bytes_per_token = layers * 2 * nkv * hd * 2
+    kv_values_per_token = layers * 2 * nkv * hd
     t = PREFILL_TOKENS
     prefill_flops = 2 * matrix_params * t + layers * 4 * hd * nh * t * (t + 1) // 2 + 2 * h * v
     return {"matrix_params": matrix_params, "head_params": v * h, "norm_params": norm_params,
-            "kv_bytes_per_token": kv_bytes_per_token, "prefill_flops": prefill_flops}
+            "kv_values_per_token": kv_values_per_token, "prefill_flops": prefill_flops}
+
+
+def step_bytes(numbers, element_bytes, cached_tokens):
+    """Bytes a decode step has to read: every weight once (matrices and head in the model's dtype, norms float32)
+    and the keys and values of the live sequences."""
+    weights = element_bytes * (numbers["matrix_params"] + numbers["head_params"]) + 4 * numbers["norm_params"]
+    return weights, weights + cached_tokens * numbers["kv_values_per_token"] * element_bytes
+
+
+def decode_point(engine, prompts, steps, warmup, repeats):
+    """`repeats` device-timed runs of `steps` decode steps after one untimed run (the reference's method,
+    benchmarks/benchmark.py:209-216: one warm-up, mean and sd of the repetitions, a fresh cache each time)."""
+    from etalii.dllm_b200.measure import mean_sd
+
+    decode_run(engine, prompts, min(4, steps), 3)  # builds kernels, work buffers and the graph before anything is timed
+    runs = [decode_run(engine, prompts, steps, warmup) for _ in range(repeats)]
+    ms, sd = mean_sd([r[0] / steps for r in runs])
+    return {"ms_per_step": ms, "sd_ms": sd, "launches_per_step": runs[-1][1], "cached": runs[-1][2],
+            "tokens_per_s": len(prompts) / (ms / 1e3),
+            "sd": mean_sd([len(prompts) * steps / (r[0] / 1e3) for r in runs])[1]}
+
+
+def prefill_point(engine, vocab, warmup, repeats=5):
+    """One prompt of PREFILL_TOKENS tokens in one step: device time by CUDA events around the step as a user calls
+    it (median of `repeats`), the host's time until the last launch is issued, and the device time of the same
+    launches replayed as a CUDA graph (no host between the kernels)."""
+    import numpy as np
+    import torch
+
+    prompt = np.random.default_rng(7).integers(0, vocab, PREFILL_TOKENS).tolist()
+    times, host = [], []
+    for index in range(warmup + repeats):
+        slot = engine.open(1)
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        began = time.perf_counter()
+        begin.record()
+        engine.step(slot, [prompt])
+        issued = time.perf_counter()
+        end.record()
+        torch.cuda.synchronize()
+        engine.close(slot)
+        if index >= warmup:
+            times.append(begin.elapsed_time(end))
+            host.append((issued - began) * 1e3)
+    slot = engine.open(1)
+    engine.step(slot, [prompt])
+    batch = engine.last_batch
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        engine.model.forward(batch)
+    device = []
+    for _ in range(repeats + 1):
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        graph.replay()
+        end.record()
+        torch.cuda.synchronize()
+        device.append(begin.elapsed_time(end))
+    engine.close(slot)
+    engine.check()
+    median = lambda values: sorted(values)[len(values) // 2]  # noqa: E731
+    return {"ms": median(times), "host_ms": median(host), "device_ms": median(device[1:])}
+
+
+def kernel_shares(engine, prompts, steps=3):
+    """Where a decode step's time goes, kernel by kernel: the step run launch by launch (no graph) with a CUDA event
+    behind every launch; the share of each kind of launch in the sum."""
+    import torch
+
+    from etalii.dllm_b200 import SamplingOptions
+    from etalii.dllm_b200.engine.decode import DecodeGraph
+    from etalii.dllm_b200.kernels import ops
+
+    slots = engine.open(len(prompts))
+    tokens = []
+    for begin in range(0, len(prompts), 8):
+        part = slice(begin, begin + 8)
+        logits = engine.step(slots[part], prompts[part])
+        tokens += engine.sampler.choose(logits, engine.last_batch.slots, SamplingOptions()).tolist()
+    run = DecodeGraph(engine, len(prompts), SamplingOptions(), use_graph=False,
+                      max_context=max(len(p) for p in prompts) + 64)
+    engine.decode_start(run, slots, tokens, steps + 2)
+    run.replay(2)
+    torch.cuda.synchronize()
+    ops.trace = []
+    first = torch.cuda.Event(enable_timing=True)
+    first.record()
+    run.replay(steps)
+    torch.cuda.synchronize()
+    events, ops.trace = ops.trace, None
+    engine.close(slots)
+    totals, counts, before = {}, {}, first
+    for name, event in events:
+        totals[name] = totals.get(name, 0.0) + before.elapsed_time(event)
+        counts[name] = counts.get(name, 0) + 1
+        before = event
+    whole = sum(totals.values())
+    return {name: {"share": round(totals[name] / whole, 4), "launches_per_step": round(counts[name] / steps, 1),
+                   "us": round(totals[name] / counts[name] * 1e3, 2)}
+            for name in sorted(totals, key=lambda n: -totals[n])}
+
+
+REFERENCE_BUDGET_S = 150.0
+
+
+def reference_worker(budget_s: float) -> int:
+    """Runs in a process of its own with only the reference's sources on the path: the reference's pure-NumPy
+    second implementation (`etalii_dllm.reference.ReferenceTransformer`, its stock code path) on the benchmark's
+    configuration, float32, the same eight prompts; prints one JSON line of what it managed within the budget."""
+    import numpy as np
+
+    import etalii_dllm.reference as ref
+    from etalii_dllm.architecture import TransformerConfig
+
+    c = SMOLLM2_135M
+    config = TransformerConfig(
+        family="llama", vocabulary_size=c["vocab_size"], hidden_size=c["hidden_size"],
+        intermediate_size=c["intermediate_size"], layers=c["num_hidden_layers"], heads=c["num_attention_heads"],
+        kv_heads=c["num_key_value_heads"], head_dim=c["head_dim"], context_length=c["max_position_embeddings"],
+        rms_norm_eps=c["rms_norm_eps"], rope_theta=c["rope_theta"], rope_scaling=None,
+        tie_word_embeddings=c["tie_word_embeddings"], eos_token_ids=(c["eos_token_id"],))
+    rng = np.random.default_rng(0)
+    tensors = {}
+    for name, shape in config.tensor_shapes().items():
+        norm = name.endswith("norm.weight")
+        tensors[name] = (rng.standard_normal(shape, dtype=np.float32) * np.float32(0.01 if norm else 0.02)
+                         + np.float32(1.0 if norm else 0.0))
+    model = ref.ReferenceTransformer(config, tensors)
+    prompts = make_prompts(8, c["vocab_size"], seed=1)
+    began = time.perf_counter()
+    fed, decoded, decode_s = 0, 0, 0.0
+    # the reference holds one sequence at a time: prompt by prompt, shortest first, 16 tokens a call
+    for prompt in sorted(prompts, key=len):
+        model.reset()
+        for at in range(0, len(prompt), 16):
+            if time.perf_counter() - began > budget_s:
+                break
+            logits = model.forward(prompt[at:at + 16])
+            fed += len(prompt[at:at + 16])
+        else:
+            token = int(np.argmax(logits))
+            while time.perf_counter() - began <= budget_s and decoded < 64:
+                t0 = time.perf_counter()
+                token = int(np.argmax(model.forward([token])))
+                decode_s += time.perf_counter() - t0
+                decoded += 1
+            continue
+        break
+    print(json.dumps({"seconds": round(time.perf_counter() - began, 1), "prompt_tokens_fed": fed,
+                      "prompt_tokens_total": sum(len(p) for p in prompts), "decoded": decoded,
+                      "decode_s": round(decode_s, 3)}))
+    return 0
+
+
+def reference_arm(args) -> int:
+    """`--impl reference`: the reference cannot be installed here (its native engine needs nanobind, which the
+    offline wheelhouse does not have), but its pure-NumPy second implementation runs from a copy of its sources
+    under baseline/_ref. It is tried on the benchmark's configuration with a time budget; what it managed is
+    reported. It goes through no file of this library."""
+    where = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isfile(os.path.join(where, "etalii_dllm", "reference.py")):
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference does not install offline (pip: no numpy in the wheelhouse; --no-deps: the "
+                          "CMake build needs nanobind, which is not installed), and no copy of its Python sources "
+                          "is under baseline/_ref"}))
+        return 0
+    budget = float(os.environ.get("DLLM_B200_REFERENCE_BUDGET_S", REFERENCE_BUDGET_S))
+    env = dict(os.environ, PYTHONPATH=where)
+    began = time.perf_counter()
+    try:
+        done = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "reference-worker",
+                               "--budget", str(budget)], env=env, capture_output=True, text=True,
+                              timeout=budget + 240)
+        report = json.loads(done.stdout.strip().splitlines()[-1])
+    except Exception as error:  # a failed import, a timeout, no JSON
+        print(json.dumps({"impl": "reference", "unavailable":
+                          f"the reference's pure-NumPy implementation did not run: {type(error).__name__}: "
+                          f"{str(error)[:160]} (after {time.perf_counter() - began:.0f} s)"}))
+        return 0
+    if report["decoded"] >= 8 and report["prompt_tokens_fed"] >= report["prompt_tokens_total"]:
+        # every prompt was fed and decoded: one sequence at a time is how the reference's second implementation
+        # runs, so the batch's tokens per second is its single-sequence rate
+        value = report["decoded"] / report["decode_s"]
+        print(json.dumps({
+            "impl": "reference (pure-NumPy second implementation, CPU, float32, one sequence at a time)",
+            "metric": "decode tokens/s (SmolLM2-135M shape, batch 8, random weights)", "value": round(value, 3),
+            "unit": "tokens/s", "n_gpus": args.gpus, "steps": report["decoded"], "warmup": 0,
+            "ms_per_step": round(1e3 / value, 1), "higher_is_better": True, "dtype": "float32", "same_config": True,
+            "data": "synthetic"}))
+        return 0
+    rate = report["prompt_tokens_fed"] / max(report["seconds"], 1e-9)
+    hours = report["prompt_tokens_total"] / max(rate, 1e-9) / 3600
+    print(json.dumps({"impl": "reference", "unavailable":
+                      f"the reference's native engine does not install offline (no nanobind); its pure-NumPy second "
+                      f"implementation (etalii_dllm.reference.ReferenceTransformer, float32, CPU) was run on the "
+                      f"benchmark's configuration and cut after {report['seconds']:.0f} s: it had fed "
+                      f"{report['prompt_tokens_fed']} of the batch's {report['prompt_tokens_total']} prompt tokens "
+                      f"({rate:.2f} tokens/s, about {hours:.1f} h for the prompts alone) and decoded "
+                      f"{report['decoded']} tokens"}))
+    return 0
 
 
 def main() -> int:
@@ -341,20 +551,21 @@ def main() -> int:
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=256)
     parser.add_argument("--warmup", type=int, default=8)
+    parser.add_argument("--repeats", type=int, default=5, help="timed repetitions of the decode run (mean and sd)")
     parser.add_argument("--shape", default="smollm2-135m", choices=sorted(SHAPES),
                         help="layer sizes: the default is the benchmark's; the others are larger shapes of the family")
     parser.add_argument("--layers", type=int, default=0, help="fewer layers than the full model (named in config)")
     parser.add_argument("--batch", type=int, default=8)
-    parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
-    parser.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 decode points")
-    parser.add_argument("--profile", choices=("decode", "prefill", "gemm", "attention", "stream"),
+    parser.add_argument("--impl", default="ours", choices=("ours", "reference", "reference-worker"))
+    parser.add_argument("--budget", type=float, default=REFERENCE_BUDGET_S, help=argparse.SUPPRESS)
+    parser.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 and the float32 points")
+    parser.add_argument("--profile", choices=("decode", "prefill", "gemm", "attention", "stream", "kernels"),
                         help="run only a few decode steps (or one prefill) and print no JSON: a small case for ncu")
     args = parser.parse_args()
+    if args.impl == "reference-worker":
+        return reference_worker(args.budget)
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference does not install offline: pip finds no numpy in the wheelhouse, and with "
-                          "--no-deps its wheel build fails in CMake because nanobind is not installed"}))
-        return 0
+        return reference_arm(args)
     if args.profile == "gemm":
         return gemm_table()
     if args.profile == "attention":
@@ -366,12 +577,10 @@ def main() -> int:
         return 2
     warmup = max(3, args.warmup)
 
-    import torch
-
     from etalii.dllm_b200 import SamplingOptions
     from etalii.dllm_b200.config.registry import config_from_dict
     from etalii.dllm_b200.engine.engine import Engine
-    from etalii.dllm_b200.kernels import ops
+    from etalii.dllm_b200.measure import measure_generation
 
     shape_name, shape = SHAPES[args.shape]
     full_layers = shape["num_hidden_layers"]
@@ -393,47 +602,76 @@ def main() -> int:
     if args.profile == "prefill":
         print(f"profile prefill: {prefill_run(engine, vocab, warmup=1, repeats=1):.4f} ms")
         return 0
-    decode_run(engine, prompts, 4, 3)  # builds kernels, work buffers and the graph before anything is timed
+    if args.profile == "kernels":
+        for name, row in kernel_shares(engine, prompts).items():
+            print(f"{row['share'] * 100:5.1f} %  {row['launches_per_step']:5.1f} x {row['us']:7.2f} us  {name}")
+        return 0
     with ClockSampler() as clocks:
-        ms, launches_per_step, cached = decode_run(engine, prompts, args.steps, warmup)
-    ms_per_step = ms / args.steps
-    value = args.batch * args.steps / (ms / 1e3)
+        point = decode_point(engine, prompts, args.steps, warmup, args.repeats)
+    ms_per_step = point["ms_per_step"]
+    mean_cached = point["cached"] - args.batch * args.steps / 2  # halfway through the timed steps
+    weight_bytes, bytes_per_step = step_bytes(numbers, 2, mean_cached)
+    achieved = bytes_per_step / (ms_per_step / 1e3) / 1e9
 
-    weight_bytes = 2 * (numbers["matrix_params"] + numbers["head_params"]) + 4 * numbers["norm_params"]
-    mean_cached = cached - args.batch * args.steps / 2  # halfway through the timed steps
-    step_bytes = weight_bytes + mean_cached * numbers["kv_bytes_per_token"]
-    achieved = step_bytes / (ms_per_step / 1e3) / 1e9
+    measured = prefill_point(engine, vocab, warmup=3)
+    prefill = {"value": round(PREFILL_TOKENS / (measured["ms"] / 1e3), 1), "tokens": PREFILL_TOKENS,
+               "ms": round(measured["ms"], 4),
+               "frac": round(numbers["prefill_flops"] / (measured["ms"] / 1e3) / (peak["bf16_tflops"] * 1e12), 5),
+               "host_ms": round(measured["host_ms"], 4), "device_ms": round(measured["device_ms"], 4)}
 
-    prefill_ms = prefill_run(engine, vocab, warmup=3)
-    prefill = {"value": round(PREFILL_TOKENS / (prefill_ms / 1e3), 1), "tokens": PREFILL_TOKENS,
-               "ms": round(prefill_ms, 4),
-               "frac": round(numbers["prefill_flops"] / (prefill_ms / 1e3) / (peak["bf16_tflops"] * 1e12), 5)}
-
-    # end to end through the public entry point: host token lists in, host token lists out
-    engine.generate(prompts, 20, SamplingOptions(), ignore_eos=True)
-    engine.generate(prompts, args.steps + 1, SamplingOptions(), ignore_eos=True)
-    stats = engine.stats
+    # end to end through the public entry point: host token lists in, host token lists out, the wall clock around
+    # the whole call (prompt step, decoding, results)
+    whole = measure_generation(engine, prompts, args.steps + 1, SamplingOptions(), repeats=args.repeats)
     graph = next(g for g in engine._graphs.values() if g.b == args.batch)
-    e2e = {"value": round(stats["decode_tokens"] / stats["decode_s"], 1), "unit": "tokens/s",
-           "h2d_bytes_per_step": round(graph.host.numel() * 4 / engine.decode_chunk, 1),
+    prompt_bytes = 4 * sum(len(p) for p in prompts)
+    e2e = {"value": round(whole["tokens_per_s"], 1), "sd": round(whole["sd"], 1), "unit": "tokens/s",
+           "what": "generated tokens / wall time of Engine.generate (prompts of 128-2048 tokens included)",
+           "call_s": round(whole["call_s"], 5), "prefill_s": round(whole["prefill_s"], 5),
+           "decode_s": round(whole["decode_s"], 5), "decode_only": round(whole["decode_tokens_per_s"], 1),
+           "h2d_bytes_per_step": round((prompt_bytes + graph.host.numel() * 4 * (args.steps / engine.decode_chunk))
+                                       / (args.steps + 1), 1),
            "d2h_bytes_per_step": args.batch * 4}
 
     points = {}
     if not args.no_points:
         # the same end-to-end run with sampling on the device instead of greedy choice
-        sampled = SamplingOptions(temperature=0.8, seed=1)
-        engine.generate(prompts, 20, sampled, ignore_eos=True)
-        engine.generate(prompts, args.steps + 1, sampled, ignore_eos=True)
-        points["e2e_temperature_0.8"] = round(engine.stats["decode_tokens"] / engine.stats["decode_s"], 1)
+        sampled = measure_generation(engine, prompts, args.steps + 1, SamplingOptions(temperature=0.8, seed=1),
+                                     repeats=2)
+        points["e2e_temperature_0.8"] = round(sampled["tokens_per_s"], 1)
         for name, batch in (("decode_b1", 1), ("decode_b64", 64)):
-            batch_prompts = make_prompts(batch, vocab, seed=2 + batch)
-            decode_run(engine, batch_prompts, 4, 3)
-            point_ms, _, _ = decode_run(engine, batch_prompts, args.steps, warmup)
-            points[name] = round(batch * args.steps / (point_ms / 1e3), 1)
+            other = decode_point(engine, make_prompts(batch, vocab, seed=2 + batch), args.steps, warmup, 3)
+            points[name] = round(other["tokens_per_s"], 1)
+            cached = other["cached"] - batch * args.steps / 2
+            points[name + "_hbm_frac"] = round(step_bytes(numbers, 2, cached)[1] / (other["ms_per_step"] / 1e3) / 1e9
+                                               / peak["hbm_gbs"], 4)
+        kernels = kernel_shares(engine, prompts)
+        del engine
+        import gc
+
+        import torch
+
+        gc.collect()
+        torch.cuda.empty_cache()
+        # the true 32-bit path of the same model: float32 weights, cache and products (no tensor cores)
+        steps32 = min(args.steps, 64)
+        engine32 = Engine.from_random(config, seed=0, dtype="float32", device="cuda:0", max_tokens=cache_tokens,
+                                      max_length=config_dict["max_position_embeddings"])
+        for name, batch in (("fp32_decode_b1", 1), ("fp32_decode_b8", 8), ("fp32_decode_b64", 64)):
+            other = decode_point(engine32, make_prompts(batch, vocab, seed=1 if batch == 8 else 2 + batch), steps32,
+                                 3, 3)
+            points[name] = round(other["tokens_per_s"], 1)
+            cached = other["cached"] - batch * steps32 / 2
+            points[name + "_hbm_frac"] = round(step_bytes(numbers, 4, cached)[1] / (other["ms_per_step"] / 1e3) / 1e9
+                                               / peak["hbm_gbs"], 4)
+        measured32 = prefill_point(engine32, vocab, warmup=1, repeats=3)
+        points["fp32_prefill_2048"] = round(PREFILL_TOKENS / (measured32["ms"] / 1e3), 1)
+        points["fp32_prefill_ms"] = round(measured32["ms"], 3)
+    else:
+        kernels = kernel_shares(engine, prompts)
 
     line = {
         "metric": f"decode tokens/s ({shape_name} shape, batch {args.batch}, bf16, random weights)",
-        "value": round(value, 1),
+        "value": round(point["tokens_per_s"], 1), "sd": round(point["sd"], 1), "repeats": args.repeats,
         "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
         "ms_per_step": round(ms_per_step, 5), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: seeded random token ids, seeded random weights N(0, 0.02)",
@@ -451,11 +689,13 @@ def main() -> int:
         },
         "clocks": clocks.summary(),
         "e2e": e2e,
-        "gpu_launches": int(launches_per_step * args.steps),
+        "gpu_launches": int(point["launches_per_step"] * args.steps),
+        "launches_per_step": point["launches_per_step"],
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / peak["hbm_gbs"], 4)},
         "points": points,
+        "kernels": kernels,
     }
     print(json.dumps(line))
     return 0

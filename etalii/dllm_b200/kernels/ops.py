@@ -13,6 +13,7 @@ from .build import library
 EPI_STORE_F32, EPI_STORE_T, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
 _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 _STATUS = {-1: "bad argument", -2: "unsupported size", -3: "kernel launch failed"}
+_EPILOGUE_NAMES = {0: "store_f32", 1: "store", 2: "residual", 3: "swiglu"}
 
 
 class KernelError(RuntimeError):
@@ -67,6 +68,10 @@ _functions: dict[tuple[str, str], ctypes._CFuncPtr] = {}
 launches = 0
 """How many kernels this module has launched (every call below launches exactly one)."""
 
+trace: list | None = None
+"""A list while a measurement wants every launch timed: each launch appends (name, CUDA event recorded behind it).
+On one stream the time between consecutive events is the kernel's (plus the gap before it)."""
+
 
 def _fn(lib: str, name: str):
     key = (lib, name)
@@ -84,6 +89,12 @@ def _check(status: int, what: str, detail="") -> None:
     formatting a message costs a launch's worth of host time)."""
     global launches
     launches += 1
+    if callable(what):
+        what = what()
+    if trace is not None and status == 0:
+        event = torch.cuda.Event(enable_timing=True)
+        event.record()
+        trace.append((what, event))
     if status != 0:
         if callable(detail):
             detail = detail()
@@ -274,7 +285,8 @@ def gemm(c: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int = EPI_
                 _stream())
     else:
         raise KernelError(f"gemm: dtype {w.dtype} is not supported")
-    _check(status, "gemm", detail)
+    _check(status, (lambda: f"gemm {_EPILOGUE_NAMES[epilogue]} M={m} N={n} K={k}"
+                    + (" +norm" if norm_weight is not None else "")) if trace is not None else "gemm", detail)
 
 
 def gemm_qkv_rope_supported(cache, rotary_dim: int, has_table: bool) -> bool:
