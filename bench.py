@@ -410,7 +410,8 @@ def prefill_point(engine, vocab, warmup, repeats=5):
 
 def kernel_shares(engine, prompts, steps=3):
     """Where a decode step's time goes, kernel by kernel: the step run launch by launch (no graph) with a CUDA event
-    behind every launch; the share of each kind of launch in the sum."""
+    behind every launch; the share of each kind of launch in the sum, and its mean time (an event between two
+    kernels keeps the second from starting under the first's tail, so the sum is above the graph's step time)."""
     import torch
 
     from etalii.dllm_b200 import SamplingOptions
@@ -428,18 +429,23 @@ def kernel_shares(engine, prompts, steps=3):
     engine.decode_start(run, slots, tokens, steps + 2)
     run.replay(2)
     torch.cuda.synchronize()
-    ops.trace = []
-    first = torch.cuda.Event(enable_timing=True)
-    first.record()
-    run.replay(steps)
-    torch.cuda.synchronize()
-    events, ops.trace = ops.trace, None
+    totals, counts = {}, {}
+    for _ in range(steps):
+        # The stream is held busy first (a kernel that spins for about 10 ms) while the host issues the whole step
+        # with an event behind every launch; the step's kernels then run back to back, as in a graph, and the
+        # events are as far apart as the kernels take, not as the host needs to launch them.
+        torch.cuda._sleep(20_000_000)
+        ops.trace = []
+        before = torch.cuda.Event(enable_timing=True)
+        before.record()
+        run.replay(1)
+        torch.cuda.synchronize()
+        events, ops.trace = ops.trace, None
+        for name, event in events:
+            totals[name] = totals.get(name, 0.0) + before.elapsed_time(event)
+            counts[name] = counts.get(name, 0) + 1
+            before = event
     engine.close(slots)
-    totals, counts, before = {}, {}, first
-    for name, event in events:
-        totals[name] = totals.get(name, 0.0) + before.elapsed_time(event)
-        counts[name] = counts.get(name, 0) + 1
-        before = event
     whole = sum(totals.values())
     return {name: {"share": round(totals[name] / whole, 4), "launches_per_step": round(counts[name] / steps, 1),
                    "us": round(totals[name] / counts[name] * 1e3, 2)}

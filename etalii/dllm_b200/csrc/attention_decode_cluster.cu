@@ -112,7 +112,19 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attention_cluster_kernel(
   int my_first = base + ((int)rank * WARPS + warp) * TILE_KEYS;
   int page0 = 0;
   if (my_first < end) page0 = copy_page(my_first);
+  // The tile that holds the newest key belongs to one warp of the cluster. That warp asks for the row right after
+  // the wait, together with the queries, and puts it into its shared-memory page when the tile's turn comes: the
+  // round trip runs under the wait for the page instead of after it.
+  int newest_tile = (newest / TILE_KEYS) * TILE_KEYS;
+  bool owns_newest = newest_tile >= my_first && (newest_tile - my_first) % ROUND == 0;
+  uint4 newest_k = make_uint4(0u, 0u, 0u, 0u), newest_v = newest_k;
   pdl_wait();
+  if (owns_newest && lane < chunks16) {
+    int page = pages[newest / TILE_KEYS];
+    int r = newest - newest_tile;
+    newest_k = __ldcg(reinterpret_cast<const uint4*>((const bf16*)cache.base + kv_offset(cache, page, 0, g, r)) + lane);
+    newest_v = __ldcg(reinterpret_cast<const uint4*>((const bf16*)cache.base + kv_offset(cache, page, 1, g, r)) + lane);
+  }
 
   for (int h0 = 0; h0 < group; h0 += 16) {
     int nh = min(16, group - h0);
@@ -141,13 +153,11 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attention_cluster_kernel(
     for (int key0 = my_first; key0 < end; key0 += ROUND) {
       asm volatile("cp.async.wait_group 0;\n" ::);
       __syncwarp();
-      if (newest >= key0 && newest < key0 + TILE_KEYS) {  // the row the projection kernel has just written
+      if (key0 == newest_tile) {  // the row the projection kernel has just written (chunks16 <= 16 lanes hold it)
         int r = newest - key0;
-        const bf16* ksrc = (const bf16*)cache.base + kv_offset(cache, page, 0, g, r);
-        const bf16* vsrc = (const bf16*)cache.base + kv_offset(cache, page, 1, g, r);
-        for (int cc = lane; cc < chunks16; cc += 32) {
-          *reinterpret_cast<uint4*>(k_s + r * LD + cc * 8) = __ldcg(reinterpret_cast<const uint4*>(ksrc + cc * 8));
-          *reinterpret_cast<uint4*>(v_s + r * LD + cc * 8) = __ldcg(reinterpret_cast<const uint4*>(vsrc + cc * 8));
+        if (lane < chunks16) {
+          *reinterpret_cast<uint4*>(k_s + r * LD + lane * 8) = newest_k;
+          *reinterpret_cast<uint4*>(v_s + r * LD + lane * 8) = newest_v;
         }
         __syncwarp();
       }
@@ -256,24 +266,43 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attention_cluster_kernel(
       cta_o[h * HD + d] = o;
       if (d == 0) { cta_ml[h][0] = m; cta_ml[h][1] = l; }
     }
-    cluster_sync();  // every block's partial result is in its shared memory
-    // block `rank` finishes the heads h = rank, rank + 8: the blocks in rank order
-    for (int h = (int)rank; h < nh; h += CLUSTER) {
-      float m = -INFINITY;
-      for (unsigned r = 0; r < CLUSTER; ++r) m = fmaxf(m, remote_float(&cta_ml[h][0], r));
-      for (int d = threadIdx.x; d < hd; d += WARPS * 32) {
+    if (CLUSTER == 1) {
+      __syncthreads();
+      for (int idx = threadIdx.x; idx < nh * hd; idx += WARPS * 32) {
+        int h = idx / hd, d = idx % hd;
+        out[((size_t)b * heads + g * group + h0 + h) * hd + d] = __float2bfloat16_rn(cta_o[h * HD + d] / cta_ml[h][1]);
+      }
+    } else {
+      cluster_sync();  // every block's partial result is in its shared memory
+      // The outputs (head, dimension) are dealt out to the blocks of the cluster in equal runs; a thread asks for all
+      // blocks' values of its output before it touches the first (one round trip through distributed shared memory,
+      // not one per block), then sums in rank order.
+      int total = nh * hd, per = (total + CLUSTER - 1) / CLUSTER;
+      int stop = min(total, ((int)rank + 1) * per);
+      for (int idx = (int)rank * per + threadIdx.x; idx < stop; idx += WARPS * 32) {
+        int h = idx / hd, d = idx % hd;
+        float mr[CLUSTER], lr[CLUSTER], orr[CLUSTER];
+#pragma unroll
+        for (unsigned r = 0; r < CLUSTER; ++r) {
+          mr[r] = remote_float(&cta_ml[h][0], r);
+          lr[r] = remote_float(&cta_ml[h][1], r);
+          orr[r] = remote_float(&cta_o[h * HD + d], r);
+        }
+        float m = -INFINITY;
+#pragma unroll
+        for (unsigned r = 0; r < CLUSTER; ++r) m = fmaxf(m, mr[r]);
         float o = 0.f, l = 0.f;
 #pragma unroll
         for (unsigned r = 0; r < CLUSTER; ++r) {
-          float mr = remote_float(&cta_ml[h][0], r);
-          float f = mr == -INFINITY ? 0.f : fast_exp2(mr - m);
-          o = fmaf(remote_float(&cta_o[h * HD + d], r), f, o);
-          l = fmaf(remote_float(&cta_ml[h][1], r), f, l);
+          float f = mr[r] == -INFINITY ? 0.f : fast_exp2(mr[r] - m);
+          o = fmaf(orr[r], f, o);
+          l = fmaf(lr[r], f, l);
         }
         out[((size_t)b * heads + g * group + h0 + h) * hd + d] = __float2bfloat16_rn(o / l);
       }
     }
-    cluster_sync();  // nobody leaves (or reuses the space) while others still read its partial result
+    if (CLUSTER > 1) cluster_sync();  // nobody leaves (or reuses the space) while others still read its partial result
+    else __syncthreads();
   }
 }
 

@@ -29,6 +29,7 @@ struct RopeArgs {
   const int* tok_pos;
   const int* slots;
   int write_cache;
+  int prefetch_window;   // -1: no prefetch; 0: every page of the tokens' sequences; w > 0: the pages of the last w keys
 };
 
 // silu(g) = g * sigmoid(g), sigmoid as 1/(1+e^-g) for g >= 0 and e^g/(1+e^g) below, in float32; the product with

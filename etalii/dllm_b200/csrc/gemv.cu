@@ -33,6 +33,33 @@ __device__ __forceinline__ void prefetch_share(const Prefetch& pf) {
     asm volatile("prefetch.global.L2 [%0];" ::"l"(pf.ptr + line * 128));
 }
 
+// The q/k/v projection of a decode step asks L2 for the keys and values that the attention kernel behind it will
+// read: the pages of every sequence in the step (a page is one contiguous piece: keys and values of all kv heads).
+// They are nobody's output in this step (the step's own rows are written below and read through L2 anyway), so the
+// request goes out before the wait on the previous kernel and the pages travel from HBM while this kernel and the
+// launch of the next one run. A sequence's pages are dealt to warps in turn, a page's lines to the warp's lanes.
+__device__ __forceinline__ void prefetch_cache_pages(const RopeArgs& rope, int M) {
+  if (rope.prefetch_window < 0 || !rope.write_cache) return;
+  const KvLayout& c = rope.cache;
+  int lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  int all_warps = (int)gridDim.x * warps, me = (int)blockIdx.x * warps + (threadIdx.x >> 5);
+  int sharers = max(1, all_warps / M);  // warps that share one token's sequence; each takes every sharers-th page
+  if (me >= sharers * M) return;
+  int m = me % M, share = me / M;
+  int seq = rope.tok_seq[m];
+  if (m > 0 && rope.tok_seq[m - 1] == seq) return;  // (a sequence's first token in the step stands for it)
+  int pos = rope.tok_pos[m];
+  int first = (rope.prefetch_window > 0 && pos + 1 > rope.prefetch_window) ? pos + 1 - rope.prefetch_window : 0;
+  const int* pages = c.page_table + (size_t)rope.slots[seq] * c.max_pages;
+  int last_page = min(pos / c.page_size, c.max_pages - 1);
+  size_t page_bytes = (size_t)2 * c.kv_heads * c.page_size * c.head_dim * sizeof(bf16);
+  int lines = (int)((page_bytes + 127) / 128);
+  for (int j = first / c.page_size + share; j <= last_page; j += sharers) {
+    const char* at = (const char*)c.base + (size_t)pages[j] * page_bytes;
+    for (int line = lane; line < lines; line += 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(at + (size_t)line * 128));
+  }
+}
+
 __device__ __forceinline__ void mma_bf16(float* c, const unsigned* a, unsigned b0, unsigned b1) {
   asm volatile(
       "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
@@ -147,6 +174,7 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(void* __restrict__ c, 
     }
   };
   if (s_begin < s_end) load_weights(s_begin, wl, wh);
+  if (EPI == EPI_QKV_ROPE) prefetch_cache_pages(rope, M);
   bool waited = false;
   for (;;) {
     for (int s0 = s_begin; s0 < s_end; s0 += MAX_STEPS) {
@@ -420,17 +448,21 @@ DLLM_EXPORT int dllm_gemv_bf16(void* c, const void* a, const float* norm_w, floa
 // The q/k/v projection of a decode step in one kernel: optional RMSNorm in front, rotation of q and k by the
 // table's angle for each token's position, q to q_out, k and v into the token's place in the paged cache.
 // W is [(heads + 2 kv_heads) * head_dim, K]. head_dim and rotary_dim must be multiples of 16.
+// prefetch_window: -1, or which cached keys the attention behind this kernel will read (0: all, w: the last w), whose
+// pages this kernel then asks into L2.
 DLLM_EXPORT int dllm_gemv_qkv_rope(const void* a, const float* norm_w, float eps, const void* w, int M, int K,
                                    void* q_out, void* cache_base, const int* page_table, int max_pages, int page_size,
                                    int heads, int kv_heads, int head_dim, const float* table, int rotary_dim,
                                    const int* tok_seq, const int* tok_pos, const int* slots, int write_cache,
-                                   const void* prefetch_ptr, long long prefetch_bytes, cudaStream_t stream) {
+                                   int prefetch_window, const void* prefetch_ptr, long long prefetch_bytes,
+                                   cudaStream_t stream) {
   if (M <= 0) return DLLM_OK;
   if (M > 64 || K <= 0 || (K & 7) || heads <= 0 || kv_heads <= 0 || head_dim <= 0 || (head_dim & 15) ||
       rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 15))
     return DLLM_UNSUPPORTED_SIZE;
   RopeArgs rope{(bf16*)q_out, KvLayout{cache_base, page_table, max_pages, page_size, kv_heads, head_dim},
-                (const float2*)table, table ? rotary_dim : 0, heads, tok_seq, tok_pos, slots, write_cache};
+                (const float2*)table, table ? rotary_dim : 0, heads, tok_seq, tok_pos, slots, write_cache,
+                prefetch_window};
   int N = (heads + 2 * kv_heads) * head_dim;
   Prefetch pf{(const char*)prefetch_ptr, prefetch_ptr ? (size_t)prefetch_bytes : 0};
   return norm_w ? dispatch<true>(nullptr, a, norm_w, eps, (const bf16*)w, M, N, K, EPI_QKV_ROPE, rope, pf, stream)

@@ -39,10 +39,12 @@ _prototypes = {
                                                      c_void_p, c_void_p, c_int, c_void_p, c_void_p],
     ("gemv", "dllm_gemv_bf16"): [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int,
                                  c_void_p, c_longlong, c_void_p],
+    ("mlp_decode", "dllm_mlp_decode"): [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
+                                        c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p],
     ("gemv_tma", "dllm_gemv_tma"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     ("gemv", "dllm_gemv_qkv_rope"): [c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_void_p, c_void_p,
                                      c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p,
-                                     c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_void_p],
+                                     c_void_p, c_void_p, c_int, c_int, c_void_p, c_longlong, c_void_p],
     ("attention", "dllm_attention_general"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                               c_int, c_void_p, c_void_p, c_void_p, c_int, c_float, c_int, c_int,
                                               c_void_p],
@@ -289,6 +291,48 @@ def gemm(c: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int = EPI_
                     + (" +norm" if norm_weight is not None else "")) if trace is not None else "gemm", detail)
 
 
+MLP_DECODE_MAX_ROWS = 16
+FUSED_FEED_FORWARD = False
+"""Whether decode steps take the one-kernel feed-forward (`mlp_decode`) where it fits. Off: measured on a B200 at the
+SmolLM2-135M layer sizes with 8 tokens, as one link of a chain of dependent launches in a CUDA graph, the fused kernel
+takes 7.4 us against 4.7 us for the two kernels it replaces. Its gate/up part costs 2.65 us, the exchange inside the
+cluster 0.6 us, the down product 0.8 us, and the fixed-order sum of the clusters' partial results through global
+memory (fence, ticket, fence, loads) 3.3 us: more than the second launch it saves. The kernel stays as a tested
+option."""
+
+
+def mlp_decode_supported(rows: int, hidden: int, intermediate: int) -> bool:
+    """Whether the feed-forward of a decode step may run as one kernel: up to 16 tokens and an intermediate size
+    that slices of 16 tile."""
+    return 0 < rows <= MLP_DECODE_MAX_ROWS and intermediate % 16 == 0 and hidden % 8 == 0
+
+
+def mlp_decode_scratch(rows: int, hidden: int, intermediate: int) -> int:
+    """Floats of scratch `mlp_decode` needs: a partial result [8 or 16 tokens, hidden] per cluster of blocks."""
+    cluster = next(c for c in (8, 4, 2, 1) if intermediate % (16 * c) == 0)
+    return (intermediate // (16 * cluster)) * (8 if rows <= 8 else 16) * hidden
+
+
+def mlp_decode(x: torch.Tensor, norm_weight: torch.Tensor, eps: float, w_gate_up: torch.Tensor, w_down: torch.Tensor,
+               scratch: torch.Tensor, tickets: torch.Tensor) -> None:
+    """x (float32 residual [rows, hidden]) += down(silu(gate(h)) * up(h)), h = RMSNorm(x) rounded to bfloat16, in one
+    kernel. w_gate_up [2 * intermediate, hidden] interleaves gate and up rows; w_down is [hidden, intermediate].
+    `scratch`: `mlp_decode_scratch` floats; `tickets`: 8 int32 zeros (the kernel leaves them zero)."""
+    _cuda(x, norm_weight, w_gate_up, w_down, scratch, tickets)
+    rows, hidden = x.shape
+    intermediate = w_down.shape[1]
+    assert x.dtype == torch.float32 and norm_weight.dtype == torch.float32 and norm_weight.numel() == hidden
+    assert w_gate_up.dtype == torch.bfloat16 and w_down.dtype == torch.bfloat16
+    assert tuple(w_gate_up.shape) == (2 * intermediate, hidden) and w_down.shape[0] == hidden
+    assert scratch.dtype == torch.float32 and scratch.numel() >= mlp_decode_scratch(rows, hidden, intermediate)
+    assert tickets.dtype == torch.int32 and tickets.numel() >= 8
+    _check(_fn("mlp_decode", "dllm_mlp_decode")(
+        x.data_ptr(), norm_weight.data_ptr(), float(eps), w_gate_up.data_ptr(), w_down.data_ptr(), rows, hidden,
+        intermediate, scratch.data_ptr(), tickets.data_ptr(), *_prefetch_of(w_gate_up), *_prefetch_of(w_down),
+        _stream()), "mlp_decode",
+        lambda: f"rows={rows} (at most 16), hidden={hidden} (multiple of 8), intermediate={intermediate} (multiple of 16)")
+
+
 def gemm_qkv_rope_supported(cache, rotary_dim: int, has_table: bool) -> bool:
     """Whether the tile kernel can end in the rotation and cache write: one head per tile, full rotation."""
     return cache.dtype == torch.bfloat16 and cache.head_dim in (32, 64, 128) and \
@@ -317,9 +361,11 @@ def gemm_qkv_rope(a: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, cache, 
 
 def gemv_qkv_rope(a: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, cache, table: torch.Tensor | None,
                   rotary_dim: int, heads: int, batch, write_cache: bool = True,
-                  norm_weight: torch.Tensor | None = None, eps: float = 0.0) -> None:
-    """The q/k/v projection of at most 16 tokens in one kernel (bfloat16): optional RMSNorm of the float32 residual
-    in front, rotation of q and k, q to q_out, k and v into the paged cache."""
+                  norm_weight: torch.Tensor | None = None, eps: float = 0.0, prefetch_window: int = -1) -> None:
+    """The q/k/v projection of at most 64 tokens in one kernel (bfloat16): optional RMSNorm of the float32 residual
+    in front, rotation of q and k, q to q_out, k and v into the paged cache. With `prefetch_window` >= 0 the kernel
+    also asks L2 for the cached keys and values of the tokens' sequences (0: all of them, w: the last w), which the
+    attention kernel behind it reads."""
     _cuda(a, w, q_out, table, norm_weight)
     m, k = batch.n_tokens, a.shape[1]
     assert w.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16 and q_out.dtype == torch.bfloat16
@@ -333,7 +379,7 @@ def gemv_qkv_rope(a: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, cache, 
         q_out.data_ptr(), cache.base_ptr, cache.page_table.data_ptr(), cache.max_pages, cache.page_size, heads,
         cache.kv_heads, cache.head_dim, table.data_ptr() if table is not None else None,
         rotary_dim if table is not None else 0, batch.tok_seq.data_ptr(), batch.tok_pos.data_ptr(),
-        batch.slots.data_ptr(), 1 if write_cache else 0, *_prefetch_of(w), _stream()),
+        batch.slots.data_ptr(), 1 if write_cache else 0, int(prefetch_window), *_prefetch_of(w), _stream()),
         "gemv_qkv_rope", lambda: f"M={m} (at most 64), K={k} (multiple of 8), head_dim and rotary_dim multiples of 16")
 
 

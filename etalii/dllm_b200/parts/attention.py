@@ -83,8 +83,11 @@ class Attention:
             if isinstance(h, NormedInput) and not fuses_norm(self.w_qkv):
                 h = h.tensor()
             pending = isinstance(h, NormedInput)
+            # (in a decode step of few sequences, where latency and not bandwidth bounds the attention kernel, it also
+            # asks L2 for the keys and values that kernel is about to read)
             ops.gemv_qkv_rope(h.x if pending else h, self.w_qkv, q, cache, table, rotary_dim, self.num_heads, batch,
-                              write_cache, norm_weight=h.weight if pending else None, eps=h.eps if pending else 0.0)
+                              write_cache, norm_weight=h.weight if pending else None, eps=h.eps if pending else 0.0,
+                              prefetch_window=(self.window or 0) if batch.is_decode and n <= 16 else -1)
         elif rt.dtype == torch.bfloat16 and ops.gemm_qkv_rope_supported(cache, rotary_dim, table is not None):
             # prefill-sized: the tile product ends in rotation and cache write
             hidden = h.tensor() if isinstance(h, NormedInput) else h

@@ -7,7 +7,7 @@ from __future__ import annotations
 import torch
 
 from ..kernels import ops
-from .norm import project, row_rule
+from .norm import NormedInput, project, row_rule
 from .registry import register_part
 from .spec import ParamSpec
 
@@ -34,6 +34,15 @@ class SwiGLU:
         self.w_down = rt.to_device(tensors["down"], rt.dtype)
 
     def forward(self, h: torch.Tensor, residual: torch.Tensor, batch, rt) -> None:
+        rows = h.shape[0]
+        if ops.FUSED_FEED_FORWARD and isinstance(h, NormedInput) and h.x is residual and \
+                rt.dtype == torch.bfloat16 and ops.mlp_decode_supported(rows, self.hidden_size, self.intermediate_size):
+            # (an option, off by default: norm, gate/up, SwiGLU, down and the residual sum in one kernel)
+            scratch = rt.ws.buffer("mlp_partial", (ops.mlp_decode_scratch(rows, self.hidden_size,
+                                                                          self.intermediate_size),), torch.float32)
+            ops.mlp_decode(residual, h.weight, h.eps, self.w_gate_up, self.w_down, scratch,
+                           rt.ws.zeros("mlp_tickets", 8, torch.int32))
+            return
         act = rt.ws.buffer("ffn_act", (h.shape[0], self.intermediate_size), rt.dtype)
         project(act, h, self.w_gate_up, ops.EPI_SWIGLU)
         ops.gemm(residual, act, self.w_down, ops.EPI_RESIDUAL)
@@ -43,6 +52,8 @@ class SwiGLU:
         if rt.dtype != torch.bfloat16:
             return {"gemm_simt"}
         names = {"gemv", "gemm_tcgen05"}
+        if ops.FUSED_FEED_FORWARD and ops.mlp_decode_supported(1, self.hidden_size, self.intermediate_size):
+            names.add("mlp_decode")
         if any(ops.streams_through_shared_memory(1, w.shape[0], w.shape[1]) for w in (self.w_gate_up, self.w_down)):
             names.add("gemv_tma")
         return names

@@ -43,6 +43,19 @@ def gemm(c, a, w, epilogue=EPI_STORE_T, kernel=0, norm_weight=None, eps=0.0):
         c.copy_(prod.to(c.dtype))
 
 
+def mlp_decode_supported(rows, hidden, intermediate):
+    return False
+
+
+def mlp_decode(x, norm_weight, eps, w_gate_up, w_down, scratch=None, tickets=None):
+    """x += down(silu(gate(h)) * up(h)) with h = RMSNorm(x): in float64 from the inputs, rounded once."""
+    xd = x.double()
+    h = xd / torch.sqrt((xd * xd).mean(dim=-1, keepdim=True) + eps) * norm_weight.double()
+    prod = h @ w_gate_up.double().T
+    gate, up = prod[:, 0::2], prod[:, 1::2]
+    x.copy_((xd + (gate * torch.sigmoid(gate) * up) @ w_down.double().T).float())
+
+
 def _kv(cache):
     return cache.storage  # [pages, 2, kv_heads, page_size, head_dim]
 
@@ -141,7 +154,8 @@ def decode_advance(tokens, tok_pos, start, chosen, history, counter, batch):
     counter[0] = row + 1
 
 
-def gemv_qkv_rope(a, w, q_out, cache, table, rotary_dim, heads, batch, write_cache=True, norm_weight=None, eps=0.0):
+def gemv_qkv_rope(a, w, q_out, cache, table, rotary_dim, heads, batch, write_cache=True, norm_weight=None, eps=0.0,
+                  prefetch_window=-1):
     n = batch.n_tokens
     qkv = torch.empty((n, w.shape[0]), dtype=torch.float32, device=a.device)
     gemm(qkv, a[:n], w, EPI_STORE_F32, norm_weight=norm_weight, eps=eps)

@@ -476,3 +476,29 @@ def test_sampled_batches_that_grow_and_shrink_keep_their_graphs_valid(name):
         run(count, sampled, lambda i: 5 + i)
     assert engine.cache.slots.held == 0
     engine.cache.check()
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_the_one_kernel_feed_forward_as_an_engine_option(name):
+    """`ops.FUSED_FEED_FORWARD` (off by default: it measured slower than the two kernels it replaces) switches decode
+    steps to the fused feed-forward kernel; the engine's logits then still agree with the plain implementation."""
+    from etalii.dllm_b200.kernels import ops
+
+    config, weights = model_case(name.lower())
+    plain = PlainLogits(config, weights)
+    prompts = prompts_for(config, (9, 20, 3), seed=51)
+    ops.FUSED_FEED_FORWARD = True
+    try:
+        engine = make_engine(config, weights, "bfloat16", max_tokens=64 * 6)
+        slots = engine.open(3)
+        engine.step(slots, [p[:-2] for p in prompts], [[], [], []])
+        before = ops.launches
+        for back in (2, 1):
+            got = host(engine.step(slots, [[p[-back]] for p in prompts]))
+            for i, p in enumerate(prompts):
+                assert rel_error(got[i], plain(p)[len(p) - back]) <= TOL["bfloat16"]
+        per_step = (ops.launches - before) // 2
+        engine.close(slots)
+    finally:
+        ops.FUSED_FEED_FORWARD = False
+    assert per_step == 3 + 4 * config["num_hidden_layers"]  # embed, head, norm-free: four launches a layer, not five

@@ -526,7 +526,9 @@ def _check_gemv_qkv_rope(heads, kv_heads, head_dim, rotary, normed, rows_extra, 
     nw = _randn((k,), torch.float32, 8) * 0.1 + 1
     q = torch.zeros((n, heads * head_dim), dtype=torch.bfloat16, device=DEV)
     before = view.storage.clone()
-    ops().gemv_qkv_rope(x, w, q, view, table, rotary, heads, batch, True, norm_weight=nw if normed else None,
+    # (with the request for the sequences' cached pages into L2, as decode steps make it: a hint, no result changes)
+    ops().gemv_qkv_rope(x, w, q, view, table, rotary, heads, batch, True, prefetch_window=0 if normed else 40,
+                        norm_weight=nw if normed else None,
                         eps=1e-6)
     h = x.double()
     if normed:
@@ -805,3 +807,39 @@ def test_a_bounded_wait_that_runs_out_is_reported_and_hangs_nothing():
     # the context is as usable as before
     x = torch.arange(8, device=DEV, dtype=torch.float32)
     assert float((x * 2).sum()) == 56.0
+
+
+@pytest.mark.parametrize("m,hidden,inter", [(1, 64, 160), (8, 576, 1536), (3, 144, 384), (16, 40, 48), (12, 72, 208),
+                                            (5, 2048, 1024), (9, 576, 1536), (8, 104, 16)])
+def test_mlp_decode_fused_feed_forward(m, hidden, inter):
+    """The one-kernel feed-forward of decode steps against the plain computation (float64 from the same inputs) and
+    against the two separate kernels it replaces; a repeated launch gives the same bits (the clusters' partial sums
+    are added in a fixed order) and the tickets are left at zero."""
+    x0 = _randn((m, hidden), torch.float32, 1, 2.0)
+    norm_w = _randn((hidden,), torch.float32, 2, 0.1) + 1
+    w_gu = _randn((2 * inter, hidden), torch.bfloat16, 3, 0.08)
+    w_d = _randn((hidden, inter), torch.bfloat16, 4, 0.08)
+    eps = 1e-5
+    scratch = torch.full((ops().mlp_decode_scratch(m, hidden, inter),), float("nan"), dtype=torch.float32, device=DEV)
+    tickets = torch.zeros(8, dtype=torch.int32, device=DEV)
+    want = x0.clone()
+    PK.mlp_decode(want, norm_w, eps, w_gu, w_d)
+    got = x0.clone()
+    ops().mlp_decode(got, norm_w, eps, w_gu, w_d, scratch, tickets)
+    update = (want - x0).abs().max().item()
+    assert (got - want).abs().max().item() <= 1.5e-2 * update
+    assert int(tickets.abs().sum()) == 0
+    again = x0.clone()
+    ops().mlp_decode(again, norm_w, eps, w_gu, w_d, scratch, tickets)
+    assert torch.equal(again, got)
+    # the two kernels it replaces: the same roundings (normed input and activations in bfloat16), other sum orders
+    act = torch.empty((m, inter), dtype=torch.bfloat16, device=DEV)
+    ops().gemm(act, x0, w_gu, ops().EPI_SWIGLU, norm_weight=norm_w, eps=eps, kernel=2)
+    two = x0.clone()
+    ops().gemm(two, act, w_d, ops().EPI_RESIDUAL, kernel=2)
+    assert (got - two).abs().max().item() <= 4e-3 * update
+    # a row's result does not depend on its batch mates
+    if m > 1:
+        alone = x0[m - 1:].clone()
+        ops().mlp_decode(alone, norm_w, eps, w_gu, w_d, scratch, tickets)
+        assert torch.equal(alone[0], got[m - 1])
