@@ -487,18 +487,20 @@ def test_the_one_kernel_feed_forward_as_an_engine_option(name):
     config, weights = model_case(name.lower())
     plain = PlainLogits(config, weights)
     prompts = prompts_for(config, (9, 20, 3), seed=51)
-    ops.FUSED_FEED_FORWARD = True
-    try:
-        engine = make_engine(config, weights, "bfloat16", max_tokens=64 * 6)
-        slots = engine.open(3)
-        engine.step(slots, [p[:-2] for p in prompts], [[], [], []])
-        before = ops.launches
-        for back in (2, 1):
-            got = host(engine.step(slots, [[p[-back]] for p in prompts]))
-            for i, p in enumerate(prompts):
-                assert rel_error(got[i], plain(p)[len(p) - back]) <= TOL["bfloat16"]
-        per_step = (ops.launches - before) // 2
-        engine.close(slots)
-    finally:
-        ops.FUSED_FEED_FORWARD = False
-    assert per_step == 3 + 4 * config["num_hidden_layers"]  # embed, head, norm-free: four launches a layer, not five
+    launches = {}
+    for fused in (True, False):
+        ops.FUSED_FEED_FORWARD = fused
+        try:
+            engine = make_engine(config, weights, "bfloat16", max_tokens=64 * 6)
+            slots = engine.open(3)
+            engine.step(slots, [p[:-2] for p in prompts], [[], [], []])
+            before = ops.launches
+            for back in (2, 1):
+                got = host(engine.step(slots, [[p[-back]] for p in prompts]))
+                for i, p in enumerate(prompts):
+                    assert rel_error(got[i], plain(p)[len(p) - back]) <= TOL["bfloat16"]
+            launches[fused] = (ops.launches - before) // 2
+            engine.close(slots)
+        finally:
+            ops.FUSED_FEED_FORWARD = False
+    assert launches[False] - launches[True] == config["num_hidden_layers"]  # one launch fewer a layer
