@@ -94,6 +94,181 @@ __global__ void __launch_bounds__(WARPS * 32) attention_warp_kernel(
     if (d < hd) orow[d] = from_float<T>(acc[i] * inv);
   }
 }
+
+// ---- the same attention, blockwise ------------------------------------------------------------------------------
+// A block serves one kv head and a run of consecutive tokens of the step; its warps are the (token, query head)
+// pairs of that run, R tokens a warp. The block copies the keys and values of the kv head page by page (64
+// positions) into shared memory, with the next page on its way (cp.async) while the warps work on this one, and
+// every warp walks the page's two tiles of 32 keys exactly as the kernel above walks its tiles: one key a lane for
+// the scores, one value dimension a lane for the weighted sum, the same running maximum and sum in the same order.
+// Tiles start at multiples of 32 from position 0, so without a window a (token, head) result has the same bits as
+// the kernel above gives (with a window the first tile is cut differently: same formula, other rounding), and it
+// depends only on the token's own query and visible keys: not on its tile mates, the cut of the steps or the batch.
+// Tokens of several sequences in one block are served sequence by sequence.
+template <typename T> struct Pad { static constexpr int N = 16 / sizeof(T); };  // 16 bytes: rows in different banks
+
+template <typename T>
+__device__ __forceinline__ void stage_page(T* k_s, T* v_s, const KvLayout& cache, int page, int g, int hd, int ld,
+                                           int tid, int threads) {
+  const T* ksrc = (const T*)cache.base + kv_offset(cache, page, 0, g, 0);
+  const T* vsrc = (const T*)cache.base + kv_offset(cache, page, 1, g, 0);
+  constexpr int VN = Vec<T>::N;
+  int pieces = hd / VN;  // 16-byte pieces of a row
+  for (int i = tid; i < 64 * pieces; i += threads) {
+    int r = i / pieces, c = (i % pieces) * VN;
+    unsigned kd = (unsigned)__cvta_generic_to_shared(k_s + r * ld + c);
+    unsigned vd = (unsigned)__cvta_generic_to_shared(v_s + r * ld + c);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(kd), "l"(ksrc + (size_t)r * hd + c));
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(vd), "l"(vsrc + (size_t)r * hd + c));
+  }
+  asm volatile("cp.async.commit_group;\n" ::);
+}
+
+template <typename T, int R>
+__global__ void __launch_bounds__(512) attention_block_kernel(
+    T* __restrict__ out, const T* __restrict__ q, KvLayout cache, const int* __restrict__ tok_seq,
+    const int* __restrict__ tok_pos, const int* __restrict__ slots, int tokens, int heads, float scale, int window,
+    int heads_per_pass, int stages) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  int hd = cache.head_dim, ld = hd + Pad<T>::N;
+  int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  int token_slots = warps / heads_per_pass;       // warps = token_slots * heads_per_pass
+  int block_tokens = token_slots * R;
+  int slot_of_warp = warp / heads_per_pass, head_of_warp = warp % heads_per_pass;
+  T* kv_s = reinterpret_cast<T*>(smem_raw);       // [stages][k|v][64][ld]
+  float* q_s = reinterpret_cast<float*>(smem_raw + (size_t)stages * 2 * 64 * ld * sizeof(T)) + (size_t)warp * R * hd;
+  int g = blockIdx.y, group = heads / cache.kv_heads;
+  int t0 = blockIdx.x * block_tokens, t_stop = min(tokens, t0 + block_tokens);
+
+  for (int pass = 0; pass < group; pass += heads_per_pass) {
+    int h = g * group + pass + head_of_warp;
+    bool head_ok = pass + head_of_warp < group;
+    for (int run_begin = t0; run_begin < t_stop;) {
+      // a run: the block's tokens of one sequence (positions ascend inside it)
+      int seq = tok_seq[run_begin], run_end = run_begin + 1;
+      while (run_end < t_stop && tok_seq[run_end] == seq) ++run_end;
+      const int* pages = cache.page_table + (size_t)slots[seq] * cache.max_pages;
+      int run_last = tok_pos[run_end - 1] + 1;   // keys [run_first, run_last) are read by somebody of the run
+      int first_end = tok_pos[run_begin] + 1;
+      int run_first = (window > 0 && first_end > window) ? first_end - window : 0;
+
+      // this warp's tokens of the run
+      int end[R], first[R];
+      float m_run[R], l_run[R], acc[R][MAX_HEAD_DIM / 32];
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        int t = t0 + slot_of_warp * R + r;
+        bool mine = head_ok && t >= run_begin && t < run_end;
+        end[r] = mine ? tok_pos[t] + 1 : 0;
+        first[r] = (window > 0 && end[r] > window) ? end[r] - window : 0;
+        m_run[r] = -INFINITY;
+        l_run[r] = 0.f;
+#pragma unroll
+        for (int i = 0; i < MAX_HEAD_DIM / 32; ++i) acc[r][i] = 0.f;
+        if (mine) {
+          const T* qrow = q + ((size_t)t * heads + h) * hd;
+          for (int d = lane; d < hd; d += 32) q_s[r * hd + d] = to_float(qrow[d]);
+        }
+      }
+      __syncwarp();
+
+      int page_first = run_first / 64, page_last = (run_last - 1) / 64;
+      __syncthreads();  // (the stages may still be read by a warp that is behind in the run before)
+      stage_page(kv_s, kv_s + 64 * ld, cache, pages[page_first], g, hd, ld, threadIdx.x, blockDim.x);
+      for (int p = page_first; p <= page_last; ++p) {
+        int stage = stages == 2 ? ((p - page_first) & 1) : 0;
+        T* k_s = kv_s + (size_t)stage * 2 * 64 * ld;
+        T* v_s = k_s + 64 * ld;
+        if (stages == 2 && p < page_last) {
+          T* next = kv_s + (size_t)(stage ^ 1) * 2 * 64 * ld;
+          stage_page(next, next + 64 * ld, cache, pages[p + 1], g, hd, ld, threadIdx.x, blockDim.x);
+          asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+        } else {
+          asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        }
+        __syncthreads();
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          for (int j0 = p * 64; j0 < p * 64 + 64; j0 += 32) {
+            if (j0 >= end[r] || j0 + 32 <= first[r]) continue;  // (warp-uniform) no visible key in this tile
+            int j = j0 + lane;
+            bool valid = j >= first[r] && j < end[r];
+            float s = -INFINITY;
+            if (valid) {
+              const T* krow = k_s + (j - p * 64) * ld;
+              float dot = 0.f;
+              for (int d = 0; d < hd; d += Vec<T>::N) dot += dot_vec(&q_s[r * hd + d], krow + d);
+              s = dot * scale;
+            }
+            float m_new = fmaxf(m_run[r], warp_max(s));
+            float pr = valid ? expf(s - m_new) : 0.f;
+            float corr = expf(m_run[r] - m_new);  // 0 on the first tile (m_run = -inf)
+            l_run[r] = l_run[r] * corr + warp_sum(pr);
+#pragma unroll
+            for (int i = 0; i < MAX_HEAD_DIM / 32; ++i) acc[r][i] *= corr;
+            m_run[r] = m_new;
+            int from = max(0, first[r] - j0), to = min(32, end[r] - j0);
+            for (int jj = from; jj < to; ++jj) {
+              float pj = __shfl_sync(0xffffffffu, pr, jj);
+              const T* vrow = v_s + (j0 + jj - p * 64) * ld;
+#pragma unroll
+              for (int i = 0; i < MAX_HEAD_DIM / 32; ++i) {
+                int d = lane + 32 * i;
+                if (d < hd) acc[r][i] = fmaf(pj, to_float(vrow[d]), acc[r][i]);
+              }
+            }
+          }
+        }
+        if (stages != 2) {
+          __syncthreads();  // one stage: it is free only when every warp is done with it
+          if (p < page_last) stage_page(kv_s, kv_s + 64 * ld, cache, pages[p + 1], g, hd, ld, threadIdx.x, blockDim.x);
+        } else {
+          __syncthreads();  // the stage read now is the one the copy after next writes
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        int t = t0 + slot_of_warp * R + r;
+        if (head_ok && t >= run_begin && t < run_end) {
+          float inv = 1.0f / l_run[r];
+          T* orow = out + ((size_t)t * heads + h) * hd;
+#pragma unroll
+          for (int i = 0; i < MAX_HEAD_DIM / 32; ++i) {
+            int d = lane + 32 * i;
+            if (d < hd) orow[d] = from_float<T>(acc[r][i] * inv);
+          }
+        }
+      }
+      run_begin = run_end;
+    }
+  }
+}
+
+template <typename T, int R>
+int launch_blocks(void* out, const void* q, const KvLayout& cache, const int* tok_seq, const int* tok_pos,
+                  const int* slots, int tokens, int heads, float scale, int window, cudaStream_t stream) {
+  int group = heads / cache.kv_heads;
+  int heads_per_pass = group < 16 ? group : 16;
+  int token_slots = R == 1 ? 1 : (16 / heads_per_pass > 0 ? 16 / heads_per_pass : 1);
+  int warps = token_slots * heads_per_pass;
+  int ld = cache.head_dim + Pad<T>::N;
+  size_t stage_bytes = (size_t)2 * 64 * ld * sizeof(T), q_bytes = (size_t)warps * R * cache.head_dim * sizeof(float);
+  int stages = 2 * stage_bytes + q_bytes <= 200 * 1024 ? 2 : 1;
+  size_t smem = stages * stage_bytes + q_bytes;
+  static size_t configured = 0;
+  if (smem > configured) {
+    if (cudaFuncSetAttribute(attention_block_kernel<T, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+        cudaSuccess)
+      return DLLM_LAUNCH_FAILED;
+    configured = smem;
+  }
+  int block_tokens = token_slots * R;
+  dim3 grid((tokens + block_tokens - 1) / block_tokens, cache.kv_heads);
+  attention_block_kernel<T, R><<<grid, warps * 32, smem, stream>>>((T*)out, (const T*)q, cache, tok_seq, tok_pos,
+                                                                  slots, tokens, heads, scale, window,
+                                                                  heads_per_pass, stages);
+  return dllm_launch_status();
+}
 }  // namespace
 
 DLLM_EXPORT int dllm_attention_general(void* out, const void* q, void* cache_base, const int* page_table,
@@ -115,4 +290,28 @@ DLLM_EXPORT int dllm_attention_general(void* out, const void* q, void* cache_bas
   else
     return DLLM_BAD_ARGUMENT;
   return dllm_launch_status();
+}
+
+// The same attention with the same arguments, blockwise (see attention_block_kernel). `max_new`: the most new
+// tokens a sequence brings in this step: with one each (decoding) a block serves one token's heads, else runs of
+// tokens with two tokens a warp. Pages of 64 positions, at most 65,535 kv heads.
+DLLM_EXPORT int dllm_attention_blocks(void* out, const void* q, void* cache_base, const int* page_table,
+                                      int max_pages, int page_size, int heads, int kv_heads, int head_dim,
+                                      const int* tok_seq, const int* tok_pos, const int* slots, int tokens,
+                                      int max_new, float scale, int window, int dtype, cudaStream_t stream) {
+  if (tokens <= 0) return DLLM_OK;
+  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads) return DLLM_BAD_ARGUMENT;
+  if (head_dim <= 0 || head_dim > MAX_HEAD_DIM || (head_dim & 7) || page_size != 64 || kv_heads > 65535)
+    return DLLM_UNSUPPORTED_SIZE;
+  KvLayout cache{cache_base, page_table, max_pages, page_size, kv_heads, head_dim};
+  bool runs = max_new > 1;
+  if (dtype == DLLM_F32)
+    return runs ? launch_blocks<float, 2>(out, q, cache, tok_seq, tok_pos, slots, tokens, heads, scale, window, stream)
+                : launch_blocks<float, 1>(out, q, cache, tok_seq, tok_pos, slots, tokens, heads, scale, window, stream);
+  if (dtype == DLLM_BF16)
+    return runs ? launch_blocks<__nv_bfloat16, 2>(out, q, cache, tok_seq, tok_pos, slots, tokens, heads, scale,
+                                                  window, stream)
+                : launch_blocks<__nv_bfloat16, 1>(out, q, cache, tok_seq, tok_pos, slots, tokens, heads, scale,
+                                                  window, stream);
+  return DLLM_BAD_ARGUMENT;
 }

@@ -48,6 +48,9 @@ _prototypes = {
     ("attention", "dllm_attention_general"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                               c_int, c_void_p, c_void_p, c_void_p, c_int, c_float, c_int, c_int,
                                               c_void_p],
+    ("attention", "dllm_attention_blocks"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                             c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int,
+                                             c_void_p],
     ("attention_decode", "dllm_attention_decode"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                                     c_int, c_void_p, c_void_p, c_int, c_float, c_int, c_int, c_int,
                                                     c_void_p, c_void_p, c_void_p],
@@ -412,6 +415,25 @@ def attention_general(out: torch.Tensor, q: torch.Tensor, cache, heads: int, sca
         heads, cache.kv_heads, cache.head_dim, batch.tok_seq.data_ptr(), batch.tok_pos.data_ptr(),
         batch.slots.data_ptr(), batch.n_tokens, float(scale), int(window or 0), _code(cache.dtype), _stream()),
         "attention", lambda: f"head_dim={cache.head_dim} must be a multiple of 8, at most 256")
+
+
+def attention_blocks_supported(cache) -> bool:
+    return cache.page_size == 64 and cache.head_dim % 8 == 0 and cache.head_dim <= 256
+
+
+def attention_blocks(out: torch.Tensor, q: torch.Tensor, cache, heads: int, scale: float, window: int, batch) -> None:
+    """`attention_general` blockwise: the keys and values of a kv head go through shared memory page by page and
+    serve every (token, head) pair of a run of tokens at once. Without a window a pair's result has the same bits
+    as `attention_general` gives; with one the same formula is rounded in other places. The float32 path's attention,
+    for whole prompts and single tokens alike."""
+    _cuda(out, q)
+    assert q.dtype == cache.dtype and out.dtype == cache.dtype and attention_blocks_supported(cache)
+    _check(_fn("attention", "dllm_attention_blocks")(
+        out.data_ptr(), q.data_ptr(), cache.base_ptr, cache.page_table.data_ptr(), cache.max_pages, cache.page_size,
+        heads, cache.kv_heads, cache.head_dim, batch.tok_seq.data_ptr(), batch.tok_pos.data_ptr(),
+        batch.slots.data_ptr(), batch.n_tokens, int(batch.max_new), float(scale), int(window or 0),
+        _code(cache.dtype), _stream()), "attention_blocks",
+        lambda: f"head_dim={cache.head_dim} must be a multiple of 8, at most 256; pages of 64")
 
 
 def add_residual(residual: torch.Tensor, update: torch.Tensor) -> None:

@@ -111,6 +111,9 @@ class Attention:
             ops.attention_prefill_tcgen05(attended, q, cache, self.num_heads, self.scale, self.window or 0, batch)
         elif not batch.is_decode and ops.attention_prefill_supported(cache):
             ops.attention_prefill(attended, q, cache, self.num_heads, self.scale, self.window or 0, batch)
+        elif ops.attention_blocks_supported(cache):
+            # the float32 path, and bfloat16 heads the tensor-core kernels do not take: one kernel for every cut
+            ops.attention_blocks(attended, q, cache, self.num_heads, self.scale, self.window or 0, batch)
         else:
             ops.attention_general(attended, q, cache, self.num_heads, self.scale, self.window or 0, batch)
         ops.gemm(residual, attended, self.w_o, ops.EPI_RESIDUAL)

@@ -197,6 +197,14 @@ def attention_prefill_tcgen05_supported(cache):
     return False
 
 
+def attention_blocks_supported(cache):
+    return True
+
+
+def attention_blocks(out, q, cache, heads, scale, window, batch):
+    attention_general(out, q, cache, heads, scale, window, batch)
+
+
 def attention_decode_cluster_supported(cache):
     return False
 

@@ -251,6 +251,44 @@ def test_attention_general(dtype, tol, heads, kv_heads, head_dim, window):
     assert rel_error(out.float().cpu(), ref.float()) <= tol
 
 
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 5e-6), (torch.bfloat16, 8e-3)])
+@pytest.mark.parametrize("heads,kv_heads,head_dim,window", [(4, 2, 16, None), (6, 3, 24, None), (9, 3, 64, None),
+                                                           (8, 1, 128, 70), (5, 5, 40, 33), (40, 2, 8, None),
+                                                           (2, 1, 256, None), (34, 2, 16, 100)])
+@pytest.mark.parametrize("decode", [False, True])
+def test_attention_blocks(dtype, tol, heads, kv_heads, head_dim, window, decode):
+    """The blockwise kernel against the plain attention, and against the warp-per-pair kernel: the same bits where
+    there is no window (the tiles of 32 keys are then the same ones), tokens of several sequences in one block,
+    whole prompts and single tokens, one and two stages of shared memory, groups of more than sixteen heads."""
+    lengths = [130, 67, 1, 200, 64, 65]
+    new = [1] * 6 if decode else [130, 1, 1, 9, 3, 65]
+    cache, view, batch = _cache_and_batch(dtype, kv_heads, head_dim, lengths, new, window)
+    n = batch.n_tokens
+    q = _randn((n, heads * head_dim), dtype, 9)
+    out = torch.full((n, heads * head_dim), float("nan"), dtype=dtype, device=DEV)
+    ops().attention_blocks(out, q, view, heads, 0.3, window or 0, batch)
+    ref = torch.zeros((n, heads * head_dim), dtype=dtype)
+    view_cpu = type(view)(view.storage.cpu(), view.page_table.cpu(), view.page_size, kv_heads, head_dim, window)
+    cpu_batch = type("B", (), {"n_tokens": n, "tok_pos": batch.tok_pos.cpu(), "tok_seq": batch.tok_seq.cpu(),
+                               "slots": batch.slots.cpu()})
+    PK.attention_general(ref, q.cpu(), view_cpu, heads, 0.3, window or 0, cpu_batch)
+    assert rel_error(out.float().cpu(), ref.float()) <= tol
+    other = torch.zeros_like(out)
+    ops().attention_general(other, q, view, heads, 0.3, window or 0, batch)
+    if window is None:
+        assert torch.equal(out, other)
+    else:
+        assert rel_error(out.float().cpu(), other.float().cpu()) <= tol
+    if not decode:  # a token alone in its step gets the bits it got among its tile mates
+        from etalii.dllm_b200.engine.batch import BatchBuffers
+
+        token = 130 + 1 + 1 + 4  # the fifth of the nine new tokens of the fourth sequence
+        single = BatchBuffers(DEV).fill([batch.h_slots[3]], [[1]], [lengths[3] - 9 + 4], [[]])
+        alone = torch.zeros((1, heads * head_dim), dtype=dtype, device=DEV)
+        ops().attention_blocks(alone, q[token:token + 1].contiguous(), view, heads, 0.3, window or 0, single)
+        assert torch.equal(alone[0], out[token])
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_attention_finds_a_far_key(dtype):
     """One key among hundreds matches the query: the output must be that key's value, wherever its page lies."""
@@ -266,6 +304,9 @@ def test_attention_finds_a_far_key(dtype):
         q = torch.full((1, heads * hd), 4.0, dtype=dtype, device=DEV)
         out = torch.zeros_like(q)
         ops().attention_general(out, q, view, heads, 1.0, 0, batch)
+        assert torch.allclose(out.float(), torch.full_like(out, 7.0).float(), atol=0.05), target
+        out.zero_()
+        ops().attention_blocks(out, q, view, heads, 1.0, 0, batch)
         assert torch.allclose(out.float(), torch.full_like(out, 7.0).float(), atol=0.05), target
         view.storage[page] = saved
 
