@@ -79,6 +79,14 @@ class Model:
                 self._views.append(self.cache.state(entry.cache))
 
         self._plan_prefetch()
+        # the C++ host side of prefill-sized steps, for models made of the parts it restates (else None)
+        from ..kernels.launcher import PreNormLayers
+
+        self.native_layers = PreNormLayers.build(self) if torch.device(rt.device).type == "cuda" else None
+        if self.native_layers is not None:
+            from ..kernels.build import prebuild
+
+            prebuild(sorted(self.native_layers.libraries()))
 
     def _layer_parts(self, block=None):
         """The parts of one block, or of all blocks: a block's `parts` mapping where it has one, else what it holds
@@ -113,8 +121,11 @@ class Model:
         rt = self.rt
         ops.prefetch_hints = self._prefetch  # this model's hints (they live and die with the model)
         x = self.embedding.forward(batch.tokens, batch.n_tokens, rt)
-        for entry, view in zip(self.order, self._views):
-            self.blocks[entry.layer].forward(x, batch, view, rt, entry.writes_cache)
+        if self.native_layers is not None and self.native_layers.takes(batch):
+            self.native_layers.run(x, batch, rt)  # every layer's launches from one C++ call
+        else:
+            for entry, view in zip(self.order, self._views):
+                self.blocks[entry.layer].forward(x, batch, view, rt, entry.writes_cache)
         if batch.n_want == 0:
             return None
         if batch.is_decode and batch.n_want == batch.n_tokens and hasattr(self.final_norm, "lazy") \

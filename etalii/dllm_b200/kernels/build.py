@@ -35,6 +35,7 @@ SOURCES = {
     "attention_prefill_tcgen05": "attention_prefill_tcgen05.cu",
     "attention_decode_static": "attention_decode_static.cu",
     "sampling": "sampling.cu",
+    "step_launcher": "step_launcher.cu",
 }
 """Library name -> source file. A library added here is built by `build_all` and loadable by `library`."""
 

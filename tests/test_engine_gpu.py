@@ -504,3 +504,38 @@ def test_the_one_kernel_feed_forward_as_an_engine_option(name):
         finally:
             ops.FUSED_FEED_FORWARD = False
     assert launches[False] - launches[True] == config["num_hidden_layers"]  # one launch fewer a layer
+
+
+@pytest.mark.parametrize("head_dim", [32, 64, 128])
+def test_the_native_launcher_of_prefill_steps_issues_what_the_parts_issue(head_dim):
+    """Steps of more than 64 tokens of a model made of the library's own parts are launched from C++ in one call;
+    the same step driven part by part from Python launches the same kernels with the same arguments: equal bits,
+    an equal number of launches. Models with other parts or head sizes have no native table."""
+    from etalii.dllm_b200.kernels import launcher, ops
+
+    config = dict(P.TINY_B, num_hidden_layers=2, head_dim=head_dim, num_attention_heads=4, num_key_value_heads=2,
+                  hidden_size=128, intermediate_size=320, max_position_embeddings=1024)
+    weights = P.random_weights(config, seed=3, std=0.05)
+    plain = PlainLogits(config, weights)
+    engine = make_engine(config, weights, "bfloat16", max_tokens=64 * 24, max_length=1024)
+    assert engine.model.native_layers is not None
+    prompts = prompts_for(config, (300, 70, 5), seed=21)
+    results = {}
+    for native in (True, False):
+        launcher.ENABLED = native
+        try:
+            slots = engine.open(3)
+            before = ops.launches
+            logits = engine.step(slots, prompts, [[0, 299], [69], [4]]).clone()
+            results[native] = (logits, ops.launches - before)
+            got = host(engine.step(slots, [p[-1:] for p in prompts]))  # single tokens: the Python path either way
+            engine.close(slots)
+        finally:
+            launcher.ENABLED = True
+    assert torch.equal(results[True][0], results[False][0]) and results[True][1] == results[False][1]
+    want = np.stack([plain(prompts[0])[0], plain(prompts[0])[299], plain(prompts[1])[69], plain(prompts[2])[4]])
+    assert rel_error(host(results[True][0]), want) <= TOL["bfloat16"]
+    engine.check()
+    tiny, tiny_weights = model_case("a")
+    assert make_engine(tiny, tiny_weights, "bfloat16", max_tokens=128).model.native_layers is None  # head_dim 16
+    assert make_engine(config, weights, "float32", max_tokens=128).model.native_layers is None
