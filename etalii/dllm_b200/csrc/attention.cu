@@ -124,7 +124,7 @@ __device__ __forceinline__ void stage_page(T* k_s, T* v_s, const KvLayout& cache
   asm volatile("cp.async.commit_group;\n" ::);
 }
 
-template <typename T, int R>
+template <typename T, int R, int CHUNKS>  // CHUNKS: head_dim / 32 rounded up (value dimensions a lane owns)
 __global__ void __launch_bounds__(512) attention_block_kernel(
     T* __restrict__ out, const T* __restrict__ q, KvLayout cache, const int* __restrict__ tok_seq,
     const int* __restrict__ tok_pos, const int* __restrict__ slots, int tokens, int heads, float scale, int window,
@@ -154,7 +154,7 @@ __global__ void __launch_bounds__(512) attention_block_kernel(
 
       // this warp's tokens of the run
       int end[R], first[R];
-      float m_run[R], l_run[R], acc[R][MAX_HEAD_DIM / 32];
+      float m_run[R], l_run[R], acc[R][CHUNKS];
 #pragma unroll
       for (int r = 0; r < R; ++r) {
         int t = t0 + slot_of_warp * R + r;
@@ -164,7 +164,7 @@ __global__ void __launch_bounds__(512) attention_block_kernel(
         m_run[r] = -INFINITY;
         l_run[r] = 0.f;
 #pragma unroll
-        for (int i = 0; i < MAX_HEAD_DIM / 32; ++i) acc[r][i] = 0.f;
+        for (int i = 0; i < CHUNKS; ++i) acc[r][i] = 0.f;
         if (mine) {
           const T* qrow = q + ((size_t)t * heads + h) * hd;
           for (int d = lane; d < hd; d += 32) q_s[r * hd + d] = to_float(qrow[d]);
@@ -197,7 +197,12 @@ __global__ void __launch_bounds__(512) attention_block_kernel(
             if (valid) {
               const T* krow = k_s + (j - p * 64) * ld;
               float dot = 0.f;
-              for (int d = 0; d < hd; d += Vec<T>::N) dot += dot_vec(&q_s[r * hd + d], krow + d);
+              if (hd == CHUNKS * 32) {
+#pragma unroll
+                for (int d = 0; d < CHUNKS * 32; d += Vec<T>::N) dot += dot_vec(&q_s[r * hd + d], krow + d);
+              } else {
+                for (int d = 0; d < hd; d += Vec<T>::N) dot += dot_vec(&q_s[r * hd + d], krow + d);
+              }
               s = dot * scale;
             }
             float m_new = fmaxf(m_run[r], warp_max(s));
@@ -205,16 +210,23 @@ __global__ void __launch_bounds__(512) attention_block_kernel(
             float corr = expf(m_run[r] - m_new);  // 0 on the first tile (m_run = -inf)
             l_run[r] = l_run[r] * corr + warp_sum(pr);
 #pragma unroll
-            for (int i = 0; i < MAX_HEAD_DIM / 32; ++i) acc[r][i] *= corr;
+            for (int i = 0; i < CHUNKS; ++i) acc[r][i] *= corr;
             m_run[r] = m_new;
             int from = max(0, first[r] - j0), to = min(32, end[r] - j0);
-            for (int jj = from; jj < to; ++jj) {
-              float pj = __shfl_sync(0xffffffffu, pr, jj);
-              const T* vrow = v_s + (j0 + jj - p * 64) * ld;
+            const T* vtile = v_s + (j0 - p * 64) * ld + lane;
+            if (from == 0 && to == 32 && hd == CHUNKS * 32) {  // a whole tile of a whole head: no bounds in the loop
+#pragma unroll 8
+              for (int jj = 0; jj < 32; ++jj) {
+                float pj = __shfl_sync(0xffffffffu, pr, jj);
 #pragma unroll
-              for (int i = 0; i < MAX_HEAD_DIM / 32; ++i) {
-                int d = lane + 32 * i;
-                if (d < hd) acc[r][i] = fmaf(pj, to_float(vrow[d]), acc[r][i]);
+                for (int i = 0; i < CHUNKS; ++i) acc[r][i] = fmaf(pj, to_float(vtile[jj * ld + 32 * i]), acc[r][i]);
+              }
+            } else {
+              for (int jj = from; jj < to; ++jj) {
+                float pj = __shfl_sync(0xffffffffu, pr, jj);
+#pragma unroll
+                for (int i = 0; i < CHUNKS; ++i)
+                  if (lane + 32 * i < hd) acc[r][i] = fmaf(pj, to_float(vtile[jj * ld + 32 * i]), acc[r][i]);
               }
             }
           }
@@ -233,7 +245,7 @@ __global__ void __launch_bounds__(512) attention_block_kernel(
           float inv = 1.0f / l_run[r];
           T* orow = out + ((size_t)t * heads + h) * hd;
 #pragma unroll
-          for (int i = 0; i < MAX_HEAD_DIM / 32; ++i) {
+          for (int i = 0; i < CHUNKS; ++i) {
             int d = lane + 32 * i;
             if (d < hd) orow[d] = from_float<T>(acc[r][i] * inv);
           }
@@ -244,7 +256,7 @@ __global__ void __launch_bounds__(512) attention_block_kernel(
   }
 }
 
-template <typename T, int R>
+template <typename T, int R, int CHUNKS>
 int launch_blocks(void* out, const void* q, const KvLayout& cache, const int* tok_seq, const int* tok_pos,
                   const int* slots, int tokens, int heads, float scale, int window, cudaStream_t stream) {
   int group = heads / cache.kv_heads;
@@ -257,14 +269,14 @@ int launch_blocks(void* out, const void* q, const KvLayout& cache, const int* to
   size_t smem = stages * stage_bytes + q_bytes;
   static size_t configured = 0;
   if (smem > configured) {
-    if (cudaFuncSetAttribute(attention_block_kernel<T, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+    if (cudaFuncSetAttribute(attention_block_kernel<T, R, CHUNKS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
         cudaSuccess)
       return DLLM_LAUNCH_FAILED;
     configured = smem;
   }
   int block_tokens = token_slots * R;
   dim3 grid((tokens + block_tokens - 1) / block_tokens, cache.kv_heads);
-  attention_block_kernel<T, R><<<grid, warps * 32, smem, stream>>>((T*)out, (const T*)q, cache, tok_seq, tok_pos,
+  attention_block_kernel<T, R, CHUNKS><<<grid, warps * 32, smem, stream>>>((T*)out, (const T*)q, cache, tok_seq, tok_pos,
                                                                   slots, tokens, heads, scale, window,
                                                                   heads_per_pass, stages);
   return dllm_launch_status();
@@ -305,13 +317,23 @@ DLLM_EXPORT int dllm_attention_blocks(void* out, const void* q, void* cache_base
     return DLLM_UNSUPPORTED_SIZE;
   KvLayout cache{cache_base, page_table, max_pages, page_size, kv_heads, head_dim};
   bool runs = max_new > 1;
-  if (dtype == DLLM_F32)
-    return runs ? launch_blocks<float, 2>(out, q, cache, tok_seq, tok_pos, slots, tokens, heads, scale, window, stream)
-                : launch_blocks<float, 1>(out, q, cache, tok_seq, tok_pos, slots, tokens, heads, scale, window, stream);
-  if (dtype == DLLM_BF16)
-    return runs ? launch_blocks<__nv_bfloat16, 2>(out, q, cache, tok_seq, tok_pos, slots, tokens, heads, scale,
-                                                  window, stream)
-                : launch_blocks<__nv_bfloat16, 1>(out, q, cache, tok_seq, tok_pos, slots, tokens, heads, scale,
-                                                  window, stream);
+  int chunks = (head_dim + 31) / 32;
+#define DLLM_GO(T, R, CHUNKS) \
+  return launch_blocks<T, R, CHUNKS>(out, q, cache, tok_seq, tok_pos, slots, tokens, heads, scale, window, stream)
+#define DLLM_BY_WIDTH(T, R)                   \
+  if (chunks <= 1) DLLM_GO(T, R, 1);          \
+  else if (chunks == 2) DLLM_GO(T, R, 2);     \
+  else if (chunks <= 4) DLLM_GO(T, R, 4);     \
+  else DLLM_GO(T, R, 8)
+  if (dtype == DLLM_F32) {
+    if (runs) { DLLM_BY_WIDTH(float, 2); }
+    DLLM_BY_WIDTH(float, 1);
+  }
+  if (dtype == DLLM_BF16) {
+    if (runs) { DLLM_BY_WIDTH(__nv_bfloat16, 2); }
+    DLLM_BY_WIDTH(__nv_bfloat16, 1);
+  }
+#undef DLLM_BY_WIDTH
+#undef DLLM_GO
   return DLLM_BAD_ARGUMENT;
 }

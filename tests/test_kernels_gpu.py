@@ -78,10 +78,17 @@ def test_gemm_f32_rows_do_not_depend_on_the_batch():
     a, w = _randn((150, 136), torch.float32, 6), _randn((200, 136), torch.float32, 7)
     whole = torch.empty((150, 200), dtype=torch.float32, device=DEV)
     ops().gemm(whole, a, w, 0)
-    for rows in ([149], [0, 64, 65], list(range(70, 90))):
+    # one row and three (the kernel for a few rows), twenty (64 x 64 tiles), 149 of 150 (128 x 128 tiles)
+    for rows in ([149], [0, 64, 65], list(range(70, 90)), list(range(1, 150))):
         part = torch.empty((len(rows), 200), dtype=torch.float32, device=DEV)
         ops().gemm(part, a[rows].contiguous(), w, 0)
         assert torch.equal(part, whole[rows])
+    # the epilogues too: the SwiGLU of sixteen rows is the SwiGLU of those rows among 150
+    act = torch.empty((150, 100), dtype=torch.float32, device=DEV)
+    ops().gemm(act, a, w, 3)
+    few = torch.empty((16, 100), dtype=torch.float32, device=DEV)
+    ops().gemm(few, a[40:56].contiguous(), w, 3)
+    assert torch.equal(few, act[40:56])
 
 
 @pytest.mark.parametrize("m,n,k", GEMM_SHAPES)
