@@ -18,6 +18,10 @@
 #define EPI_T_STORE_T 6
 #define EPI_T_RESIDUAL 7
 #define EPI_T_SWIGLU 8
+// The head product of a greedy step (weight-streaming kernel only): no logits are stored; every tile of 16 output
+// features writes its largest value per token and the feature that has it (the lowest on ties) as a candidate,
+// C = [tokens][tiles](value, feature as an int's bits); a second small kernel picks each token's winner.
+#define EPI_ARGMAX 9
 
 // What the q/k/v epilogue needs: where queries go, where the cache is, the rotation table, who the tokens are.
 struct RopeArgs {

@@ -292,6 +292,8 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(void* __restrict__ c, 
     }
     __syncthreads();
 
+    float best_value = -INFINITY;  // EPI_ARGMAX: the larger of this thread's two features (the lower on a tie)
+    int best_feature = 0x7fffffff;
     // one thread per (pair of tile rows, token): rows (2p, 2p+1), or (p, p + 8) for rotary pairs
     for (int idx = tid; idx < 8 * NT * 8; idx += WARPS * 32) {
       int p = idx / (NT * 8), m = idx % (NT * 8);
@@ -344,8 +346,31 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_kernel(void* __restrict__ c, 
         float* dst = (float*)c + (size_t)m * N + item * TILE + 2 * p;
         dst[0] = early.r0 + v0;
         if (early.have > 1) dst[1] = early.r1 + v1;
+      } else if (EPI == EPI_ARGMAX) {
+        int n = item * TILE + 2 * p;  // (a value that is not a number is never larger: it is never chosen)
+        if (n < N && v0 > best_value) { best_value = v0; best_feature = n; }
+        if (n + 1 < N && v1 > best_value) { best_value = v1; best_feature = n + 1; }
       } else {
         epilogue_pair<EPI, bf16>(c, m, item * TILE + 2 * p, M, N, v0, v1);
+      }
+    }
+    if (EPI == EPI_ARGMAX) {  // (at most one item a thread: the launch gives 8 * NT * 8 threads or more)
+      __syncthreads();        // every partial tile has been read: the space now takes the threads' candidates
+      float* values = exchange;
+      int* features = reinterpret_cast<int*>(exchange + 8 * NT * 8);
+      if (tid < 8 * NT * 8) { values[tid] = best_value; features[tid] = best_feature; }
+      __syncthreads();
+      if (tid < NT * 8 && tid < M) {  // pairs in ascending order of their features: the first largest wins
+        float best = -INFINITY;
+        int feature = 0x7fffffff;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          float v = values[q * (NT * 8) + tid];
+          if (v > best) { best = v; feature = features[q * (NT * 8) + tid]; }
+        }
+        float* out = (float*)c + ((size_t)tid * items + item) * 2;
+        out[0] = best;
+        out[1] = __int_as_float(feature);
       }
     }
     if (!PIPE || next >= items) break;
@@ -425,6 +450,7 @@ int dispatch(void* c, const void* a, const float* norm_w, float eps, const bf16*
     case EPI_RESIDUAL: return launch<EPI_RESIDUAL, NORM>(c, a, norm_w, eps, w, M, N, K, rope, pf, stream);
     case EPI_SWIGLU: return launch<EPI_SWIGLU, NORM>(c, a, norm_w, eps, w, M, N, K, rope, pf, stream);
     case EPI_QKV_ROPE: return launch<EPI_QKV_ROPE, NORM>(c, a, norm_w, eps, w, M, N, K, rope, pf, stream);
+    case EPI_ARGMAX: return launch<EPI_ARGMAX, NORM>(c, a, norm_w, eps, w, M, N, K, rope, pf, stream);
     default: return DLLM_BAD_ARGUMENT;
   }
 }
@@ -437,12 +463,53 @@ DLLM_EXPORT int dllm_gemv_bf16(void* c, const void* a, const float* norm_w, floa
                                int K, int epilogue, const void* prefetch_ptr, long long prefetch_bytes,
                                cudaStream_t stream) {
   if (M <= 0 || N <= 0) return DLLM_OK;
-  if (M > 64 || K <= 0 || (K & 7) || ((N & 1) && epilogue == EPI_SWIGLU) || epilogue < 0 || epilogue > EPI_SWIGLU)
+  if (M > 64 || K <= 0 || (K & 7) || ((N & 1) && epilogue == EPI_SWIGLU) || epilogue < 0 ||
+      (epilogue > EPI_SWIGLU && epilogue != EPI_ARGMAX))
     return DLLM_UNSUPPORTED_SIZE;
   RopeArgs rope{};
   Prefetch pf{(const char*)prefetch_ptr, prefetch_ptr ? (size_t)prefetch_bytes : 0};
   return norm_w ? dispatch<true>(c, a, norm_w, eps, (const bf16*)w, M, N, K, epilogue, rope, pf, stream)
                 : dispatch<false>(c, a, nullptr, eps, (const bf16*)w, M, N, K, epilogue, rope, pf, stream);
+}
+
+// The second stage of the greedy head product (epilogue EPI_ARGMAX above): token r's winner among its `tiles`
+// candidates (value, feature), the lowest feature on ties; a token without a candidate (no value above -inf) gets 0.
+namespace {
+__global__ void __launch_bounds__(256) argmax_candidates_kernel(int* __restrict__ out_tokens,
+                                                                const float* __restrict__ candidates, int tiles) {
+  __shared__ float values[8];
+  __shared__ int features[8];
+  pdl_launch_dependents();
+  pdl_wait();
+  const float* row = candidates + (size_t)blockIdx.x * tiles * 2;
+  float best = -INFINITY;
+  int feature = 0x7fffffff;
+  for (int i = threadIdx.x; i < tiles; i += 256) {
+    float v = row[2 * i];
+    int f = __float_as_int(row[2 * i + 1]);
+    if (v > best || (v == best && f < feature)) { best = v; feature = f; }
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    int of = __shfl_xor_sync(0xffffffffu, feature, o);
+    if (ov > best || (ov == best && of < feature)) { best = ov; feature = of; }
+  }
+  if ((threadIdx.x & 31) == 0) { values[threadIdx.x >> 5] = best; features[threadIdx.x >> 5] = feature; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < 8; ++i)
+      if (values[i] > best || (values[i] == best && features[i] < feature)) { best = values[i]; feature = features[i]; }
+    out_tokens[blockIdx.x] = feature == 0x7fffffff ? 0 : feature;
+  }
+}
+}  // namespace
+
+// out_tokens[r] = the feature of the largest candidate of token r; candidates: [rows][tiles](value, feature).
+DLLM_EXPORT int dllm_argmax_candidates(int* out_tokens, const float* candidates, int rows, int tiles,
+                                       cudaStream_t stream) {
+  if (rows <= 0) return DLLM_OK;
+  if (tiles <= 0 || out_tokens == nullptr || candidates == nullptr) return DLLM_BAD_ARGUMENT;
+  return dllm_launch_pdl(argmax_candidates_kernel, dim3(rows), dim3(256), 0, stream, out_tokens, candidates, tiles);
 }
 
 // The q/k/v projection of a decode step in one kernel: optional RMSNorm in front, rotation of q and k by the

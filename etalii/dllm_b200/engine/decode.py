@@ -52,13 +52,18 @@ class DecodeGraph:
         self.launches_per_step = 0
         self.logits = None
         """The work buffer the captured step writes its logits to, [batch, vocab] float32: after a run of steps it
-        holds the last step's logits (tests compare them with a plain implementation without a second forward)."""
+        holds the last step's logits (tests compare them with a plain implementation without a second forward).
+        None where the step makes the greedy choice inside the head product (engines built with
+        `decode_logits=True` always compute them)."""
 
     def _body(self) -> None:
-        logits = self.logits = self.engine.model.forward(self.batch)
-        if self.blocked is not None:
-            ops.mask_tokens(logits, self.blocked, self.produced, self.counter, self.min_tokens)
-        self.engine.sampler.choose(logits, self.batch.slots, self.options, out=self.chosen)
+        # a greedy step that masks nothing needs no logits: the head product may make the choice itself
+        fused = self.options.temperature == 0 and self.blocked is None and not self.engine.decode_logits
+        logits = self.logits = self.engine.model.forward(self.batch, greedy_out=self.chosen if fused else None)
+        if logits is not None:
+            if self.blocked is not None:
+                ops.mask_tokens(logits, self.blocked, self.produced, self.counter, self.min_tokens)
+            self.engine.sampler.choose(logits, self.batch.slots, self.options, out=self.chosen)
         ops.decode_advance(self.batch.tokens, self.batch.tok_pos, self.batch.start, self.chosen, self.history,
                            self.counter, self.b)
 

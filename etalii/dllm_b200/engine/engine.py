@@ -41,11 +41,13 @@ def parse_dtype(dtype) -> torch.dtype:
 class Engine:
     def __init__(self, config, tensors, dtype="bfloat16", device="cuda:0", max_tokens: int | None = None,
                  max_length: int | None = None, max_slots: int | None = None, cuda_graphs: bool = True,
-                 decode_chunk: int = 16) -> None:
+                 decode_chunk: int = 16, decode_logits: bool = False) -> None:
         """`max_length`: the longest sequence the cache holds (default: the model's max_position_embeddings).
         `max_tokens`: the most tokens all live sequences hold together, each rounded up to whole pages of 64
         (default: four sequences of max_length). `cuda_graphs`: replay decode steps as CUDA graphs (turn off for
-        parts that cannot be captured). `decode_chunk`: decode steps between looks at the chosen tokens."""
+        parts that cannot be captured). `decode_chunk`: decode steps between looks at the chosen tokens.
+        `decode_logits`: decode runs always compute the logits (they stay readable in the run's buffer); by default
+        a greedy run lets the head product choose the token itself and stores no logits."""
         if not torch.cuda.is_available():
             raise RuntimeError("no CUDA device: this library has no CPU path")
         self.config = config
@@ -65,6 +67,7 @@ class Engine:
         self.steps_run = 0
         self.cuda_graphs = bool(cuda_graphs)
         self.decode_chunk = int(decode_chunk)
+        self.decode_logits = bool(decode_logits)
         self._graphs: dict = {}
         self.stats: dict = {}
 

@@ -113,9 +113,11 @@ class Model:
         for index, tensor in enumerate(order[:-ahead] if len(order) > ahead else []):
             self._prefetch[tensor.data_ptr()] = order[index + ahead]
 
-    def forward(self, batch) -> torch.Tensor:
+    def forward(self, batch, greedy_out: torch.Tensor | None = None) -> torch.Tensor:
         """Runs the batch's tokens through every scheduled layer; returns float32 logits [wanted rows, vocab]
-        (None when no row is wanted: the cache is still filled)."""
+        (None when no row is wanted: the cache is still filled). With `greedy_out` (int32 [wanted rows]) a head
+        that can make the greedy choice inside its product writes the chosen tokens there and no logits are
+        computed: the return value is then None."""
         from ..kernels import ops
 
         rt = self.rt
@@ -130,7 +132,11 @@ class Model:
             return None
         if batch.is_decode and batch.n_want == batch.n_tokens and hasattr(self.final_norm, "lazy") \
                 and getattr(self.head, "accepts_pending_norm", False):
-            return self.head.forward(self.final_norm.lazy(x, rt), rt)  # every row is wanted, in order: no gather
+            pending = self.final_norm.lazy(x, rt)  # every row is wanted, in order: no gather
+            if greedy_out is not None and hasattr(self.head, "choose_greedy") and \
+                    self.head.choose_greedy(pending, rt, greedy_out):
+                return None
+            return self.head.forward(pending, rt)
         hidden = self.final_norm.forward(x, rt, rows=batch.want_rows, n_rows=batch.n_want, name="final_hidden")
         return self.head.forward(hidden, rt)
 

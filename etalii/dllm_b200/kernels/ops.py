@@ -41,6 +41,7 @@ _prototypes = {
                                  c_void_p, c_longlong, c_void_p],
     ("mlp_decode", "dllm_mlp_decode"): [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
                                         c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p],
+    ("gemv", "dllm_argmax_candidates"): [c_void_p, c_void_p, c_int, c_int, c_void_p],
     ("gemv_tma", "dllm_gemv_tma"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     ("gemv", "dllm_gemv_qkv_rope"): [c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_void_p, c_void_p,
                                      c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p,
@@ -334,6 +335,40 @@ def mlp_decode(x: torch.Tensor, norm_weight: torch.Tensor, eps: float, w_gate_up
         intermediate, scratch.data_ptr(), tickets.data_ptr(), *_prefetch_of(w_gate_up), *_prefetch_of(w_down),
         _stream()), "mlp_decode",
         lambda: f"rows={rows} (at most 16), hidden={hidden} (multiple of 8), intermediate={intermediate} (multiple of 16)")
+
+
+EPI_ARGMAX = 9
+ARGMAX_MAX_ROWS = 16
+
+
+def head_argmax_supported(rows: int, w: torch.Tensor) -> bool:
+    """Whether the greedy choice can be made inside the head product: bfloat16 weights and a step small enough for
+    the weight-streaming kernel (up to 16 rows)."""
+    return w.dtype == torch.bfloat16 and 0 < rows <= ARGMAX_MAX_ROWS and w.shape[1] % 8 == 0
+
+
+def head_argmax_scratch(rows: int, outputs: int) -> int:
+    """Floats of scratch: a (value, feature) candidate per token and tile of 16 output features."""
+    return 2 * rows * (-(-outputs // 16))
+
+
+def head_argmax(out_tokens: torch.Tensor, a: torch.Tensor, w: torch.Tensor, scratch: torch.Tensor,
+                norm_weight: torch.Tensor | None = None, eps: float = 0.0) -> None:
+    """out_tokens[r] = the index of the largest of a[r] @ w^T (the lowest index on ties; 0 if no value is above
+    -inf), without the logits ever being stored: the product's tiles leave one candidate each, a second small
+    kernel picks the winner. With `norm_weight`, `a` is the float32 residual stream, RMS-normed on the way in."""
+    _cuda(out_tokens, a, w, scratch, norm_weight)
+    m, k = a.shape
+    n = w.shape[0]
+    assert head_argmax_supported(m, w) and w.shape[1] == k and out_tokens.dtype == torch.int32
+    assert scratch.dtype == torch.float32 and scratch.numel() >= head_argmax_scratch(m, n)
+    assert a.dtype == (torch.float32 if norm_weight is not None else torch.bfloat16)
+    _check(_fn("gemv", "dllm_gemv_bf16")(
+        scratch.data_ptr(), a.data_ptr(), norm_weight.data_ptr() if norm_weight is not None else None, float(eps),
+        w.data_ptr(), m, n, k, EPI_ARGMAX, *_prefetch_of(w), _stream()), "head_argmax product",
+        lambda: f"M={m} N={n} K={k}")
+    _check(_fn("gemv", "dllm_argmax_candidates")(out_tokens.data_ptr(), scratch.data_ptr(), m, -(-n // 16),
+                                                 _stream()), "head_argmax choice")
 
 
 def gemm_qkv_rope_supported(cache, rotary_dim: int, has_table: bool) -> bool:

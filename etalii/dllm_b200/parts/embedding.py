@@ -48,6 +48,23 @@ class LinearHead:
     def supports(self, rt) -> str | None:
         return row_rule(rt, hidden_size=self.hidden_size)
 
+    def choose_greedy(self, hidden, rt, out: torch.Tensor) -> bool:
+        """The greedy choice without logits: out[r] = argmax of row r's logits (lowest index on ties), made inside
+        the head product. Returns False, having done nothing, where that kernel does not take the step."""
+        from .norm import NormedInput, fuses_norm
+
+        rows = hidden.shape[0]
+        if not ops.head_argmax_supported(rows, self.weight):
+            return False
+        scratch = rt.ws.buffer("head_candidates", (ops.head_argmax_scratch(rows, self.vocab_size),), torch.float32)
+        if isinstance(hidden, NormedInput):
+            if fuses_norm(self.weight):
+                ops.head_argmax(out, hidden.x, self.weight, scratch, norm_weight=hidden.weight, eps=hidden.eps)
+                return True
+            hidden = hidden.tensor()
+        ops.head_argmax(out, hidden, self.weight, scratch)
+        return True
+
     def forward(self, hidden, rt) -> torch.Tensor:
         """hidden: final-normed rows, or the norm still pending (`NormedInput`)."""
         logits = rt.ws.buffer("logits", (hidden.shape[0], self.vocab_size), torch.float32)

@@ -539,3 +539,17 @@ def test_the_native_launcher_of_prefill_steps_issues_what_the_parts_issue(head_d
     tiny, tiny_weights = model_case("a")
     assert make_engine(tiny, tiny_weights, "bfloat16", max_tokens=128).model.native_layers is None  # head_dim 16
     assert make_engine(config, weights, "float32", max_tokens=128).model.native_layers is None
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_decoding_without_logits_chooses_the_same_tokens(name):
+    """By default a greedy decode run makes its choice inside the head product and stores no logits; an engine
+    built with decode_logits=True stores them and chooses from them. Same kernels up to the epilogue: same tokens."""
+    config, weights = model_case(name.lower())
+    prompts = prompts_for(config, (9, 20, 3, 33), seed=61)
+    outputs = {}
+    for keep in (False, True):
+        engine = make_engine(config, weights, "bfloat16", max_tokens=64 * 8, decode_logits=keep)
+        outputs[keep] = [r.tokens for r in engine.generate(prompts, 24, ignore_eos=True)]
+        assert (engine.last_decode_graph.logits is not None) == keep
+    assert outputs[False] == outputs[True]

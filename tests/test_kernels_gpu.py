@@ -891,3 +891,28 @@ def test_mlp_decode_fused_feed_forward(m, hidden, inter):
         alone = x0[m - 1:].clone()
         ops().mlp_decode(alone, norm_w, eps, w_gu, w_d, scratch, tickets)
         assert torch.equal(alone[0], got[m - 1])
+
+
+@pytest.mark.parametrize("m,n,k,normed", [(1, 384, 64, True), (8, 49153, 576, True), (16, 1000, 136, False),
+                                          (5, 17, 72, False), (9, 4096, 2240, True)])
+def test_head_argmax_chooses_what_the_logits_would(m, n, k, normed):
+    """The greedy choice made inside the head product against the argmax of the stored logits of the same kernel
+    (the same sums, so the same winner, ties included), at vocabularies that are no multiple of 16."""
+    x = _randn((m, k), torch.float32 if normed else torch.bfloat16, 1)
+    w = _randn((n, k), torch.bfloat16, 2, 0.1)
+    w[n // 2] = w[3]            # two features with equal logits in every row ...
+    x[0] = 0                    # ... and a row whose logits are all equal (zero): the lowest index wins
+    if m > 2:
+        x[2, 0] = float("nan")  # a row without any number: token 0, as the sampler answers it
+    nw = _randn((k,), torch.float32, 3, 0.1) + 1 if normed else None
+    logits = torch.empty((m, n), dtype=torch.float32, device=DEV)
+    ops().gemm(logits, x, w, ops().EPI_STORE_F32, kernel=2, norm_weight=nw, eps=1e-5)
+    want = torch.empty(m, dtype=torch.int32, device=DEV)
+    ops().sample(want, logits, None, None, None, 0.0)
+    got = torch.full((m,), -1, dtype=torch.int32, device=DEV)
+    scratch = torch.full((ops().head_argmax_scratch(m, n),), float("nan"), dtype=torch.float32, device=DEV)
+    ops().head_argmax(got, x, w, scratch, norm_weight=nw, eps=1e-5)
+    assert got.tolist() == want.tolist()
+    assert got[0].item() == 0 and (m <= 2 or got[2].item() == 0)
+    finite = [r for r in range(m) if r not in (0, 2)]
+    assert got[finite].tolist() == logits[finite].argmax(dim=1).tolist()

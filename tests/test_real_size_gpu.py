@@ -110,7 +110,7 @@ def test_a_batch_of_64_through_the_decode_graph_at_real_size(real_size, dtype):
     rng = np.random.default_rng(64)
     lengths = rng.integers(8, 81, 64).tolist()
     prompts = prompts_for(config, lengths, seed=65)
-    engine = make_engine(config, weights, dtype, max_tokens=64 * 2 * 64, max_length=192)
+    engine = make_engine(config, weights, dtype, max_tokens=64 * 2 * 64, max_length=192, decode_logits=True)
     slots = engine.open(64)
     first = np.concatenate([host(engine.step(slots[:32], prompts[:32])), host(engine.step(slots[32:], prompts[32:]))])
     _decode_and_compare(engine, config, weights, dtype, prompts, slots, first, steps=3)
@@ -152,7 +152,7 @@ def test_eight_long_contexts_through_the_decode_graph(dtype):
     weights = P.random_weights(config, seed=9)
     lengths = [1900, 2048, 1987, 2001, 1923, 2040, 1961, 2017]
     prompts = prompts_for(config, lengths, seed=67)
-    engine = make_engine(config, weights, dtype, max_tokens=8 * 2112, max_length=2112)
+    engine = make_engine(config, weights, dtype, max_tokens=8 * 2112, max_length=2112, decode_logits=True)
     slots = engine.open(8)
     first = np.concatenate([host(engine.step(slots[i:i + 2], prompts[i:i + 2])) for i in range(0, 8, 2)])
     _decode_and_compare(engine, config, weights, dtype, prompts, slots, first, steps=2)
@@ -196,7 +196,7 @@ def test_two_layers_at_the_sizes_of_larger_models(larger_layers, dtype):
     rows of W), the tile product with W as the 128-row operand (33 rows against the head and the gate/up matrix),
     256-wide tiles, heads of 128 in every attention kernel, llama3 rotary scaling and an untied head."""
     config, weights, prompt, short, plain = larger_layers
-    engine = make_engine(config, weights, dtype, max_tokens=64 * 40, max_length=128)
+    engine = make_engine(config, weights, dtype, max_tokens=64 * 40, max_length=128, decode_logits=True)
     slot = engine.open(1)
     got = [host(engine.step(slot, [prompt[:40]], [[0, 20, 39]]))]
     for token in prompt[40:]:
