@@ -109,9 +109,12 @@ class PagedCache:
                 raise CacheError(f"unknown cache kind {need.kind!r}")
         for need, entries in by_need.items():
             pages = self.n_pages
-            if need.window:  # a windowed group holds at most the window (plus the page being filled) per sequence
+            if need.window:
+                # A windowed group holds at most the window (plus the page being filled) per sequence while it
+                # decodes; but a whole prompt enters in one step and needs all its positions at once, so there is
+                # room for one sequence of the longest length on top of every slot's window.
                 per_sequence = -(-need.window // self.page_size) + 1
-                pages = min(self.n_pages, per_sequence * self.n_slots)
+                pages = min(self.n_pages, per_sequence * self.n_slots + -(-self.max_length // self.page_size))
             group = _KvGroup(need, entries, pages, self.n_slots, self.max_pages, self.page_size, dtype, device)
             self._groups.append(group)
             for index, entry in enumerate(entries):
@@ -222,6 +225,11 @@ class PagedCache:
 
     def groups(self) -> list[tuple[CacheNeed, list[int]]]:
         return [(g.need, list(g.entries)) for g in self._groups]
+
+    def smallest_pool(self) -> int:
+        """Pages of the smallest group's pool: what a planner may count on for every group (a windowed group's pool
+        is smaller than the cache's page count)."""
+        return min((g.pool.count for g in self._groups), default=self.n_pages)
 
     def pages_held(self) -> int:
         return sum(g.pool.held for g in self._groups)

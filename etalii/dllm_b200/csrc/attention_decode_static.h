@@ -13,7 +13,9 @@
 //     DLLM_STATIC_TOO_LARGE (-4) and prints the sizes to standard error; nothing is launched.
 //     Needed: sequences * heads * ceil(max_context / chunk) * (head_dim + 2) floats, sequences * kv_heads counters.
 //   - The first call on a device looks up the array's device address (cudaGetSymbolAddress, once per device, with
-//     that device current). Make that first call outside any stream capture.
+//     that device current). Make that first call outside any stream capture, and from one thread: the look-up is
+//     not synchronised, so two threads must not both make a device's first call at the same time. The address is
+//     kept for the life of the device's context; after cudaDeviceReset the library must be loaded afresh.
 //   - It calls no cudaMalloc, no cudaFree and no library routine that allocates.
 //   - All calls share the one array and it keeps what the last call left. The counters are cleared on the stream
 //     before every launch; partial results are overwritten before they are read. Two calls that overlap on the

@@ -215,7 +215,7 @@ class Engine:
         stops = set() if ignore_eos else set(self.spec.stop_token_ids)
         stops.update(int(t) for t in (stop_token_ids or ()))
         batches = plan_batches([len(p) for p in prompts], max_new_tokens, window, self.cache.page_size,
-                               self.cache.n_pages, self.cache.n_slots, max_batch)
+                               self.cache.smallest_pool(), self.cache.n_slots, max_batch)
 
         held_back = tuple(sorted(stops)) if min_tokens > 0 else ()
         produced = [0]  # tokens of output every running sequence of the batch has (they start together)

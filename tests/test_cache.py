@@ -115,3 +115,28 @@ def test_a_released_slot_starts_again_from_zero():
     assert again == slot and cache.length(again) == 0
     cache.reserve(again, 1)
     assert cache._groups[0].pages_of[again][0] in pages  # the same storage is used again
+
+
+def test_a_windowed_group_has_room_for_a_whole_prompt_of_several_windows():
+    """A windowed group keeps only the window per sequence while it decodes, but a whole prompt enters in one step
+    and needs all its positions at once: with a single slot and a window of 100, a prompt of 500 tokens must still
+    find its pages in the windowed pool, and the planner counts with the smallest pool."""
+    from etalii.dllm_b200.cache.paged import CacheNeed, PagedCache
+    from etalii.dllm_b200.engine.generate import plan_batches
+
+    cache = PagedCache([CacheNeed("kv", 2, 16, window=100), CacheNeed("kv", 2, 16)], max_tokens=64 * 40,
+                       max_length=1024, dtype=None, device=None, max_slots=1)
+    slot = cache.acquire(1)[0]
+    cache.reserve(slot, 500)       # eight pages in both groups at once
+    cache.advance(slot, 500)
+    held_after_prompt = cache.pages_held()
+    for _ in range(200):           # decoding: the windowed group gives pages behind the window back
+        cache.reserve(slot, 1)
+        cache.advance(slot, 1)
+    cache.check()
+    assert cache.pages_held() < held_after_prompt + 4
+    assert cache.smallest_pool() < cache.n_pages
+    assert plan_batches([900, 900], 50, 1024, 64, cache.smallest_pool(), 4) == [[0], [1]]
+    cache.release([slot])
+    cache.check()
+    assert cache.pages_held() == 0

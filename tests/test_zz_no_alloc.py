@@ -1,6 +1,8 @@
 """The allocation-free decode attention (`dllm_attention_decode_static`), called through its exported C symbol the
 way a caller without an allocator would: inputs and outputs only. Its result must equal the regular entry point's,
-on two calls in a row (the built-in scratch keeps the first call's contents). This file is collected last on purpose."""
+on two calls in a row (the built-in scratch keeps the first call's contents), it must agree with a plain attention
+computed from the same inputs, and a call must leave the device's free memory as it found it. This file is collected
+last on purpose."""
 import ctypes
 from ctypes import c_float, c_int, c_void_p
 
@@ -58,13 +60,26 @@ def test_static_scratch_entry_point_matches_the_regular_one(heads, kv_heads, hea
         tickets = torch.zeros(n * kv_heads, dtype=torch.int32, device=DEV)
         ops.attention_decode(want, q, view, heads, 0.3, 0, batch, chunk, scratch, tickets)
         got = torch.zeros_like(want)
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0] if call == 1 else None  # (the first call may load the library)
         status = function(got.data_ptr(), q.data_ptr(), view.base_ptr, view.page_table.data_ptr(), view.max_pages,
                           view.page_size, heads, kv_heads, head_dim, batch.tok_pos.data_ptr(), batch.slots.data_ptr(),
                           n, 0.3, 0, chunk, 1024, stream)
         assert status == 0
         torch.cuda.synchronize()
+        if free_before is not None:  # what the entry point exists for: the call took no device memory
+            assert torch.cuda.mem_get_info()[0] == free_before
         assert rel_error(got.float().cpu(), want.float().cpu()) <= 8e-3
         assert torch.equal(got, want)  # the same kernels in the same order: the same bits
+        # and the numbers themselves, against the plain attention of the same queries, keys and values
+        import plain_kernels as PK
+
+        plain = torch.zeros((n, heads * head_dim), dtype=torch.bfloat16)
+        view_cpu = type(view)(view.storage.cpu(), view.page_table.cpu(), view.page_size, kv_heads, head_dim, None)
+        cpu_batch = type("B", (), {"n_tokens": n, "tok_pos": batch.tok_pos.cpu(), "tok_seq": batch.tok_seq.cpu(),
+                                   "slots": batch.slots.cpu()})
+        PK.attention_general(plain, q.cpu(), view_cpu, heads, 0.3, 0, cpu_batch)
+        assert rel_error(got.float().cpu(), plain.float()) <= 8e-3
 
 
 def test_static_scratch_entry_point_refuses_what_does_not_fit(capfd):
