@@ -135,6 +135,35 @@ DLLM_EXPORT int dllm_rmsnorm(void* out, const float* x, const float* weight, con
   return dllm_launch_status();
 }
 
+// ---- what a norm folded around the next product needs of the first rows of a step -------------------------------
+// copy[r] = bfloat16(x[r]) and ssq[r] = sum of x[r]^2 (one part a row): a warp a row, any width that is a multiple
+// of 4 (see NormArgs in gemm_common.cuh; later rows come from the epilogue of the products that write the residual).
+__global__ void __launch_bounds__(256) cast_ssq_kernel(__nv_bfloat16* __restrict__ copy, float* __restrict__ ssq,
+                                                       const float* __restrict__ x, int n_rows, int hidden) {
+  pdl_launch_dependents();
+  pdl_wait();
+  int lane = threadIdx.x & 31;
+  int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= n_rows) return;
+  const float4* src = reinterpret_cast<const float4*>(x + (size_t)r * hidden);
+  float sum = 0.f;
+  for (int idx = lane; idx < (hidden >> 2); idx += 32) {
+    float4 v = src[idx];
+    sum = fmaf(v.x, v.x, sum); sum = fmaf(v.y, v.y, sum);
+    sum = fmaf(v.z, v.z, sum); sum = fmaf(v.w, v.w, sum);
+    store4(copy + (size_t)r * hidden + 4 * idx, v.x, v.y, v.z, v.w);
+  }
+  sum = warp_sum(sum);
+  if (lane == 0) ssq[r] = sum;
+}
+
+DLLM_EXPORT int dllm_cast_ssq(void* copy, float* ssq, const float* x, int n_rows, int hidden, cudaStream_t stream) {
+  if (n_rows <= 0) return DLLM_OK;
+  if (hidden <= 0 || (hidden & 3) || copy == nullptr || ssq == nullptr) return DLLM_UNSUPPORTED_SIZE;
+  return dllm_launch_pdl(cast_ssq_kernel, dim3((n_rows + 7) / 8), dim3(256), 0, stream, (__nv_bfloat16*)copy, ssq, x,
+                         n_rows, hidden);
+}
+
 // ---- rotary encoding + cache write --------------------------------------------------------------------------------
 // qkv is the float32 output of the fused q/k/v projection, [tokens, (heads + 2 kv_heads) * head_dim]. Queries and
 // keys rotate pairs (i, i + rotary_dim/2) by the angle whose cosine and sine the table holds for the token's

@@ -36,6 +36,35 @@ struct RopeArgs {
   int prefetch_window;   // -1: no prefetch; 0: every page of the tokens' sequences; w > 0: the pages of the last w keys
 };
 
+// RMSNorm around the tile product of prefill-sized steps, without a kernel of its own. The product that writes the
+// residual stream (`x += A W^T`) also writes a bfloat16 copy of the new rows and, per row and tile of columns, the
+// sum of the squares of what it wrote; the product that reads the residual next takes the bfloat16 copy as its
+// operand (its weights carry the norm's weight in their columns) and scales every row of its result by
+// 1 / sqrt(sum of the parts / width + eps): norm(x) W^T = (x W'^T) / rms(x). The parts are summed in tile order by
+// every reader, so the scale has the same bits everywhere.
+struct NormArgs {
+  const float* ssq_in;      // [parts_in][rows] sums of squares of the rows of the operand, or null (no scaling)
+  int parts_in;
+  float inv_width, eps;     // 1 / (width of the normed rows), the norm's eps
+  float* ssq_out;           // [column tiles of this product][rows], or null
+  __nv_bfloat16* copy_out;  // [rows][N] bfloat16 copy of the new residual rows, or null
+};
+
+// (The parts of a row lie `M` floats apart, so the 32 rows of a warp read 128 contiguous bytes per part; up to
+// sixteen parts are asked for before the first is summed: one round trip, not one per part.)
+__device__ __forceinline__ float row_scale(const NormArgs& norm, int m, int M) {
+  if (norm.ssq_in == nullptr || m >= M) return 1.0f;
+  float sum = 0.f;
+  for (int j0 = 0; j0 < norm.parts_in; j0 += 16) {
+    float v[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = j0 + j < norm.parts_in ? norm.ssq_in[(size_t)(j0 + j) * M + m] : 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) sum += v[j];
+  }
+  return 1.0f / sqrtf(sum * norm.inv_width + norm.eps);
+}
+
 // silu(g) = g * sigmoid(g), sigmoid as 1/(1+e^-g) for g >= 0 and e^g/(1+e^g) below, in float32; the product with
 // `up` is a separate float32 multiply of the rounded activation.
 __device__ __forceinline__ float silu_f32(float g) {
@@ -88,15 +117,18 @@ __device__ __forceinline__ void epilogue_row16(void* __restrict__ c, int m, int 
   if (EPI == EPI_STORE_F32 || EPI == EPI_RESIDUAL) {
     float* dst = (float*)c + (size_t)m * N + n;
     if (whole && (N & 3) == 0) {
+      float4 o[4];
 #pragma unroll
-      for (int i = 0; i < 16; i += 4) {
-        float4 o = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-        if (EPI == EPI_RESIDUAL) {
-          float4 r = *reinterpret_cast<float4*>(dst + i);
-          o.x += r.x; o.y += r.y; o.z += r.z; o.w += r.w;
-        }
-        *reinterpret_cast<float4*>(dst + i) = o;
+      for (int i = 0; i < 4; ++i) o[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+      if (EPI == EPI_RESIDUAL) {  // all four loads before the first store: one round trip, not four
+        float4 r[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) r[i] = *reinterpret_cast<const float4*>(dst + 4 * i);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { o[i].x += r[i].x; o[i].y += r[i].y; o[i].z += r[i].z; o[i].w += r[i].w; }
       }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) *reinterpret_cast<float4*>(dst + 4 * i) = o[i];
       return;
     }
   } else if (EPI == EPI_STORE_T) {

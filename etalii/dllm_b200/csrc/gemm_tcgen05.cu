@@ -43,7 +43,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
                                                                const __grid_constant__ CUtensorMap map_w,
                                                                void* __restrict__ c, int M, int N, int K,
                                                                int* __restrict__ status, RopeArgs rope, int m_tiles,
-                                                               int n_tiles) {
+                                                               int n_tiles, NormArgs norm) {
   typedef Shape<BN, DEEP> S;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);  // swizzle atoms: 1 KB
@@ -126,6 +126,28 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
       int buf = lt & 1;
       int m0 = (t % m_tiles) * BM, n_tile = t / m_tiles, n0 = n_tile * BN;
       int m = m0 + quarter * 32 + lane;
+      // (narrow tiles: the row's old residual values are all asked for before the accumulator is read, so their
+      // round trip runs under the wait for the products instead of after it, once per 16 columns)
+      constexpr bool EARLY = EPI == EPI_RESIDUAL && BN <= 64;
+      float4 old[EARLY ? BN / 4 : 1];
+      if (EARLY && norm.copy_out != nullptr && m < M) {
+#pragma unroll
+        for (int i = 0; i < BN / 4; ++i)
+          old[i] = n0 + 4 * i < N ? *reinterpret_cast<const float4*>((const float*)c + (size_t)m * N + n0 + 4 * i)
+                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+      // the token's position and cache page (q/k/v epilogue): a chain of dependent loads that runs under the products
+      int pos = 0, page = 0;
+      if (EPI == EPI_QKV_ROPE && m < M) {
+        pos = rope.tok_pos[m];
+        if (rope.write_cache) {
+          int slot = rope.slots[rope.tok_seq[m]];
+          page = rope.cache.page_table[(size_t)slot * rope.cache.max_pages + pos / rope.cache.page_size];
+        }
+      }
+      // (1 unless the operand is the un-normed copy of the residual; its sums are read while the products run)
+      float scale_row = (EPI == EPI_STORE_F32 || EPI == EPI_STORE_T || EPI == EPI_SWIGLU || EPI == EPI_QKV_ROPE)
+                            ? row_scale(norm, m, M) : 1.0f;
       if (!mbar_wait(&acc_full[buf], (lt >> 1) & 1)) {
         if (lane == 0) *(volatile int*)status = 4;
         break;
@@ -137,7 +159,6 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
         // (i, i + rotary_dim / 2) and writes the query, or the key / value into the token's cache row
         constexpr int HEAD = HD > 0 ? HD : BN;  // (HD is 0 only in instantiations that never take this branch)
         int heads = rope.heads, nkv = rope.cache.kv_heads;
-        int pos = m < M ? rope.tok_pos[m] : 0;
 #pragma unroll 1
         for (int seg = 0; seg < BN / HEAD; ++seg) {
           float f[HEAD];
@@ -146,7 +167,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
             unsigned v[16];
             tmem_load16(acc + (unsigned)(seg * HEAD + col), v);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) f[col + i] = __uint_as_float(v[i]);
+            for (int i = 0; i < 16; ++i) f[col + i] = __uint_as_float(v[i]) * scale_row;
           }
           if (seg == BN / HEAD - 1) {  // the last values are in registers: the accumulator may be reused
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -171,8 +192,6 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
           } else {
             int which = head < heads + nkv ? 0 : 1;
             int kvh = head - heads - which * nkv;
-            int slot = rope.slots[rope.tok_seq[m]];
-            int page = rope.cache.page_table[(size_t)slot * rope.cache.max_pages + pos / rope.cache.page_size];
             dst = (bf16*)rope.cache.base + kv_offset(rope.cache, page, which, kvh, pos % rope.cache.page_size);
           }
 #pragma unroll
@@ -185,6 +204,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
           }
         }
       } else {
+        float ssq = 0.f;  // EPI_RESIDUAL with norm.copy_out: the squares of the new residual values of this tile
 #pragma unroll
         for (int col = 0; col < BN; col += 16) {
           unsigned v[16];
@@ -196,10 +216,39 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
           }
           float f[16];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) f[i] = __uint_as_float(v[i]);
-          if (EPI >= EPI_T_STORE_F32) epilogue_col16<EPI, bf16>(c, m, n0 + col, M, N, f);  // the tile is C^T
-          else epilogue_row16<EPI, bf16>(c, m, n0 + col, M, N, f);
+          for (int i = 0; i < 16; ++i) f[i] = __uint_as_float(v[i]) * scale_row;
+          if (EPI == EPI_RESIDUAL && norm.copy_out != nullptr) {
+            // the residual sum, its bfloat16 copy and its squares (N is a multiple of 16 in this mode)
+            int n = n0 + col;
+            if (m < M && n < N) {
+              float* __restrict__ dst = (float*)c + (size_t)m * N + n;
+              float4 r[4];
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                r[i] = EARLY ? old[EARLY ? col / 4 + i : 0] : *reinterpret_cast<const float4*>(dst + 4 * i);
+              unsigned pk[8];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                r[i].x += f[4 * i]; r[i].y += f[4 * i + 1]; r[i].z += f[4 * i + 2]; r[i].w += f[4 * i + 3];
+                ssq = fmaf(r[i].x, r[i].x, ssq); ssq = fmaf(r[i].y, r[i].y, ssq);
+                ssq = fmaf(r[i].z, r[i].z, ssq); ssq = fmaf(r[i].w, r[i].w, ssq);
+                __nv_bfloat162 lo = __floats2bfloat162_rn(r[i].x, r[i].y), hi = __floats2bfloat162_rn(r[i].z, r[i].w);
+                pk[2 * i] = *reinterpret_cast<unsigned*>(&lo);
+                pk[2 * i + 1] = *reinterpret_cast<unsigned*>(&hi);
+              }
+#pragma unroll
+              for (int i = 0; i < 4; ++i) *reinterpret_cast<float4*>(dst + 4 * i) = r[i];
+              uint4* __restrict__ copy = reinterpret_cast<uint4*>(norm.copy_out + (size_t)m * N + n);
+              copy[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+              copy[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+            }
+          } else if (EPI >= EPI_T_STORE_F32) {
+            epilogue_col16<EPI, bf16>(c, m, n0 + col, M, N, f);  // the tile is C^T
+          } else {
+            epilogue_row16<EPI, bf16>(c, m, n0 + col, M, N, f);
+          }
         }
+        if (EPI == EPI_RESIDUAL && norm.ssq_out != nullptr && m < M) norm.ssq_out[(size_t)n_tile * M + m] = ssq;
       }
     }
   }
@@ -212,7 +261,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
 
 template <int BN, int EPI, bool DEEP, int HD>
 int launch_shape(void* c, const CUtensorMap& map_a, const CUtensorMap& map_w, int M, int N, int K, int* status,
-                 cudaStream_t stream, const RopeArgs& rope, int m_tiles, int n_tiles, int sms) {
+                 cudaStream_t stream, const RopeArgs& rope, int m_tiles, int n_tiles, int sms, const NormArgs& norm) {
   typedef Shape<BN, DEEP> S;
   static bool configured = false;
   if (!configured) {
@@ -225,12 +274,12 @@ int launch_shape(void* c, const CUtensorMap& map_a, const CUtensorMap& map_w, in
   int blocks = sms * S::BLOCKS_PER_SM;
   if (blocks > total) blocks = (int)total;
   return dllm_launch_pdl(gemm_tcgen05_kernel<BN, EPI, DEEP, HD>, dim3(blocks), dim3(THREADS), S::SMEM, stream, map_a, map_w,
-                         c, M, N, K, status, rope, m_tiles, n_tiles);
+                         c, M, N, K, status, rope, m_tiles, n_tiles, norm);
 }
 
 template <int BN, int EPI, int HD = 0>
 int launch(void* c, const void* a, const void* w, int M, int N, int K, int* status, cudaStream_t stream,
-           const RopeArgs& rope = RopeArgs{}) {
+           const RopeArgs& rope = RopeArgs{}, const NormArgs& norm = NormArgs{}) {
   alignas(64) CUtensorMap map_a, map_w;
   if (!make_map(&map_a, a, M, K, BM) || !make_map(&map_w, w, N, K, BN)) return DLLM_LAUNCH_FAILED;
   int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
@@ -245,18 +294,19 @@ int launch(void* c, const void* a, const void* w, int M, int N, int K, int* stat
   }
   constexpr bool CAN_DEEP = BN == 64 && EPI <= EPI_QKV_ROPE;  // (the shapes where it was measured to pay)
   if (CAN_DEEP && total <= sms && K > 4 * BK)
-    return launch_shape<BN, EPI, CAN_DEEP, HD>(c, map_a, map_w, M, N, K, status, stream, rope, m_tiles, n_tiles, sms);
-  return launch_shape<BN, EPI, false, HD>(c, map_a, map_w, M, N, K, status, stream, rope, m_tiles, n_tiles, sms);
+    return launch_shape<BN, EPI, CAN_DEEP, HD>(c, map_a, map_w, M, N, K, status, stream, rope, m_tiles, n_tiles, sms,
+                                               norm);
+  return launch_shape<BN, EPI, false, HD>(c, map_a, map_w, M, N, K, status, stream, rope, m_tiles, n_tiles, sms, norm);
 }
 
 template <int BN>
 int dispatch(void* c, const void* a, const void* w, int M, int N, int K, int epilogue, int* status,
-             cudaStream_t stream) {
+             cudaStream_t stream, const NormArgs& norm = NormArgs{}) {
   switch (epilogue) {
-    case EPI_STORE_F32: return launch<BN, EPI_STORE_F32>(c, a, w, M, N, K, status, stream);
-    case EPI_STORE_T: return launch<BN, EPI_STORE_T>(c, a, w, M, N, K, status, stream);
-    case EPI_RESIDUAL: return launch<BN, EPI_RESIDUAL>(c, a, w, M, N, K, status, stream);
-    case EPI_SWIGLU: return launch<BN, EPI_SWIGLU>(c, a, w, M, N, K, status, stream);
+    case EPI_STORE_F32: return launch<BN, EPI_STORE_F32>(c, a, w, M, N, K, status, stream, RopeArgs{}, norm);
+    case EPI_STORE_T: return launch<BN, EPI_STORE_T>(c, a, w, M, N, K, status, stream, RopeArgs{}, norm);
+    case EPI_RESIDUAL: return launch<BN, EPI_RESIDUAL>(c, a, w, M, N, K, status, stream, RopeArgs{}, norm);
+    case EPI_SWIGLU: return launch<BN, EPI_SWIGLU>(c, a, w, M, N, K, status, stream, RopeArgs{}, norm);
     case EPI_T_STORE_F32: return launch<BN, EPI_T_STORE_F32>(c, a, w, M, N, K, status, stream);
     case EPI_T_STORE_T: return launch<BN, EPI_T_STORE_T>(c, a, w, M, N, K, status, stream);
     case EPI_T_RESIDUAL: return launch<BN, EPI_T_RESIDUAL>(c, a, w, M, N, K, status, stream);
@@ -273,8 +323,8 @@ int dispatch(void* c, const void* a, const void* w, int M, int N, int K, int epi
 // Epilogues 5..8 are 0..3 for a product taken the other way round: the caller passes W as A (M = output features)
 // and the activations as W (N = tokens), and C is still [tokens, features]; for a few tokens and a large W this
 // streams W through 128-row tiles once instead of re-reading it for every 128 rows of a mostly empty tile of tokens.
-DLLM_EXPORT int dllm_gemm_tcgen05(void* c, const void* a, const void* w, int M, int N, int K, int epilogue, int tile_n,
-                                  int* status, cudaStream_t stream) {
+static int gemm_entry(void* c, const void* a, const void* w, int M, int N, int K, int epilogue, int tile_n,
+                      int* status, cudaStream_t stream, const NormArgs& norm, int* n_tiles_out) {
   if (M <= 0 || N <= 0) return DLLM_OK;
   if (K <= 0 || (K & 7) || ((N & 1) && epilogue == EPI_SWIGLU) || ((M & 1) && epilogue == EPI_T_SWIGLU) ||
       ((uintptr_t)a & 15) || ((uintptr_t)w & 15) || status == nullptr)
@@ -288,23 +338,55 @@ DLLM_EXPORT int dllm_gemm_tcgen05(void* c, const void* a, const void* w, int M, 
     else if (N % 128 == 0 && N >= 2048 && K >= 1024) tile_n = 128;  // (2048 x 3072 x 576: 64 wins, 15.3 against 17.2 µs)
     else tile_n = 64;
   }
+  if (n_tiles_out != nullptr) *n_tiles_out = (N + tile_n - 1) / tile_n;
   switch (tile_n) {
-    case 32: return dispatch<32>(c, a, w, M, N, K, epilogue, status, stream);
-    case 64: return dispatch<64>(c, a, w, M, N, K, epilogue, status, stream);
-    case 128: return dispatch<128>(c, a, w, M, N, K, epilogue, status, stream);
-    case 256: return dispatch<256>(c, a, w, M, N, K, epilogue, status, stream);
+    case 32: return dispatch<32>(c, a, w, M, N, K, epilogue, status, stream, norm);
+    case 64: return dispatch<64>(c, a, w, M, N, K, epilogue, status, stream, norm);
+    case 128: return dispatch<128>(c, a, w, M, N, K, epilogue, status, stream, norm);
+    case 256: return dispatch<256>(c, a, w, M, N, K, epilogue, status, stream, norm);
     default: return DLLM_BAD_ARGUMENT;
   }
+}
+
+DLLM_EXPORT int dllm_gemm_tcgen05(void* c, const void* a, const void* w, int M, int N, int K, int epilogue, int tile_n,
+                                  int* status, cudaStream_t stream) {
+  return gemm_entry(c, a, w, M, N, K, epilogue, tile_n, status, stream, NormArgs{}, nullptr);
+}
+
+// The same product with an RMSNorm folded around it (see NormArgs in gemm_common.cuh), for prefill-sized steps.
+// `a` is the bfloat16 copy of the un-normed residual rows, `w` carries the norm's weight in its columns, and every
+// row of the result is scaled by 1 / sqrt(sum of its `parts_in` sums of squares / K + eps) before the epilogue
+// (store float32, store bfloat16 or SwiGLU).
+DLLM_EXPORT int dllm_gemm_tcgen05_normed(void* c, const void* a, const void* w, int M, int N, int K, int epilogue,
+                                         const float* ssq_in, int parts_in, float eps, int* status,
+                                         cudaStream_t stream) {
+  if (ssq_in == nullptr || parts_in <= 0 || (epilogue != EPI_STORE_F32 && epilogue != EPI_STORE_T &&
+                                             epilogue != EPI_SWIGLU))
+    return DLLM_BAD_ARGUMENT;
+  NormArgs norm{ssq_in, parts_in, 1.0f / (float)K, eps, nullptr, nullptr};
+  return gemm_entry(c, a, w, M, N, K, epilogue, 0, status, stream, norm, nullptr);
+}
+
+// x[M,N] (float32) += A W^T, and for the norm that reads x next: copy_out[M,N] = bfloat16(new x) and
+// ssq_out[tile][m] = the sum of the squares of row m's new values in column tile `tile`; *parts_out = the number of
+// column tiles (what the reader passes as parts_in). N must be a multiple of 16; ssq_out holds M * ceil(N / 32)
+// floats at least.
+DLLM_EXPORT int dllm_gemm_tcgen05_residual_norm(void* x, void* copy_out, float* ssq_out, int* parts_out, const void* a,
+                                                const void* w, int M, int N, int K, int* status,
+                                                cudaStream_t stream) {
+  if (copy_out == nullptr || ssq_out == nullptr || parts_out == nullptr) return DLLM_BAD_ARGUMENT;
+  if ((N & 15) || ((uintptr_t)copy_out & 15) || ((uintptr_t)x & 15)) return DLLM_UNSUPPORTED_SIZE;
+  NormArgs norm{nullptr, 0, 0.f, 0.f, ssq_out, (bf16*)copy_out};
+  return gemm_entry(x, a, w, M, N, K, EPI_RESIDUAL, 0, status, stream, norm, parts_out);
 }
 
 // The q/k/v projection of a prefill-sized step in one kernel: W is [(heads + 2 kv_heads) * head_dim, K], every tile
 // of the product is one or several whole heads (head_dim 32, 64 or 128; rotary_dim equal to head_dim, or no table), its epilogue
 // rotates q and k by the table's angle for each token's position and writes q to q_out and k, v into the paged cache.
-DLLM_EXPORT int dllm_gemm_tcgen05_qkv_rope(const void* a, const void* w, int M, int K, void* q_out, void* cache_base,
-                                           const int* page_table, int max_pages, int page_size, int heads,
-                                           int kv_heads, int head_dim, const float* table, int rotary_dim,
-                                           const int* tok_seq, const int* tok_pos, const int* slots, int write_cache,
-                                           int* status, cudaStream_t stream) {
+static int qkv_rope_entry(const void* a, const void* w, int M, int K, void* q_out, void* cache_base,
+                          const int* page_table, int max_pages, int page_size, int heads, int kv_heads, int head_dim,
+                          const float* table, int rotary_dim, const int* tok_seq, const int* tok_pos, const int* slots,
+                          int write_cache, int* status, cudaStream_t stream, const NormArgs& norm) {
   if (M <= 0) return DLLM_OK;
   if (K <= 0 || (K & 7) || ((uintptr_t)a & 15) || ((uintptr_t)w & 15) || status == nullptr || heads <= 0 ||
       kv_heads <= 0)
@@ -318,12 +400,36 @@ DLLM_EXPORT int dllm_gemm_tcgen05_qkv_rope(const void* a, const void* w, int M, 
   // the wide tiles (which reuse A four times as often: 1.0 to 1.2 PFLOP/s against 0.6)
   bool wide = M >= 1024 && K >= 1024 && (long long)((M + BM - 1) / BM) * ((N + 255) / 256) >= 64;
   switch (head_dim) {
-    case 32: return launch<32, EPI_QKV_ROPE, 32>(nullptr, a, w, M, N, K, status, stream, rope);
+    case 32: return launch<32, EPI_QKV_ROPE, 32>(nullptr, a, w, M, N, K, status, stream, rope, norm);
     case 64:
-      if (wide) return launch<256, EPI_QKV_ROPE, 64>(nullptr, a, w, M, N, K, status, stream, rope);
-      return launch<64, EPI_QKV_ROPE, 64>(nullptr, a, w, M, N, K, status, stream, rope);
+      if (wide) return launch<256, EPI_QKV_ROPE, 64>(nullptr, a, w, M, N, K, status, stream, rope, norm);
+      return launch<64, EPI_QKV_ROPE, 64>(nullptr, a, w, M, N, K, status, stream, rope, norm);
     default:
-      if (wide) return launch<256, EPI_QKV_ROPE, 128>(nullptr, a, w, M, N, K, status, stream, rope);
-      return launch<128, EPI_QKV_ROPE, 128>(nullptr, a, w, M, N, K, status, stream, rope);
+      if (wide) return launch<256, EPI_QKV_ROPE, 128>(nullptr, a, w, M, N, K, status, stream, rope, norm);
+      return launch<128, EPI_QKV_ROPE, 128>(nullptr, a, w, M, N, K, status, stream, rope, norm);
   }
+}
+
+DLLM_EXPORT int dllm_gemm_tcgen05_qkv_rope(const void* a, const void* w, int M, int K, void* q_out, void* cache_base,
+                                           const int* page_table, int max_pages, int page_size, int heads,
+                                           int kv_heads, int head_dim, const float* table, int rotary_dim,
+                                           const int* tok_seq, const int* tok_pos, const int* slots, int write_cache,
+                                           int* status, cudaStream_t stream) {
+  return qkv_rope_entry(a, w, M, K, q_out, cache_base, page_table, max_pages, page_size, heads, kv_heads, head_dim,
+                        table, rotary_dim, tok_seq, tok_pos, slots, write_cache, status, stream, NormArgs{});
+}
+
+// The same with the RMSNorm folded around it: `a` is the bfloat16 copy of the un-normed residual rows, `w` carries
+// the norm's weight in its columns, rows are scaled by 1 / sqrt(sum of parts / K + eps) before rotation and stores.
+DLLM_EXPORT int dllm_gemm_tcgen05_qkv_rope_normed(const void* a, const void* w, int M, int K, void* q_out,
+                                                  void* cache_base, const int* page_table, int max_pages,
+                                                  int page_size, int heads, int kv_heads, int head_dim,
+                                                  const float* table, int rotary_dim, const int* tok_seq,
+                                                  const int* tok_pos, const int* slots, int write_cache,
+                                                  const float* ssq_in, int parts_in, float eps, int* status,
+                                                  cudaStream_t stream) {
+  if (ssq_in == nullptr || parts_in <= 0 || K <= 0) return DLLM_BAD_ARGUMENT;
+  NormArgs norm{ssq_in, parts_in, 1.0f / (float)K, eps, nullptr, nullptr};
+  return qkv_rope_entry(a, w, M, K, q_out, cache_base, page_table, max_pages, page_size, heads, kv_heads, head_dim,
+                        table, rotary_dim, tok_seq, tok_pos, slots, write_cache, status, stream, norm);
 }

@@ -19,7 +19,8 @@ from .build import library
 
 class KernelTable(Structure):
     _fields_ = [(name, c_void_p) for name in ("rmsnorm", "gemm_tcgen05", "gemm_tcgen05_qkv_rope", "attention_prefill",
-                                              "attention_prefill_tcgen05")]
+                                              "attention_prefill_tcgen05", "cast_ssq", "gemm_tcgen05_normed",
+                                              "gemm_tcgen05_qkv_rope_normed", "gemm_tcgen05_residual_norm")]
 
 
 class PreNormLayer(Structure):
@@ -39,11 +40,11 @@ class PrefillStep(Structure):
         ("x", c_void_p), ("normed", c_void_p), ("q", c_void_p), ("attended", c_void_p), ("activations", c_void_p),
         ("tok_seq", c_void_p), ("tok_pos", c_void_p), ("slots", c_void_p), ("cu_seqlens", c_void_p),
         ("start", c_void_p), ("tile_seq", c_void_p), ("tile_first", c_void_p), ("status", c_void_p),
-        ("tokens", c_int), ("tiles", c_int), ("max_context", c_int),
+        ("row_ssq", c_void_p), ("tokens", c_int), ("tiles", c_int), ("max_context", c_int), ("norms_folded", c_int),
     ]
 
 
-_STAGES = ("the norm before attention", "the q/k/v product", "attention", "the output product",
+_STAGES = ("the norm before attention (or the step's first sums of squares)", "the q/k/v product", "attention", "the output product",
            "the norm before the feed-forward", "the gate/up product", "the down product")
 ENABLED = True
 """Turn off to drive every step from Python (measurements of the difference, debugging)."""
@@ -58,7 +59,8 @@ class PreNormLayers:
 
     MIN_TOKENS = ops.GEMV_MAX_ROWS + 1
 
-    def __init__(self, layers: list[PreNormLayer], widths: dict, keep: list) -> None:
+    def __init__(self, layers: list[PreNormLayer], widths: dict, keep: list, norms_folded: bool) -> None:
+        self.norms_folded = norms_folded
         self.count = len(layers)
         self.array = (PreNormLayer * self.count)(*layers)
         self.widths = widths
@@ -80,7 +82,7 @@ class PreNormLayers:
         rt = model.rt
         if rt.dtype != torch.bfloat16 or model.spec.schedule or not model.blocks:
             return None
-        layers, keep = [], []
+        layers, keep, folded = [], [], []
         for block, view in zip(model.blocks, model._views):
             if type(block) is not PreNormBlock:
                 return None
@@ -109,10 +111,14 @@ class PreNormLayers:
                      ffn.w_down, table, view]
             if ffn.hidden_size != mixer.hidden_size:
                 return None
+            folded.append(bool(getattr(block.mixer_norm, "folded", False)) and
+                          bool(getattr(block.feed_forward_norm, "folded", False)) and mixer.hidden_size % 16 == 0)
+        if any(folded) and not all(folded) or len({layer.hidden for layer in layers}) > 1 and any(folded):
+            return None  # (a model that mixes folded and unfolded norms, or widths, keeps the Python path)
         widths = {"hidden": max(layer.hidden for layer in layers),
                   "q": max(layer.heads * layer.head_dim for layer in layers),
                   "intermediate": max(layer.intermediate for layer in layers)}
-        return cls(layers, widths, keep)
+        return cls(layers, widths, keep, norms_folded=all(folded))
 
     def libraries(self) -> set[str]:
         names = {"step_launcher", "elementwise", "gemm_tcgen05", "attention_prefill"}
@@ -129,7 +135,10 @@ class PreNormLayers:
             _address("gemm_tcgen05", "dllm_gemm_tcgen05_qkv_rope"),
             _address("attention_prefill", "dllm_attention_prefill"),
             _address("attention_prefill_tcgen05", "dllm_attention_prefill_tcgen05")
-            if self._uses_tcgen05_attention else None)
+            if self._uses_tcgen05_attention else None,
+            _address("elementwise", "dllm_cast_ssq"), _address("gemm_tcgen05", "dllm_gemm_tcgen05_normed"),
+            _address("gemm_tcgen05", "dllm_gemm_tcgen05_qkv_rope_normed"),
+            _address("gemm_tcgen05", "dllm_gemm_tcgen05_residual_norm"))
         function = library("step_launcher").dllm_prefill_pre_norm_layers
         function.argtypes = [POINTER(KernelTable), POINTER(PreNormLayer), c_int, POINTER(PrefillStep), POINTER(c_int),
                              POINTER(c_int), c_void_p]
@@ -149,7 +158,10 @@ class PreNormLayers:
             ws.buffer("ffn_act", (n, self.widths["intermediate"]), torch.bfloat16).data_ptr(),
             batch.tok_seq.data_ptr(), batch.tok_pos.data_ptr(), batch.slots.data_ptr(), batch.cu_seqlens.data_ptr(),
             batch.start.data_ptr(), batch.tile_seq.data_ptr(), batch.tile_first.data_ptr(),
-            ops._status_word().data_ptr(), n, batch.n_tiles, batch.max_context)
+            ops._status_word().data_ptr(),
+            ws.buffer("row_ssq", (n, -(-self.widths["hidden"] // 32)), torch.float32).data_ptr()
+            if self.norms_folded else None,
+            n, batch.n_tiles, batch.max_context, 1 if self.norms_folded else 0)
         launched, failed_at = c_int(0), c_int(-1)
         status = self._function(byref(self._table), self.array, self.count, byref(step), byref(launched),
                                 byref(failed_at), ops._stream())

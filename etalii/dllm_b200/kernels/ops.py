@@ -37,6 +37,15 @@ _prototypes = {
     ("gemm_tcgen05", "dllm_gemm_tcgen05_qkv_rope"): [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                                      c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p,
                                                      c_void_p, c_void_p, c_int, c_void_p, c_void_p],
+    ("gemm_tcgen05", "dllm_gemm_tcgen05_normed"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
+                                                   c_int, c_float, c_void_p, c_void_p],
+    ("gemm_tcgen05", "dllm_gemm_tcgen05_residual_norm"): [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                          c_int, c_int, c_int, c_void_p, c_void_p],
+    ("gemm_tcgen05", "dllm_gemm_tcgen05_qkv_rope_normed"): [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                                                            c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                                            c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                                            c_int, c_float, c_void_p, c_void_p],
+    ("elementwise", "dllm_cast_ssq"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
     ("gemv", "dllm_gemv_bf16"): [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int,
                                  c_void_p, c_longlong, c_void_p],
     ("mlp_decode", "dllm_mlp_decode"): [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
@@ -369,6 +378,48 @@ def head_argmax(out_tokens: torch.Tensor, a: torch.Tensor, w: torch.Tensor, scra
         lambda: f"M={m} N={n} K={k}")
     _check(_fn("gemv", "dllm_argmax_candidates")(out_tokens.data_ptr(), scratch.data_ptr(), m, -(-n // 16),
                                                  _stream()), "head_argmax choice")
+
+
+def cast_ssq(copy: torch.Tensor, ssq: torch.Tensor, x: torch.Tensor) -> None:
+    """copy = bfloat16(x) and ssq[r] = sum of x[r]^2: what a norm folded around the next tile product needs of rows
+    that no product's epilogue has written (a step's first rows)."""
+    _cuda(copy, ssq, x)
+    rows, hidden = x.shape
+    assert x.dtype == torch.float32 and copy.dtype == torch.bfloat16 and tuple(copy.shape) == (rows, hidden)
+    assert ssq.dtype == torch.float32 and ssq.numel() >= rows
+    _check(_fn("elementwise", "dllm_cast_ssq")(copy.data_ptr(), ssq.data_ptr(), x.data_ptr(), rows, hidden, _stream()),
+           "cast_ssq", lambda: f"hidden={hidden} must be a multiple of 4")
+
+
+def gemm_normed(c: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int, ssq: torch.Tensor, parts: int,
+                eps: float) -> None:
+    """c = epilogue((a @ w^T) * 1 / sqrt(sum(ssq[:parts, row]) / K + eps)): the tile product with an RMSNorm folded
+    around it. `a` is the bfloat16 copy of the un-normed rows, `w` carries the norm's weight in its columns;
+    epilogues EPI_STORE_F32, EPI_STORE_T and EPI_SWIGLU."""
+    _cuda(c, a, w, ssq)
+    m, k = a.shape
+    n = w.shape[0]
+    assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and ssq.dtype == torch.float32
+    assert ssq.numel() >= m * parts
+    _check(_fn("gemm_tcgen05", "dllm_gemm_tcgen05_normed")(
+        c.data_ptr(), a.data_ptr(), w.data_ptr(), m, n, k, epilogue, ssq.data_ptr(), int(parts), float(eps),
+        _status_word().data_ptr(), _stream()), "gemm_normed", lambda: f"M={m} N={n} K={k}")
+
+
+def gemm_residual_norm(x: torch.Tensor, copy: torch.Tensor, ssq: torch.Tensor, a: torch.Tensor,
+                       w: torch.Tensor) -> int:
+    """x (float32) += a @ w^T; copy = bfloat16(new x); ssq[tile, row] = the sum of the squares of the new values of
+    the row in each tile of columns. Returns the number of tiles (the reader's `parts`). N a multiple of 16."""
+    _cuda(x, copy, ssq, a, w)
+    m, k = a.shape
+    n = w.shape[0]
+    assert x.dtype == torch.float32 and tuple(x.shape) == (m, n) and copy.dtype == torch.bfloat16
+    assert tuple(copy.shape) == (m, n) and ssq.dtype == torch.float32 and ssq.numel() >= m * (-(-n // 32))
+    parts = c_int(0)
+    _check(_fn("gemm_tcgen05", "dllm_gemm_tcgen05_residual_norm")(
+        x.data_ptr(), copy.data_ptr(), ssq.data_ptr(), ctypes.addressof(parts), a.data_ptr(), w.data_ptr(), m, n, k,
+        _status_word().data_ptr(), _stream()), "gemm_residual_norm", lambda: f"M={m} N={n} (multiple of 16) K={k}")
+    return parts.value
 
 
 def gemm_qkv_rope_supported(cache, rotary_dim: int, has_table: bool) -> bool:

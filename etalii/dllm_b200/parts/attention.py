@@ -71,6 +71,14 @@ class Attention:
         if self.position is not None:
             self.position.bind({}, rt)
 
+    def absorb_input_scale(self, scale: torch.Tensor) -> bool:
+        """Takes a per-input-feature scale (the weight of the norm in front) into the columns of the q/k/v matrix.
+        Only in bfloat16, where products round anyway; the float32 path keeps the norm's own multiplication."""
+        if self.w_qkv is None or self.w_qkv.dtype != torch.bfloat16:
+            return False
+        self.w_qkv = (self.w_qkv.float() * scale.to(self.w_qkv.device).float()[None, :]).to(torch.bfloat16).contiguous()
+        return True
+
     def forward(self, h: torch.Tensor, residual: torch.Tensor, batch, cache, rt, write_cache: bool = True) -> None:
         """h: normed activations [tokens, hidden]; adds the attention output to `residual` (float32) in place."""
         n = batch.n_tokens

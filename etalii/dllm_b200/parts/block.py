@@ -24,6 +24,10 @@ class PreNormBlock:
         self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
         self.parts = {"mixer": mixer, "feed_forward": feed_forward, "mixer_norm": mixer_norm,
                       "feed_forward_norm": feed_forward_norm}
+        # each norm feeds exactly one part here, so its weight may move into that part's first product
+        for norm, consumer in ((mixer_norm, mixer), (feed_forward_norm, feed_forward)):
+            if hasattr(norm, "give_weight_to"):
+                norm.give_weight_to(consumer)
 
     def forward(self, x, batch, cache, rt, write_cache: bool = True) -> None:
         self.mixer.forward(normed(self.mixer_norm, self.mixer, x, rt), x, batch, cache, rt, write_cache)

@@ -33,6 +33,15 @@ class SwiGLU:
         self.w_gate_up = fused.contiguous().to(rt.device)
         self.w_down = rt.to_device(tensors["down"], rt.dtype)
 
+    def absorb_input_scale(self, scale: torch.Tensor) -> bool:
+        """Takes a per-input-feature scale (the weight of the norm in front) into the columns of the gate/up
+        matrix (bfloat16 only)."""
+        if self.w_gate_up is None or self.w_gate_up.dtype != torch.bfloat16:
+            return False
+        self.w_gate_up = (self.w_gate_up.float() * scale.to(self.w_gate_up.device).float()[None, :]) \
+            .to(torch.bfloat16).contiguous()
+        return True
+
     def forward(self, h: torch.Tensor, residual: torch.Tensor, batch, rt) -> None:
         rows = h.shape[0]
         if ops.FUSED_FEED_FORWARD and isinstance(h, NormedInput) and h.x is residual and \

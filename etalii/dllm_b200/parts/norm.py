@@ -37,6 +37,19 @@ class RMSNorm:
 
     def bind(self, tensors, rt) -> None:
         self.weight = rt.to_device(tensors["weight"], torch.float32)
+        self.folded = False
+
+    def give_weight_to(self, consumer) -> bool:
+        """Offers the norm's weight to the part that reads the normed rows: norm(x) W^T = (x / rms(x)) (W diag(w))^T,
+        so a consumer whose first operation is a product may take w into the columns of its weight
+        (`absorb_input_scale(w) -> bool`). The norm then keeps a weight of ones: every kernel that applies it still
+        gives the right result, and kernels that fold the norm around the product need no weight at all."""
+        absorb = getattr(consumer, "absorb_input_scale", None)
+        if self.folded or absorb is None or not absorb(self.weight):
+            return False
+        self.weight = torch.ones_like(self.weight)
+        self.folded = True
+        return True
 
     def forward(self, x: torch.Tensor, rt, rows: torch.Tensor | None = None, n_rows: int | None = None,
                 name: str = "normed") -> torch.Tensor:

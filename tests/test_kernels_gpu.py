@@ -916,3 +916,44 @@ def test_head_argmax_chooses_what_the_logits_would(m, n, k, normed):
     assert got[0].item() == 0 and (m <= 2 or got[2].item() == 0)
     finite = [r for r in range(m) if r not in (0, 2)]
     assert got[finite].tolist() == logits[finite].argmax(dim=1).tolist()
+
+
+@pytest.mark.parametrize("m,hidden,inner", [(130, 576, 1536), (300, 144, 96), (2048, 576, 576), (65, 2048, 512)])
+def test_tile_products_with_the_norm_folded_around_them(m, hidden, inner):
+    """x += a W^T with the bfloat16 copy and the sums of squares of the new rows from the epilogue, then a product
+    that reads the copy and scales its rows: together RMSNorm(x) W2^T without a norm kernel. Against float64."""
+    x0 = _randn((m, hidden), torch.float32, 1, 2.0)
+    a = _randn((m, inner), torch.bfloat16, 2)
+    w = _randn((hidden, inner), torch.bfloat16, 3, 0.05)
+    x = x0.clone()
+    copy = torch.full((m, hidden), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ssq = torch.full((m * (-(-hidden // 32)),), float("nan"), dtype=torch.float32, device=DEV)
+    parts = ops().gemm_residual_norm(x, copy, ssq, a, w)
+    want_x = x0.double() + a.double() @ w.double().T
+    assert rel_error(x.cpu(), want_x.cpu()) <= 2e-5
+    assert torch.equal(copy, x.to(torch.bfloat16))
+    sums = ssq[: m * parts].view(parts, m).sum(dim=0)
+    assert rel_error(sums.cpu(), (x.double() ** 2).sum(dim=1).cpu()) <= 1e-5
+    # the reader: SwiGLU and plain stores of (norm(x) * weight) @ w2^T with the weight folded into w2's columns
+    eps = 1e-5
+    norm_w = _randn((hidden,), torch.float32, 4, 0.1) + 1
+    w2 = _randn((256, hidden), torch.bfloat16, 5, 0.05)
+    folded = (w2.float() * norm_w[None, :]).to(torch.bfloat16)
+    normed = x.double() / torch.sqrt((x.double() ** 2).mean(dim=1, keepdim=True) + eps)
+    prod = normed @ folded.double().T
+    got = torch.empty((m, 256), dtype=torch.float32, device=DEV)
+    ops().gemm_normed(got, copy, folded, ops().EPI_STORE_F32, ssq, parts, eps)
+    assert rel_error(got.cpu(), prod.float().cpu()) <= 8e-3
+    act = torch.empty((m, 128), dtype=torch.bfloat16, device=DEV)
+    ops().gemm_normed(act, copy, folded, ops().EPI_SWIGLU, ssq, parts, eps)
+    gate, up = prod[:, 0::2], prod[:, 1::2]
+    assert rel_error(act.float().cpu(), (gate * torch.sigmoid(gate) * up).float().cpu()) <= 1.2e-2
+    # a step's first rows: the cast kernel gives the copy and one sum a row
+    copy1 = torch.empty_like(copy)
+    ssq1 = torch.empty(m, dtype=torch.float32, device=DEV)
+    ops().cast_ssq(copy1, ssq1, x)
+    assert torch.equal(copy1, copy) and rel_error(ssq1.cpu(), sums.cpu()) <= 1e-6
+    again = torch.empty_like(got)
+    ops().gemm_normed(again, copy1, folded, ops().EPI_STORE_F32, ssq1, 1, eps)
+    assert rel_error(again.cpu(), got.cpu()) <= 1e-5
+    ops().raise_if_failed()
