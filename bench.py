@@ -2,7 +2,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--repeats R] [--layers L] [--impl ours|reference]
                     [--shape smollm2-135m|smollm2-1.7b|llama-3.1-8b] [--batch B] [--no-points]
-                    [--profile decode|prefill|kernels|gemm|attention|stream]
+                    [--profile decode|prefill|kernels|ablate|ablate-fused|feed-forward|gemm|attention|stream]
 
 Default workload: the SmolLM2-135M shape (30 layers, hidden 576, 9 heads, 3 kv heads, head_dim 64, intermediate 1536,
 vocabulary 49152, tied head) with seeded random bfloat16 weights; a batch of 8 sequences with unequal prompt lengths
@@ -169,8 +169,8 @@ def prefill_run(engine, vocab, warmup, repeats=5):
 
 
 def gemm_table() -> int:
-    """Times the tile products alone (CUDA events, 20 launches after 3) at layer shapes of the three model sizes:
-    the tcgen05 kernel at each tile width and the mma.sync kernel, in TFLOP/s."""
+    """Times the tile products alone (CUDA events around a CUDA graph of 20 dependent launches, warm) at layer shapes
+    of the three model sizes: the tcgen05 kernel at each tile width and the mma.sync kernel, in TFLOP/s."""
     import torch
 
     from etalii.dllm_b200.kernels import ops
@@ -184,24 +184,32 @@ def gemm_table() -> int:
         for _ in range(3):
             ops.gemm(c, a, w, epilogue, kernel=kernel, tile_n=tile_n)
         torch.cuda.synchronize()
-        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        begin.record()
-        for _ in range(20):
-            ops.gemm(c, a, w, epilogue, kernel=kernel, tile_n=tile_n)
-        end.record()
+        graph = torch.cuda.CUDAGraph()  # 20 dependent launches without the host between them
+        with torch.cuda.graph(graph):
+            for _ in range(20):
+                ops.gemm(c, a, w, epilogue, kernel=kernel, tile_n=tile_n)
+        graph.replay()
         torch.cuda.synchronize()
+        best = None
+        for _ in range(3):
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record()
+            graph.replay()
+            end.record()
+            torch.cuda.synchronize()
+            ms = begin.elapsed_time(end) / 20
+            best = ms if best is None else min(best, ms)
         ops.raise_if_failed()
-        ms = begin.elapsed_time(end) / 20
-        return ms * 1e3, 2 * m * n * k / ms / 1e9
+        return best * 1e3, 2 * m * n * k / best / 1e9
 
     shapes = [(2048, 576, 576, ops.EPI_RESIDUAL), (2048, 576, 1536, ops.EPI_RESIDUAL), (2048, 3072, 576, ops.EPI_SWIGLU),
               (2048, 2048, 8192, ops.EPI_RESIDUAL), (2048, 16384, 2048, ops.EPI_SWIGLU),
               (2048, 4096, 4096, ops.EPI_RESIDUAL), (2048, 28672, 4096, ops.EPI_SWIGLU),
               (2048, 4096, 14336, ops.EPI_RESIDUAL), (8192, 4096, 4096, ops.EPI_STORE_T)]
-    print("M N K epilogue | tcgen05 tile 64 | 128 | 256 | chosen | mma.sync   (microseconds, TFLOP/s)")
+    print("M N K epilogue | tcgen05 tile 32 | 64 | 128 | 256 | chosen | mma.sync   (microseconds, TFLOP/s)")
     for m, n, k, epilogue in shapes:
         cells = []
-        for tile_n in (64, 128, 256, 0):
+        for tile_n in (32, 64, 128, 256, 0):
             if tile_n and n % tile_n:
                 cells.append("-")
                 continue
@@ -452,6 +460,108 @@ def kernel_shares(engine, prompts, steps=3):
             for name in sorted(totals, key=lambda n: -totals[n])}
 
 
+def ablation_table(engine, prompts, layers, fused_feed_forward=False) -> int:
+    """What each kind of launch costs inside the decode step: the step's CUDA graph timed whole and with one kind of
+    launch left out (the results are then wrong, the timing is what is read). Printed per layer."""
+    from etalii.dllm_b200.kernels import ops
+
+    ops.FUSED_FEED_FORWARD = fused_feed_forward
+    real = {name: getattr(ops, name) for name in ("gemv_qkv_rope", "attention_decode_cluster", "gemm", "mlp_decode",
+                                                  "head_argmax")}
+
+    def run(label):
+        engine._graphs.clear()
+        ms, launches, _ = decode_run(engine, prompts, 64, 3)
+        print(f"{label}: {ms / 64 * 1e3:.1f} us per step, {launches} launches", flush=True)
+        return ms / 64 * 1e3
+
+    full = run("full step")
+
+    def without(label, per=layers, **patch):
+        for name, function in patch.items():
+            setattr(ops, name, function)
+        try:
+            t = run("without " + label)
+        finally:
+            for name in patch:
+                setattr(ops, name, real[name])
+        print(f"   -> {label}: {(full - t) / per:.2f} us per {'layer' if per == layers else 'step'}", flush=True)
+
+    def nothing(*args, **kwargs):
+        return None
+
+    def gemm_without(leave_out):
+        def gemm(c, a, w, epilogue=1, **kwargs):
+            if leave_out(w, epilogue):
+                return None
+            return real["gemm"](c, a, w, epilogue, **kwargs)
+        return gemm
+
+    hidden = engine.model.hidden_size
+    without("attention", attention_decode_cluster=nothing)
+    without("q/k/v product", gemv_qkv_rope=nothing)
+    without("output product", gemm=gemm_without(lambda w, e: e == ops.EPI_RESIDUAL and w.shape[1] == hidden))
+    if fused_feed_forward:
+        without("feed-forward (one kernel)", mlp_decode=nothing)
+    else:
+        without("gate/up product", gemm=gemm_without(lambda w, e: e == ops.EPI_SWIGLU))
+        without("down product", gemm=gemm_without(lambda w, e: e == ops.EPI_RESIDUAL and w.shape[1] != hidden))
+    without("head product and choice", per=1, head_argmax=nothing)
+    ops.FUSED_FEED_FORWARD = False
+    return 0
+
+
+def feed_forward_chain(config_dict, rows=8, links=30) -> int:
+    """The one-kernel feed-forward against the two kernels it replaces, each as a chain of `links` dependent launches
+    with weights of their own (more than L2 holds together) in a CUDA graph: microseconds per link."""
+    import torch
+
+    from etalii.dllm_b200.kernels import ops
+
+    device = "cuda:0"
+    hidden, inter = config_dict["hidden_size"], config_dict["intermediate_size"]
+    torch.manual_seed(0)
+    x = torch.randn(rows, hidden, device=device)
+    norm_w = torch.ones(hidden, device=device)
+    gate_up = [(torch.randn(2 * inter, hidden, device=device) * 0.05).bfloat16() for _ in range(links)]
+    down = [(torch.randn(hidden, inter, device=device) * 0.05).bfloat16() for _ in range(links)]
+    scratch = torch.zeros(ops.mlp_decode_scratch(rows, hidden, inter), device=device)
+    tickets = torch.zeros(8, dtype=torch.int32, device=device)
+    act = torch.zeros(rows, inter, device=device, dtype=torch.bfloat16)
+
+    def timed(body, name):
+        for _ in range(2):
+            body()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            body()
+        graph.replay()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(5):
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record()
+            graph.replay()
+            end.record()
+            torch.cuda.synchronize()
+            times.append(begin.elapsed_time(end) * 1e3 / links)
+        print(f"{name}: {min(times):.2f} us per link ({rows} rows, hidden {hidden}, intermediate {inter})", flush=True)
+
+    def two_kernels():
+        for i in range(links):
+            ops.gemm(act, x, gate_up[i], ops.EPI_SWIGLU, norm_weight=norm_w, eps=1e-5)
+            ops.gemm(x, act, down[i], ops.EPI_RESIDUAL)
+
+    def one_kernel():
+        for i in range(links):
+            ops.mlp_decode(x, norm_w, 1e-5, gate_up[i], down[i], scratch, tickets)
+
+    timed(two_kernels, "norm + gate/up + SwiGLU, then down + residual (two kernels)")
+    timed(one_kernel, "the same in one kernel")
+    return 0
+
+
 REFERENCE_BUDGET_S = 150.0
 
 
@@ -565,7 +675,8 @@ def main() -> int:
     parser.add_argument("--impl", default="ours", choices=("ours", "reference", "reference-worker"))
     parser.add_argument("--budget", type=float, default=REFERENCE_BUDGET_S, help=argparse.SUPPRESS)
     parser.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 and the float32 points")
-    parser.add_argument("--profile", choices=("decode", "prefill", "gemm", "attention", "stream", "kernels"),
+    parser.add_argument("--profile", choices=("decode", "prefill", "gemm", "attention", "stream", "kernels", "ablate",
+                                              "ablate-fused", "feed-forward"),
                         help="run only a few decode steps (or one prefill) and print no JSON: a small case for ncu")
     args = parser.parse_args()
     if args.impl == "reference-worker":
@@ -608,6 +719,10 @@ def main() -> int:
     if args.profile == "prefill":
         print(f"profile prefill: {prefill_run(engine, vocab, warmup=1, repeats=1):.4f} ms")
         return 0
+    if args.profile in ("ablate", "ablate-fused"):
+        return ablation_table(engine, prompts, args.layers, fused_feed_forward=args.profile == "ablate-fused")
+    if args.profile == "feed-forward":
+        return feed_forward_chain(config_dict, rows=args.batch)
     if args.profile == "kernels":
         for name, row in kernel_shares(engine, prompts).items():
             print(f"{row['share'] * 100:5.1f} %  {row['launches_per_step']:5.1f} x {row['us']:7.2f} us  {name}")
