@@ -658,7 +658,9 @@ def reference_arm(args) -> int:
                       f"benchmark's configuration and cut after {report['seconds']:.0f} s: it had fed "
                       f"{report['prompt_tokens_fed']} of the batch's {report['prompt_tokens_total']} prompt tokens "
                       f"({rate:.2f} tokens/s, about {hours:.1f} h for the prompts alone) and decoded "
-                      f"{report['decoded']} tokens"}))
+                      f"{report['decoded']} tokens of its shortest prompt"
+                      + (f" at {report['decoded'] / report['decode_s']:.2f} tokens/s (one sequence; it holds one at a "
+                         f"time)" if report["decoded"] and report["decode_s"] > 0 else "")}))
     return 0
 
 
