@@ -24,6 +24,9 @@ def decode_chunk(sequences: int, kv_heads: int, max_context: int, head_dim: int 
     return 1024
 
 
+KV_REQUEST_LIMIT = 32 << 20
+"""The decode q/k/v kernel asks L2 for the layer's cache pages only while they are at most this many bytes."""
+
 TCGEN05_ATTENTION_FROM = {64: 512, 128: 192}
 """Prefill steps whose longest context is above this (by head size) take the tcgen05 attention kernel. Measured: with
 heads of 128 it leads from 256 keys on (1.4 to 1.8 times from 384 on, one prompt or eight); with heads of 64 it leads
@@ -91,11 +94,14 @@ class Attention:
             if isinstance(h, NormedInput) and not fuses_norm(self.w_qkv):
                 h = h.tensor()
             pending = isinstance(h, NormedInput)
-            # (in a decode step of few sequences, where latency and not bandwidth bounds the attention kernel, it also
-            # asks L2 for the keys and values that kernel is about to read)
+            # (in a decode step of a few sequences whose keys and values are a small part of L2, it also asks L2 for
+            # the pages the attention kernel is about to read: measured, it gains 2 % of the step at the 135M shape
+            # with eight sequences and costs 3 to 4 % with one sequence or where a layer's pages are tens of MB)
+            pages_bytes = n * batch.max_context * 4 * self.num_kv_heads * self.head_dim
+            ask = batch.is_decode and 2 <= n <= 16 and pages_bytes <= KV_REQUEST_LIMIT
             ops.gemv_qkv_rope(h.x if pending else h, self.w_qkv, q, cache, table, rotary_dim, self.num_heads, batch,
                               write_cache, norm_weight=h.weight if pending else None, eps=h.eps if pending else 0.0,
-                              prefetch_window=(self.window or 0) if batch.is_decode and n <= 16 else -1)
+                              prefetch_window=(self.window or 0) if ask else -1)
         elif rt.dtype == torch.bfloat16 and ops.gemm_qkv_rope_supported(cache, rotary_dim, table is not None):
             # prefill-sized: the tile product ends in rotation and cache write
             hidden = h.tensor() if isinstance(h, NormedInput) else h
