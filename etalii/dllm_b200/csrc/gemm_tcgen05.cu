@@ -6,7 +6,8 @@
 //   warp 1   allocates tensor memory; one lane issues tcgen05.mma (cta_group::1, kind::f16, M=128, N=BN, K=16) four
 //            per stage and commits each stage back to the producer (tcgen05.commit -> mbarrier), then commits the
 //            whole accumulator to the epilogue;
-//   warps 2-5 read the accumulator (tcgen05.ld 32x32b, a lane per row) and apply the epilogue: store float32 or
+//   warps 2.. read the accumulator (tcgen05.ld 32x32b, a lane per row; four warps for tiles up to 64 columns, eight
+//            for wider ones: two per 32 rows, with half the columns each) and apply the epilogue: store float32 or
 //            bfloat16, add into the float32 residual, or SwiGLU on interleaved gate/up columns.
 // Rows of A beyond M and columns of K beyond the matrix are zero-filled by TMA; rows of W beyond N give columns
 // that are never stored. No multicast, no clusters. Every wait on an mbarrier is bounded: after the limit the role
@@ -18,7 +19,6 @@ namespace {
 using namespace tc5;
 typedef __nv_bfloat16 bf16;
 constexpr int BM = 128, BK = 64, UMMA_K = 16;
-constexpr int THREADS = 192;
 
 // DEEP: a ring of nine or ten stages (about 215 KB) for a block that has its multiprocessor to itself: a product
 // with no more tiles than the device has multiprocessors and a short reduction then brings a tile's whole operand
@@ -32,6 +32,12 @@ template <int BN, bool DEEP = false> struct Shape {
   static constexpr int STAGES = DEEP ? (220 * 1024) / (A_BYTES + B_BYTES) : (BN >= 256 ? 4 : (BN >= 128 ? 3 : 4));
   static constexpr size_t SMEM = (size_t)STAGES * (A_BYTES + B_BYTES) + 1024;
   static constexpr int BLOCKS_PER_SM = (DEEP || BN >= 256) ? 1 : 2;
+  // Epilogue warps: one per quarter of the tensor memory's lanes, or two that take half the columns each. A row's
+  // epilogue is a chain of loads and special functions, so wide tiles gain from twice the warps (2048 x 2048 x 8192
+  // with the residual: 128-wide 70 against 114 µs, 256-wide 61 against 64); narrow tiles of short products lose
+  // (2048 x 576 x 576, 64-wide: 9.5 against 8.6 µs), their blocks being set up and torn down once per tile.
+  static constexpr int EPI_WARPS = BN >= 128 ? 8 : 4;
+  static constexpr int THREADS = 64 + 32 * EPI_WARPS;
 };
 
 // A persistent block: it takes tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... of the m_tiles x n_tiles grid
@@ -39,7 +45,7 @@ template <int BN, bool DEEP = false> struct Shape {
 // tiles; the accumulator alternates between two halves of the block's tensor memory, so the epilogue of one tile
 // overlaps the products of the next.
 template <int BN, int EPI, bool DEEP, int HD>
-__global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
+__global__ void __launch_bounds__(Shape<BN, DEEP>::THREADS, Shape<BN, DEEP>::BLOCKS_PER_SM) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                const __grid_constant__ CUtensorMap map_w,
                                                                void* __restrict__ c, int M, int N, int K,
                                                                int* __restrict__ status, RopeArgs rope, int m_tiles,
@@ -56,7 +62,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }  // 4 epilogue warps
+    for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], S::EPI_WARPS); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -119,8 +125,12 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
       }
     }
   } else {
-    // epilogue warps 2..5: warp w may read tensor-memory lanes 32 * (w % 4) .. + 31
-    int quarter = warp & 3;
+    // epilogue warps: warp w may read tensor-memory lanes 32 * (w % 4) .. + 31; where there are eight, warps 2..5
+    // take the first half of a tile's columns and warps 6..9 the second
+    constexpr int HALVES = S::EPI_WARPS / 4;
+    int quarter = warp & 3, half = HALVES == 2 ? (warp - 2) >> 2 : 0;
+    constexpr int HALF = BN / HALVES;
+    int c0 = half * HALF;
     int lt = 0;
     for (int t = blockIdx.x; t < total; t += gridDim.x, ++lt) {
       int buf = lt & 1;
@@ -129,12 +139,13 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
       // (narrow tiles: the row's old residual values are all asked for before the accumulator is read, so their
       // round trip runs under the wait for the products instead of after it, once per 16 columns)
       constexpr bool EARLY = EPI == EPI_RESIDUAL && BN <= 64;
-      float4 old[EARLY ? BN / 4 : 1];
+      float4 old[EARLY ? HALF / 4 : 1];
       if (EARLY && norm.copy_out != nullptr && m < M) {
 #pragma unroll
-        for (int i = 0; i < BN / 4; ++i)
-          old[i] = n0 + 4 * i < N ? *reinterpret_cast<const float4*>((const float*)c + (size_t)m * N + n0 + 4 * i)
-                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int i = 0; i < HALF / 4; ++i)
+          old[i] = n0 + c0 + 4 * i < N
+                       ? *reinterpret_cast<const float4*>((const float*)c + (size_t)m * N + n0 + c0 + 4 * i)
+                       : make_float4(0.f, 0.f, 0.f, 0.f);
       }
       // the token's position and cache page (q/k/v epilogue): a chain of dependent loads that runs under the products
       int pos = 0, page = 0;
@@ -154,36 +165,50 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       unsigned acc = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(buf * S::ACC_COLS);
+      auto release_accumulator = [&]() {  // this warp's last values are in registers: the accumulator may be reused
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[buf]);
+      };
       if (EPI == EPI_QKV_ROPE) {
-        // the tile is BN / HD whole heads: the thread holds its token's head, one after the other, rotates the pairs
-        // (i, i + rotary_dim / 2) and writes the query, or the key / value into the token's cache row
+        // The tile is BN / HD whole heads. The thread holds W rotary pairs (i, i + HD / 2) of its token's head at a
+        // time: whole heads, one after the other; with eight warps each half of them takes half of the heads where
+        // the tile has at least two, else half of the one head's pairs. It rotates them and writes the query, or
+        // the key / value into the token's cache row.
         constexpr int HEAD = HD > 0 ? HD : BN;  // (HD is 0 only in instantiations that never take this branch)
+        constexpr int SEGS = BN / HEAD;
+        constexpr bool SPLIT_HEAD = HALVES == 2 && SEGS == 1 && HEAD >= 64;
+        constexpr int W = SPLIT_HEAD ? HEAD / 4 : HEAD / 2;
         int heads = rope.heads, nkv = rope.cache.kv_heads;
+        constexpr bool SPLIT_SEGS = HALVES == 2 && SEGS >= 2;
+        int seg_begin = SPLIT_SEGS ? half * (SEGS / 2) : 0;
+        int seg_end = SPLIT_SEGS ? seg_begin + SEGS / 2 : ((HALVES == 1 || SPLIT_HEAD || half == 0) ? SEGS : 0);
+        int first_pair = SPLIT_HEAD ? half * W : 0;
+        if (seg_begin >= seg_end) release_accumulator();
 #pragma unroll 1
-        for (int seg = 0; seg < BN / HEAD; ++seg) {
-          float f[HEAD];
+        for (int seg = seg_begin; seg < seg_end; ++seg) {
+          float lo[W], hi[W];
 #pragma unroll
-          for (int col = 0; col < HEAD; col += 16) {
+          for (int col = 0; col < W; col += 16) {
             unsigned v[16];
-            tmem_load16(acc + (unsigned)(seg * HEAD + col), v);
+            tmem_load16(acc + (unsigned)(seg * HEAD + first_pair + col), v);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) f[col + i] = __uint_as_float(v[i]) * scale_row;
+            for (int i = 0; i < 16; ++i) lo[col + i] = __uint_as_float(v[i]) * scale_row;
+            tmem_load16(acc + (unsigned)(seg * HEAD + HEAD / 2 + first_pair + col), v);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) hi[col + i] = __uint_as_float(v[i]) * scale_row;
           }
-          if (seg == BN / HEAD - 1) {  // the last values are in registers: the accumulator may be reused
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[buf]);
-          }
-          int head = n_tile * (BN / HEAD) + seg;
+          if (seg == seg_end - 1) release_accumulator();
+          int head = n_tile * SEGS + seg;
           if (m >= M || head >= heads + 2 * nkv || !(head < heads || rope.write_cache)) continue;
           if (rope.table != nullptr && head < heads + nkv) {
-            const float2* cs = rope.table + (size_t)pos * (rope.rotary_dim / 2);
+            const float2* cs = rope.table + (size_t)pos * (rope.rotary_dim / 2) + first_pair;
 #pragma unroll
-            for (int i = 0; i < HEAD / 2; ++i) {  // rotary_dim == head_dim here: the partner sits half a head away
+            for (int i = 0; i < W; ++i) {  // rotary_dim == head_dim here: the partner sits half a head away
               float2 tc = cs[i];
-              float x = f[i], y = f[i + HEAD / 2];
-              f[i] = fmaf(x, tc.x, -(y * tc.y));
-              f[i + HEAD / 2] = fmaf(x, tc.y, y * tc.x);
+              float x = lo[i], y = hi[i];
+              lo[i] = fmaf(x, tc.x, -(y * tc.y));
+              hi[i] = fmaf(x, tc.y, y * tc.x);
             }
           }
           bf16* dst;
@@ -195,25 +220,25 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
             dst = (bf16*)rope.cache.base + kv_offset(rope.cache, page, which, kvh, pos % rope.cache.page_size);
           }
 #pragma unroll
-          for (int i = 0; i < HEAD; i += 8) {
+          for (int i = 0; i < W; i += 8) {
             uint4 o;
             __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) po[j] = __floats2bfloat162_rn(f[i + 2 * j], f[i + 2 * j + 1]);
-            *reinterpret_cast<uint4*>(dst + i) = o;
+            for (int j = 0; j < 4; ++j) po[j] = __floats2bfloat162_rn(lo[i + 2 * j], lo[i + 2 * j + 1]);
+            *reinterpret_cast<uint4*>(dst + first_pair + i) = o;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) po[j] = __floats2bfloat162_rn(hi[i + 2 * j], hi[i + 2 * j + 1]);
+            *reinterpret_cast<uint4*>(dst + HEAD / 2 + first_pair + i) = o;
           }
         }
       } else {
-        float ssq = 0.f;  // EPI_RESIDUAL with norm.copy_out: the squares of the new residual values of this tile
+        float ssq = 0.f;  // EPI_RESIDUAL with norm.copy_out: the squares of the new residual values of this half tile
 #pragma unroll
-        for (int col = 0; col < BN; col += 16) {
+        for (int cc = 0; cc < HALF; cc += 16) {
+          int col = c0 + cc;
           unsigned v[16];
           tmem_load16(acc + (unsigned)col, v);
-          if (col + 16 >= BN) {  // the last columns are in registers: the accumulator may be reused
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[buf]);
-          }
+          if (cc + 16 >= HALF) release_accumulator();
           float f[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) f[i] = __uint_as_float(v[i]) * scale_row;
@@ -225,7 +250,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
               float4 r[4];
 #pragma unroll
               for (int i = 0; i < 4; ++i)
-                r[i] = EARLY ? old[EARLY ? col / 4 + i : 0] : *reinterpret_cast<const float4*>(dst + 4 * i);
+                r[i] = EARLY ? old[EARLY ? cc / 4 + i : 0] : *reinterpret_cast<const float4*>(dst + 4 * i);
               unsigned pk[8];
 #pragma unroll
               for (int i = 0; i < 4; ++i) {
@@ -248,7 +273,9 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
             epilogue_row16<EPI, bf16>(c, m, n0 + col, M, N, f);
           }
         }
-        if (EPI == EPI_RESIDUAL && norm.ssq_out != nullptr && m < M) norm.ssq_out[(size_t)n_tile * M + m] = ssq;
+        // (a part per warp's share of the tile's columns: the reader sums parts in order, whoever wrote them)
+        if (EPI == EPI_RESIDUAL && norm.ssq_out != nullptr && m < M)
+          norm.ssq_out[(size_t)(HALVES * n_tile + half) * M + m] = ssq;
       }
     }
   }
@@ -273,7 +300,7 @@ int launch_shape(void* c, const CUtensorMap& map_a, const CUtensorMap& map_w, in
   long long total = (long long)m_tiles * n_tiles;
   int blocks = sms * S::BLOCKS_PER_SM;
   if (blocks > total) blocks = (int)total;
-  return dllm_launch_pdl(gemm_tcgen05_kernel<BN, EPI, DEEP, HD>, dim3(blocks), dim3(THREADS), S::SMEM, stream, map_a, map_w,
+  return dllm_launch_pdl(gemm_tcgen05_kernel<BN, EPI, DEEP, HD>, dim3(blocks), dim3(S::THREADS), S::SMEM, stream, map_a, map_w,
                          c, M, N, K, status, rope, m_tiles, n_tiles, norm);
 }
 
@@ -330,15 +357,20 @@ static int gemm_entry(void* c, const void* a, const void* w, int M, int N, int K
       ((uintptr_t)a & 15) || ((uintptr_t)w & 15) || status == nullptr)
     return DLLM_UNSUPPORTED_SIZE;
   if (tile_n == 0) {
-    long long tiles256 = (long long)((M + BM - 1) / BM) * ((N + 255) / 256);
+    long long m_tiles = (M + BM - 1) / BM;
+    long long tiles256 = m_tiles * ((N + 255) / 256), tiles64 = m_tiles * ((N + 63) / 64);
     if (M <= 256) tile_n = 32;  // few rows: many narrow tiles
-    // long reductions with enough tiles: the widest tile reuses A most (measured: 1.0 to 1.4 PFLOP/s from K = 2048
-    // up, against 0.6 to 1.2 for the 128-wide tile); short reductions are epilogue-bound and prefer narrow tiles
-    else if (N % 256 == 0 && K >= 1024 && tiles256 >= 64) tile_n = 256;
-    else if (N % 128 == 0 && N >= 2048 && K >= 1024) tile_n = 128;  // (2048 x 3072 x 576: 64 wins, 15.3 against 17.2 µs)
+    // enough 256-wide tiles to give every multiprocessor one: the widest tile reuses A most (measured: 1.0 to 1.4
+    // PFLOP/s from K = 2048 up, against 0.6 to 1.2 for the 128-wide tile; at K = 576, 2048 x 3072 with SwiGLU:
+    // 11.5 µs against 12.7 and 13.5 for 128 and 64)
+    else if (N % 256 == 0 && tiles256 >= 128) tile_n = 256;
+    else if (N % 128 == 0 && N >= 2048 && K >= 1024) tile_n = 128;
+    // (32-wide tiles for a narrow output, 2048 x 576, are 0.2 to 0.5 µs faster alone and slower in a step: twice
+    // the parts of the rows' sums of squares for the next product to read)
     else tile_n = 64;
   }
-  if (n_tiles_out != nullptr) *n_tiles_out = (N + tile_n - 1) / tile_n;
+  if (n_tiles_out != nullptr)  // (a part per epilogue warp's share of a tile: see the epilogue)
+    *n_tiles_out = (tile_n >= 128 ? 2 : 1) * ((N + tile_n - 1) / tile_n);
   switch (tile_n) {
     case 32: return dispatch<32>(c, a, w, M, N, K, epilogue, status, stream, norm);
     case 64: return dispatch<64>(c, a, w, M, N, K, epilogue, status, stream, norm);
@@ -369,8 +401,8 @@ DLLM_EXPORT int dllm_gemm_tcgen05_normed(void* c, const void* a, const void* w, 
 
 // x[M,N] (float32) += A W^T, and for the norm that reads x next: copy_out[M,N] = bfloat16(new x) and
 // ssq_out[tile][m] = the sum of the squares of row m's new values in column tile `tile`; *parts_out = the number of
-// column tiles (what the reader passes as parts_in). N must be a multiple of 16; ssq_out holds M * ceil(N / 32)
-// floats at least.
+// parts, two a column tile (what the reader passes as parts_in). N must be a multiple of 16; ssq_out holds
+// M * ceil(N / 16) floats at least.
 DLLM_EXPORT int dllm_gemm_tcgen05_residual_norm(void* x, void* copy_out, float* ssq_out, int* parts_out, const void* a,
                                                 const void* w, int M, int N, int K, int* status,
                                                 cudaStream_t stream) {

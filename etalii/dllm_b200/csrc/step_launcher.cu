@@ -76,7 +76,7 @@ struct DllmPrefillStep {
   const int* tile_seq;
   const int* tile_first;
   int* status;       // the kernels' shared status word
-  float* row_ssq;    // [ceil(hidden / 32)][tokens] sums of squares (folded norms), or null
+  float* row_ssq;    // [up to ceil(hidden / 16)][tokens] sums of squares (folded norms), or null
   int tokens, tiles, max_context;
   int norms_folded;  // the norms' weights live in the columns of w_qkv and w_gate_up: five launches a layer
 };

@@ -159,7 +159,7 @@ class PreNormLayers:
             batch.tok_seq.data_ptr(), batch.tok_pos.data_ptr(), batch.slots.data_ptr(), batch.cu_seqlens.data_ptr(),
             batch.start.data_ptr(), batch.tile_seq.data_ptr(), batch.tile_first.data_ptr(),
             ops._status_word().data_ptr(),
-            ws.buffer("row_ssq", (n, -(-self.widths["hidden"] // 32)), torch.float32).data_ptr()
+            ws.buffer("row_ssq", (n, -(-self.widths["hidden"] // 16)), torch.float32).data_ptr()
             if self.norms_folded else None,
             n, batch.n_tiles, batch.max_context, 1 if self.norms_folded else 0)
         launched, failed_at = c_int(0), c_int(-1)

@@ -409,12 +409,12 @@ def gemm_normed(c: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int
 def gemm_residual_norm(x: torch.Tensor, copy: torch.Tensor, ssq: torch.Tensor, a: torch.Tensor,
                        w: torch.Tensor) -> int:
     """x (float32) += a @ w^T; copy = bfloat16(new x); ssq[tile, row] = the sum of the squares of the new values of
-    the row in each tile of columns. Returns the number of tiles (the reader's `parts`). N a multiple of 16."""
+    the row in each half tile of columns. Returns the number of parts (the reader's `parts`). N a multiple of 16."""
     _cuda(x, copy, ssq, a, w)
     m, k = a.shape
     n = w.shape[0]
     assert x.dtype == torch.float32 and tuple(x.shape) == (m, n) and copy.dtype == torch.bfloat16
-    assert tuple(copy.shape) == (m, n) and ssq.dtype == torch.float32 and ssq.numel() >= m * (-(-n // 32))
+    assert tuple(copy.shape) == (m, n) and ssq.dtype == torch.float32 and ssq.numel() >= m * (-(-n // 16))
     parts = c_int(0)
     _check(_fn("gemm_tcgen05", "dllm_gemm_tcgen05_residual_norm")(
         x.data_ptr(), copy.data_ptr(), ssq.data_ptr(), ctypes.addressof(parts), a.data_ptr(), w.data_ptr(), m, n, k,

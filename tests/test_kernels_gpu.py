@@ -927,7 +927,7 @@ def test_tile_products_with_the_norm_folded_around_them(m, hidden, inner):
     w = _randn((hidden, inner), torch.bfloat16, 3, 0.05)
     x = x0.clone()
     copy = torch.full((m, hidden), float("nan"), dtype=torch.bfloat16, device=DEV)
-    ssq = torch.full((m * (-(-hidden // 32)),), float("nan"), dtype=torch.float32, device=DEV)
+    ssq = torch.full((m * (-(-hidden // 16)),), float("nan"), dtype=torch.float32, device=DEV)
     parts = ops().gemm_residual_norm(x, copy, ssq, a, w)
     want_x = x0.double() + a.double() @ w.double().T
     assert rel_error(x.cpu(), want_x.cpu()) <= 2e-5
