@@ -26,6 +26,7 @@ SOURCES = {
     "gemm_bf16": "gemm_bf16.cu",
     "gemv": "gemv.cu",
     "gemv_tma": "gemv_tma.cu",
+    "gemv_cluster": "gemv_cluster.cu",
     "mlp_decode": "mlp_decode.cu",
     "gemm_tcgen05": "gemm_tcgen05.cu",
     "attention": "attention.cu",

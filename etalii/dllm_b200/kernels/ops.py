@@ -48,6 +48,12 @@ _prototypes = {
     ("elementwise", "dllm_cast_ssq"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
     ("gemv", "dllm_gemv_bf16"): [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int,
                                  c_void_p, c_longlong, c_void_p],
+    ("gemv_cluster", "dllm_gemv_cluster"): [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int,
+                                            c_int, c_void_p, c_longlong, c_void_p],
+    ("gemv_cluster", "dllm_gemv_cluster_qkv_rope"): [c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_void_p,
+                                                     c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                                     c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                                     c_void_p, c_longlong, c_void_p],
     ("mlp_decode", "dllm_mlp_decode"): [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
                                         c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p],
     ("gemv", "dllm_argmax_candidates"): [c_void_p, c_void_p, c_int, c_int, c_void_p],
@@ -213,11 +219,31 @@ GEMV_MAX_ROWS = 64
 """The weight-streaming kernel takes at most this many activation rows."""
 
 
-def streams(rows: int, outputs: int) -> bool:
-    """Whether a bfloat16 product of `rows` activation rows and `outputs` weight rows runs in the weight-streaming
-    kernel: always up to 16 rows; up to 64 rows unless the matrix has so many rows that its blocks (16 weight rows
-    each) would together re-read the activations far more often than the weights."""
+CLUSTER_SPLIT_BYTES = (1 << 20, 16 << 20)
+
+
+def splits_over_clusters(rows: int, outputs: int, inner: int) -> bool:
+    """Whether a product with 9 to 64 rows of activations takes the kernel that splits the reduction over the
+    blocks of a thread-block cluster (`gemv_cluster.cu`): weights of a few megabytes, where bringing the activations
+    to the multiprocessors is the cost and a block per 16 rows of W reads them far too often. Measured at the layer
+    sizes of a 576-wide model, as links of a chain of dependent launches: with 64 rows 4.0 to 7.4 µs against 4.9 to
+    10.8; with 16 rows 3.2 to 3.6 against 3.8 to 4.5, but 2.5 against 2.3 for the smallest matrix (576 x 576); with 8
+    rows the kernel with a block per 16 rows of W wins everywhere (1.5 to 2.5 against 2.4 to 3.3)."""
+    size = 2 * outputs * inner
+    if 16 < rows <= GEMV_MAX_ROWS:
+        return size <= CLUSTER_SPLIT_BYTES[1]
+    return 8 < rows <= 16 and CLUSTER_SPLIT_BYTES[0] <= size <= CLUSTER_SPLIT_BYTES[1]
+
+
+def streams(rows: int, outputs: int, inner: int | None = None) -> bool:
+    """Whether a bfloat16 product of `rows` activation rows and `outputs` weight rows (of `inner` values, if given)
+    runs in one of the weight-streaming kernels, which can take an RMSNorm in front: always up to 16 rows; up to 64
+    rows where the weights are small enough for the kernel that splits the reduction over a cluster, or unless the
+    matrix has so many rows that its blocks (16 weight rows each) would together re-read the activations far more
+    often than the weights."""
     if rows <= 16:
+        return True
+    if inner is not None and splits_over_clusters(rows, outputs, inner):
         return True
     if rows <= 32:
         return outputs <= 4096
@@ -246,13 +272,14 @@ def takes_weights_as_rows(rows: int, outputs: int, inner: int) -> bool:
 
 
 def gemm(c: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int = EPI_STORE_T, kernel: int = 0,
-         norm_weight: torch.Tensor | None = None, eps: float = 0.0, tile_n: int = 0) -> None:
+         norm_weight: torch.Tensor | None = None, eps: float = 0.0, tile_n: int = 0, cluster: int = 0) -> None:
     """c = a[M,K] @ w[N,K]^T with float32 accumulation, then the epilogue: EPI_STORE_F32 (c float32), EPI_STORE_T
     (c in the weights' dtype), EPI_RESIDUAL (c float32 += product), EPI_SWIGLU (w interleaves gate and up rows;
     c[M,N/2] = silu(gate) * up). float32 weights run the true 32-bit kernel; bfloat16 the tcgen05/TMA tile kernel
     or, for M <= 64, a weight-streaming kernel (`kernel`: 0 chooses by the sizes, 1 forces the mma.sync tile kernel,
     2 forces streaming through registers, 3 forces tcgen05, 4 forces streaming through shared memory, 5 forces
-    tcgen05 with W as the 128-row operand (for at most 256 rows of `a`); `tile_n` picks the tcgen05 tile width).
+    tcgen05 with W as the 128-row operand (for at most 256 rows of `a`), 6 forces the reduction split over a cluster
+    (`cluster` blocks, 0 chooses); `tile_n` picks the tcgen05 tile width).
     With `norm_weight` (streaming kernel only), `a` is the float32 residual stream and is RMS-normed on the way in."""
     _cuda(c, a, w, norm_weight)
     m, k = a.shape
@@ -269,7 +296,7 @@ def gemm(c: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int = EPI_
         status = _fn("gemm_simt", "dllm_gemm_f32")(c.data_ptr(), a.data_ptr(), w.data_ptr(), m, n, k, epilogue,
                                                    _stream())
     elif w.dtype == torch.bfloat16:
-        streaming = (kernel == 2 and m <= GEMV_MAX_ROWS) or (kernel == 0 and streams(m, n))
+        streaming = (kernel == 2 and m <= GEMV_MAX_ROWS) or (kernel == 0 and streams(m, n, k))
         if kernel == 5 or (kernel == 0 and norm_weight is None and takes_weights_as_rows(m, n, k)):
             # the product the other way round: W is the 128-row operand, the tokens are the tile's columns
             assert a.dtype == torch.bfloat16 and norm_weight is None and m <= 256
@@ -281,6 +308,14 @@ def gemm(c: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int = EPI_
             assert a.dtype == torch.bfloat16 and norm_weight is None
             status = _fn("gemv_tma", "dllm_gemv_tma")(c.data_ptr(), a.data_ptr(), w.data_ptr(), m, n, k, epilogue,
                                                       _status_word().data_ptr(), _stream())
+        elif (kernel == 6 and m <= GEMV_MAX_ROWS) or (kernel == 0 and streaming and splits_over_clusters(m, n, k)):
+            if norm_weight is not None:
+                assert a.dtype == torch.float32 and norm_weight.dtype == torch.float32 and norm_weight.numel() == k
+            else:
+                assert a.dtype == torch.bfloat16
+            status = _fn("gemv_cluster", "dllm_gemv_cluster")(
+                c.data_ptr(), a.data_ptr(), norm_weight.data_ptr() if norm_weight is not None else None, float(eps),
+                w.data_ptr(), m, n, k, epilogue, int(cluster), *_prefetch_of(w), _stream())
         elif streaming:
             if norm_weight is not None:
                 assert a.dtype == torch.float32 and norm_weight.dtype == torch.float32 and norm_weight.numel() == k
@@ -450,11 +485,13 @@ def gemm_qkv_rope(a: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, cache, 
 
 def gemv_qkv_rope(a: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, cache, table: torch.Tensor | None,
                   rotary_dim: int, heads: int, batch, write_cache: bool = True,
-                  norm_weight: torch.Tensor | None = None, eps: float = 0.0, prefetch_window: int = -1) -> None:
+                  norm_weight: torch.Tensor | None = None, eps: float = 0.0, prefetch_window: int = -1,
+                  kernel: int = 0, cluster: int = 0) -> None:
     """The q/k/v projection of at most 64 tokens in one kernel (bfloat16): optional RMSNorm of the float32 residual
     in front, rotation of q and k, q to q_out, k and v into the paged cache. With `prefetch_window` >= 0 the kernel
     also asks L2 for the cached keys and values of the tokens' sequences (0: all of them, w: the last w), which the
-    attention kernel behind it reads."""
+    attention kernel behind it reads. `kernel`: 0 chooses, 2 forces a block per 16 rows of W, 6 the reduction split
+    over a cluster (`cluster` blocks, 0 chooses)."""
     _cuda(a, w, q_out, table, norm_weight)
     m, k = batch.n_tokens, a.shape[1]
     assert w.dtype == torch.bfloat16 and cache.dtype == torch.bfloat16 and q_out.dtype == torch.bfloat16
@@ -463,6 +500,17 @@ def gemv_qkv_rope(a: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, cache, 
     if table is not None:
         assert table.dtype == torch.float32 and table.shape[0] > batch.max_position, "position beyond the table"
         assert table.shape[1] == rotary_dim // 2 and table.shape[2] == 2
+    if kernel == 6 or (kernel == 0 and splits_over_clusters(m, w.shape[0], k)):
+        _check(_fn("gemv_cluster", "dllm_gemv_cluster_qkv_rope")(
+            a.data_ptr(), norm_weight.data_ptr() if norm_weight is not None else None, float(eps), w.data_ptr(), m, k,
+            q_out.data_ptr(), cache.base_ptr, cache.page_table.data_ptr(), cache.max_pages, cache.page_size, heads,
+            cache.kv_heads, cache.head_dim, table.data_ptr() if table is not None else None,
+            rotary_dim if table is not None else 0, batch.tok_seq.data_ptr(), batch.tok_pos.data_ptr(),
+            batch.slots.data_ptr(), 1 if write_cache else 0, int(prefetch_window), int(cluster), *_prefetch_of(w),
+            _stream()),
+            "gemv_cluster_qkv_rope",
+            lambda: f"M={m} (at most 64), K={k} (multiple of 8), head_dim and rotary_dim multiples of 16")
+        return
     _check(_fn("gemv", "dllm_gemv_qkv_rope")(
         a.data_ptr(), norm_weight.data_ptr() if norm_weight is not None else None, float(eps), w.data_ptr(), m, k,
         q_out.data_ptr(), cache.base_ptr, cache.page_table.data_ptr(), cache.max_pages, cache.page_size, heads,

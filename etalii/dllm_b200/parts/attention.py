@@ -139,6 +139,8 @@ class Attention:
             return {"gemm_simt", "elementwise", "attention"}
         hd = self.head_dim
         names = {"gemv", "gemm_tcgen05", "elementwise"}
+        if any(ops.splits_over_clusters(64, w.shape[0], w.shape[1]) for w in (self.w_qkv, self.w_o)):
+            names.add("gemv_cluster")  # (steps of 17 to 64 tokens with weights this small)
         names.add("attention_decode_cluster" if hd % 16 == 0 and hd <= 128 else "attention_decode")
         if hd in (64, 128):
             names.add("attention_prefill_tcgen05")  # (long prompts; short ones take the mma.sync kernel)

@@ -61,6 +61,8 @@ class SwiGLU:
         if rt.dtype != torch.bfloat16:
             return {"gemm_simt"}
         names = {"gemv", "gemm_tcgen05"}
+        if any(ops.splits_over_clusters(64, w.shape[0], w.shape[1]) for w in (self.w_gate_up, self.w_down)):
+            names.add("gemv_cluster")  # (steps of 17 to 64 tokens with weights this small)
         if ops.FUSED_FEED_FORWARD and ops.mlp_decode_supported(1, self.hidden_size, self.intermediate_size):
             names.add("mlp_decode")
         if any(ops.streams_through_shared_memory(1, w.shape[0], w.shape[1]) for w in (self.w_gate_up, self.w_down)):

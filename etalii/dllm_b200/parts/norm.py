@@ -89,7 +89,7 @@ def project(out: torch.Tensor, h, w: torch.Tensor, epilogue: int) -> None:
     """out = epilogue(h @ w^T). `h` is a tensor of activations or a `NormedInput`; a decode-sized bfloat16 product
     applies the pending norm inside the kernel, anything else computes the normed activations first."""
     if isinstance(h, NormedInput):
-        if w.dtype == torch.bfloat16 and ops.streams(h.shape[0], w.shape[0]) and fuses_norm(w):
+        if w.dtype == torch.bfloat16 and ops.streams(h.shape[0], w.shape[0], w.shape[1]) and fuses_norm(w):
             ops.gemm(out, h.x, w, epilogue, norm_weight=h.weight, eps=h.eps)
             return
         h = h.tensor()

@@ -124,6 +124,10 @@ def test_kernel_choice_rules_for_products():
     assert ops.streams(32, 3072) and not ops.streams(32, 49152)       # 17 to 32 rows: unless the matrix is wide
     assert ops.streams(64, 576) and not ops.streams(64, 3072)         # 33 to 64 rows: only narrow matrices
     assert not ops.streams(65, 576)
+    # small weights with 17 to 64 rows: the reduction split over a cluster, whatever the number of weight rows
+    assert ops.streams(64, 3072, 576) and ops.splits_over_clusters(17, 3072, 576)
+    assert ops.splits_over_clusters(16, 3072, 576) and not ops.splits_over_clusters(16, 576, 576)
+    assert not ops.splits_over_clusters(8, 3072, 576) and not ops.splits_over_clusters(64, 16384, 2048)
     assert ops.streams_through_shared_memory(1, 28672, 4096) and not ops.streams_through_shared_memory(8, 28672, 4096)
     assert not ops.streams_through_shared_memory(1, 16384, 2048)      # short rows of W
     assert not ops.streams_through_shared_memory(1, 4096, 4096 + 8)   # a reduction that is no multiple of 64

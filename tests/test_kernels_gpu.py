@@ -561,7 +561,7 @@ def test_gemv_qkv_rope_long_rows_and_more_tiles_than_blocks(normed):
     _check_gemv_qkv_rope(40, 8, 128, 128, normed, 3, 2240)
 
 
-def _check_gemv_qkv_rope(heads, kv_heads, head_dim, rotary, normed, rows_extra, k):
+def _check_gemv_qkv_rope(heads, kv_heads, head_dim, rotary, normed, rows_extra, k, kernel=2, cluster=0):
     lengths, new = [70, 5, 129, 64, 200, 33], [1, 1, 3, 2, rows_extra, 1]
     cache, view, batch = _cache_and_batch(torch.bfloat16, kv_heads, head_dim, lengths, new)
     n = batch.n_tokens
@@ -576,8 +576,7 @@ def _check_gemv_qkv_rope(heads, kv_heads, head_dim, rotary, normed, rows_extra, 
     before = view.storage.clone()
     # (with the request for the sequences' cached pages into L2, as decode steps make it: a hint, no result changes)
     ops().gemv_qkv_rope(x, w, q, view, table, rotary, heads, batch, True, prefetch_window=0 if normed else 40,
-                        norm_weight=nw if normed else None,
-                        eps=1e-6)
+                        norm_weight=nw if normed else None, eps=1e-6, kernel=kernel, cluster=cluster)
     h = x.double()
     if normed:
         h = torch.empty((n, k), dtype=torch.float64, device=DEV)
@@ -593,8 +592,51 @@ def _check_gemv_qkv_rope(heads, kv_heads, head_dim, rotary, normed, rows_extra, 
     assert (view.storage != before).any(dim=-1).sum().item() <= n * kv_heads * 2
     q2, snapshot = torch.zeros_like(q), view.storage.clone()
     ops().gemv_qkv_rope(x, w, q2, view, table, rotary, heads, batch, False, norm_weight=nw if normed else None,
-                        eps=1e-6)
+                        eps=1e-6, kernel=kernel, cluster=cluster)
     assert torch.equal(q2, q) and torch.equal(view.storage, snapshot)
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 64, 64), (3, 130, 72), (16, 96, 144), (17, 200, 136), (33, 576, 576),
+                                   (64, 960, 576), (50, 66, 1544), (64, 576, 1536), (40, 3072, 576), (29, 48, 2048)])
+@pytest.mark.parametrize("epilogue", [0, 1, 2, 3])
+@pytest.mark.parametrize("normed", [False, True])
+def test_gemv_cluster(m, n, k, epilogue, normed):
+    """The product whose reduction is split over the blocks of a cluster, at every cluster size its rows allow:
+    against the plain product, and the same bits on a second run (fixed order of the sums)."""
+    x = _randn((m, k), torch.float32 if normed else torch.bfloat16, 3, 2.0 if normed else 1.0)
+    nw = _randn((k,), torch.float32, 8) * 0.1 + 1
+    w = _randn((n, k), torch.bfloat16, 4, 0.2)
+    cols = n // 2 if epilogue == 3 else n
+    start = _randn((m, cols), torch.float32 if epilogue in (0, 2) else torch.bfloat16, 5)
+    ref = start.clone()
+    h = x
+    if normed:
+        h = torch.empty((m, k), dtype=torch.float64, device=DEV)
+        PK.rmsnorm(h, x, nw, 1e-5)
+    PK.gemm(ref, h, w, epilogue)
+    most = 4 if m <= 16 else 8
+    for cluster in [c for c in (0, 1, 2, 4, 8) if c <= most]:
+        c = start.clone()
+        ops().gemm(c, x, w, epilogue, kernel=6, cluster=cluster, norm_weight=nw if normed else None, eps=1e-5)
+        assert rel_error(c.float().cpu(), ref.float().cpu()) <= 8e-3, cluster
+        again = start.clone()
+        ops().gemm(again, x, w, epilogue, kernel=6, cluster=cluster, norm_weight=nw if normed else None, eps=1e-5)
+        assert torch.equal(again, c), cluster
+    with pytest.raises(Exception):
+        ops().gemm(start.clone(), x, w, epilogue, kernel=6, cluster=3, norm_weight=nw if normed else None, eps=1e-5)
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,rotary", [(4, 2, 16, 16), (6, 3, 48, 32), (2, 1, 64, 32),
+                                                           (9, 3, 64, 64), (3, 1, 128, 0)])
+@pytest.mark.parametrize("normed", [False, True])
+@pytest.mark.parametrize("rows_extra,cluster", [(1, 0), (1, 4), (12, 2), (24, 8), (40, 0), (40, 1), (40, 8), (56, 4)])
+def test_gemv_cluster_qkv_rope(heads, kv_heads, head_dim, rotary, normed, rows_extra, cluster):
+    _check_gemv_qkv_rope(heads, kv_heads, head_dim, rotary, normed, rows_extra, 136, kernel=6, cluster=cluster)
+
+
+@pytest.mark.parametrize("normed", [False, True])
+def test_gemv_cluster_qkv_rope_long_rows(normed):
+    _check_gemv_qkv_rope(40, 8, 128, 128, normed, 30, 2240, kernel=6)
 
 
 @pytest.mark.parametrize("heads,kv_heads,head_dim,window", [(4, 2, 16, None), (9, 3, 64, None), (8, 1, 128, 70),
