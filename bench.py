@@ -338,6 +338,57 @@ def stream_table() -> int:
     return 0
 
 
+def cluster_table(rows: int) -> int:
+    """Times the products of a step of 9 to 64 rows at the layer shapes of a 576-wide model, as links of a chain of
+    30 dependent launches in a CUDA graph: the kernel with a block per 16 rows of W against the one that splits the
+    reduction over a thread-block cluster, at every cluster size."""
+    import torch
+
+    from etalii.dllm_b200.kernels import ops
+
+    device = "cuda:0"
+    shapes = [("output", 576, 576, ops.EPI_RESIDUAL, False), ("down", 576, 1536, ops.EPI_RESIDUAL, False),
+              ("gate/up + norm", 3072, 576, ops.EPI_SWIGLU, True), ("960 x 576 + norm", 960, 576, ops.EPI_STORE_T, True)]
+    links = 30
+    print(f"{rows} rows | a block per 16 rows of W | cluster of 1 | 2 | 4 | 8   (microseconds per launch)")
+    for name, n, k, epilogue, normed in shapes:
+        ws = [(torch.randn(n, k, device=device) * 0.05).bfloat16() for _ in range(8)]
+        x = torch.randn(rows, k, device=device)
+        x = x if normed else x.bfloat16()
+        norm_weight = torch.ones(k, device=device) if normed else None
+        cols = n // 2 if epilogue == ops.EPI_SWIGLU else n
+        dtype = torch.float32 if epilogue == ops.EPI_RESIDUAL else torch.bfloat16
+        c = torch.zeros(rows, cols, device=device, dtype=dtype)
+        cells = []
+        for kernel, cluster in ((2, 0), (6, 1), (6, 2), (6, 4), (6, 8)):
+            if cluster > (4 if rows <= 16 else 8):
+                continue
+
+            def chain():
+                for i in range(links):
+                    ops.gemm(c, x, ws[i % 8], epilogue, kernel=kernel, cluster=cluster, norm_weight=norm_weight,
+                             eps=1e-5)
+
+            chain()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                chain()
+            for _ in range(3):
+                graph.replay()
+            torch.cuda.synchronize()
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record()
+            for _ in range(20):
+                graph.replay()
+            end.record()
+            torch.cuda.synchronize()
+            cells.append(f"{begin.elapsed_time(end) * 1e3 / (20 * links):.2f}")
+        print(f"{name} {n} x {k} | " + " | ".join(cells))
+    ops.raise_if_failed()
+    return 0
+
+
 def model_numbers(config, layers):
     h, i, v = config["hidden_size"], config["intermediate_size"], config["vocab_size"]
     nh, nkv, hd = config["num_attention_heads"], config["num_key_value_heads"], config["head_dim"]
@@ -677,8 +728,8 @@ def main() -> int:
     parser.add_argument("--impl", default="ours", choices=("ours", "reference", "reference-worker"))
     parser.add_argument("--budget", type=float, default=REFERENCE_BUDGET_S, help=argparse.SUPPRESS)
     parser.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 and the float32 points")
-    parser.add_argument("--profile", choices=("decode", "prefill", "gemm", "attention", "stream", "kernels", "ablate",
-                                              "ablate-fused", "feed-forward"),
+    parser.add_argument("--profile", choices=("decode", "prefill", "gemm", "attention", "stream", "cluster", "kernels",
+                                              "ablate", "ablate-fused", "feed-forward"),
                         help="run only a few decode steps (or one prefill) and print no JSON: a small case for ncu")
     args = parser.parse_args()
     if args.impl == "reference-worker":
@@ -691,6 +742,8 @@ def main() -> int:
         return attention_table()
     if args.profile == "stream":
         return stream_table()
+    if args.profile == "cluster":
+        return cluster_table(args.batch if args.batch > 8 else 64)
     if args.gpus != 1:
         print(f"bench.py measures one GPU: --gpus {args.gpus} is not supported (this library runs on a single device)")
         return 2

@@ -112,6 +112,14 @@ class Model:
         self._prefetch = {}
         for index, tensor in enumerate(order[:-ahead] if len(order) > ahead else []):
             self._prefetch[tensor.data_ptr()] = order[index + ahead]
+        # A last matrix too large for one request (the head's) but well inside L2 is asked for in slices of its rows
+        # by the products before it, one slice each.
+        last = order[-1] if len(order) > ahead else None
+        if last is not None and ops.PREFETCH_LIMIT < last.numel() * last.element_size() <= ops.PREFETCH_SLICED_LIMIT:
+            pieces = min(2 * ahead, len(order) - 1)
+            rows = -(-last.shape[0] // pieces)
+            for index, tensor in enumerate(order[-1 - pieces:-1]):
+                self._prefetch[tensor.data_ptr()] = last[index * rows:(index + 1) * rows]
 
     def forward(self, batch, greedy_out: torch.Tensor | None = None) -> torch.Tensor:
         """Runs the batch's tokens through every scheduled layer; returns float32 logits [wanted rows, vocab]

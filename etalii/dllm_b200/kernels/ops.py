@@ -182,6 +182,10 @@ PREFETCH_LIMIT = 16 << 20
 """Larger weights are not asked into L2 ahead of time: four products of them would not fit there anyway."""
 
 
+PREFETCH_SLICED_LIMIT = 64 << 20
+"""A step's last matrix (the head's) up to this size is asked into L2 in slices by the products before it."""
+
+
 def _prefetch_of(w: torch.Tensor):
     hint = prefetch_hints.get(w.data_ptr())
     if hint is None or hint.numel() * hint.element_size() > PREFETCH_LIMIT:

@@ -557,3 +557,38 @@ def test_greedy_decoding_without_logits_chooses_the_same_tokens(name):
         outputs[keep] = [r.tokens for r in engine.generate(prompts, 24, ignore_eos=True)]
         assert (engine.last_decode_graph.logits is not None) == keep
     assert outputs[False] == outputs[True]
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("sequences", [9, 17, 40, 64])
+def test_steps_of_nine_to_sixty_four_rows(name, sequences):
+    """Steps whose products split their reduction over a cluster (17 rows and more at these sizes): a prompt step
+    of at most 64 tokens, then single tokens for all sequences, every row against the plain implementation; and the
+    same through the decode graph."""
+    config, weights = model_case(name.lower())
+    plain = PlainLogits(config, weights)
+    rng = np.random.default_rng(sequences)
+    lengths = [1] * sequences
+    for _ in range(64 - sequences):  # prompts of unequal lengths, 64 tokens in all
+        lengths[int(rng.integers(0, sequences))] += 1
+    prompts = prompts_for(config, lengths, seed=sequences)
+    engine = make_engine(config, weights, "bfloat16", max_tokens=64 * sequences, decode_logits=True)
+    slots = engine.open(sequences)
+    logits = host(engine.step(slots, prompts))
+    contexts = [list(p) for p in prompts]
+    for step in range(3):
+        for i, context in enumerate(contexts):
+            assert rel_error(logits[i], plain(context)[-1]) <= TOL["bfloat16"], (step, i)
+        chosen = np.argmax(logits, axis=1).tolist()
+        for context, token in zip(contexts, chosen):
+            context.append(int(token))
+        if step < 2:
+            logits = host(engine.step(slots, [[t] for t in chosen]))
+        else:
+            out = engine.decode(slots, chosen, 1)
+            logits = host(engine.last_decode_graph.logits)
+            assert out[0] == np.argmax(logits, axis=1).tolist()
+    for i, context in enumerate(contexts):
+        assert rel_error(logits[i], plain(context)[-1]) <= TOL["bfloat16"], ("graph", i)
+    engine.close(slots)
+    engine.cache.check()

@@ -119,6 +119,22 @@ def test_a_batch_of_64_through_the_decode_graph_at_real_size(real_size, dtype):
     engine.cache.check()
 
 
+def test_a_batch_of_12_through_the_decode_graph_at_real_size(real_size):
+    """Twelve rows of activations: the products whose weights are above a megabyte split their reduction over a
+    cluster (four blocks at most with so few rows), the output product (smaller) keeps a block per 16 rows of W."""
+    weights, _ = real_size
+    config = SMOLLM2_135M_SHAPE
+    lengths = np.random.default_rng(12).integers(8, 60, 12).tolist()
+    prompts = prompts_for(config, lengths, seed=13)
+    engine = make_engine(config, weights, "bfloat16", max_tokens=64 * 2 * 12, max_length=192, decode_logits=True)
+    slots = engine.open(12)
+    first = host(engine.step(slots, prompts))
+    _decode_and_compare(engine, config, weights, "bfloat16", prompts, slots, first, steps=3)
+    engine.check()
+    engine.close(slots)
+    engine.cache.check()
+
+
 @pytest.fixture(scope="module")
 def long_prompt_case(real_size):
     weights, _ = real_size
