@@ -44,8 +44,9 @@ class Engine:
                  decode_chunk: int = 16, decode_logits: bool = False) -> None:
         """`max_length`: the longest sequence the cache holds (default: the model's max_position_embeddings).
         `max_tokens`: the most tokens all live sequences hold together, each rounded up to whole pages of 64
-        (default: four sequences of max_length). `cuda_graphs`: replay decode steps as CUDA graphs (turn off for
-        parts that cannot be captured). `decode_chunk`: decode steps between looks at the chosen tokens.
+        (default: four sequences of max_length). `cuda_graphs`: replay decode steps as CUDA graphs; switched
+        off by itself when a part or block of the model declares `CAPTURABLE = False` (a part made of allocating
+        torch ops: a captured graph cannot hold those). `decode_chunk`: decode steps between looks at the chosen tokens.
         `decode_logits`: decode runs always compute the logits (they stay readable in the run's buffer); by default
         a greedy run lets the head product choose the token itself and stores no logits."""
         if not torch.cuda.is_available():
@@ -65,7 +66,7 @@ class Engine:
         self.buffers = BatchBuffers(self.rt.device)
         self.sampler = Sampler(self.cache.n_slots, self.vocab_size, self.rt.device, self.rt.ws)
         self.steps_run = 0
-        self.cuda_graphs = bool(cuda_graphs)
+        self.cuda_graphs = bool(cuda_graphs) and self.model.capturable()
         self.decode_chunk = int(decode_chunk)
         self.decode_logits = bool(decode_logits)
         self._graphs: dict = {}

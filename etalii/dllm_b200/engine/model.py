@@ -97,6 +97,12 @@ class Model:
                 parts = {name: getattr(b, name) for name in getattr(type(b), "PARTS", {}) if hasattr(b, name)}
             yield from parts.values()
 
+    def capturable(self) -> bool:
+        """Whether a decode step of this model can be captured in a CUDA graph: every block and part may say no
+        (`CAPTURABLE = False`, e.g. a part written with allocating torch ops); the library's own all can."""
+        things = [*self.blocks, *self._layer_parts(), self.embedding, self.final_norm, self.head]
+        return all(getattr(thing, "CAPTURABLE", True) for thing in things)
+
     def _plan_prefetch(self, ahead: int = 4) -> None:
         """Tells the decode-sized products which weights come `ahead` products later in the run order, so that they
         can be brought into L2 before they are needed (kernels/ops.py::prefetch_hints)."""

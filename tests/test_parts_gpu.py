@@ -117,6 +117,8 @@ def test_swiglu_part(dtype, tol, rows):
 class DecayMixer:
     """state <- decay * state + h (per sequence, token by token); output = state @ w^T. State: [hidden] per slot."""
 
+    CAPTURABLE = False  # written with allocating torch ops: the engine then decodes without CUDA graphs
+
     def __init__(self, hidden_size, decay):
         self.hidden_size, self.decay = hidden_size, decay
 
@@ -224,7 +226,8 @@ def test_toy_architecture_with_a_stateful_mixer(dtype):
         g = torch.Generator().manual_seed(3)
         tensors = {name: ((torch.randn(p.shape, generator=g) * 0.2 + (1 if p.init == "ones" else 0))
                           .to(torch.bfloat16)) for name, p in expected_tensors(spec).items()}
-        engine = Engine(ToyConfig(), tensors, dtype=dtype, max_tokens=64 * 8, cuda_graphs=False)
+        engine = Engine(ToyConfig(), tensors, dtype=dtype, max_tokens=64 * 8)
+        assert engine.cuda_graphs is False  # the mixer said so
         groups = engine.cache.groups()
         assert len(groups) == 1 and groups[0][1] == [1] and groups[0][0].window == 5  # one kv entry, shared
         assert engine.cache.state(0).shape == (engine.cache.n_slots, 32) and engine.cache.state(2) is not None

@@ -20,6 +20,8 @@ class RoutedExperts:
     """Feed-forward with routing: router logits in float32, the two largest choose the experts, their softmax (over
     the two) weighs the experts' SwiGLU outputs."""
 
+    CAPTURABLE = False  # written with allocating torch ops: the engine then decodes without CUDA graphs
+
     def __init__(self, hidden_size, intermediate_size, experts):
         self.hidden_size, self.intermediate_size, self.experts = hidden_size, intermediate_size, experts
 
@@ -157,7 +159,8 @@ def test_routed_feed_forward_and_another_position_encoding(dtype, tol):
             scale = 1.5 if name == "l0.router" else 0.1  # clear routing decisions, moderate activations
             tensors[name] = (torch.randn(p.shape, generator=g) * scale + (1 if p.init == "ones" else 0)).to(torch.bfloat16)
         w = {k: v.float().numpy() for k, v in tensors.items()}
-        engine = Engine(ToyConfig(), tensors, dtype=dtype, max_tokens=64 * 8, cuda_graphs=False)
+        engine = Engine(ToyConfig(), tensors, dtype=dtype, max_tokens=64 * 8)
+        assert engine.cuda_graphs is False  # the feed-forward said so
         prompts = [[int(t) for t in torch.randint(0, VOCAB, (n,), generator=g)] for n in (23, 9)]
         want = []
         for prompt in prompts:
