@@ -39,18 +39,18 @@ __device__ __forceinline__ void store_to_block(float* local, unsigned rank, floa
 }
 
 // One (pair of tile rows, token) of the owner's epilogue: where it goes and what it needs from memory besides the
-// sums. The token's cache page hangs on a chain of three dependent loads (sequence -> slot -> page), the rotation on
-// two (position -> angle); a warp stops at the first instruction that needs a value still on its way, so the chain
-// is asked for link by link, each at a place where the link before has arrived and other work follows.
+// sums (old residual values; the token's position, rotation and cache page). Asked for right after the wait on the
+// previous kernel, so that the loads run under the products. (Asking for the chains of dependent loads link by link
+// at later places, each behind other work, was measured and changed nothing here; in `gemv.cu` it cost 5 %.)
 template <int EPI>
 struct Unit {
   int m = 0, item = 0, p = 0, head = 0, dim0 = 0;
   bool valid = false, paired = false;
   float r0 = 0.f, r1 = 0.f;
-  int pos = 0, page = 0, seq = 0, slot = 0;
+  int pos = 0, page = 0;
   float2 cs = make_float2(1.f, 0.f);
-  __device__ __forceinline__ void first(const void* c, int m_, int item_, int p_, int M, int N, int items,
-                                        const RopeArgs& rope) {
+  __device__ __forceinline__ void prepare(const void* c, int m_, int item_, int p_, int M, int N, int items,
+                                          const RopeArgs& rope) {
     m = m_; item = item_; p = p_;
     valid = m < M && item < items;
     if (!valid) return;
@@ -62,18 +62,12 @@ struct Unit {
       if (n + 1 < N) r1 = src[1];
     } else if (EPI == EPI_QKV_ROPE) {
       pos = rope.tok_pos[m];
-      seq = rope.tok_seq[m];
+      if (paired) cs = rope.table[(size_t)pos * (rope.rotary_dim / 2) + dim0 + p];
+      if (head >= rope.heads && rope.write_cache) {
+        int slot = rope.slots[rope.tok_seq[m]];
+        page = rope.cache.page_table[(size_t)slot * rope.cache.max_pages + pos / rope.cache.page_size];
+      }
     }
-  }
-  __device__ __forceinline__ void second(const RopeArgs& rope) {
-    if (EPI != EPI_QKV_ROPE || !valid) return;
-    if (paired) cs = rope.table[(size_t)pos * (rope.rotary_dim / 2) + dim0 + p];
-    if (head >= rope.heads && rope.write_cache) slot = rope.slots[seq];
-  }
-  __device__ __forceinline__ void third(const RopeArgs& rope) {
-    if (EPI != EPI_QKV_ROPE || !valid) return;
-    if (head >= rope.heads && rope.write_cache)
-      page = rope.cache.page_table[(size_t)slot * rope.cache.max_pages + pos / rope.cache.page_size];
   }
   __device__ __forceinline__ void finish(void* c, int M, int N, const RopeArgs& rope, float v0, float v1) const {
     if (EPI == EPI_QKV_ROPE) {
@@ -174,16 +168,13 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_cluster_kernel(void* __restri
   // the owner's first two units (pair p fastest, then tile, then token: neighbouring threads store side by side)
   int units = ITEMS * 8 * tokens_here;
   Unit<EPI> early[2];
-  auto ask_first = [&]() {
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      int idx = tid + j * WARPS * 32;
-      if (idx < units)
-        early[j].first(c, (int)rank * tokens_here + idx / (ITEMS * 8), cluster * ITEMS + (idx >> 3) % ITEMS, idx & 7, M,
+  for (int j = 0; j < 2; ++j) {
+    int idx = tid + j * WARPS * 32;
+    if (idx < units)
+      early[j].prepare(c, (int)rank * tokens_here + idx / (ITEMS * 8), cluster * ITEMS + (idx >> 3) % ITEMS, idx & 7, M,
                        N, items, rope);
-    }
-  };
-  if (s_begin >= s_end) ask_first();
+  }
 
   for (int s0 = s_begin; s0 < s_end; s0 += STEPS) {
     uint4 xb[STEPS][NT];
@@ -209,7 +200,6 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_cluster_kernel(void* __restri
           }
         }
       }
-      if (s0 == s_begin) ask_first();
 #pragma unroll
       for (int i = 0; i < STEPS; ++i) {
 #pragma unroll
@@ -234,7 +224,6 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_cluster_kernel(void* __restri
           xb[i][n] = (ok && m < M) ? *((const uint4*)((const bf16*)a + (size_t)m * K) + ch) : zero;
         }
       }
-      if (s0 == s_begin) ask_first();
     }
 #pragma unroll
     for (int i = 0; i < STEPS; ++i) {
@@ -252,8 +241,6 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_cluster_kernel(void* __restri
     if (s0 + STEPS < s_end) load_weights(s0 + STEPS);
   }
 
-  early[0].second(rope);
-  early[1].second(rope);
   // the warp's partial tile (and sums of squares) to shared memory
   float* mine = red + warp * (ROWS + 1) * STRIDE;
 #pragma unroll
@@ -272,8 +259,6 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_cluster_kernel(void* __restri
       if (t == 0) mine[ROWS * STRIDE + n * 8 + g] = v;
     }
   }
-  early[0].third(rope);
-  early[1].third(rope);
   __syncthreads();
   cluster_wait_acquire();  // (pairs with the arrival at the top)
 
@@ -324,10 +309,8 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_cluster_kernel(void* __restri
   if (tid + WARPS * 32 < units) finish(tid + WARPS * 32, early[1]);
   for (int idx = tid + 2 * WARPS * 32; idx < units; idx += WARPS * 32) {
     Unit<EPI> late;
-    late.first(c, (int)rank * tokens_here + idx / (ITEMS * 8), cluster * ITEMS + (idx >> 3) % ITEMS, idx & 7, M, N,
-               items, rope);
-    late.second(rope);
-    late.third(rope);
+    late.prepare(c, (int)rank * tokens_here + idx / (ITEMS * 8), cluster * ITEMS + (idx >> 3) % ITEMS, idx & 7, M, N,
+                 items, rope);
     finish(idx, late);
   }
 }
