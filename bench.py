@@ -804,7 +804,8 @@ def main() -> int:
            "what": "generated tokens / wall time of Engine.generate (prompts of 128-2048 tokens included)",
            "call_s": round(whole["call_s"], 5), "prefill_s": round(whole["prefill_s"], 5),
            "decode_s": round(whole["decode_s"], 5), "decode_only": round(whole["decode_tokens_per_s"], 1),
-           "h2d_bytes_per_step": round((prompt_bytes + graph.host.numel() * 4 * (args.steps / engine.decode_chunk))
+           # (no stop tokens in this run: the decode steps go in runs of up to DecodeGraph.CAPACITY, one load each)
+           "h2d_bytes_per_step": round((prompt_bytes + graph.host.numel() * 4 * -(-args.steps // graph.CAPACITY))
                                        / (args.steps + 1), 1),
            "d2h_bytes_per_step": args.batch * 4}
 

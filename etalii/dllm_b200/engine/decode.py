@@ -14,7 +14,7 @@ from .batch import StepBatch, StepLayout, step_values
 
 
 class DecodeGraph:
-    CAPACITY = 64
+    CAPACITY = 256
     """Most steps one run may take before the host reads the tokens."""
 
     def __init__(self, engine, batch_size: int, options, use_graph: bool = True, max_context: int | None = None,

@@ -210,7 +210,7 @@ class Engine:
             raise ValueError("seeds: one per prompt")
         stats = self.stats = {"prefill_s": 0.0, "prefill_tokens": 0, "decode_s": 0.0, "decode_steps": 0,
                               "decode_tokens": 0}
-        prompts = [list(map(int, p)) for p in prompts]
+        prompts = [np.asarray(p, dtype=np.int64).reshape(-1) for p in prompts]  # one pass over each list
         window = min(self.context_length, self.max_length)
         check_prompts(prompts, self.vocab_size, window)
         stops = set() if ignore_eos else set(self.spec.stop_token_ids)
@@ -260,7 +260,8 @@ class Engine:
             else:
                 self.close([slots[p] for p in positions])
 
-        return run_batches(prompts, batches, make_run, start, prefill, decode, finish, chunk=self.decode_chunk)
+        return run_batches(prompts, batches, make_run, start, prefill, decode, finish, chunk=self.decode_chunk,
+                           free_chunk=DecodeGraph.CAPACITY)
 
     def complete(self, prompt: Sequence[int], max_tokens: int = 64,
                  options: SamplingOptions | None = None, **kwargs) -> GenerationResult:

@@ -32,15 +32,19 @@ class GenerationResult:
 
 
 def check_prompts(prompts: Sequence[Sequence[int]], vocab_size: int, context_length: int) -> None:
+    """Raises for an empty prompt, a prompt that fills the context window, or a token outside the vocabulary (one
+    vectorised look at each prompt: lists of thousands of ids are common)."""
     for index, prompt in enumerate(prompts):
         if len(prompt) == 0:
             raise ValueError(f"prompt {index} is empty")
         if len(prompt) >= context_length:
             raise ContextLengthError(
                 f"the prompt has {len(prompt)} tokens; the context window holds {context_length}")
-        for token in prompt:
-            if not 0 <= int(token) < vocab_size:
-                raise ValueError(f"prompt {index}: token {token} is outside the vocabulary of {vocab_size}")
+        tokens = np.asarray(prompt)
+        outside = (tokens < 0) | (tokens >= vocab_size)
+        if outside.any():
+            token = tokens[int(np.argmax(outside))]
+            raise ValueError(f"prompt {index}: token {token} is outside the vocabulary of {vocab_size}")
 
 
 def plan_batches(prompt_lengths: Sequence[int], max_new_tokens: int, context_length: int, page_size: int,
@@ -123,7 +127,7 @@ class BatchRun:
 
 def run_batches(prompts: Sequence[Sequence[int]], batches: Sequence[Sequence[int]],
                 make_run: Callable[[list[int]], BatchRun], start: Callable, prefill: Callable, decode: Callable,
-                finish: Callable, chunk: int = 16) -> list[GenerationResult]:
+                finish: Callable, chunk: int = 16, free_chunk: int | None = None) -> list[GenerationResult]:
     """Drives batches one after another. `start(indices) -> handle` takes cache room for a batch;
     `prefill(handle, positions, prompts) -> tokens` runs the whole prompts of the named batch positions and chooses
     each one's first token; `decode(handle, positions, last_tokens, steps) -> [step][position] tokens` runs up to
@@ -131,7 +135,8 @@ def run_batches(prompts: Sequence[Sequence[int]], batches: Sequence[Sequence[int
     what ended sequences hold (None: everything, after an error).
 
     A sequence that ends inside a run of decode steps keeps its place until the run is over; what was chosen for
-    it after its end is dropped."""
+    it after its end is dropped. A batch without stop tokens can only end by length, which is known beforehand:
+    there the host has nothing to decide in between and a run may take `free_chunk` steps (if given) at a time."""
     results: list[GenerationResult | None] = [None] * len(prompts)
     for indices in batches:
         run = make_run(list(indices))
@@ -145,10 +150,11 @@ def run_batches(prompts: Sequence[Sequence[int]], batches: Sequence[Sequence[int
             while run.active:
                 positions = list(run.active)
                 if first:
-                    steps = [prefill(handle, positions, [list(prompts[indices[p]]) for p in positions])]
+                    steps = [prefill(handle, positions, [prompts[indices[p]] for p in positions])]
                     first = False
                 else:
-                    steps = decode(handle, positions, [last[p] for p in positions], min(chunk, run.steps_left()))
+                    at_most = free_chunk if free_chunk and not run.stop_ids else chunk
+                    steps = decode(handle, positions, [last[p] for p in positions], min(at_most, run.steps_left()))
                 ended: list[int] = []
                 for chosen in steps:
                     by_position = dict(zip(positions, chosen))

@@ -75,11 +75,28 @@ class Scripted:
             self.open[handle].remove(p)  # KeyError if something is given back twice
 
 
-def _run(prompts, batches, fake, max_new, stops, window=100, chunk=16):
+def _run(prompts, batches, fake, max_new, stops, window=100, chunk=16, free_chunk=None):
     def make_run(indices):
         return BatchRun([len(prompts[i]) for i in indices], max_new, frozenset(stops), window)
 
-    return run_batches(prompts, batches, make_run, fake.start, fake.prefill, fake.decode, fake.finish, chunk=chunk)
+    return run_batches(prompts, batches, make_run, fake.start, fake.prefill, fake.decode, fake.finish, chunk=chunk,
+                       free_chunk=free_chunk)
+
+
+def test_a_batch_without_stop_tokens_decodes_in_longer_runs():
+    """Without stop tokens only the lengths end sequences, and those are known: the host need not look in between.
+    With stop tokens the runs stay short, whatever the longer limit is."""
+    prompts = [[1, 2, 3], [10]]
+    fake = Scripted()
+    results = _run(prompts, [[0, 1]], fake, 41, set(), chunk=4, free_chunk=32)
+    assert [entry[3] for entry in fake.log if entry[0] == "decode"] == [32, 8]
+    assert [len(r.tokens) for r in results] == [41, 41] and results[0].tokens[:3] == (4, 5, 6)
+    fake = Scripted()
+    _run(prompts, [[0, 1]], fake, 41, {1000}, chunk=4, free_chunk=32)
+    assert [entry[3] for entry in fake.log if entry[0] == "decode"] == [4] * 10
+    fake = Scripted()
+    _run(prompts, [[0, 1]], fake, 41, set(), window=30, chunk=4, free_chunk=32)   # the context ends the first sooner
+    assert [entry[3] for entry in fake.log if entry[0] == "decode"][0] == 26
 
 
 @pytest.mark.parametrize("chunk", [1, 2, 16])
