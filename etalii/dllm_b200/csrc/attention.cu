@@ -31,6 +31,24 @@ __device__ __forceinline__ float dot_vec(const float* q, const __nv_bfloat16* k)
   return s;
 }
 
+// The same sums from a vector that is already in registers (one load of a key for several queries).
+__device__ __forceinline__ float4 load_vec(const float* k) { return *(const float4*)k; }
+__device__ __forceinline__ uint4 load_vec(const __nv_bfloat16* k) { return *(const uint4*)k; }
+__device__ __forceinline__ float dot_loaded(const float* q, float4 v) {
+  return fmaf(q[3], v.w, fmaf(q[2], v.z, fmaf(q[1], v.y, q[0] * v.x)));
+}
+__device__ __forceinline__ float dot_loaded(const float* q, uint4 raw) {
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 x = __bfloat1622float2(p[i]);
+    s = fmaf(q[2 * i], x.x, s);
+    s = fmaf(q[2 * i + 1], x.y, s);
+  }
+  return s;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(WARPS * 32) attention_warp_kernel(
     T* __restrict__ out, const T* __restrict__ q, KvLayout cache, const int* __restrict__ tok_seq,
@@ -136,9 +154,12 @@ __global__ void __launch_bounds__(512) attention_block_kernel(
   int block_tokens = token_slots * R;
   int slot_of_warp = warp / heads_per_pass, head_of_warp = warp % heads_per_pass;
   T* kv_s = reinterpret_cast<T*>(smem_raw);       // [stages][k|v][64][ld]
-  float* q_s = reinterpret_cast<float*>(smem_raw + (size_t)stages * 2 * 64 * ld * sizeof(T)) + (size_t)warp * R * hd;
+  float* q_all = reinterpret_cast<float*>(smem_raw + (size_t)stages * 2 * 64 * ld * sizeof(T));
+  float* q_s = q_all + (size_t)warp * R * hd;                        // this warp's R queries
+  float* p_s = q_all + (size_t)warps * R * hd + (size_t)warp * R * 32;  // and their weights for the tile at hand
   int g = blockIdx.y, group = heads / cache.kv_heads;
-  int t0 = blockIdx.x * block_tokens, t_stop = min(tokens, t0 + block_tokens);
+  // (the last tokens of a prompt see the most keys: their blocks go first, the short ones fill the gaps behind)
+  int t0 = (int)(gridDim.x - 1 - blockIdx.x) * block_tokens, t_stop = min(tokens, t0 + block_tokens);
 
   for (int pass = 0; pass < group; pass += heads_per_pass) {
     int h = g * group + pass + head_of_warp;
@@ -187,43 +208,81 @@ __global__ void __launch_bounds__(512) attention_block_kernel(
           asm volatile("cp.async.wait_group 0;\n" ::: "memory");
         }
         __syncthreads();
+        // The warp's R tokens walk the tile together: a key is loaded once for the R scores and a value once for the
+        // R weighted sums (what a token computes, and in which order, is what it would compute alone).
+        for (int j0 = p * 64; j0 < p * 64 + 64; j0 += 32) {
+          bool active[R], any = false, whole = hd == CHUNKS * 32;
 #pragma unroll
-        for (int r = 0; r < R; ++r) {
-          for (int j0 = p * 64; j0 < p * 64 + 64; j0 += 32) {
-            if (j0 >= end[r] || j0 + 32 <= first[r]) continue;  // (warp-uniform) no visible key in this tile
-            int j = j0 + lane;
-            bool valid = j >= first[r] && j < end[r];
-            float s = -INFINITY;
-            if (valid) {
-              const T* krow = k_s + (j - p * 64) * ld;
-              float dot = 0.f;
-              if (hd == CHUNKS * 32) {
+          for (int r = 0; r < R; ++r) {
+            active[r] = j0 < end[r] && j0 + 32 > first[r];  // (warp-uniform) a visible key in this tile
+            any = any || active[r];
+            whole = whole && (!active[r] || (first[r] <= j0 && j0 + 32 <= end[r]));
+          }
+          if (!any) continue;
+          int j = j0 + lane;
+          const T* krow = k_s + (j - p * 64) * ld;
+          float dot[R];
 #pragma unroll
-                for (int d = 0; d < CHUNKS * 32; d += Vec<T>::N) dot += dot_vec(&q_s[r * hd + d], krow + d);
-              } else {
-                for (int d = 0; d < hd; d += Vec<T>::N) dot += dot_vec(&q_s[r * hd + d], krow + d);
-              }
-              s = dot * scale;
+          for (int r = 0; r < R; ++r) dot[r] = 0.f;
+          if (hd == CHUNKS * 32) {
+#pragma unroll
+            for (int d = 0; d < CHUNKS * 32; d += Vec<T>::N) {
+              auto key = load_vec(krow + d);
+#pragma unroll
+              for (int r = 0; r < R; ++r) dot[r] += dot_loaded(&q_s[r * hd + d], key);
             }
-            float m_new = fmaxf(m_run[r], warp_max(s));
-            float pr = valid ? expf(s - m_new) : 0.f;
+          } else {
+            for (int d = 0; d < hd; d += Vec<T>::N) {
+              auto key = load_vec(krow + d);
+#pragma unroll
+              for (int r = 0; r < R; ++r) dot[r] += dot_loaded(&q_s[r * hd + d], key);
+            }
+          }
+          __syncwarp();  // (the weights of the tile before have been read by every lane)
+#pragma unroll
+          for (int r = 0; r < R; ++r) {
+            if (!active[r]) continue;
+            bool valid = j >= first[r] && j < end[r];
+            float sc = valid ? dot[r] * scale : -INFINITY;
+            float m_new = fmaxf(m_run[r], warp_max(sc));
+            float pr = valid ? expf(sc - m_new) : 0.f;
             float corr = expf(m_run[r] - m_new);  // 0 on the first tile (m_run = -inf)
             l_run[r] = l_run[r] * corr + warp_sum(pr);
 #pragma unroll
             for (int i = 0; i < CHUNKS; ++i) acc[r][i] *= corr;
             m_run[r] = m_new;
-            int from = max(0, first[r] - j0), to = min(32, end[r] - j0);
-            const T* vtile = v_s + (j0 - p * 64) * ld + lane;
-            if (from == 0 && to == 32 && hd == CHUNKS * 32) {  // a whole tile of a whole head: no bounds in the loop
-#pragma unroll 8
-              for (int jj = 0; jj < 32; ++jj) {
-                float pj = __shfl_sync(0xffffffffu, pr, jj);
+            p_s[r * 32 + lane] = pr;
+          }
+          __syncwarp();
+          const T* vtile = v_s + (j0 - p * 64) * ld + lane;
+          if (whole) {  // whole tiles of a whole head for every token that sees the tile: no bounds in the loop
+#pragma unroll 4
+            for (int jj = 0; jj < 32; jj += 4) {
+              float v[4][CHUNKS];
 #pragma unroll
-                for (int i = 0; i < CHUNKS; ++i) acc[r][i] = fmaf(pj, to_float(vtile[jj * ld + 32 * i]), acc[r][i]);
+              for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int i = 0; i < CHUNKS; ++i) v[u][i] = to_float(vtile[(jj + u) * ld + 32 * i]);
+#pragma unroll
+              for (int r = 0; r < R; ++r) {
+                if (!active[r]) continue;  // (a token that does not see the tile must not meet what lies there)
+                float4 pj = *reinterpret_cast<const float4*>(&p_s[r * 32 + jj]);
+#pragma unroll
+                for (int i = 0; i < CHUNKS; ++i) {
+                  acc[r][i] = fmaf(pj.x, v[0][i], acc[r][i]);
+                  acc[r][i] = fmaf(pj.y, v[1][i], acc[r][i]);
+                  acc[r][i] = fmaf(pj.z, v[2][i], acc[r][i]);
+                  acc[r][i] = fmaf(pj.w, v[3][i], acc[r][i]);
+                }
               }
-            } else {
+            }
+          } else {
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+              if (!active[r]) continue;
+              int from = max(0, first[r] - j0), to = min(32, end[r] - j0);
               for (int jj = from; jj < to; ++jj) {
-                float pj = __shfl_sync(0xffffffffu, pr, jj);
+                float pj = p_s[r * 32 + jj];
 #pragma unroll
                 for (int i = 0; i < CHUNKS; ++i)
                   if (lane + 32 * i < hd) acc[r][i] = fmaf(pj, to_float(vtile[jj * ld + 32 * i]), acc[r][i]);
@@ -264,7 +323,8 @@ int launch_blocks(void* out, const void* q, const KvLayout& cache, const int* to
   int token_slots = R == 1 ? 1 : (16 / heads_per_pass > 0 ? 16 / heads_per_pass : 1);
   int warps = token_slots * heads_per_pass;
   int ld = cache.head_dim + Pad<T>::N;
-  size_t stage_bytes = (size_t)2 * 64 * ld * sizeof(T), q_bytes = (size_t)warps * R * cache.head_dim * sizeof(float);
+  size_t stage_bytes = (size_t)2 * 64 * ld * sizeof(T);
+  size_t q_bytes = (size_t)warps * R * (cache.head_dim + 32) * sizeof(float);  // queries and a tile's weights
   int stages = 2 * stage_bytes + q_bytes <= 200 * 1024 ? 2 : 1;
   size_t smem = stages * stage_bytes + q_bytes;
   static size_t configured = 0;
@@ -326,11 +386,11 @@ DLLM_EXPORT int dllm_attention_blocks(void* out, const void* q, void* cache_base
   else if (chunks <= 4) DLLM_GO(T, R, 4);     \
   else DLLM_GO(T, R, 8)
   if (dtype == DLLM_F32) {
-    if (runs) { DLLM_BY_WIDTH(float, 2); }
+    if (runs) { DLLM_BY_WIDTH(float, 4); }
     DLLM_BY_WIDTH(float, 1);
   }
   if (dtype == DLLM_BF16) {
-    if (runs) { DLLM_BY_WIDTH(__nv_bfloat16, 2); }
+    if (runs) { DLLM_BY_WIDTH(__nv_bfloat16, 4); }
     DLLM_BY_WIDTH(__nv_bfloat16, 1);
   }
 #undef DLLM_BY_WIDTH
