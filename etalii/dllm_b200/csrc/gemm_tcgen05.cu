@@ -23,14 +23,15 @@ constexpr int BM = 128, BK = 64, UMMA_K = 16;
 // DEEP: a ring of nine or ten stages (about 215 KB) for a block that has its multiprocessor to itself: a product
 // with no more tiles than the device has multiprocessors and a short reduction then brings a tile's whole operand
 // panels in one round trip instead of three.
-template <int BN, bool DEEP = false> struct Shape {
+template <int BN, bool DEEP = false, int EPI_STAGE = 0> struct Shape {
   static constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
   static constexpr int ACC_COLS = BN < 32 ? 32 : BN;   // columns of one accumulator
   static constexpr int TMEM_COLS = 2 * ACC_COLS;       // two accumulators: a power of two, at least 32
   // about 96 KB a block where that is enough (two blocks share an SM, 2 x TMEM_COLS <= 512 columns); the 256-wide
   // tile takes four 48 KB stages and all of the tensor memory, so one block owns the SM
   static constexpr int STAGES = DEEP ? (220 * 1024) / (A_BYTES + B_BYTES) : (BN >= 256 ? 4 : (BN >= 128 ? 3 : 4));
-  static constexpr size_t SMEM = (size_t)STAGES * (A_BYTES + B_BYTES) + 1024;
+  // (EPI_STAGE: bytes behind the ring through which an epilogue makes its global stores whole lines)
+  static constexpr size_t SMEM = (size_t)STAGES * (A_BYTES + B_BYTES) + 1024 + EPI_STAGE;
   static constexpr int BLOCKS_PER_SM = (DEEP || BN >= 256) ? 1 : 2;
   // Epilogue warps: one per quarter of the tensor memory's lanes, or two that take half the columns each. A row's
   // epilogue is a chain of loads and special functions, so wide tiles gain from twice the warps (2048 x 2048 x 8192
@@ -44,13 +45,19 @@ template <int BN, bool DEEP = false> struct Shape {
 // (neighbouring blocks share a tile of W and read different rows of A). The producer's ring of stages runs on across
 // tiles; the accumulator alternates between two halves of the block's tensor memory, so the epilogue of one tile
 // overlaps the products of the next.
+// The SwiGLU epilogue of the 256-wide tile writes 128 bytes of a row per warp: it goes through 4 KB of shared memory
+// per warp behind the ring, so that eight lanes write a row's 128 bytes together (see the residual epilogue below).
+template <int BN, int EPI, bool DEEP> struct EpilogueStage {
+  static constexpr int BYTES = (EPI == EPI_SWIGLU && BN == 256 && !DEEP) ? 8 * 4096 : 0;
+};
+
 template <int BN, int EPI, bool DEEP, int HD>
 __global__ void __launch_bounds__(Shape<BN, DEEP>::THREADS, Shape<BN, DEEP>::BLOCKS_PER_SM) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                const __grid_constant__ CUtensorMap map_w,
                                                                void* __restrict__ c, int M, int N, int K,
                                                                int* __restrict__ status, RopeArgs rope, int m_tiles,
                                                                int n_tiles, NormArgs norm) {
-  typedef Shape<BN, DEEP> S;
+  typedef Shape<BN, DEEP, EpilogueStage<BN, EPI, DEEP>::BYTES> S;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);  // swizzle atoms: 1 KB
   __shared__ uint64_t full_bar[S::STAGES], empty_bar[S::STAGES], acc_full[2], acc_empty[2];
@@ -139,8 +146,29 @@ __global__ void __launch_bounds__(Shape<BN, DEEP>::THREADS, Shape<BN, DEEP>::BLO
       // (narrow tiles: the row's old residual values are all asked for before the accumulator is read, so their
       // round trip runs under the wait for the products instead of after it, once per 16 columns)
       constexpr bool EARLY = EPI == EPI_RESIDUAL && BN <= 64;
+      // A block with the deep ring has one tile, and when its accumulator is full every stage of the ring has been
+      // read: the residual epilogue then goes through that shared memory, so that the rows it reads and writes in
+      // global memory are whole 128-byte lines per eight lanes instead of 16 bytes of 32 different rows per
+      // instruction (a thread's accumulator row goes to shared memory, four rows of 32 columns come back per
+      // instruction). Measured as links of a chain, with the residual, its copy and the sums of squares: 2048 x 576 x 576
+      // 8.3 -> 6.2 µs, 2048 x 576 x 1536 12.9 -> 11.0 µs (the same products with a plain bfloat16 store: 5.9 and 10.8).
+      constexpr bool STAGED = DEEP && EPI == EPI_RESIDUAL && BN == 64;
+      const bool staged = STAGED && (N & 3) == 0;
+      const int sub = lane >> 3, seg = lane & 7;  // staged: row i * 4 + sub of the warp's 32, floats seg * 4 .. + 3
+      float4 old_rows[STAGED ? BN / 32 : 1][STAGED ? 8 : 1];
+      if (staged) {
+#pragma unroll
+        for (int ch = 0; ch < BN / 32; ++ch)
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            int mr = m0 + quarter * 32 + i * 4 + sub, nc = n0 + ch * 32 + seg * 4;
+            old_rows[STAGED ? ch : 0][STAGED ? i : 0] =
+                (mr < M && nc < N) ? *reinterpret_cast<const float4*>((const float*)c + (size_t)mr * N + nc)
+                                   : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+      }
       float4 old[EARLY ? HALF / 4 : 1];
-      if (EARLY && norm.copy_out != nullptr && m < M) {
+      if (EARLY && !staged && norm.copy_out != nullptr && m < M) {
 #pragma unroll
         for (int i = 0; i < HALF / 4; ++i)
           old[i] = n0 + c0 + 4 * i < N
@@ -231,6 +259,83 @@ __global__ void __launch_bounds__(Shape<BN, DEEP>::THREADS, Shape<BN, DEEP>::BLO
             *reinterpret_cast<uint4*>(dst + HEAD / 2 + first_pair + i) = o;
           }
         }
+      } else if (EpilogueStage<BN, EPI, DEEP>::BYTES > 0 && (N & 15) == 0) {
+        // SwiGLU, 256-wide tile: the thread's 64 outputs (eight 16-byte pieces) go to its row of the warp's staging
+        // space, piece p at place p ^ (row % 8) so that a quarter warp's stores and loads meet different banks; then
+        // eight lanes write a row's 128 bytes to global memory together, four rows an instruction.
+        unsigned char* stage = tiles + (size_t)S::STAGES * (S::A_BYTES + S::B_BYTES) + (size_t)(warp - 2) * 4096;
+#pragma unroll
+        for (int cc = 0; cc < HALF; cc += 16) {
+          unsigned v[16];
+          tmem_load16(acc + (unsigned)(c0 + cc), v);
+          if (cc + 16 >= HALF) release_accumulator();
+          uint4 o;
+          __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            po[i] = __floats2bfloat162_rn(
+                silu_for<bf16>(__uint_as_float(v[4 * i]) * scale_row) * (__uint_as_float(v[4 * i + 1]) * scale_row),
+                silu_for<bf16>(__uint_as_float(v[4 * i + 2]) * scale_row) * (__uint_as_float(v[4 * i + 3]) * scale_row));
+          *reinterpret_cast<uint4*>(stage + lane * 128 + ((((cc >> 4)) ^ (lane & 7)) << 4)) = o;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          int row = i * 4 + (lane >> 3), piece = lane & 7;
+          uint4 o = *reinterpret_cast<const uint4*>(stage + row * 128 + ((piece ^ (row & 7)) << 4));
+          int mr = m0 + quarter * 32 + row, nc = n0 + c0 + piece * 16;  // (the piece's first accumulator column)
+          if (mr < M && nc < N) *reinterpret_cast<uint4*>((bf16*)c + (size_t)mr * (N / 2) + (nc >> 1)) = o;
+        }
+        __syncwarp();  // (the block's next tile overwrites the staged rows)
+      } else if (staged) {
+        constexpr int LD = 36;  // floats per staged row: 16-byte pieces, rows of a quarter warp in different banks
+        float* st = reinterpret_cast<float*>(tiles) + (size_t)(warp - 2) * 32 * LD;
+        float squares[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) squares[i] = 0.f;
+#pragma unroll
+        for (int ch = 0; ch < BN / 32; ++ch) {
+#pragma unroll
+          for (int part = 0; part < 2; ++part) {
+            unsigned v[16];
+            tmem_load16(acc + (unsigned)(ch * 32 + part * 16), v);
+#pragma unroll
+            for (int i = 0; i < 16; i += 4)
+              *reinterpret_cast<float4*>(st + lane * LD + part * 16 + i) =
+                  make_float4(__uint_as_float(v[i]), __uint_as_float(v[i + 1]), __uint_as_float(v[i + 2]),
+                              __uint_as_float(v[i + 3]));
+          }
+          if (ch == BN / 32 - 1) release_accumulator();
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            int row = i * 4 + sub, mr = m0 + quarter * 32 + row, nc = n0 + ch * 32 + seg * 4;
+            float4 a = *reinterpret_cast<const float4*>(st + row * LD + seg * 4);
+            if (mr < M && nc < N) {
+              float4 r = old_rows[STAGED ? ch : 0][STAGED ? i : 0];
+              r.x += a.x; r.y += a.y; r.z += a.z; r.w += a.w;
+              *reinterpret_cast<float4*>((float*)c + (size_t)mr * N + nc) = r;
+              if (norm.copy_out != nullptr) {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(r.x, r.y), hi = __floats2bfloat162_rn(r.z, r.w);
+                *reinterpret_cast<uint2*>(norm.copy_out + (size_t)mr * N + nc) =
+                    make_uint2(*reinterpret_cast<unsigned*>(&lo), *reinterpret_cast<unsigned*>(&hi));
+                squares[i] = fmaf(r.x, r.x, fmaf(r.y, r.y, fmaf(r.z, r.z, fmaf(r.w, r.w, squares[i]))));
+              }
+            }
+          }
+          __syncwarp();  // (the next 32 columns overwrite the staged rows)
+        }
+        if (norm.ssq_out != nullptr) {  // a row's eight lanes, summed in a fixed order
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            float v = squares[i];
+            v += __shfl_xor_sync(0xffffffffu, v, 1);
+            v += __shfl_xor_sync(0xffffffffu, v, 2);
+            v += __shfl_xor_sync(0xffffffffu, v, 4);
+            int mr = m0 + quarter * 32 + i * 4 + sub;
+            if (seg == 0 && mr < M) norm.ssq_out[(size_t)n_tile * M + mr] = v;
+          }
+        }
       } else {
         float ssq = 0.f;  // EPI_RESIDUAL with norm.copy_out: the squares of the new residual values of this half tile
 #pragma unroll
@@ -289,7 +394,7 @@ __global__ void __launch_bounds__(Shape<BN, DEEP>::THREADS, Shape<BN, DEEP>::BLO
 template <int BN, int EPI, bool DEEP, int HD>
 int launch_shape(void* c, const CUtensorMap& map_a, const CUtensorMap& map_w, int M, int N, int K, int* status,
                  cudaStream_t stream, const RopeArgs& rope, int m_tiles, int n_tiles, int sms, const NormArgs& norm) {
-  typedef Shape<BN, DEEP> S;
+  typedef Shape<BN, DEEP, EpilogueStage<BN, EPI, DEEP>::BYTES> S;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, EPI, DEEP, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -358,7 +463,7 @@ static int gemm_entry(void* c, const void* a, const void* w, int M, int N, int K
     return DLLM_UNSUPPORTED_SIZE;
   if (tile_n == 0) {
     long long m_tiles = (M + BM - 1) / BM;
-    long long tiles256 = m_tiles * ((N + 255) / 256), tiles64 = m_tiles * ((N + 63) / 64);
+    long long tiles256 = m_tiles * ((N + 255) / 256);
     if (M <= 256) tile_n = 32;  // few rows: many narrow tiles
     // enough 256-wide tiles to give every multiprocessor one: the widest tile reuses A most (measured: 1.0 to 1.4
     // PFLOP/s from K = 2048 up, against 0.6 to 1.2 for the 128-wide tile; at K = 576, 2048 x 3072 with SwiGLU:
