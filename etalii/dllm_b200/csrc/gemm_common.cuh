@@ -34,6 +34,7 @@ struct RopeArgs {
   const int* slots;
   int write_cache;
   int prefetch_window;   // -1: no prefetch; 0: every page of the tokens' sequences; w > 0: the pages of the last w keys
+  int table_positions;   // the tile product only: its table is [rotary_dim / 2][table_positions] (see gemm_tcgen05.cu)
 };
 
 // RMSNorm around the tile product of prefill-sized steps, without a kernel of its own. The product that writes the

@@ -230,10 +230,14 @@ __global__ void __launch_bounds__(Shape<BN, DEEP>::THREADS, Shape<BN, DEEP>::BLO
           int head = n_tile * SEGS + seg;
           if (m >= M || head >= heads + 2 * nkv || !(head < heads || rope.write_cache)) continue;
           if (rope.table != nullptr && head < heads + nkv) {
-            const float2* cs = rope.table + (size_t)pos * (rope.rotary_dim / 2) + first_pair;
+            // The table lies pair by pair here, [pair][position]: the 32 tokens of a warp, at consecutive positions in a
+            // prompt, then read 256 consecutive bytes per pair. (Position by position, [position][pair], every lane
+            // read its own row: 32 lines an instruction, and the rotation cost 5 of the product's 12.5 µs at
+            // 2048 x 960 x 576.)
+            const float2* cs = rope.table + (size_t)first_pair * rope.table_positions + pos;
 #pragma unroll
             for (int i = 0; i < W; ++i) {  // rotary_dim == head_dim here: the partner sits half a head away
-              float2 tc = cs[i];
+              float2 tc = cs[(size_t)i * rope.table_positions];
               float x = lo[i], y = hi[i];
               lo[i] = fmaf(x, tc.x, -(y * tc.y));
               hi[i] = fmaf(x, tc.y, y * tc.x);
@@ -520,18 +524,22 @@ DLLM_EXPORT int dllm_gemm_tcgen05_residual_norm(void* x, void* copy_out, float* 
 // The q/k/v projection of a prefill-sized step in one kernel: W is [(heads + 2 kv_heads) * head_dim, K], every tile
 // of the product is one or several whole heads (head_dim 32, 64 or 128; rotary_dim equal to head_dim, or no table), its epilogue
 // rotates q and k by the table's angle for each token's position and writes q to q_out and k, v into the paged cache.
+// The table is laid out pair by pair: [rotary_dim / 2][table_positions](cos, sin).
 static int qkv_rope_entry(const void* a, const void* w, int M, int K, void* q_out, void* cache_base,
                           const int* page_table, int max_pages, int page_size, int heads, int kv_heads, int head_dim,
-                          const float* table, int rotary_dim, const int* tok_seq, const int* tok_pos, const int* slots,
-                          int write_cache, int* status, cudaStream_t stream, const NormArgs& norm) {
+                          const float* table, int rotary_dim, int table_positions, const int* tok_seq,
+                          const int* tok_pos, const int* slots, int write_cache, int* status, cudaStream_t stream,
+                          const NormArgs& norm) {
   if (M <= 0) return DLLM_OK;
+  if (table != nullptr && table_positions <= 0) return DLLM_BAD_ARGUMENT;
   if (K <= 0 || (K & 7) || ((uintptr_t)a & 15) || ((uintptr_t)w & 15) || status == nullptr || heads <= 0 ||
       kv_heads <= 0)
     return DLLM_UNSUPPORTED_SIZE;
   if ((head_dim != 32 && head_dim != 64 && head_dim != 128) || (table != nullptr && rotary_dim != head_dim))
     return DLLM_UNSUPPORTED_SIZE;
   RopeArgs rope{(bf16*)q_out, KvLayout{cache_base, page_table, max_pages, page_size, kv_heads, head_dim},
-                (const float2*)table, table ? rotary_dim : 0, heads, tok_seq, tok_pos, slots, write_cache};
+                (const float2*)table, table ? rotary_dim : 0, heads, tok_seq, tok_pos, slots, write_cache, -1,
+                table_positions};
   int N = (heads + 2 * kv_heads) * head_dim;
   // a tile is one head, or four heads of 64 / two of 128 where the product is large enough to fill the device with
   // the wide tiles (which reuse A four times as often: 1.0 to 1.2 PFLOP/s against 0.6)
@@ -550,10 +558,11 @@ static int qkv_rope_entry(const void* a, const void* w, int M, int K, void* q_ou
 DLLM_EXPORT int dllm_gemm_tcgen05_qkv_rope(const void* a, const void* w, int M, int K, void* q_out, void* cache_base,
                                            const int* page_table, int max_pages, int page_size, int heads,
                                            int kv_heads, int head_dim, const float* table, int rotary_dim,
-                                           const int* tok_seq, const int* tok_pos, const int* slots, int write_cache,
-                                           int* status, cudaStream_t stream) {
+                                           int table_positions, const int* tok_seq, const int* tok_pos,
+                                           const int* slots, int write_cache, int* status, cudaStream_t stream) {
   return qkv_rope_entry(a, w, M, K, q_out, cache_base, page_table, max_pages, page_size, heads, kv_heads, head_dim,
-                        table, rotary_dim, tok_seq, tok_pos, slots, write_cache, status, stream, NormArgs{});
+                        table, rotary_dim, table_positions, tok_seq, tok_pos, slots, write_cache, status, stream,
+                        NormArgs{});
 }
 
 // The same with the RMSNorm folded around it: `a` is the bfloat16 copy of the un-normed residual rows, `w` carries
@@ -561,12 +570,12 @@ DLLM_EXPORT int dllm_gemm_tcgen05_qkv_rope(const void* a, const void* w, int M, 
 DLLM_EXPORT int dllm_gemm_tcgen05_qkv_rope_normed(const void* a, const void* w, int M, int K, void* q_out,
                                                   void* cache_base, const int* page_table, int max_pages,
                                                   int page_size, int heads, int kv_heads, int head_dim,
-                                                  const float* table, int rotary_dim, const int* tok_seq,
-                                                  const int* tok_pos, const int* slots, int write_cache,
-                                                  const float* ssq_in, int parts_in, float eps, int* status,
-                                                  cudaStream_t stream) {
+                                                  const float* table, int rotary_dim, int table_positions,
+                                                  const int* tok_seq, const int* tok_pos, const int* slots,
+                                                  int write_cache, const float* ssq_in, int parts_in, float eps,
+                                                  int* status, cudaStream_t stream) {
   if (ssq_in == nullptr || parts_in <= 0 || K <= 0) return DLLM_BAD_ARGUMENT;
   NormArgs norm{ssq_in, parts_in, 1.0f / (float)K, eps, nullptr, nullptr};
   return qkv_rope_entry(a, w, M, K, q_out, cache_base, page_table, max_pages, page_size, heads, kv_heads, head_dim,
-                        table, rotary_dim, tok_seq, tok_pos, slots, write_cache, status, stream, norm);
+                        table, rotary_dim, table_positions, tok_seq, tok_pos, slots, write_cache, status, stream, norm);
 }

@@ -18,8 +18,8 @@ struct DllmKernelTable {
                       int* status, cudaStream_t stream);
   int (*gemm_tcgen05_qkv_rope)(const void* a, const void* w, int M, int K, void* q_out, void* cache_base,
                                const int* page_table, int max_pages, int page_size, int heads, int kv_heads,
-                               int head_dim, const float* table, int rotary_dim, const int* tok_seq,
-                               const int* tok_pos, const int* slots, int write_cache, int* status,
+                               int head_dim, const float* table, int rotary_dim, int table_positions,
+                               const int* tok_seq, const int* tok_pos, const int* slots, int write_cache, int* status,
                                cudaStream_t stream);
   int (*attention_prefill)(void* out, const void* q, void* cache_base, const int* page_table, int max_pages,
                            int page_size, int heads, int kv_heads, int head_dim, const int* tile_seq,
@@ -36,9 +36,9 @@ struct DllmKernelTable {
                              const float* ssq_in, int parts_in, float eps, int* status, cudaStream_t stream);
   int (*gemm_tcgen05_qkv_rope_normed)(const void* a, const void* w, int M, int K, void* q_out, void* cache_base,
                                       const int* page_table, int max_pages, int page_size, int heads, int kv_heads,
-                                      int head_dim, const float* table, int rotary_dim, const int* tok_seq,
-                                      const int* tok_pos, const int* slots, int write_cache, const float* ssq_in,
-                                      int parts_in, float eps, int* status, cudaStream_t stream);
+                                      int head_dim, const float* table, int rotary_dim, int table_positions,
+                                      const int* tok_seq, const int* tok_pos, const int* slots, int write_cache,
+                                      const float* ssq_in, int parts_in, float eps, int* status, cudaStream_t stream);
   int (*gemm_tcgen05_residual_norm)(void* x, void* copy_out, float* ssq_out, int* parts_out, const void* a,
                                     const void* w, int M, int N, int K, int* status, cudaStream_t stream);
 };
@@ -51,7 +51,7 @@ struct DllmPreNormLayer {
   const void* w_o;         // [hidden, heads * head_dim]
   const void* w_gate_up;   // [2 * intermediate, hidden], gate and up rows interleaved
   const void* w_down;      // [hidden, intermediate]
-  const float* rotary_table;  // [positions, rotary_dim / 2, (cos, sin)] or null
+  const float* rotary_table;  // [rotary_dim / 2, rotary_positions, (cos, sin)] (pair by pair) or null
   void* cache_base;
   const int* page_table;
   long long cache_pages;
@@ -59,6 +59,7 @@ struct DllmPreNormLayer {
   int hidden, heads, kv_heads, head_dim, intermediate, rotary_dim, window;
   int max_pages, page_size;
   int tcgen05_attention_from;  // contexts above this take the tcgen05 attention kernel; negative: never
+  int rotary_positions;        // positions the rotary table covers
 };
 
 // The step: the residual stream, work buffers (sized for the widest layer) and the step's metadata on the device.
@@ -118,7 +119,8 @@ DLLM_EXPORT int dllm_prefill_pre_norm_layers(const DllmKernelTable* k, const Dll
       DLLM_STAGE(1, k->gemm_tcgen05_qkv_rope_normed(s->normed, l.w_qkv, s->tokens, l.hidden, s->q, l.cache_base,
                                                     l.page_table, l.max_pages, l.page_size, l.heads, l.kv_heads,
                                                     l.head_dim, l.rotary_table, l.rotary_table ? l.rotary_dim : 0,
-                                                    s->tok_seq, s->tok_pos, s->slots, 1, s->row_ssq, parts,
+                                                    l.rotary_positions, s->tok_seq, s->tok_pos, s->slots, 1,
+                                                    s->row_ssq, parts,
                                                     l.mixer_norm_eps, s->status, stream));
       if (l.tcgen05_attention_from >= 0 && s->max_context > l.tcgen05_attention_from)
         DLLM_STAGE(2, k->attention_prefill_tcgen05(s->attended, s->q, s->tokens, l.cache_base, l.cache_pages,
@@ -146,8 +148,8 @@ DLLM_EXPORT int dllm_prefill_pre_norm_layers(const DllmKernelTable* k, const Dll
                              DLLM_BF16, stream));
     DLLM_STAGE(1, k->gemm_tcgen05_qkv_rope(s->normed, l.w_qkv, s->tokens, l.hidden, s->q, l.cache_base, l.page_table,
                                            l.max_pages, l.page_size, l.heads, l.kv_heads, l.head_dim, l.rotary_table,
-                                           l.rotary_table ? l.rotary_dim : 0, s->tok_seq, s->tok_pos, s->slots, 1,
-                                           s->status, stream));
+                                           l.rotary_table ? l.rotary_dim : 0, l.rotary_positions, s->tok_seq,
+                                           s->tok_pos, s->slots, 1, s->status, stream));
     if (l.tcgen05_attention_from >= 0 && s->max_context > l.tcgen05_attention_from)
       DLLM_STAGE(2, k->attention_prefill_tcgen05(s->attended, s->q, s->tokens, l.cache_base, l.cache_pages,
                                                  l.page_table, l.max_pages, l.page_size, l.heads, l.kv_heads,

@@ -31,7 +31,7 @@ class PreNormLayer(Structure):
         ("mixer_norm_eps", c_float), ("feed_forward_norm_eps", c_float), ("scale", c_float),
         ("hidden", c_int), ("heads", c_int), ("kv_heads", c_int), ("head_dim", c_int), ("intermediate", c_int),
         ("rotary_dim", c_int), ("window", c_int), ("max_pages", c_int), ("page_size", c_int),
-        ("tcgen05_attention_from", c_int),
+        ("tcgen05_attention_from", c_int), ("rotary_positions", c_int),
     ]
 
 
@@ -100,15 +100,17 @@ class PreNormLayers:
                 return None
             from_context = TCGEN05_ATTENTION_FROM.get(mixer.head_dim, 512) \
                 if ops.attention_prefill_tcgen05_supported(view) else -1
+            by_pair = ops.table_by_pair(table) if table is not None else None  # (as the tile product reads it)
             layers.append(PreNormLayer(
                 block.mixer_norm.weight.data_ptr(), block.feed_forward_norm.weight.data_ptr(),
                 mixer.w_qkv.data_ptr(), mixer.w_o.data_ptr(), ffn.w_gate_up.data_ptr(), ffn.w_down.data_ptr(),
-                table.data_ptr() if table is not None else None, view.base_ptr, view.page_table.data_ptr(),
+                by_pair.data_ptr() if by_pair is not None else None, view.base_ptr, view.page_table.data_ptr(),
                 view.storage.shape[0], block.mixer_norm.eps, block.feed_forward_norm.eps, mixer.scale,
                 mixer.hidden_size, mixer.num_heads, mixer.num_kv_heads, mixer.head_dim, ffn.intermediate_size,
-                rotary_dim, mixer.window or 0, view.max_pages, view.page_size, from_context))
+                rotary_dim, mixer.window or 0, view.max_pages, view.page_size, from_context,
+                table.shape[0] if table is not None else 0))
             keep += [block.mixer_norm.weight, block.feed_forward_norm.weight, mixer.w_qkv, mixer.w_o, ffn.w_gate_up,
-                     ffn.w_down, table, view]
+                     ffn.w_down, table, by_pair, view]
             if ffn.hidden_size != mixer.hidden_size:
                 return None
             folded.append(bool(getattr(block.mixer_norm, "folded", False)) and

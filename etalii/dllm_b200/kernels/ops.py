@@ -35,16 +35,16 @@ _prototypes = {
     ("gemm_tcgen05", "dllm_gemm_tcgen05"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                             c_void_p],
     ("gemm_tcgen05", "dllm_gemm_tcgen05_qkv_rope"): [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
-                                                     c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p,
-                                                     c_void_p, c_void_p, c_int, c_void_p, c_void_p],
+                                                     c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int,
+                                                     c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
     ("gemm_tcgen05", "dllm_gemm_tcgen05_normed"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
                                                    c_int, c_float, c_void_p, c_void_p],
     ("gemm_tcgen05", "dllm_gemm_tcgen05_residual_norm"): [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                           c_int, c_int, c_int, c_void_p, c_void_p],
     ("gemm_tcgen05", "dllm_gemm_tcgen05_qkv_rope_normed"): [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
                                                             c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
-                                                            c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
-                                                            c_int, c_float, c_void_p, c_void_p],
+                                                            c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                                            c_void_p, c_int, c_float, c_void_p, c_void_p],
     ("elementwise", "dllm_cast_ssq"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
     ("gemv", "dllm_gemv_bf16"): [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int,
                                  c_void_p, c_longlong, c_void_p],
@@ -467,6 +467,21 @@ def gemm_qkv_rope_supported(cache, rotary_dim: int, has_table: bool) -> bool:
         (not has_table or rotary_dim == cache.head_dim)
 
 
+_tables_by_pair: dict[int, tuple[torch.Tensor, torch.Tensor]] = {}
+
+
+def table_by_pair(table: torch.Tensor) -> torch.Tensor:
+    """The rotary table [positions, pairs, (cos, sin)] laid out pair by pair, [pairs, positions, (cos, sin)], as the
+    tile product reads it (a warp's tokens, at consecutive positions, then read consecutive bytes). Made once per
+    table and kept with it."""
+    found = _tables_by_pair.get(table.data_ptr())
+    if found is None or found[0] is not table:
+        if len(_tables_by_pair) > 64:
+            _tables_by_pair.clear()
+        found = _tables_by_pair[table.data_ptr()] = (table, table.transpose(0, 1).contiguous())
+    return found[1]
+
+
 def gemm_qkv_rope(a: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, cache, table: torch.Tensor | None,
                   rotary_dim: int, heads: int, batch, write_cache: bool = True) -> None:
     """The q/k/v projection of a prefill-sized step in the tcgen05 tile kernel, ending in the rotation of q and k and
@@ -479,10 +494,12 @@ def gemm_qkv_rope(a: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, cache, 
     if table is not None:
         assert table.dtype == torch.float32 and table.shape[0] > batch.max_position, "position beyond the table"
         assert table.shape[1] == rotary_dim // 2 and table.shape[2] == 2
+    by_pair = table_by_pair(table) if table is not None else None  # (the layout this kernel reads)
     _check(_fn("gemm_tcgen05", "dllm_gemm_tcgen05_qkv_rope")(
         a.data_ptr(), w.data_ptr(), m, k, q_out.data_ptr(), cache.base_ptr, cache.page_table.data_ptr(),
         cache.max_pages, cache.page_size, heads, cache.kv_heads, cache.head_dim,
-        table.data_ptr() if table is not None else None, rotary_dim if table is not None else 0,
+        by_pair.data_ptr() if by_pair is not None else None, rotary_dim if table is not None else 0,
+        table.shape[0] if table is not None else 0,
         batch.tok_seq.data_ptr(), batch.tok_pos.data_ptr(), batch.slots.data_ptr(), 1 if write_cache else 0,
         _status_word().data_ptr(), _stream()), "gemm_qkv_rope", lambda: f"M={m} K={k} head_dim={cache.head_dim}")
 
