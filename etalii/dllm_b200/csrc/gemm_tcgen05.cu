@@ -29,7 +29,9 @@ template <int BN, bool DEEP = false, int EPI_STAGE = 0> struct Shape {
   static constexpr int TMEM_COLS = 2 * ACC_COLS;       // two accumulators: a power of two, at least 32
   // about 96 KB a block where that is enough (two blocks share an SM, 2 x TMEM_COLS <= 512 columns); the 256-wide
   // tile takes four 48 KB stages and all of the tensor memory, so one block owns the SM
-  static constexpr int STAGES = DEEP ? (220 * 1024) / (A_BYTES + B_BYTES) : (BN >= 256 ? 4 : (BN >= 128 ? 3 : 4));
+  // (a 64-wide tile that stages its epilogue gives one of its four stages for it, so that two blocks still fit)
+  static constexpr int STAGES = DEEP ? (220 * 1024) / (A_BYTES + B_BYTES)
+                                     : (BN >= 256 ? 4 : (BN >= 128 ? 3 : (EPI_STAGE > 0 ? 3 : 4)));
   // (EPI_STAGE: bytes behind the ring through which an epilogue makes its global stores whole lines)
   static constexpr size_t SMEM = (size_t)STAGES * (A_BYTES + B_BYTES) + 1024 + EPI_STAGE;
   static constexpr int BLOCKS_PER_SM = (DEEP || BN >= 256) ? 1 : 2;
@@ -47,8 +49,12 @@ template <int BN, bool DEEP = false, int EPI_STAGE = 0> struct Shape {
 // overlaps the products of the next.
 // The SwiGLU epilogue of the 256-wide tile writes 128 bytes of a row per warp: it goes through 4 KB of shared memory
 // per warp behind the ring, so that eight lanes write a row's 128 bytes together (see the residual epilogue below).
+// The residual epilogue of the 64-wide tile goes through 32 rows x 36 floats per warp: behind the ring, or in the
+// ring itself where the block has a single tile (the deep ring: every stage has been read when the accumulator is
+// full).
 template <int BN, int EPI, bool DEEP> struct EpilogueStage {
-  static constexpr int BYTES = (EPI == EPI_SWIGLU && BN == 256 && !DEEP) ? 8 * 4096 : 0;
+  static constexpr int BYTES = (EPI == EPI_SWIGLU && BN == 256 && !DEEP) ? 8 * 4096
+                               : ((EPI == EPI_RESIDUAL && BN == 64 && !DEEP) ? 4 * 32 * 36 * 4 : 0);
 };
 
 template <int BN, int EPI, bool DEEP, int HD>
@@ -146,13 +152,14 @@ __global__ void __launch_bounds__(Shape<BN, DEEP>::THREADS, Shape<BN, DEEP>::BLO
       // (narrow tiles: the row's old residual values are all asked for before the accumulator is read, so their
       // round trip runs under the wait for the products instead of after it, once per 16 columns)
       constexpr bool EARLY = EPI == EPI_RESIDUAL && BN <= 64;
-      // A block with the deep ring has one tile, and when its accumulator is full every stage of the ring has been
-      // read: the residual epilogue then goes through that shared memory, so that the rows it reads and writes in
-      // global memory are whole 128-byte lines per eight lanes instead of 16 bytes of 32 different rows per
+      // The residual epilogue of the 64-wide tile goes through shared memory, so that the rows it reads and writes
+      // in global memory are whole 128-byte lines per eight lanes instead of 16 bytes of 32 different rows per
       // instruction (a thread's accumulator row goes to shared memory, four rows of 32 columns come back per
       // instruction). Measured as links of a chain, with the residual, its copy and the sums of squares: 2048 x 576 x 576
-      // 8.3 -> 6.2 µs, 2048 x 576 x 1536 12.9 -> 11.0 µs (the same products with a plain bfloat16 store: 5.9 and 10.8).
-      constexpr bool STAGED = DEEP && EPI == EPI_RESIDUAL && BN == 64;
+      // 8.3 -> 6.2 µs, 2048 x 576 x 1536 12.9 -> 11.0 µs (the same products with a plain bfloat16 store: 5.9 and 10.8);
+      // with 10,946 rows (persistent blocks, the ring in use: the rows are staged behind it, which costs the ring one
+      // of its four stages) 33.1 -> 24.1 µs and 42.7 -> 36.0 µs.
+      constexpr bool STAGED = EPI == EPI_RESIDUAL && BN == 64;
       const bool staged = STAGED && (N & 3) == 0;
       const int sub = lane >> 3, seg = lane & 7;  // staged: row i * 4 + sub of the warp's 32, floats seg * 4 .. + 3
       float4 old_rows[STAGED ? BN / 32 : 1][STAGED ? 8 : 1];
@@ -263,7 +270,7 @@ __global__ void __launch_bounds__(Shape<BN, DEEP>::THREADS, Shape<BN, DEEP>::BLO
             *reinterpret_cast<uint4*>(dst + HEAD / 2 + first_pair + i) = o;
           }
         }
-      } else if (EpilogueStage<BN, EPI, DEEP>::BYTES > 0 && (N & 15) == 0) {
+      } else if (EPI == EPI_SWIGLU && EpilogueStage<BN, EPI, DEEP>::BYTES > 0 && (N & 15) == 0) {
         // SwiGLU, 256-wide tile: the thread's 64 outputs (eight 16-byte pieces) go to its row of the warp's staging
         // space, piece p at place p ^ (row % 8) so that a quarter warp's stores and loads meet different banks; then
         // eight lanes write a row's 128 bytes to global memory together, four rows an instruction.
@@ -293,7 +300,8 @@ __global__ void __launch_bounds__(Shape<BN, DEEP>::THREADS, Shape<BN, DEEP>::BLO
         __syncwarp();  // (the block's next tile overwrites the staged rows)
       } else if (staged) {
         constexpr int LD = 36;  // floats per staged row: 16-byte pieces, rows of a quarter warp in different banks
-        float* st = reinterpret_cast<float*>(tiles) + (size_t)(warp - 2) * 32 * LD;
+        float* st = reinterpret_cast<float*>(DEEP ? tiles : tiles + (size_t)S::STAGES * (S::A_BYTES + S::B_BYTES)) +
+                    (size_t)(warp - 2) * 32 * LD;
         float squares[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) squares[i] = 0.f;
