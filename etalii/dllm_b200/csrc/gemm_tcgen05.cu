@@ -54,7 +54,8 @@ template <int BN, bool DEEP = false, int EPI_STAGE = 0> struct Shape {
 // full).
 template <int BN, int EPI, bool DEEP> struct EpilogueStage {
   static constexpr int BYTES = (EPI == EPI_SWIGLU && BN == 256 && !DEEP) ? 8 * 4096
-                               : ((EPI == EPI_RESIDUAL && BN == 64 && !DEEP) ? 4 * 32 * 36 * 4 : 0);
+                               : ((EPI == EPI_RESIDUAL && BN == 64 && !DEEP) ? 4 * 32 * 36 * 4
+                               : ((EPI == EPI_RESIDUAL && BN == 256 && !DEEP) ? 8 * 32 * 20 * 4 : 0));  // (see below)
 };
 
 template <int BN, int EPI, bool DEEP, int HD>
@@ -298,6 +299,77 @@ __global__ void __launch_bounds__(Shape<BN, DEEP>::THREADS, Shape<BN, DEEP>::BLO
           if (mr < M && nc < N) *reinterpret_cast<uint4*>((bf16*)c + (size_t)mr * (N / 2) + (nc >> 1)) = o;
         }
         __syncwarp();  // (the block's next tile overwrites the staged rows)
+      } else if (EPI == EPI_RESIDUAL && BN == 256 && !DEEP && (N & 3) == 0) {
+        // The residual epilogue of the 256-wide tile, through shared memory as well: 16 columns at a time (there is
+        // room for 32 rows x 20 floats per warp behind four stages of 48 KB), four lanes a row, eight rows an
+        // instruction; the old values of the next 32 columns are asked for before these are summed. Measured as links
+        // of a chain, with the copy and the sums of squares: 2048 x 2048 x 2048 27.0 µs (a plain bfloat16 store of
+        // the same product: 15.2) -> 20.7 µs, 2048 x 4096 x 4096 74.8 µs (53.5) -> 66.5 µs.
+        constexpr int LD = 20, CHUNKS = HALF / 16;
+        float* st = reinterpret_cast<float*>(tiles + (size_t)S::STAGES * (S::A_BYTES + S::B_BYTES)) +
+                    (size_t)(warp - 2) * 32 * LD;
+        const int sub8 = lane >> 2, seg4 = lane & 3;  // row i * 8 + sub8 of the warp's 32, floats seg4 * 4 .. + 3
+        float squares[4] = {0.f, 0.f, 0.f, 0.f};
+        float4 old_now[2][4], old_next[2][4];
+        auto ask = [&](float4 (*into)[4], int chunk0) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              int mr = m0 + quarter * 32 + i * 8 + sub8, nc = n0 + c0 + (chunk0 + h) * 16 + seg4 * 4;
+              into[h][i] = (mr < M && nc < N) ? *reinterpret_cast<const float4*>((const float*)c + (size_t)mr * N + nc)
+                                              : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        };
+        ask(old_now, 0);
+#pragma unroll
+        for (int pair = 0; pair < CHUNKS / 2; ++pair) {
+          if (pair + 1 < CHUNKS / 2) ask(old_next, 2 * pair + 2);
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            int chunk = 2 * pair + h;
+            unsigned v[16];
+            tmem_load16(acc + (unsigned)(c0 + chunk * 16), v);
+            if (chunk == CHUNKS - 1) release_accumulator();
+#pragma unroll
+            for (int i = 0; i < 16; i += 4)
+              *reinterpret_cast<float4*>(st + lane * LD + i) =
+                  make_float4(__uint_as_float(v[i]), __uint_as_float(v[i + 1]), __uint_as_float(v[i + 2]),
+                              __uint_as_float(v[i + 3]));
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              int row = i * 8 + sub8, mr = m0 + quarter * 32 + row, nc = n0 + c0 + chunk * 16 + seg4 * 4;
+              float4 a = *reinterpret_cast<const float4*>(st + row * LD + seg4 * 4);
+              if (mr < M && nc < N) {
+                float4 r = old_now[h][i];
+                r.x += a.x; r.y += a.y; r.z += a.z; r.w += a.w;
+                *reinterpret_cast<float4*>((float*)c + (size_t)mr * N + nc) = r;
+                if (norm.copy_out != nullptr) {
+                  __nv_bfloat162 lo = __floats2bfloat162_rn(r.x, r.y), hi = __floats2bfloat162_rn(r.z, r.w);
+                  *reinterpret_cast<uint2*>(norm.copy_out + (size_t)mr * N + nc) =
+                      make_uint2(*reinterpret_cast<unsigned*>(&lo), *reinterpret_cast<unsigned*>(&hi));
+                  squares[i] = fmaf(r.x, r.x, fmaf(r.y, r.y, fmaf(r.z, r.z, fmaf(r.w, r.w, squares[i]))));
+                }
+              }
+            }
+            __syncwarp();  // (the next 16 columns overwrite the staged rows)
+          }
+#pragma unroll
+          for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) old_now[h][i] = old_next[h][i];
+        }
+        if (norm.ssq_out != nullptr) {  // a row's four lanes, summed in a fixed order
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            float v = squares[i];
+            v += __shfl_xor_sync(0xffffffffu, v, 1);
+            v += __shfl_xor_sync(0xffffffffu, v, 2);
+            int mr = m0 + quarter * 32 + i * 8 + sub8;
+            if (seg4 == 0 && mr < M) norm.ssq_out[(size_t)(HALVES * n_tile + half) * M + mr] = v;
+          }
+        }
       } else if (staged) {
         constexpr int LD = 36;  // floats per staged row: 16-byte pieces, rows of a quarter warp in different banks
         float* st = reinterpret_cast<float*>(DEEP ? tiles : tiles + (size_t)S::STAGES * (S::A_BYTES + S::B_BYTES)) +

@@ -960,8 +960,12 @@ def test_head_argmax_chooses_what_the_logits_would(m, n, k, normed):
     assert got[finite].tolist() == logits[finite].argmax(dim=1).tolist()
 
 
-@pytest.mark.parametrize("m,hidden,inner", [(130, 576, 1536), (300, 144, 96), (2048, 576, 576), (65, 2048, 512)])
-def test_tile_products_with_the_norm_folded_around_them(m, hidden, inner):
+@pytest.mark.parametrize("m,hidden,inner,outputs", [
+    (130, 576, 1536, 256), (300, 144, 96, 256), (2048, 576, 576, 256), (65, 2048, 512, 256),
+    (2048, 2048, 256, 3072),   # 256-wide tiles for both products: their epilogues go through shared memory
+    (4100, 576, 320, 256),     # more 64-wide tiles than blocks: persistent blocks, the rows staged behind the ring
+])
+def test_tile_products_with_the_norm_folded_around_them(m, hidden, inner, outputs):
     """x += a W^T with the bfloat16 copy and the sums of squares of the new rows from the epilogue, then a product
     that reads the copy and scales its rows: together RMSNorm(x) W2^T without a norm kernel. Against float64."""
     x0 = _randn((m, hidden), torch.float32, 1, 2.0)
@@ -979,14 +983,14 @@ def test_tile_products_with_the_norm_folded_around_them(m, hidden, inner):
     # the reader: SwiGLU and plain stores of (norm(x) * weight) @ w2^T with the weight folded into w2's columns
     eps = 1e-5
     norm_w = _randn((hidden,), torch.float32, 4, 0.1) + 1
-    w2 = _randn((256, hidden), torch.bfloat16, 5, 0.05)
+    w2 = _randn((outputs, hidden), torch.bfloat16, 5, 0.05)
     folded = (w2.float() * norm_w[None, :]).to(torch.bfloat16)
     normed = x.double() / torch.sqrt((x.double() ** 2).mean(dim=1, keepdim=True) + eps)
     prod = normed @ folded.double().T
-    got = torch.empty((m, 256), dtype=torch.float32, device=DEV)
+    got = torch.empty((m, outputs), dtype=torch.float32, device=DEV)
     ops().gemm_normed(got, copy, folded, ops().EPI_STORE_F32, ssq, parts, eps)
     assert rel_error(got.cpu(), prod.float().cpu()) <= 8e-3
-    act = torch.empty((m, 128), dtype=torch.bfloat16, device=DEV)
+    act = torch.empty((m, outputs // 2), dtype=torch.bfloat16, device=DEV)
     ops().gemm_normed(act, copy, folded, ops().EPI_SWIGLU, ssq, parts, eps)
     gate, up = prod[:, 0::2], prod[:, 1::2]
     assert rel_error(act.float().cpu(), (gate * torch.sigmoid(gate) * up).float().cpu()) <= 1.2e-2
