@@ -182,9 +182,16 @@ class PagedCache:
         for group in self._groups:
             if group.dirty and group.table is not None:
                 rows = sorted(group.dirty)
-                stage, index = self._staging(len(rows), group.table.shape[1])
+                width = group.table.shape[1]
+                stage, index = self._staging(len(rows), width)
                 stage.numpy()[:] = group.table_host[rows]
-                if len(rows) <= 4:
+                if len(rows) <= 4 and group.table.is_cuda:
+                    from ..kernels import ops
+
+                    for i, row in enumerate(rows):  # (raw copies: a fraction of the tensor library's dispatch)
+                        ops.copy_to_device(group.table.data_ptr() + 4 * row * width, stage.data_ptr() + 4 * i * width,
+                                           4 * width)
+                elif len(rows) <= 4:
                     for i, row in enumerate(rows):
                         group.table[row].copy_(stage[i], non_blocking=True)
                 else:
@@ -208,9 +215,10 @@ class PagedCache:
         return entry[0][: rows * width].view(rows, width), entry[1][:rows]
 
     def _staged(self) -> None:
-        event = torch.cuda.Event()
-        event.record()
-        self._stage_ring[self._stage_at][2] = event
+        entry = self._stage_ring[self._stage_at]
+        if entry[2] is None:
+            entry[2] = torch.cuda.Event()
+        entry[2].record()  # (the same event object again and again: recording it anew is all a step needs)
         self._stage_at = (self._stage_at + 1) % self.STAGING_RING
 
     # ---- views ----

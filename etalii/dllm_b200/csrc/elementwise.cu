@@ -273,6 +273,16 @@ DLLM_EXPORT int dllm_decode_advance(int* tokens, int* tok_pos, int* start, const
                          history, counter, batch, capacity);
 }
 
+// A copy from pinned host memory to the device on the given stream (the host side of a step makes two small ones: the
+// step's metadata and the page-table rows that changed; through this entry point each costs the host a few
+// microseconds less than through the tensor library's dispatch).
+DLLM_EXPORT int dllm_copy_to_device(void* dst, const void* src, long long bytes, cudaStream_t stream) {
+  if (bytes <= 0) return DLLM_OK;
+  if (dst == nullptr || src == nullptr) return DLLM_BAD_ARGUMENT;
+  return cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyHostToDevice, stream) == cudaSuccess ? DLLM_OK
+                                                                                                 : DLLM_LAUNCH_FAILED;
+}
+
 // Takes token ids out of the choice while an output is shorter than it has to be: logits[row, ids[i]] = -inf for
 // every row, if *produced + *steps < min_tokens (`produced`: tokens every sequence of the batch has so far when a run
 // of steps begins; `steps`: the steps of that run so far, or null). A probability of exactly zero is never drawn and

@@ -136,6 +136,7 @@ class BatchBuffers:
     def _grow(self, capacity: int) -> None:
         self.capacity = capacity
         self.host = [torch.empty(capacity, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
+        self.host_arrays = [h.numpy() for h in self.host]  # (views, made once: a step costs no object for them)
         self.events = [None] * self.RING
         self.dev = torch.empty(capacity, dtype=torch.int32, device=self.device)
         self.generation = getattr(self, "generation", 0) + 1
@@ -152,11 +153,16 @@ class BatchBuffers:
         self._ring = (ring + 1) % self.RING
         if self.events[ring] is not None:
             self.events[ring].synchronize()
-        layout.write(self.host[ring].numpy(), step_values(slots, new_tokens, starts, want, tiles))
-        self.dev[:layout.total].copy_(self.host[ring][:layout.total], non_blocking=True)
-        event = torch.cuda.Event()
-        event.record()
-        self.events[ring] = event
+        layout.write(self.host_arrays[ring], step_values(slots, new_tokens, starts, want, tiles))
+        if self.dev.is_cuda:
+            from ..kernels import ops
+
+            ops.copy_to_device(self.dev.data_ptr(), self.host[ring].data_ptr(), 4 * layout.total)
+            if self.events[ring] is None:
+                self.events[ring] = torch.cuda.Event()
+            self.events[ring].record()  # (the staging buffer is free again when this has passed)
+        else:
+            self.dev[:layout.total].copy_(self.host[ring][:layout.total])
 
         batch = StepBatch()
         layout.attach(batch, self.dev)

@@ -5,6 +5,7 @@
 (src/etalii_dllm/engine.py:416-595 loads, 694-748 completes)."""
 from __future__ import annotations
 
+import array
 import time
 from typing import Sequence
 
@@ -36,6 +37,17 @@ def parse_dtype(dtype) -> torch.dtype:
         return _DTYPES[str(dtype).lower()]
     except KeyError:
         raise ValueError(f"dtype {dtype!r}: use bfloat16 or float32") from None
+
+
+def _token_array(tokens) -> np.ndarray:
+    """Token ids as an int64 array. A list of Python ints goes through `array.array` (about half the time of
+    numpy's own conversion of a list, which looks at every element's type); anything else as numpy takes it."""
+    if type(tokens) is list:
+        try:
+            return np.frombuffer(array.array("q", tokens), dtype=np.int64)
+        except (TypeError, OverflowError):
+            pass
+    return np.asarray(tokens, dtype=np.int64)
 
 
 class Engine:
@@ -113,7 +125,7 @@ class Engine:
             raise CacheError("a sequence appears twice in one step")  # src/etalii_dllm/transformer.py:405-406
         if want is None:
             want = [[len(t) - 1] for t in new_tokens]
-        new_tokens = [np.asarray(tokens, dtype=np.int64) for tokens in new_tokens]  # one pass over each list
+        new_tokens = [_token_array(tokens) for tokens in new_tokens]  # one pass over each list
         for tokens, rows in zip(new_tokens, want):
             if tokens.ndim != 1 or tokens.size == 0:
                 raise ValueError("a sequence in a step needs at least one token")

@@ -26,6 +26,7 @@ _prototypes = {
     ("elementwise", "dllm_rope_cache_write"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                                c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                                c_int, c_void_p],
+    ("elementwise", "dllm_copy_to_device"): [c_void_p, c_void_p, c_longlong, c_void_p],
     ("elementwise", "dllm_add_residual"): [c_void_p, c_void_p, c_longlong, c_int, c_void_p],
     ("elementwise", "dllm_decode_advance"): [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                              c_void_p],
@@ -158,6 +159,14 @@ def embed(out: torch.Tensor, table: torch.Tensor, tokens: torch.Tensor, status: 
     _check(_fn("elementwise", "dllm_embed")(out.data_ptr(), table.data_ptr(), tokens.data_ptr(), rows, hidden,
                                             table.shape[0], _code(table.dtype), status.data_ptr(), _stream()),
            "embed")
+
+
+def copy_to_device(dst_ptr: int, src_ptr: int, nbytes: int) -> None:
+    """Copies `nbytes` from pinned host memory to device memory on the current stream, without a host wait (the
+    caller keeps the source alive and unchanged until the copy has run: an event behind it tells)."""
+    status = _fn("elementwise", "dllm_copy_to_device")(dst_ptr, src_ptr, int(nbytes), _stream())
+    if status != 0:
+        raise KernelError(f"copy to the device: {_STATUS.get(status, status)}")
 
 
 def rmsnorm(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, eps: float,
