@@ -58,8 +58,10 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attention_cluster_kernel(
   constexpr int LD = HD + 8;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* kv_s = reinterpret_cast<bf16*>(smem_raw);        // per warp: K [64][LD], V [64][LD]
-  float* red_o = reinterpret_cast<float*>(smem_raw);      // after the products: [WARPS][16][HD]
-  float* cta_o = red_o + WARPS * 16 * HD;                 // this block's partial output [16][HD]
+  constexpr int RLD = HD + 8;  // floats per row of the warps' partial outputs: the eight rows a warp writes with one
+                               // instruction then lie in different banks (at a stride of HD they all met the same)
+  float* red_o = reinterpret_cast<float*>(smem_raw);      // after the products: [WARPS][16][RLD]
+  float* cta_o = red_o + WARPS * 16 * RLD;                // this block's partial output [16][HD]
   __shared__ float sm_ml[WARPS][16][2];
   __shared__ float cta_ml[16][2];
   int b = blockIdx.z, g = blockIdx.y;
@@ -246,8 +248,8 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attention_cluster_kernel(
 #pragma unroll
     for (int i = 0; i < HD / 8; ++i) {
       int d = i * 8 + tq * 2;
-      *reinterpret_cast<float2*>(red_o + ((size_t)warp * 16 + gq) * HD + d) = make_float2(o_acc[i][0], o_acc[i][1]);
-      *reinterpret_cast<float2*>(red_o + ((size_t)warp * 16 + gq + 8) * HD + d) = make_float2(o_acc[i][2], o_acc[i][3]);
+      *reinterpret_cast<float2*>(red_o + ((size_t)warp * 16 + gq) * RLD + d) = make_float2(o_acc[i][0], o_acc[i][1]);
+      *reinterpret_cast<float2*>(red_o + ((size_t)warp * 16 + gq + 8) * RLD + d) = make_float2(o_acc[i][2], o_acc[i][3]);
     }
     __syncthreads();
     // the block's partial result: warps in warp order
@@ -260,7 +262,7 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attention_cluster_kernel(
 #pragma unroll
       for (int w = 0; w < WARPS; ++w) {
         float f = sm_ml[w][h][0] == -INFINITY ? 0.f : fast_exp2(sm_ml[w][h][0] - m);
-        o = fmaf(red_o[((size_t)w * 16 + h) * HD + d], f, o);
+        o = fmaf(red_o[((size_t)w * 16 + h) * RLD + d], f, o);
         l = fmaf(sm_ml[w][h][1], f, l);
       }
       cta_o[h * HD + d] = o;
@@ -309,7 +311,7 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attention_cluster_kernel(
 template <int HD, int WARPS>
 constexpr size_t block_smem() {
   size_t kv_bytes = (size_t)WARPS * 2 * TILE_KEYS * (HD + 8) * sizeof(bf16);
-  size_t red_bytes = (size_t)(WARPS + 1) * 16 * HD * sizeof(float);
+  size_t red_bytes = (size_t)(WARPS * 16 * (HD + 8) + 16 * HD) * sizeof(float);
   return kv_bytes > red_bytes ? kv_bytes : red_bytes;
 }
 
