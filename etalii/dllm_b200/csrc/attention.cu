@@ -238,9 +238,13 @@ __global__ void __launch_bounds__(512) attention_block_kernel(
               for (int r = 0; r < R; ++r) dot[r] += dot_loaded(&q_s[r * hd + d], key);
             }
           }
-          __syncwarp();  // (the weights of the tile before have been read by every lane)
+          // (a single token a warp, as in decoding, hands its weights from lane to lane by shuffles; several go
+          // through shared memory, four weights a load)
+          float weight[R];
+          if (R > 1) __syncwarp();  // (the weights of the tile before have been read by every lane)
 #pragma unroll
           for (int r = 0; r < R; ++r) {
+            weight[r] = 0.f;
             if (!active[r]) continue;
             bool valid = j >= first[r] && j < end[r];
             float sc = valid ? dot[r] * scale : -INFINITY;
@@ -251,9 +255,10 @@ __global__ void __launch_bounds__(512) attention_block_kernel(
 #pragma unroll
             for (int i = 0; i < CHUNKS; ++i) acc[r][i] *= corr;
             m_run[r] = m_new;
-            p_s[r * 32 + lane] = pr;
+            weight[r] = pr;
+            if (R > 1) p_s[r * 32 + lane] = pr;
           }
-          __syncwarp();
+          if (R > 1) __syncwarp();
           const T* vtile = v_s + (j0 - p * 64) * ld + lane;
           if (whole) {  // whole tiles of a whole head for every token that sees the tile: no bounds in the loop
 #pragma unroll 4
@@ -266,7 +271,15 @@ __global__ void __launch_bounds__(512) attention_block_kernel(
 #pragma unroll
               for (int r = 0; r < R; ++r) {
                 if (!active[r]) continue;  // (a token that does not see the tile must not meet what lies there)
-                float4 pj = *reinterpret_cast<const float4*>(&p_s[r * 32 + jj]);
+                float4 pj;
+                if (R > 1) {
+                  pj = *reinterpret_cast<const float4*>(&p_s[r * 32 + jj]);
+                } else {
+                  pj.x = __shfl_sync(0xffffffffu, weight[r], jj);
+                  pj.y = __shfl_sync(0xffffffffu, weight[r], jj + 1);
+                  pj.z = __shfl_sync(0xffffffffu, weight[r], jj + 2);
+                  pj.w = __shfl_sync(0xffffffffu, weight[r], jj + 3);
+                }
 #pragma unroll
                 for (int i = 0; i < CHUNKS; ++i) {
                   acc[r][i] = fmaf(pj.x, v[0][i], acc[r][i]);
@@ -282,7 +295,7 @@ __global__ void __launch_bounds__(512) attention_block_kernel(
               if (!active[r]) continue;
               int from = max(0, first[r] - j0), to = min(32, end[r] - j0);
               for (int jj = from; jj < to; ++jj) {
-                float pj = p_s[r * 32 + jj];
+                float pj = R > 1 ? p_s[r * 32 + jj] : __shfl_sync(0xffffffffu, weight[r], jj);
 #pragma unroll
                 for (int i = 0; i < CHUNKS; ++i)
                   if (lane + 32 * i < hd) acc[r][i] = fmaf(pj, to_float(vtile[jj * ld + 32 * i]), acc[r][i]);
