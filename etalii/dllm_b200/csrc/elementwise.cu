@@ -247,6 +247,35 @@ DLLM_EXPORT int dllm_add_residual(float* residual, const void* update, long long
   return dllm_launch_status();
 }
 
+// ---- residual += parts[0] + parts[1] + ... (the partial results of a product whose reduction was cut) ------------
+// parts holds `k_split` float32 arrays of `count` values one behind the other; they are summed in that order, then
+// added to the residual. count must be a multiple of 4 and the arrays 16-byte aligned.
+__global__ void __launch_bounds__(256) sum_parts_residual_kernel(float* __restrict__ residual,
+                                                                 const float* __restrict__ parts, int k_split,
+                                                                 size_t count) {
+  pdl_launch_dependents();
+  pdl_wait();
+  size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i >= count) return;
+  float4 old = *reinterpret_cast<const float4*>(residual + i);
+  float4 sum = __ldcg(reinterpret_cast<const float4*>(parts + i));
+  for (int s = 1; s < k_split; ++s) {
+    float4 p = __ldcg(reinterpret_cast<const float4*>(parts + (size_t)s * count + i));
+    sum.x += p.x; sum.y += p.y; sum.z += p.z; sum.w += p.w;
+  }
+  old.x += sum.x; old.y += sum.y; old.z += sum.z; old.w += sum.w;
+  *reinterpret_cast<float4*>(residual + i) = old;
+}
+
+DLLM_EXPORT int dllm_sum_parts_residual(float* residual, const float* parts, int k_split, long long count,
+                                        cudaStream_t stream) {
+  if (count <= 0) return DLLM_OK;
+  if (k_split < 1 || (count & 3) || ((uintptr_t)residual & 15) || ((uintptr_t)parts & 15)) return DLLM_UNSUPPORTED_SIZE;
+  unsigned blocks = (unsigned)((count / 4 + 255) / 256);
+  return dllm_launch_pdl(sum_parts_residual_kernel, dim3(blocks), dim3(256), 0, stream, residual, parts, k_split,
+                         (size_t)count);
+}
+
 // ---- decode feedback: the chosen tokens become the next step's input, positions move on by one -------------------
 // Lets single-token steps follow one another on the device without the host: tokens[b] = chosen[b], positions and
 // cached lengths + 1, and the chosen tokens are appended to `history` ([capacity, batch]) at row *counter.

@@ -63,7 +63,7 @@ __global__ void __launch_bounds__(Shape<BN, DEEP>::THREADS, Shape<BN, DEEP>::BLO
                                                                const __grid_constant__ CUtensorMap map_w,
                                                                void* __restrict__ c, int M, int N, int K,
                                                                int* __restrict__ status, RopeArgs rope, int m_tiles,
-                                                               int n_tiles, NormArgs norm) {
+                                                               int n_tiles, int k_split, NormArgs norm) {
   typedef Shape<BN, DEEP, EpilogueStage<BN, EPI, DEEP>::BYTES> S;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);  // swizzle atoms: 1 KB
@@ -72,6 +72,9 @@ __global__ void __launch_bounds__(Shape<BN, DEEP>::THREADS, Shape<BN, DEEP>::BLO
   int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int k_tiles = (K + BK - 1) / BK;
   int total = m_tiles * n_tiles;
+  // k_split > 1 (EPI_T_STORE_F32 only): an item is a tile and one of k_split stretches of the reduction; its sums
+  // go to part `split` of C, which then holds k_split partial results [N, M] one behind the other
+  int items = total * k_split;
   pdl_launch_dependents();  // the next kernel may set itself up (barriers, tensor memory) while this one runs
 
   if (threadIdx.x == 0) {
@@ -96,9 +99,11 @@ __global__ void __launch_bounds__(Shape<BN, DEEP>::THREADS, Shape<BN, DEEP>::BLO
     if (lane == 0) {
       int it = 0;  // k tiles issued so far, over all of this block's tiles
       bool ok = true;
-      for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+      for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
+        int t = item % total, split = item / total;
         int m0 = (t % m_tiles) * BM, n0 = (t / m_tiles) * BN;
-        for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+        int kt_end = (int)((long long)(split + 1) * k_tiles / k_split);
+        for (int kt = (int)((long long)split * k_tiles / k_split); kt < kt_end; ++kt, ++it) {
           int s = it % S::STAGES;
           if (it >= S::STAGES && !mbar_wait(&empty_bar[s], ((it / S::STAGES) - 1) & 1)) {
             *(volatile int*)status = 2;
@@ -117,12 +122,15 @@ __global__ void __launch_bounds__(Shape<BN, DEEP>::THREADS, Shape<BN, DEEP>::BLO
       constexpr unsigned idesc = instr_desc(BM, BN);
       int it = 0, lt = 0;  // k tiles consumed, tiles started
       bool ok = true;
-      for (int t = blockIdx.x; t < total && ok; t += gridDim.x, ++lt) {
+      for (int item = blockIdx.x; item < items && ok; item += gridDim.x, ++lt) {
         int buf = lt & 1;
         if (lt >= 2 && !mbar_wait(&acc_empty[buf], ((lt >> 1) - 1) & 1)) { *(volatile int*)status = 5; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         unsigned acc = tmem_base + (unsigned)(buf * S::ACC_COLS);
-        for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+        int split = item / total;
+        int kt_begin = (int)((long long)split * k_tiles / k_split);
+        int kt_end = (int)((long long)(split + 1) * k_tiles / k_split);
+        for (int kt = kt_begin; kt < kt_end; ++kt, ++it) {
           int s = it % S::STAGES;
           if (!mbar_wait(&full_bar[s], (it / S::STAGES) & 1)) { *(volatile int*)status = 3; ok = false; break; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -131,7 +139,7 @@ __global__ void __launch_bounds__(Shape<BN, DEEP>::THREADS, Shape<BN, DEEP>::BLO
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             uint64_t adesc = smem_desc(a_addr + k * UMMA_K * 2), bdesc = smem_desc(b_addr + k * UMMA_K * 2);
-            umma(acc, adesc, bdesc, idesc, (kt > 0 || k > 0) ? 1u : 0u);
+            umma(acc, adesc, bdesc, idesc, (kt > kt_begin || k > 0) ? 1u : 0u);
           }
           tcgen05_commit(&empty_bar[s]);  // the stage is free once these products have read it
         }
@@ -146,9 +154,11 @@ __global__ void __launch_bounds__(Shape<BN, DEEP>::THREADS, Shape<BN, DEEP>::BLO
     constexpr int HALF = BN / HALVES;
     int c0 = half * HALF;
     int lt = 0;
-    for (int t = blockIdx.x; t < total; t += gridDim.x, ++lt) {
+    for (int item = blockIdx.x; item < items; item += gridDim.x, ++lt) {
       int buf = lt & 1;
+      int t = item % total;
       int m0 = (t % m_tiles) * BM, n_tile = t / m_tiles, n0 = n_tile * BN;
+      void* c_part = EPI == EPI_T_STORE_F32 ? (void*)((float*)c + (size_t)(item / total) * M * N) : c;
       int m = m0 + quarter * 32 + lane;
       // (narrow tiles: the row's old residual values are all asked for before the accumulator is read, so their
       // round trip runs under the wait for the products instead of after it, once per 16 columns)
@@ -457,7 +467,7 @@ __global__ void __launch_bounds__(Shape<BN, DEEP>::THREADS, Shape<BN, DEEP>::BLO
               copy[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
             }
           } else if (EPI >= EPI_T_STORE_F32) {
-            epilogue_col16<EPI, bf16>(c, m, n0 + col, M, N, f);  // the tile is C^T
+            epilogue_col16<EPI, bf16>(c_part, m, n0 + col, M, N, f);  // the tile is C^T
           } else {
             epilogue_row16<EPI, bf16>(c, m, n0 + col, M, N, f);
           }
@@ -477,7 +487,8 @@ __global__ void __launch_bounds__(Shape<BN, DEEP>::THREADS, Shape<BN, DEEP>::BLO
 
 template <int BN, int EPI, bool DEEP, int HD>
 int launch_shape(void* c, const CUtensorMap& map_a, const CUtensorMap& map_w, int M, int N, int K, int* status,
-                 cudaStream_t stream, const RopeArgs& rope, int m_tiles, int n_tiles, int sms, const NormArgs& norm) {
+                 cudaStream_t stream, const RopeArgs& rope, int m_tiles, int n_tiles, int sms, const NormArgs& norm,
+                 int k_split = 1) {
   typedef Shape<BN, DEEP, EpilogueStage<BN, EPI, DEEP>::BYTES> S;
   static bool configured = false;
   if (!configured) {
@@ -486,21 +497,21 @@ int launch_shape(void* c, const CUtensorMap& map_a, const CUtensorMap& map_w, in
       return DLLM_LAUNCH_FAILED;
     configured = true;
   }
-  long long total = (long long)m_tiles * n_tiles;
+  long long total = (long long)m_tiles * n_tiles * k_split;
   int blocks = sms * S::BLOCKS_PER_SM;
   if (blocks > total) blocks = (int)total;
   return dllm_launch_pdl(gemm_tcgen05_kernel<BN, EPI, DEEP, HD>, dim3(blocks), dim3(S::THREADS), S::SMEM, stream, map_a, map_w,
-                         c, M, N, K, status, rope, m_tiles, n_tiles, norm);
+                         c, M, N, K, status, rope, m_tiles, n_tiles, k_split, norm);
 }
 
 template <int BN, int EPI, int HD = 0>
 int launch(void* c, const void* a, const void* w, int M, int N, int K, int* status, cudaStream_t stream,
-           const RopeArgs& rope = RopeArgs{}, const NormArgs& norm = NormArgs{}) {
+           const RopeArgs& rope = RopeArgs{}, const NormArgs& norm = NormArgs{}, int k_split = 1) {
   alignas(64) CUtensorMap map_a, map_w;
   if (!make_map(&map_a, a, M, K, BM) || !make_map(&map_w, w, N, K, BN)) return DLLM_LAUNCH_FAILED;
   int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
   long long total = (long long)m_tiles * n_tiles;
-  if (total > 0x7fffffff) return DLLM_UNSUPPORTED_SIZE;
+  if (total * k_split > 0x7fffffff) return DLLM_UNSUPPORTED_SIZE;
   static int sms = 0;
   if (sms == 0) {
     int device = 0;
@@ -512,18 +523,20 @@ int launch(void* c, const void* a, const void* w, int M, int N, int K, int* stat
   if (CAN_DEEP && total <= sms && K > 4 * BK)
     return launch_shape<BN, EPI, CAN_DEEP, HD>(c, map_a, map_w, M, N, K, status, stream, rope, m_tiles, n_tiles, sms,
                                                norm);
-  return launch_shape<BN, EPI, false, HD>(c, map_a, map_w, M, N, K, status, stream, rope, m_tiles, n_tiles, sms, norm);
+  return launch_shape<BN, EPI, false, HD>(c, map_a, map_w, M, N, K, status, stream, rope, m_tiles, n_tiles, sms, norm,
+                                          k_split);
 }
 
 template <int BN>
 int dispatch(void* c, const void* a, const void* w, int M, int N, int K, int epilogue, int* status,
-             cudaStream_t stream, const NormArgs& norm = NormArgs{}) {
+             cudaStream_t stream, const NormArgs& norm = NormArgs{}, int k_split = 1) {
   switch (epilogue) {
     case EPI_STORE_F32: return launch<BN, EPI_STORE_F32>(c, a, w, M, N, K, status, stream, RopeArgs{}, norm);
     case EPI_STORE_T: return launch<BN, EPI_STORE_T>(c, a, w, M, N, K, status, stream, RopeArgs{}, norm);
     case EPI_RESIDUAL: return launch<BN, EPI_RESIDUAL>(c, a, w, M, N, K, status, stream, RopeArgs{}, norm);
     case EPI_SWIGLU: return launch<BN, EPI_SWIGLU>(c, a, w, M, N, K, status, stream, RopeArgs{}, norm);
-    case EPI_T_STORE_F32: return launch<BN, EPI_T_STORE_F32>(c, a, w, M, N, K, status, stream);
+    case EPI_T_STORE_F32:
+      return launch<BN, EPI_T_STORE_F32>(c, a, w, M, N, K, status, stream, RopeArgs{}, NormArgs{}, k_split);
     case EPI_T_STORE_T: return launch<BN, EPI_T_STORE_T>(c, a, w, M, N, K, status, stream);
     case EPI_T_RESIDUAL: return launch<BN, EPI_T_RESIDUAL>(c, a, w, M, N, K, status, stream);
     case EPI_T_SWIGLU: return launch<BN, EPI_T_SWIGLU>(c, a, w, M, N, K, status, stream);
@@ -540,8 +553,10 @@ int dispatch(void* c, const void* a, const void* w, int M, int N, int K, int epi
 // and the activations as W (N = tokens), and C is still [tokens, features]; for a few tokens and a large W this
 // streams W through 128-row tiles once instead of re-reading it for every 128 rows of a mostly empty tile of tokens.
 static int gemm_entry(void* c, const void* a, const void* w, int M, int N, int K, int epilogue, int tile_n,
-                      int* status, cudaStream_t stream, const NormArgs& norm, int* n_tiles_out) {
+                      int* status, cudaStream_t stream, const NormArgs& norm, int* n_tiles_out, int k_split = 1) {
   if (M <= 0 || N <= 0) return DLLM_OK;
+  if (k_split < 1 || k_split > (K + BK - 1) / BK || (k_split > 1 && epilogue != EPI_T_STORE_F32))
+    return DLLM_BAD_ARGUMENT;
   if (K <= 0 || (K & 7) || ((N & 1) && epilogue == EPI_SWIGLU) || ((M & 1) && epilogue == EPI_T_SWIGLU) ||
       ((uintptr_t)a & 15) || ((uintptr_t)w & 15) || status == nullptr)
     return DLLM_UNSUPPORTED_SIZE;
@@ -561,10 +576,10 @@ static int gemm_entry(void* c, const void* a, const void* w, int M, int N, int K
   if (n_tiles_out != nullptr)  // (a part per epilogue warp's share of a tile: see the epilogue)
     *n_tiles_out = (tile_n >= 128 ? 2 : 1) * ((N + tile_n - 1) / tile_n);
   switch (tile_n) {
-    case 32: return dispatch<32>(c, a, w, M, N, K, epilogue, status, stream, norm);
-    case 64: return dispatch<64>(c, a, w, M, N, K, epilogue, status, stream, norm);
-    case 128: return dispatch<128>(c, a, w, M, N, K, epilogue, status, stream, norm);
-    case 256: return dispatch<256>(c, a, w, M, N, K, epilogue, status, stream, norm);
+    case 32: return dispatch<32>(c, a, w, M, N, K, epilogue, status, stream, norm, k_split);
+    case 64: return dispatch<64>(c, a, w, M, N, K, epilogue, status, stream, norm, k_split);
+    case 128: return dispatch<128>(c, a, w, M, N, K, epilogue, status, stream, norm, k_split);
+    case 256: return dispatch<256>(c, a, w, M, N, K, epilogue, status, stream, norm, k_split);
     default: return DLLM_BAD_ARGUMENT;
   }
 }
@@ -572,6 +587,17 @@ static int gemm_entry(void* c, const void* a, const void* w, int M, int N, int K
 DLLM_EXPORT int dllm_gemm_tcgen05(void* c, const void* a, const void* w, int M, int N, int K, int epilogue, int tile_n,
                                   int* status, cudaStream_t stream) {
   return gemm_entry(c, a, w, M, N, K, epilogue, tile_n, status, stream, NormArgs{}, nullptr);
+}
+
+// A product of few tokens with a W of few rows and a long reduction, the other way round as epilogues 5..8 and with the
+// reduction cut into `k_split` stretches so that the device's multiprocessors all stream a part of W:
+// parts[s][tokens, features] (float32, k_split of them one behind the other) = X W^T over stretch s of the k tiles.
+// `w` is [features, K], `x` is [tokens, K]; the caller sums the parts in order (dllm_sum_parts_residual).
+DLLM_EXPORT int dllm_gemm_tcgen05_split(float* parts, const void* w, const void* x, int features, int tokens, int K,
+                                        int k_split, int tile_n, int* status, cudaStream_t stream) {
+  if (tile_n != 32 && tile_n != 64) return DLLM_BAD_ARGUMENT;
+  return gemm_entry(parts, w, x, features, tokens, K, EPI_T_STORE_F32, tile_n, status, stream, NormArgs{}, nullptr,
+                    k_split);
 }
 
 // The same product with an RMSNorm folded around it (see NormArgs in gemm_common.cuh), for prefill-sized steps.

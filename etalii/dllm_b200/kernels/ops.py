@@ -28,6 +28,9 @@ _prototypes = {
                                                c_int, c_void_p],
     ("elementwise", "dllm_copy_to_device"): [c_void_p, c_void_p, c_longlong, c_void_p],
     ("elementwise", "dllm_add_residual"): [c_void_p, c_void_p, c_longlong, c_int, c_void_p],
+    ("elementwise", "dllm_sum_parts_residual"): [c_void_p, c_void_p, c_int, c_longlong, c_void_p],
+    ("gemm_tcgen05", "dllm_gemm_tcgen05_split"): [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                                  c_void_p, c_void_p],
     ("elementwise", "dllm_decode_advance"): [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                              c_void_p],
     ("elementwise", "dllm_mask_tokens"): [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p],
@@ -233,6 +236,7 @@ GEMV_MAX_ROWS = 64
 
 
 CLUSTER_SPLIT_BYTES = (1 << 20, 16 << 20)
+CLUSTER_NARROW_ROWS = 8192
 
 
 def splits_over_clusters(rows: int, outputs: int, inner: int) -> bool:
@@ -241,10 +245,13 @@ def splits_over_clusters(rows: int, outputs: int, inner: int) -> bool:
     to the multiprocessors is the cost and a block per 16 rows of W reads them far too often. Measured at the layer
     sizes of a 576-wide model, as links of a chain of dependent launches: with 64 rows 4.0 to 7.4 µs against 4.9 to
     10.8; with 16 rows 3.2 to 3.6 against 3.8 to 4.5, but 2.5 against 2.3 for the smallest matrix (576 x 576); with 8
-    rows the kernel with a block per 16 rows of W wins everywhere (1.5 to 2.5 against 2.4 to 3.3)."""
+    rows the kernel with a block per 16 rows of W wins everywhere (1.5 to 2.5 against 2.4 to 3.3).
+    With 17 to 64 rows it also takes larger weights of few rows (at most 8,192: 6144 x 4096 with 32 rows 16.6 µs
+    against 21.1 for a block per 16 rows and 23.7 for the tile kernel, with 64 rows 22.3 against 47.3 and 23.9;
+    4096 x 14336 with 32 rows 29.9 against 40.0 and 73.9), where the tile kernel has too few tiles for the device."""
     size = 2 * outputs * inner
     if 16 < rows <= GEMV_MAX_ROWS:
-        return size <= CLUSTER_SPLIT_BYTES[1]
+        return size <= CLUSTER_SPLIT_BYTES[1] or outputs <= CLUSTER_NARROW_ROWS
     return 8 < rows <= 16 and CLUSTER_SPLIT_BYTES[0] <= size <= CLUSTER_SPLIT_BYTES[1]
 
 
@@ -273,15 +280,61 @@ def streams_through_shared_memory(rows: int, outputs: int, inner: int) -> bool:
     Measured against the kernel that streams through registers: it wins (0.71 to 0.97 of the HBM rate against 0.65 to
     0.89) for one or two rows of activations, long rows of W (its copies are 2 KB pieces of a row) and matrices of
     tens of megabytes; with more rows the copies of the activations cost it the lead."""
-    return rows <= 2 and inner >= 4096 and inner % 64 == 0 and 2 * outputs * inner >= TMA_STREAM_BYTES
+    if inner % 64 or 2 * outputs * inner < TMA_STREAM_BYTES:
+        return False
+    # (up to 4 rows its lead holds, 6144 x 4096: 11.3 µs against 12.2; up to 8 rows only for very long rows of W,
+    # 4096 x 14336: 24.2 against 28.8)
+    return (rows <= 4 and inner >= 4096) or (rows <= 8 and inner >= 8192)
 
 
 def takes_weights_as_rows(rows: int, outputs: int, inner: int) -> bool:
-    """Whether a product with 17 to 64 rows of activations runs the other way round on the tile kernel (W as the
+    """Whether a product with 3 to 64 rows of activations runs the other way round on the tile kernel (W as the
     128-row operand, read once). Measured: it wins where W has at least as many 128-row tiles as the device has
     multiprocessors (28672 x 4096 with 64 rows: 49 µs against 89 µs for the tile kernel and 187 µs for the streaming
     one; 16384 x 2048: 17 against 25); with fewer tiles a block's rate is bound by its one lane issuing products."""
-    return 16 < rows <= 64 and outputs >= 16384 and 2 * outputs * inner >= (32 << 20)
+    if not (outputs >= 16384 and 2 * outputs * inner >= (32 << 20)):
+        return False
+    # with 3 to 16 rows (the tile kernel's time does not depend on the rows): from 9 rows on, where the streaming
+    # kernels need a second fragment of tokens (16384 x 2048 with 16 rows: 16.6 µs against 19.6; 49152 x 2048: 39.0
+    # against 47.1), and from 3 rows on for rows of W of 4,096 values or more (128256 x 4096 with 8 rows: 176 against
+    # 194; 28672 x 4096: 43.8 against 46.6; with rows of 2,048 values and up to 8 rows the streaming kernel reads at
+    # 0.9 to 1.0 of the memory rate and keeps them)
+    return 16 < rows <= 64 or (8 < rows <= 16 and inner >= 2048) or (3 <= rows <= 8 and inner >= 4096)
+
+
+SPLIT_MIN_BYTES = 16 << 20
+
+
+def reduction_split(rows: int, outputs: int, inner: int, multiprocessors: int = 148) -> int:
+    """Into how many stretches the reduction of a residual product with 33 to 64 rows of activations is cut, 1 for
+    not at all. A W of few rows and a long reduction (an output or down projection: 4096 x 14336, 2048 x 8192) has
+    fewer 128-row tiles than the device has multiprocessors, and a multiprocessor takes in about 80 GB/s: with 32
+    tiles the whole device reads W at a quarter of its memory rate. Cut, the tiles of every stretch run side by side
+    and a second small kernel sums their partial results in order. Measured with 64 rows, both kernels together,
+    against the best of the other kernels: 4096 x 14336 29.3 µs against 73.3, 4096 x 4096 12.9 against 20.0,
+    2048 x 8192 13.4 against 19.1; with 32 rows and fewer, and for weights under 16 MB, the kernel that splits the
+    reduction over a cluster is as fast or faster (2048 x 2048 with 64 rows: 7.6 against 8.9)."""
+    if not (32 < rows <= GEMV_MAX_ROWS) or inner % 8 or outputs % 4 or 2 * outputs * inner <= SPLIT_MIN_BYTES:
+        return 1
+    tiles, k_tiles = -(-outputs // 128), -(-inner // 64)
+    if tiles >= multiprocessors:
+        return 1
+    split = 1
+    while split < 8 and tiles * split * 2 <= 2 * multiprocessors and k_tiles // (split * 2) >= 8:
+        split *= 2
+    return split
+
+
+_parts: dict = {}
+
+
+def _parts_buffer(device, floats: int) -> torch.Tensor:
+    """Scratch for partial results, one buffer per size for the life of the process: a captured graph may hold its
+    address."""
+    key = (str(device), floats)
+    if key not in _parts:
+        _parts[key] = torch.empty(floats, device=device, dtype=torch.float32)
+    return _parts[key]
 
 
 def gemm(c: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int = EPI_STORE_T, kernel: int = 0,
@@ -310,7 +363,20 @@ def gemm(c: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int = EPI_
                                                    _stream())
     elif w.dtype == torch.bfloat16:
         streaming = (kernel == 2 and m <= GEMV_MAX_ROWS) or (kernel == 0 and streams(m, n, k))
-        if kernel == 5 or (kernel == 0 and norm_weight is None and takes_weights_as_rows(m, n, k)):
+        split = reduction_split(m, n, k) if (kernel == 0 and epilogue == EPI_RESIDUAL and norm_weight is None) else 1
+        if kernel == 7 or split > 1:
+            # W as the 128-row operand, the reduction cut into stretches, the parts summed into c by a second kernel
+            assert a.dtype == torch.bfloat16 and norm_weight is None and epilogue == EPI_RESIDUAL and m <= 64
+            split = split if kernel == 0 else max(1, int(cluster) or reduction_split(m, n, k))
+            parts = _parts_buffer(c.device, 8 * GEMV_MAX_ROWS * n)
+            assert split <= 8
+            status = _fn("gemm_tcgen05", "dllm_gemm_tcgen05_split")(
+                parts.data_ptr(), w.data_ptr(), a.data_ptr(), n, m, k, split, 32 if m <= 32 else 64,
+                _status_word().data_ptr(), _stream())
+            if status == 0:
+                status = _fn("elementwise", "dllm_sum_parts_residual")(c.data_ptr(), parts.data_ptr(), split, m * n,
+                                                                       _stream())
+        elif kernel == 5 or (kernel == 0 and norm_weight is None and takes_weights_as_rows(m, n, k)):
             # the product the other way round: W is the 128-row operand, the tokens are the tile's columns
             assert a.dtype == torch.bfloat16 and norm_weight is None and m <= 256
             width = 32 if m <= 32 else (64 if m <= 64 else (128 if m <= 128 else 256))

@@ -145,8 +145,18 @@ def test_kernel_choice_rules_for_products():
     assert ops.streams(64, 3072, 576) and ops.splits_over_clusters(17, 3072, 576)
     assert ops.splits_over_clusters(16, 3072, 576) and not ops.splits_over_clusters(16, 576, 576)
     assert not ops.splits_over_clusters(8, 3072, 576) and not ops.splits_over_clusters(64, 16384, 2048)
+    assert ops.splits_over_clusters(64, 6144, 4096) and not ops.splits_over_clusters(16, 6144, 4096)  # few rows of W
     assert ops.streams_through_shared_memory(1, 28672, 4096) and not ops.streams_through_shared_memory(8, 28672, 4096)
+    assert ops.streams_through_shared_memory(8, 4096, 14336) and not ops.streams_through_shared_memory(9, 4096, 14336)
     assert not ops.streams_through_shared_memory(1, 16384, 2048)      # short rows of W
     assert not ops.streams_through_shared_memory(1, 4096, 4096 + 8)   # a reduction that is no multiple of 64
+    # a narrow W with a long reduction and 33 to 64 rows: the reduction is cut so that every multiprocessor reads
+    assert ops.reduction_split(64, 4096, 14336) == 8 and ops.reduction_split(64, 2048, 8192) == 8
+    assert ops.reduction_split(48, 4096, 4096) == 8 and ops.reduction_split(33, 576, 1536) == 1
+    assert ops.reduction_split(32, 4096, 14336) == 1 and ops.reduction_split(64, 28672, 4096) == 1
+    assert ops.reduction_split(64, 2048, 2048) == 1                   # small: the cluster kernel's
     assert ops.takes_weights_as_rows(64, 28672, 4096) and not ops.takes_weights_as_rows(64, 4096, 14336)
-    assert not ops.takes_weights_as_rows(16, 28672, 4096) and not ops.takes_weights_as_rows(65, 28672, 4096)
+    assert ops.takes_weights_as_rows(16, 28672, 4096) and not ops.takes_weights_as_rows(65, 28672, 4096)
+    assert ops.takes_weights_as_rows(3, 28672, 4096) and not ops.takes_weights_as_rows(2, 28672, 4096)
+    assert ops.takes_weights_as_rows(9, 16384, 2048) and not ops.takes_weights_as_rows(8, 16384, 2048)
+    assert not ops.takes_weights_as_rows(16, 49152, 576) and ops.takes_weights_as_rows(17, 49152, 576)

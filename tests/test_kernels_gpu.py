@@ -169,6 +169,25 @@ def test_gemm_with_weights_as_rows(m, n, k, epilogue):
     assert rel_error(c.float().cpu(), ref.float().cpu()) <= (2e-5 if epilogue in (0, 2) else 8e-3)
 
 
+@pytest.mark.parametrize("m", [1, 17, 33, 64])
+@pytest.mark.parametrize("n,k,split", [(128, 1024, 2), (132, 576, 8), (1000, 1088, 3), (4100, 512, 4), (300, 2240, 5),
+                                       (2048, 1088, 1), (520, 8200, 8)])
+def test_gemm_with_the_reduction_cut(m, n, k, split):
+    """The tile kernel with W as the 128-row operand and the reduction cut into stretches whose partial results a
+    second kernel adds to the residual in order: stretches of unequal length, more and fewer items than blocks,
+    features beyond the last tile; twice the same bits."""
+    a, w = _randn((m, k), torch.bfloat16, 3), _randn((n, k), torch.bfloat16, 4, 0.2)
+    c = _randn((m, n), torch.float32, 5)
+    ref, again = c.clone(), c.clone()
+    ops().gemm(c, a, w, 2, kernel=7, cluster=split)
+    ops().gemm(again, a, w, 2, kernel=7, cluster=split)
+    torch.cuda.synchronize()
+    ops().raise_if_failed()
+    PK.gemm(ref, a, w, 2)
+    assert rel_error(c.cpu(), ref.cpu()) <= 2e-5
+    assert torch.equal(again, c)
+
+
 def test_gemm_streaming_through_shared_memory_refuses_what_it_cannot_run():
     from etalii.dllm_b200.kernels.ops import KernelError
 

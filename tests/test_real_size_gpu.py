@@ -209,7 +209,8 @@ def larger_layers(request):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_two_layers_at_the_sizes_of_larger_models(larger_layers, dtype):
     """Reaches, through the engine's own rules: products that stream W through shared memory (one or two rows, long
-    rows of W), the tile product with W as the 128-row operand (33 rows against the head and the gate/up matrix),
+    rows of W), the tile product with W as the 128-row operand (33 rows against the head and the gate/up matrix), the
+    same with the reduction cut (33 rows against the output and down projections), the cluster kernel on large W,
     256-wide tiles, heads of 128 in every attention kernel, llama3 rotary scaling and an untied head."""
     config, weights, prompt, short, plain = larger_layers
     engine = make_engine(config, weights, dtype, max_tokens=64 * 40, max_length=128, decode_logits=True)
@@ -234,4 +235,14 @@ def test_two_layers_at_the_sizes_of_larger_models(larger_layers, dtype):
     for i in range(33):
         assert rel_error(graph_logits[i], plain[1 + i][1]) <= TOL[dtype], i
     engine.close(many + slot)
+    # six and twelve of them as batches of their own: with 3 to 16 rows the rules send wide matrices to the tile
+    # product with W as the 128-row operand and very long rows of W through shared memory
+    for count in (6, 12):
+        few = engine.open(count)
+        engine.step(few, [s[:-1] for s in short[:count]], [[] for _ in range(count)])
+        last = host(engine.step(few, [[s[-1]] for s in short[:count]]))
+        engine.check()
+        for i in range(count):
+            assert rel_error(last[i], plain[1 + i][1]) <= TOL[dtype], (count, i)
+        engine.close(few)
     engine.cache.check()
