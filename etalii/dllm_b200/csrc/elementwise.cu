@@ -168,12 +168,15 @@ DLLM_EXPORT int dllm_cast_ssq(void* copy, float* ssq, const float* x, int n_rows
 // qkv is the float32 output of the fused q/k/v projection, [tokens, (heads + 2 kv_heads) * head_dim]. Queries and
 // keys rotate pairs (i, i + rotary_dim/2) by the angle whose cosine and sine the table holds for the token's
 // position; dimensions beyond rotary_dim pass through. Queries go to q_out, keys and values into the token's
-// place in the paged cache (page_table[slot][pos / page_size], row pos % page_size).
+// place in the paged cache (page_table[slot][pos / page_size], row pos % page_size). With parts > 1, qkv is that
+// many partial results of the projection, `part_stride` floats apart, and a value is their sum in order.
 template <typename T>
 __global__ void rope_cache_kernel(const float* __restrict__ qkv, T* __restrict__ q_out, KvLayout cache,
                                   const float2* __restrict__ table, int rotary_dim, int heads,
                                   const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
-                                  const int* __restrict__ slots, int write_cache) {
+                                  const int* __restrict__ slots, int write_cache, int parts, size_t part_stride) {
+  pdl_launch_dependents();
+  pdl_wait();
   int t = blockIdx.x, h = blockIdx.y;
   int hd = cache.head_dim, nkv = cache.kv_heads;
   if (!write_cache && h >= heads) return;
@@ -191,12 +194,17 @@ __global__ void rope_cache_kernel(const float* __restrict__ qkv, T* __restrict__
     dst = (T*)cache.base + kv_offset(cache, page, which, g, pos % cache.page_size);
   }
   int half = rotary_dim / 2;
+  auto value = [&](int i) {
+    float sum = src[i];
+    for (int p = 1; p < parts; ++p) sum += src[(size_t)p * part_stride + i];
+    return sum;
+  };
   for (int i = threadIdx.x; i < hd; i += blockDim.x) {
-    float v = src[i];
+    float v = value(i);
     if (rotate && i < rotary_dim) {
       int j = i < half ? i : i - half;
       float2 cs = table[(size_t)pos * half + j];
-      float a = src[j], b = src[j + half];
+      float a = value(j), b = value(j + half);
       v = i < half ? fmaf(a, cs.x, -(b * cs.y)) : fmaf(a, cs.y, b * cs.x);
     }
     dst[i] = from_float<T>(v);
@@ -206,24 +214,24 @@ __global__ void rope_cache_kernel(const float* __restrict__ qkv, T* __restrict__
 DLLM_EXPORT int dllm_rope_cache_write(const float* qkv, void* q_out, void* cache_base, const int* page_table,
                                       int max_pages, int page_size, int heads, int kv_heads, int head_dim,
                                       const float* table, int rotary_dim, const int* tok_seq, const int* tok_pos,
-                                      const int* slots, int tokens, int write_cache, int dtype,
-                                      cudaStream_t stream) {
+                                      const int* slots, int tokens, int write_cache, int dtype, int parts,
+                                      long long part_stride, cudaStream_t stream) {
   if (tokens <= 0) return DLLM_OK;
-  if (heads <= 0 || kv_heads <= 0 || head_dim <= 0 || rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1))
+  if (heads <= 0 || kv_heads <= 0 || head_dim <= 0 || rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1) ||
+      parts < 1 || part_stride < 0)
     return DLLM_BAD_ARGUMENT;
   KvLayout cache{cache_base, page_table, max_pages, page_size, kv_heads, head_dim};
   dim3 grid(tokens, heads + 2 * kv_heads);
   int threads = head_dim >= 128 ? 128 : (head_dim > 32 ? 64 : 32);
   if (dtype == DLLM_F32)
-    rope_cache_kernel<float><<<grid, threads, 0, stream>>>(qkv, (float*)q_out, cache, (const float2*)table,
-                                                           rotary_dim, heads, tok_seq, tok_pos, slots, write_cache);
-  else if (dtype == DLLM_BF16)
-    rope_cache_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(qkv, (__nv_bfloat16*)q_out, cache,
-                                                                   (const float2*)table, rotary_dim, heads, tok_seq,
-                                                                   tok_pos, slots, write_cache);
-  else
-    return DLLM_BAD_ARGUMENT;
-  return dllm_launch_status();
+    return dllm_launch_pdl(rope_cache_kernel<float>, grid, dim3(threads), 0, stream, qkv, (float*)q_out, cache,
+                           (const float2*)table, rotary_dim, heads, tok_seq, tok_pos, slots, write_cache, parts,
+                           (size_t)part_stride);
+  if (dtype == DLLM_BF16)
+    return dllm_launch_pdl(rope_cache_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, qkv,
+                           (__nv_bfloat16*)q_out, cache, (const float2*)table, rotary_dim, heads, tok_seq, tok_pos,
+                           slots, write_cache, parts, (size_t)part_stride);
+  return DLLM_BAD_ARGUMENT;
 }
 
 // ---- residual += update (float32 sum) -----------------------------------------------------------------------------

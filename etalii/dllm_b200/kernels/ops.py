@@ -25,7 +25,7 @@ _prototypes = {
     ("elementwise", "dllm_rmsnorm"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
     ("elementwise", "dllm_rope_cache_write"): [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                                c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                                               c_int, c_void_p],
+                                               c_int, c_int, c_longlong, c_void_p],
     ("elementwise", "dllm_copy_to_device"): [c_void_p, c_void_p, c_longlong, c_void_p],
     ("elementwise", "dllm_add_residual"): [c_void_p, c_void_p, c_longlong, c_int, c_void_p],
     ("elementwise", "dllm_sum_parts_residual"): [c_void_p, c_void_p, c_int, c_longlong, c_void_p],
@@ -337,6 +337,26 @@ def _parts_buffer(device, floats: int) -> torch.Tensor:
     return _parts[key]
 
 
+MAX_REDUCTION_SPLIT = 8
+
+
+def gemm_parts(a: torch.Tensor, w: torch.Tensor, split: int) -> torch.Tensor:
+    """The product a[M,K] @ w[N,K]^T (bfloat16, M <= 64) as `split` partial results over stretches of the reduction:
+    a float32 tensor [split, M, N] in scratch that the next call of the same width overwrites. The tile kernel runs
+    it with W as the 128-row operand; whoever reads the parts sums them in order."""
+    _cuda(a, w)
+    m, k = a.shape
+    n = w.shape[0]
+    assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] == k
+    assert 0 < m <= GEMV_MAX_ROWS and 1 <= split <= MAX_REDUCTION_SPLIT
+    parts = _parts_buffer(a.device, MAX_REDUCTION_SPLIT * GEMV_MAX_ROWS * n)
+    _check(_fn("gemm_tcgen05", "dllm_gemm_tcgen05_split")(
+        parts.data_ptr(), w.data_ptr(), a.data_ptr(), n, m, k, split, 32 if m <= 32 else 64,
+        _status_word().data_ptr(), _stream()), "gemm_parts",
+        lambda: f"M={m} N={n} K={k} (multiple of 8) in {split} stretches (at most one per 64 values of K)")
+    return parts[:split * m * n].view(split, m, n)
+
+
 def gemm(c: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int = EPI_STORE_T, kernel: int = 0,
          norm_weight: torch.Tensor | None = None, eps: float = 0.0, tile_n: int = 0, cluster: int = 0) -> None:
     """c = a[M,K] @ w[N,K]^T with float32 accumulation, then the epilogue: EPI_STORE_F32 (c float32), EPI_STORE_T
@@ -368,14 +388,9 @@ def gemm(c: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int = EPI_
             # W as the 128-row operand, the reduction cut into stretches, the parts summed into c by a second kernel
             assert a.dtype == torch.bfloat16 and norm_weight is None and epilogue == EPI_RESIDUAL and m <= 64
             split = split if kernel == 0 else max(1, int(cluster) or reduction_split(m, n, k))
-            parts = _parts_buffer(c.device, 8 * GEMV_MAX_ROWS * n)
-            assert split <= 8
-            status = _fn("gemm_tcgen05", "dllm_gemm_tcgen05_split")(
-                parts.data_ptr(), w.data_ptr(), a.data_ptr(), n, m, k, split, 32 if m <= 32 else 64,
-                _status_word().data_ptr(), _stream())
-            if status == 0:
-                status = _fn("elementwise", "dllm_sum_parts_residual")(c.data_ptr(), parts.data_ptr(), split, m * n,
-                                                                       _stream())
+            parts = gemm_parts(a, w, split)
+            status = _fn("elementwise", "dllm_sum_parts_residual")(c.data_ptr(), parts.data_ptr(), split, m * n,
+                                                                   _stream())
         elif kernel == 5 or (kernel == 0 and norm_weight is None and takes_weights_as_rows(m, n, k)):
             # the product the other way round: W is the 128-row operand, the tokens are the tile's columns
             assert a.dtype == torch.bfloat16 and norm_weight is None and m <= 256
@@ -619,10 +634,16 @@ def gemv_qkv_rope(a: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, cache, 
 def rope_cache_write(qkv: torch.Tensor, q_out: torch.Tensor, cache, table: torch.Tensor | None, rotary_dim: int,
                      heads: int, batch, write_cache: bool = True) -> None:
     """Rotates queries and keys of qkv (float32 [tokens, (heads + 2 kv_heads) * head_dim]) by the table's angle for
-    each token's position; queries go to q_out, keys and values into the token's place in the paged cache."""
+    each token's position; queries go to q_out, keys and values into the token's place in the paged cache. A qkv
+    of three dimensions is partial results [parts, tokens, ...] (`gemm_parts`), summed in order on the way in."""
     _cuda(qkv, q_out, table)
     tokens = batch.n_tokens
     assert qkv.dtype == torch.float32 and q_out.dtype == cache.dtype
+    n_parts, part_stride = 1, 0
+    if qkv.dim() == 3:
+        assert qkv.is_contiguous()
+        n_parts, part_stride = qkv.shape[0], qkv.shape[1] * qkv.shape[2]
+        qkv = qkv[0]
     assert qkv.shape[0] >= tokens and qkv.shape[1] == (heads + 2 * cache.kv_heads) * cache.head_dim
     if table is not None:
         assert table.dtype == torch.float32 and table.shape[0] > batch.max_position, "position beyond the table"
@@ -631,7 +652,8 @@ def rope_cache_write(qkv: torch.Tensor, q_out: torch.Tensor, cache, table: torch
         qkv.data_ptr(), q_out.data_ptr(), cache.base_ptr, cache.page_table.data_ptr(), cache.max_pages,
         cache.page_size, heads, cache.kv_heads, cache.head_dim, table.data_ptr() if table is not None else None,
         rotary_dim if table is not None else 0, batch.tok_seq.data_ptr(), batch.tok_pos.data_ptr(),
-        batch.slots.data_ptr(), tokens, 1 if write_cache else 0, _code(cache.dtype), _stream()), "rope_cache_write")
+        batch.slots.data_ptr(), tokens, 1 if write_cache else 0, _code(cache.dtype), n_parts, part_stride,
+        _stream()), "rope_cache_write")
 
 
 def attention_general(out: torch.Tensor, q: torch.Tensor, cache, heads: int, scale: float, window: int,

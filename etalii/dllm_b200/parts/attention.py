@@ -89,7 +89,14 @@ class Attention:
         q = rt.ws.buffer("q", (n, q_size), rt.dtype)
         table = self.position.table() if self.position is not None else None
         rotary_dim = self.position.rotary_dim if self.position is not None else 0
-        if rt.dtype == torch.bfloat16 and n <= ops.GEMV_MAX_ROWS and self.head_dim % 16 == 0 and rotary_dim % 16 == 0:
+        split = ops.reduction_split(n, *self.w_qkv.shape) if rt.dtype == torch.bfloat16 else 1
+        if split > 1:
+            # 33 to 64 tokens against a large W of few rows: the reduction is cut so that the whole device reads W,
+            # and the rotation sums the partial results
+            hidden = h.tensor() if isinstance(h, NormedInput) else h
+            ops.rope_cache_write(ops.gemm_parts(hidden, self.w_qkv, split), q, cache, table, rotary_dim,
+                                 self.num_heads, batch, write_cache)
+        elif rt.dtype == torch.bfloat16 and n <= ops.GEMV_MAX_ROWS and self.head_dim % 16 == 0 and rotary_dim % 16 == 0:
             # decode-sized: norm, projection, rotation and cache write in one kernel
             if isinstance(h, NormedInput) and not fuses_norm(self.w_qkv):
                 h = h.tensor()

@@ -363,6 +363,14 @@ def test_rope_cache_write(dtype, tol, heads, kv_heads, head_dim, rotary):
     snapshot = view.storage.clone()
     ops().rope_cache_write(qkv, q2, view, table, rotary, heads, batch, False)
     assert torch.equal(q2, q) and torch.equal(view.storage, snapshot)
+    # three partial results summed in order on the way in: the bits of their float32 sum
+    parts = torch.stack([_randn(tuple(qkv.shape), torch.float32, 10 + i) for i in range(3)]).contiguous()
+    summed = (parts[0] + parts[1]) + parts[2]
+    q3, q4 = torch.zeros_like(q), torch.zeros_like(q)
+    ops().rope_cache_write(parts, q3, view, table, rotary, heads, batch, True)
+    from_parts = view.storage.clone()
+    ops().rope_cache_write(summed, q4, view, table, rotary, heads, batch, True)
+    assert torch.equal(q3, q4) and torch.equal(from_parts, view.storage)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
