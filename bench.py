@@ -291,9 +291,9 @@ def attention_table() -> int:
 
 
 def stream_table() -> int:
-    """Times the decode products alone at layer shapes of the larger models: the kernel that streams W through
-    registers against the one that streams it through shared memory, as fractions of the measured HBM rate (a CUDA
-    graph of 20 launches over several copies of W, so that W comes from HBM)."""
+    """Times the decode products alone at layer shapes of the larger models, every kernel that can run them, as
+    fractions of the measured HBM rate (a CUDA graph of 20 launches over several copies of W, so that W comes from
+    HBM): the rules in `kernels/ops.py` that choose among them rest on these tables."""
     import torch
 
     from etalii.dllm_b200.kernels import ops
@@ -301,7 +301,7 @@ def stream_table() -> int:
     device = "cuda:0"
     rate = peaks()["hbm_gbs"]
 
-    def run(m, n, k, epilogue, kernel):
+    def run(m, n, k, epilogue, kernel, cluster=0):
         copies = max(2, int(300e6 // (n * k * 2)) + 1)
         ws = [(torch.randn(n, k, device=device) * 0.05).bfloat16() for _ in range(copies)]
         x = torch.randn(m, k, device=device).bfloat16()
@@ -309,12 +309,12 @@ def stream_table() -> int:
         dtype = torch.float32 if epilogue in (ops.EPI_STORE_F32, ops.EPI_RESIDUAL) else torch.bfloat16
         c = torch.zeros(m, cols, device=device, dtype=dtype)
         for i in range(3):
-            ops.gemm(c, x, ws[i % copies], epilogue, kernel=kernel)
+            ops.gemm(c, x, ws[i % copies], epilogue, kernel=kernel, cluster=cluster)
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             for i in range(20):
-                ops.gemm(c, x, ws[i % copies], epilogue, kernel=kernel)
+                ops.gemm(c, x, ws[i % copies], epilogue, kernel=kernel, cluster=cluster)
         graph.replay()
         torch.cuda.synchronize()
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -330,11 +330,30 @@ def stream_table() -> int:
               (4096, 14336, ops.EPI_RESIDUAL), (128256, 4096, ops.EPI_STORE_F32), (6144, 2048, ops.EPI_STORE_T),
               (16384, 2048, ops.EPI_SWIGLU), (2048, 8192, ops.EPI_RESIDUAL), (49152, 2048, ops.EPI_STORE_F32),
               (49152, 576, ops.EPI_STORE_F32)]
-    print("rows of activations, W rows x row length, epilogue | registers: us, of HBM | shared memory: us, of HBM")
-    for m in (1, 8, 16):
+
+    def cell(m, n, k, epilogue, kernel):
+        us, fraction = run(m, n, k, epilogue, kernel)
+        return f"{us:.1f} {fraction:.2f}"
+
+    print("rows of activations, W rows x row length, epilogue | registers: us, of HBM | shared memory | tile kernel, "
+          "W as its rows")
+    for m in (1, 4, 8, 16):
         for n, k, epilogue in shapes:
-            a, b = run(m, n, k, epilogue, 2), run(m, n, k, epilogue, 4)
-            print(f"{m} {n} x {k} {epilogue} | {a[0]:.1f} {a[1]:.2f} | {b[0]:.1f} {b[1]:.2f}")
+            ring = cell(m, n, k, epilogue, 4) if k % 64 == 0 else "-"
+            print(f"{m} {n} x {k} {epilogue} | {cell(m, n, k, epilogue, 2)} | {ring} | {cell(m, n, k, epilogue, 5)}")
+    # 32 and 64 rows against matrices of few rows: a block per 16 rows of W, the tile kernel, the same with W as its
+    # rows, the reduction split over a cluster, and W as rows with the reduction cut (residual products only)
+    print("rows, W | registers | tile kernel | W as its rows | cluster | reduction cut in 2 | 4 | 8")
+    narrow = [(4096, 4096, ops.EPI_RESIDUAL), (4096, 14336, ops.EPI_RESIDUAL), (2048, 2048, ops.EPI_RESIDUAL),
+              (2048, 8192, ops.EPI_RESIDUAL), (6144, 4096, ops.EPI_STORE_T), (6144, 2048, ops.EPI_STORE_T)]
+    for m in (32, 64):
+        for n, k, epilogue in narrow:
+            cells = [cell(m, n, k, epilogue, kernel) for kernel in (2, 3, 5, 6)]
+            if epilogue == ops.EPI_RESIDUAL:
+                for split in (2, 4, 8):
+                    us, fraction = run(m, n, k, epilogue, 7, split)
+                    cells.append(f"{us:.1f} {fraction:.2f}")
+            print(f"{m} {n} x {k} {epilogue} | " + " | ".join(cells))
     return 0
 
 
