@@ -58,6 +58,14 @@ template <int BN, int EPI, bool DEEP> struct EpilogueStage {
                                : ((EPI == EPI_RESIDUAL && BN == 256 && !DEEP) ? 8 * 32 * 20 * 4 : 0));  // (see below)
 };
 
+// Item `item` of a block's list: a tile and, where the reduction is cut (k_split > 1), one stretch of its k tiles.
+struct WorkItem { int tile, split, kt_begin, kt_end; };
+__device__ __forceinline__ WorkItem work_item(int item, int total, int k_tiles, int k_split) {
+  if (k_split == 1) return WorkItem{item, 0, 0, k_tiles};
+  int split = item / total;
+  return WorkItem{item - split * total, split, split * k_tiles / k_split, (split + 1) * k_tiles / k_split};
+}
+
 template <int BN, int EPI, bool DEEP, int HD>
 __global__ void __launch_bounds__(Shape<BN, DEEP>::THREADS, Shape<BN, DEEP>::BLOCKS_PER_SM) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                const __grid_constant__ CUtensorMap map_w,
@@ -100,10 +108,9 @@ __global__ void __launch_bounds__(Shape<BN, DEEP>::THREADS, Shape<BN, DEEP>::BLO
       int it = 0;  // k tiles issued so far, over all of this block's tiles
       bool ok = true;
       for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
-        int t = item % total, split = item / total;
-        int m0 = (t % m_tiles) * BM, n0 = (t / m_tiles) * BN;
-        int kt_end = (int)((long long)(split + 1) * k_tiles / k_split);
-        for (int kt = (int)((long long)split * k_tiles / k_split); kt < kt_end; ++kt, ++it) {
+        WorkItem w = work_item(item, total, k_tiles, k_split);
+        int m0 = (w.tile % m_tiles) * BM, n0 = (w.tile / m_tiles) * BN;
+        for (int kt = w.kt_begin; kt < w.kt_end; ++kt, ++it) {
           int s = it % S::STAGES;
           if (it >= S::STAGES && !mbar_wait(&empty_bar[s], ((it / S::STAGES) - 1) & 1)) {
             *(volatile int*)status = 2;
@@ -127,10 +134,8 @@ __global__ void __launch_bounds__(Shape<BN, DEEP>::THREADS, Shape<BN, DEEP>::BLO
         if (lt >= 2 && !mbar_wait(&acc_empty[buf], ((lt >> 1) - 1) & 1)) { *(volatile int*)status = 5; break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         unsigned acc = tmem_base + (unsigned)(buf * S::ACC_COLS);
-        int split = item / total;
-        int kt_begin = (int)((long long)split * k_tiles / k_split);
-        int kt_end = (int)((long long)(split + 1) * k_tiles / k_split);
-        for (int kt = kt_begin; kt < kt_end; ++kt, ++it) {
+        WorkItem w = work_item(item, total, k_tiles, k_split);
+        for (int kt = w.kt_begin; kt < w.kt_end; ++kt, ++it) {
           int s = it % S::STAGES;
           if (!mbar_wait(&full_bar[s], (it / S::STAGES) & 1)) { *(volatile int*)status = 3; ok = false; break; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -139,7 +144,7 @@ __global__ void __launch_bounds__(Shape<BN, DEEP>::THREADS, Shape<BN, DEEP>::BLO
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             uint64_t adesc = smem_desc(a_addr + k * UMMA_K * 2), bdesc = smem_desc(b_addr + k * UMMA_K * 2);
-            umma(acc, adesc, bdesc, idesc, (kt > kt_begin || k > 0) ? 1u : 0u);
+            umma(acc, adesc, bdesc, idesc, (kt > w.kt_begin || k > 0) ? 1u : 0u);
           }
           tcgen05_commit(&empty_bar[s]);  // the stage is free once these products have read it
         }
@@ -156,9 +161,10 @@ __global__ void __launch_bounds__(Shape<BN, DEEP>::THREADS, Shape<BN, DEEP>::BLO
     int lt = 0;
     for (int item = blockIdx.x; item < items; item += gridDim.x, ++lt) {
       int buf = lt & 1;
-      int t = item % total;
+      WorkItem w = work_item(item, total, k_tiles, k_split);
+      int t = w.tile;
       int m0 = (t % m_tiles) * BM, n_tile = t / m_tiles, n0 = n_tile * BN;
-      void* c_part = EPI == EPI_T_STORE_F32 ? (void*)((float*)c + (size_t)(item / total) * M * N) : c;
+      void* c_part = EPI == EPI_T_STORE_F32 ? (void*)((float*)c + (size_t)w.split * M * N) : c;
       int m = m0 + quarter * 32 + lane;
       // (narrow tiles: the row's old residual values are all asked for before the accumulator is read, so their
       // round trip runs under the wait for the products instead of after it, once per 16 columns)
@@ -555,7 +561,7 @@ int dispatch(void* c, const void* a, const void* w, int M, int N, int K, int epi
 static int gemm_entry(void* c, const void* a, const void* w, int M, int N, int K, int epilogue, int tile_n,
                       int* status, cudaStream_t stream, const NormArgs& norm, int* n_tiles_out, int k_split = 1) {
   if (M <= 0 || N <= 0) return DLLM_OK;
-  if (k_split < 1 || k_split > (K + BK - 1) / BK || (k_split > 1 && epilogue != EPI_T_STORE_F32))
+  if (k_split < 1 || k_split > 32 || k_split > (K + BK - 1) / BK || (k_split > 1 && epilogue != EPI_T_STORE_F32))
     return DLLM_BAD_ARGUMENT;
   if (K <= 0 || (K & 7) || ((N & 1) && epilogue == EPI_SWIGLU) || ((M & 1) && epilogue == EPI_T_SWIGLU) ||
       ((uintptr_t)a & 15) || ((uintptr_t)w & 15) || status == nullptr)
