@@ -371,6 +371,10 @@ int launch_shape(int shape, void* out, const void* q, const KvLayout& cache, con
     long long places = (long long)sms * (long long)(per_sm > 8 ? 8 : per_sm);
     if (pairs * 8 <= sms) shape = 4;
     else for (shape = 0; shape < 3 && (pairs << shape) * 20 < places * 17; ++shape) {}
+    // (heads above 64: a block is two warps, and two blocks a pair even out contexts of unequal length better than
+    // one; measured with 32 query and 8 kv heads of 128, contexts 128 to 2,304: 64 sequences 62.5 µs against 69.0,
+    // 128 sequences 129.3 against 134.0)
+    if (HD > 64 && shape == 0 && pairs <= 4 * places) shape = 1;
   }
 #define DLLM_GO(CL, WARPS) \
   return launch<HD, CL, WARPS>(out, q, cache, tok_pos, slots, heads, sequences, scale, window, stream)

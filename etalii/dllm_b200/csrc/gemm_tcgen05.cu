@@ -9,6 +9,9 @@
 //   warps 2.. read the accumulator (tcgen05.ld 32x32b, a lane per row; four warps for tiles up to 64 columns, eight
 //            for wider ones: two per 32 rows, with half the columns each) and apply the epilogue: store float32 or
 //            bfloat16, add into the float32 residual, or SwiGLU on interleaved gate/up columns.
+// A product of few tokens can run the other way round (W as the 128-row operand, the tile is C^T), and then also with
+// its reduction cut into stretches: a block's work items are (tile, stretch) pairs and every stretch stores its own
+// partial result, which a second kernel sums in order (for a W with fewer tiles than the device has multiprocessors).
 // Rows of A beyond M and columns of K beyond the matrix are zero-filled by TMA; rows of W beyond N give columns
 // that are never stored. No multicast, no clusters. Every wait on an mbarrier is bounded: after the limit the role
 // records a status word and leaves, the block still frees its tensor memory, and the host raises.

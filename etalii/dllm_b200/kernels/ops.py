@@ -365,7 +365,8 @@ def gemm(c: torch.Tensor, a: torch.Tensor, w: torch.Tensor, epilogue: int = EPI_
     or, for M <= 64, a weight-streaming kernel (`kernel`: 0 chooses by the sizes, 1 forces the mma.sync tile kernel,
     2 forces streaming through registers, 3 forces tcgen05, 4 forces streaming through shared memory, 5 forces
     tcgen05 with W as the 128-row operand (for at most 256 rows of `a`), 6 forces the reduction split over a cluster
-    (`cluster` blocks, 0 chooses); `tile_n` picks the tcgen05 tile width).
+    (`cluster` blocks, 0 chooses), 7 forces W as the 128-row operand with the reduction cut into `cluster` stretches
+    (residual epilogue, at most 64 rows; 0 chooses); `tile_n` picks the tcgen05 tile width).
     With `norm_weight` (streaming kernel only), `a` is the float32 residual stream and is RMS-normed on the way in."""
     _cuda(c, a, w, norm_weight)
     m, k = a.shape
