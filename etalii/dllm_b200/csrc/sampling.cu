@@ -43,7 +43,7 @@ struct Shared {
   double reduce_d[32];
   float reduce_f[32];
   int reduce_i[32];
-  unsigned tie_counts[THREADS];
+  unsigned warp_ties[THREADS / 32];
 };
 
 // ---- the cluster: barrier and reads of the same variable in another block's shared memory
@@ -91,24 +91,27 @@ __device__ __forceinline__ unsigned long long to_fx(float p) {
 // on a handful of shared counters), then the bins are summed over the threads (a fixed tree) and over the blocks of
 // the cluster in rank order. Every block walks the same totals and finds the same boundary.
 template <int CL>
-__device__ void find_prefix(const float* __restrict__ p, int vocab, int kind, unsigned long long target, Shared& sh,
+__device__ __forceinline__ void find_prefix(const float* __restrict__ p, int vocab, int kind, unsigned long long target, Shared& sh,
                             unsigned* __restrict__ hist_count, unsigned long long* __restrict__ hist_mass,
-                            unsigned rank, Turn& turn) {
+                            unsigned rank, Turn& turn, const float (&kept)[8], bool fits) {
   unsigned prefix = 0;
   unsigned long long above_count = 0, above_mass = 0;
   int tid = threadIdx.x;
-  for (int shift = 28; shift >= 0; shift -= 4) {
+  // The thread's bins start at zero and whoever sums them below leaves them at zero again. Where the thread's
+  // stripe of the vocabulary is at most eight elements (`fits`), the caller holds them in registers (`kept`, -1 for
+  // none) and no pass reads them again.
 #pragma unroll
-    for (int bin = 0; bin < BINS; ++bin) {
-      hist_count[bin * THREADS + tid] = 0u;
-      hist_mass[bin * THREADS + tid] = 0ull;
-    }
+  for (int bin = 0; bin < BINS; ++bin) {
+    hist_count[bin * THREADS + tid] = 0u;
+    hist_mass[bin * THREADS + tid] = 0ull;
+  }
+  for (int shift = 28; shift >= 0; shift -= 4) {
     if (tid == 0) sh.found.ok = 0;
     for (int i0 = (int)rank * THREADS + tid; i0 < vocab; i0 += 8 * CL * THREADS) {
       float v[8];
 #pragma unroll
       for (int u = 0; u < 8; ++u)  // loads first
-        v[u] = i0 + u * CL * THREADS < vocab ? p[i0 + u * CL * THREADS] : -1.f;
+        v[u] = fits ? kept[u] : (i0 + u * CL * THREADS < vocab ? p[i0 + u * CL * THREADS] : -1.f);
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
         unsigned key = __float_as_uint(v[u]) << 1;
@@ -127,8 +130,11 @@ __device__ void find_prefix(const float* __restrict__ p, int vocab, int kind, un
       unsigned long long c = 0, m = 0;
 #pragma unroll
       for (int j = 0; j < THREADS / 64; ++j) {
-        c += hist_count[bin * THREADS + half * (THREADS / 2) + j * 32 + lane];
-        m += hist_mass[bin * THREADS + half * (THREADS / 2) + j * 32 + lane];
+        int at = bin * THREADS + half * (THREADS / 2) + j * 32 + lane;
+        c += hist_count[at];
+        m += hist_mass[at];
+        hist_count[at] = 0u;  // (every entry is read by exactly one thread: it leaves it empty for the next pass)
+        hist_mass[at] = 0ull;
       }
       for (int o = 16; o > 0; o >>= 1) {
         c += __shfl_xor_sync(0xffffffffu, c, o);
@@ -314,7 +320,7 @@ __device__ void cluster_argmax(float& v, int& idx, Shared& sh, Turn& turn) {
 }
 
 template <int CL>
-__global__ void __launch_bounds__(THREADS) sample_kernel(
+__global__ void __launch_bounds__(THREADS, 1) sample_kernel(
     int* __restrict__ out_tokens, const float* __restrict__ logits, long long row_stride, int vocab,
     float* __restrict__ scratch, unsigned long long* __restrict__ rng, const int* __restrict__ rng_rows,
     float temperature, int top_k, double top_p, double min_p) {
@@ -342,10 +348,27 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(
     return;
   }
   float* p = scratch + (size_t)row * vocab;
-  for (int i = first; i < vocab; i += stride) {
-    float z = __fdiv_rn(l[i], temperature);
-    p[i] = z;
-    if (z > best) { best = z; best_i = i; }
+  // A thread's stripe of the vocabulary, where it is at most eight logits, lives in registers from here to the
+  // search (the same operations in the same order as the loops that go through global memory otherwise).
+  const bool fits = vocab <= 8 * stride;
+  float kept[8];
+  if (fits) {
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      int i = first + u * stride;
+      kept[u] = -1.f;
+      if (i < vocab) {
+        float z = __fdiv_rn(l[i], temperature);
+        kept[u] = z;
+        if (z > best) { best = z; best_i = i; }
+      }
+    }
+  } else {
+    for (int i = first; i < vocab; i += stride) {
+      float z = __fdiv_rn(l[i], temperature);
+      p[i] = z;
+      if (z > best) { best = z; best_i = i; }
+    }
   }
   cluster_argmax<CL>(best, best_i, sh, turn);
   if (best_i == 0x7fffffff) {
@@ -359,24 +382,50 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(
   size_t floats = (((size_t)rows * vocab) + 1) & ~(size_t)1;  // the doubles start 8-byte aligned behind the floats
   double* e = reinterpret_cast<double*>(scratch + floats) + (size_t)row * vocab;
   double partial = 0.0;
-  for (int i = first; i < vocab; i += stride) {
-    double ex = exp((double)p[i] - (double)best);  // once per logit, kept in double for the division below
-    e[i] = ex;
-    partial += ex;
-  }
-  double inverse = 1.0 / cluster_sum_d<CL>(partial, sh, turn);
   unsigned long long all_mass = 0;  // this thread's share of the total mass, in fixed point (exact integer sums)
-  for (int i = first; i < vocab; i += stride) {
-    float v = (float)(e[i] * inverse);
-    p[i] = v;
-    all_mass += to_fx(v);
+  if (fits) {
+    // (the exponentials wait in the shared memory that the search's histograms take afterwards)
+    double* ex = reinterpret_cast<double*>(hist_raw) + tid;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      if (first + u * stride < vocab) {
+        double value = exp((double)kept[u] - (double)best);  // once per logit, kept in double for the division below
+        ex[u * THREADS] = value;
+        partial += value;
+      }
+    }
+    double inverse = 1.0 / cluster_sum_d<CL>(partial, sh, turn);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      int i = first + u * stride;
+      if (i < vocab) {
+        float v = (float)(ex[u * THREADS] * inverse);
+        p[i] = v;
+        kept[u] = v;
+        all_mass += to_fx(v);
+      } else {
+        kept[u] = -1.f;
+      }
+    }
+  } else {
+    for (int i = first; i < vocab; i += stride) {
+      double ex = exp((double)p[i] - (double)best);
+      e[i] = ex;
+      partial += ex;
+    }
+    double inverse = 1.0 / cluster_sum_d<CL>(partial, sh, turn);
+    for (int i = first; i < vocab; i += stride) {
+      float v = (float)(e[i] * inverse);
+      p[i] = v;
+      all_mass += to_fx(v);
+    }
   }
   __syncthreads();
 
   unsigned long long keep = (unsigned long long)vocab;
   if (top_k > 0 && (unsigned long long)top_k < keep) keep = (unsigned long long)top_k;
   if (top_p < 1.0) {
-    find_prefix<CL>(p, vocab, FIND_MASS_GE, (unsigned long long)(top_p * FX_ONE), sh, hist_count, hist_mass, rank, turn);
+    find_prefix<CL>(p, vocab, FIND_MASS_GE, (unsigned long long)(top_p * FX_ONE), sh, hist_count, hist_mass, rank, turn, kept, fits);
     if (sh.found.ok) {
       unsigned long long n = sh.found.above_count + sh.found.rank;
       if (n < keep) keep = n;
@@ -395,7 +444,7 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(
   if (keep >= (unsigned long long)vocab) {  // everything is kept: the total is a plain sum, no search needed
     total = cluster_sum_u64<CL>(all_mass, sh, turn);
   } else {
-    find_prefix<CL>(p, vocab, FIND_COUNT, keep, sh, hist_count, hist_mass, rank, turn);
+    find_prefix<CL>(p, vocab, FIND_COUNT, keep, sh, hist_count, hist_mass, rank, turn, kept, fits);
     unsigned long long each = sh.found.tie_count ? sh.found.tie_mass / sh.found.tie_count : 0;
     total = sh.found.above_mass + sh.found.rank * each;
   }
@@ -413,7 +462,7 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(
   unsigned long long target = (unsigned long long)(u * (double)total);
   if (total > 0 && target >= total) target = total - 1;
   __syncthreads();
-  find_prefix<CL>(p, vocab, FIND_MASS_GT, target, sh, hist_count, hist_mass, rank, turn);
+  find_prefix<CL>(p, vocab, FIND_MASS_GT, target, sh, hist_count, hist_mass, rank, turn, kept, fits);
   unsigned want_bits;
   unsigned long long want_rank;
   if (sh.found.ok) {
@@ -424,7 +473,7 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(
     if (position > keep) want_rank = keep > sh.found.above_count ? keep - sh.found.above_count : 1;
   } else {  // nothing exceeds the target (all mass is zero): the reference takes the last kept candidate
     __syncthreads();
-    find_prefix<CL>(p, vocab, FIND_COUNT, keep, sh, hist_count, hist_mass, rank, turn);
+    find_prefix<CL>(p, vocab, FIND_COUNT, keep, sh, hist_count, hist_mass, rank, turn, kept, fits);
     want_bits = sh.found.bits;
     want_rank = sh.found.rank;
   }
@@ -435,34 +484,32 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(
   int lo = min(first * chunk, vocab), hi = min(lo + chunk, vocab);
   unsigned mine = 0;
   for (int i = lo; i < hi; ++i) mine += __float_as_uint(__ldcg(p + i)) == want_bits ? 1u : 0u;
-  sh.tie_counts[tid] = mine;
-  __syncthreads();
-  int set = turn.next();
-  if (tid == 0) {
-    unsigned block_ties = 0;
-    for (int i = 0; i < THREADS; ++i) block_ties += sh.tie_counts[i];
-    sh.out_u32[set] = block_ties;
+  // ties before this thread's piece: in its warp (a scan by shuffles), in the warps before, in the blocks before
+  const int warp = tid >> 5, lane = tid & 31;
+  unsigned through_me = mine;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    unsigned other = __shfl_up_sync(0xffffffffu, through_me, o);
+    if (lane >= o) through_me += other;
   }
+  if (lane == 31) sh.warp_ties[warp] = through_me;
+  __syncthreads();
+  unsigned before_warp = 0, block_ties = 0;
+  for (int w = 0; w < THREADS / 32; ++w) {
+    unsigned ties = sh.warp_ties[w];
+    if (w < warp) before_warp += ties;
+    block_ties += ties;
+  }
+  int set = turn.next();
+  if (tid == 0) sh.out_u32[set] = block_ties;
   cluster_sync();
-  unsigned long long before_block = 0;  // ties in the blocks of lower rank (their ids are lower)
+  unsigned long long before = 0;  // ties in the blocks of lower rank (their ids are lower)
 #pragma unroll
   for (unsigned r = 0; r < CL; ++r)
-    if (r < rank) before_block += remote_u32(&sh.out_u32[set], r);
-  unsigned my_ties = remote_u32(&sh.out_u32[set], rank);
-  bool here = before_block < want_rank && want_rank <= before_block + my_ties;  // true in exactly one block
-  if (here && tid == 0) {
-    unsigned long long seen = before_block;
-    int owner = THREADS - 1;
-    for (int i = 0; i < THREADS; ++i) {
-      if (seen + sh.tie_counts[i] >= want_rank) { owner = i; break; }
-      seen += sh.tie_counts[i];
-    }
-    sh.reduce_i[0] = owner;
-    sh.found.above_count = seen;
-  }
-  __syncthreads();
-  if (here && tid == sh.reduce_i[0]) {
-    unsigned long long seen = sh.found.above_count;
+    if (r < rank) before += remote_u32(&sh.out_u32[set], r);
+  before += before_warp + through_me - mine;
+  if (before < want_rank && want_rank <= before + mine) {  // true in exactly one thread of the cluster
+    unsigned long long seen = before;
     int chosen = best_i;
     for (int i = lo; i < hi; ++i) {
       if (__float_as_uint(__ldcg(p + i)) == want_bits && ++seen == want_rank) { chosen = i; break; }

@@ -431,6 +431,18 @@ def test_sample_with_many_rows_and_flat_or_peaked_distributions(rows, spread):
         assert got == want, options
 
 
+@pytest.mark.parametrize("rows,vocab", [(19, 40001), (40, 20000), (80, 9001)])
+def test_sample_where_a_thread_holds_more_of_the_vocabulary_than_it_caches(rows, vocab):
+    """With many rows a row has few blocks, and a thread's stripe of a large vocabulary is longer than the eight
+    elements it keeps in registers over the passes: those rows re-read their probabilities in every pass."""
+    g = torch.Generator().manual_seed(rows + vocab)
+    logits = torch.randn((rows, vocab), generator=g) * 2.5
+    seeds = [7 * r + 1 for r in range(rows)]
+    for options in ({"temperature": 0.8}, {"temperature": 1.2, "top_k": 40, "top_p": 0.85}):
+        got, want = _sample_both(logits, options, seeds)
+        assert got == want, options
+
+
 def test_mask_tokens_holds_stop_tokens_back_until_the_output_is_long_enough():
     """logits[:, ids] = -inf while produced + steps < min_tokens, nothing otherwise; ids outside the vocabulary are
     skipped; and the sampler's choice on the masked rows is the plain sampler's choice among the other tokens."""
