@@ -27,6 +27,7 @@ struct Found {
 };
 
 constexpr int BINS = 16;  // four bits of the key per pass
+constexpr int FEW = 32;   // a search ends by ordering its candidates once this many are left
 
 
 struct Shared {
@@ -44,6 +45,7 @@ struct Shared {
   float reduce_f[32];
   int reduce_i[32];
   unsigned warp_ties[THREADS / 32];
+  unsigned few_n, few_key[FEW], few_sorted[FEW];  // the last candidates of a search (see find_prefix)
 };
 
 // ---- the cluster: barrier and reads of the same variable in another block's shared memory
@@ -191,24 +193,77 @@ __device__ __forceinline__ void find_prefix(const float* __restrict__ p, int voc
     prefix = sh.found.bits;
     above_count = sh.found.above_count;
     above_mass = sh.found.above_mass;
-    bool single = sh.found.tie_count == 1 && shift > 0;
+    bool few = sh.found.tie_count <= (unsigned long long)FEW && shift > 0;
     __syncthreads();
-    if (single) {
-      // one candidate is left under this prefix: no need to descend bit by bit; whoever holds it tells its bits
-      int set2 = turn.next();
-      if (tid == 0) sh.out_u32[set2] = 0u;
+    if (few) {
+      // At most 32 candidates are left under this prefix: no need to descend bit by bit. Whoever holds one puts its
+      // key on its block's list; every block then reads all lists, orders the keys (descending) in its first warp
+      // and walks the groups of equal keys from the top, as the passes above walk bins.
+      if (tid == 0) sh.few_n = 0u;
       __syncthreads();
-      for (int i = (int)rank * THREADS + tid; i < vocab; i += CL * THREADS) {
-        float v = p[i];
+      auto offer = [&](float v) {
         unsigned key = __float_as_uint(v) << 1;
-        if (v >= 0.f && (key >> shift) == prefix) sh.out_u32[set2] = key;  // exactly one thread of the cluster
+        if (v >= 0.f && (key >> shift) == prefix) sh.few_key[atomicAdd(&sh.few_n, 1u) & (FEW - 1)] = key;
+      };
+      if (fits) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) offer(kept[u]);
+      } else {
+        for (int i = (int)rank * THREADS + tid; i < vocab; i += CL * THREADS) offer(p[i]);
       }
       cluster_sync();
-      unsigned key = 0;
+      if (tid < 32) {
+        unsigned key = 0u;
+        bool have = false;
+        unsigned before = 0;  // the candidates on the lists of lower ranks
 #pragma unroll
-      for (unsigned r = 0; r < CL; ++r) key |= remote_u32(&sh.out_u32[set2], r);
-      __syncthreads();
-      if (tid == 0) sh.found.bits = key;
+        for (unsigned r = 0; r < CL; ++r) {
+          unsigned n = remote_u32(&sh.few_n, r);
+          if (n > (unsigned)FEW) n = FEW;
+          if ((unsigned)tid >= before && (unsigned)tid < before + n) {
+            key = remote_u32(&sh.few_key[tid - before], r);
+            have = true;
+          }
+          before += n;
+        }
+        unsigned total = before < 32u ? before : 32u;
+        // this candidate's place in the order: the keys above it, and equal keys in lower lanes
+        unsigned place = 0;
+        for (unsigned j = 0; j < 32u; ++j) {
+          unsigned other = __shfl_sync(0xffffffffu, key, (int)j);
+          bool other_has = __shfl_sync(0xffffffffu, (int)have, (int)j) != 0;
+          if (other_has && (other > key || (other == key && j < (unsigned)tid))) ++place;
+        }
+        if (have) sh.few_sorted[place] = key;
+        __syncwarp();
+        if (tid == 0) {
+          Found& f = sh.found;
+          unsigned long long ac = f.above_count, am = f.above_mass;
+          unsigned at = 0;
+          bool done = false;
+          while (at < total && !done) {
+            unsigned k = sh.few_sorted[at];
+            unsigned long long c = 1;
+            while (at + c < total && sh.few_sorted[at + c] == k) ++c;
+            unsigned long long m = c * to_fx(__uint_as_float(k >> 1));
+            bool hit;
+            if (kind == FIND_COUNT) hit = ac < target && target <= ac + c;
+            else if (kind == FIND_MASS_GE) hit = am < target && target <= am + m;
+            else hit = am <= target && target < am + m;
+            if (hit || at + c >= total) {  // (the bin held the boundary, so a group does; the last one if none says so)
+              f.bits = k;
+              f.above_count = ac;
+              f.above_mass = am;
+              f.tie_count = c;
+              f.tie_mass = m;
+              done = true;
+            }
+            ac += c;
+            am += m;
+            at += (unsigned)c;
+          }
+        }
+      }
       __syncthreads();
       break;
     }
