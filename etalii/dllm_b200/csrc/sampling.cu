@@ -9,7 +9,10 @@
 //   xoshiro256** state, scaled by the kept mass, picks the first candidate whose running sum exceeds it.
 // The order is never materialised: a prefix of it is found by descending the bits of p four at a time with counting
 // histograms (private to each thread, then summed in a fixed order); masses are summed as 64-bit fixed point (2^-62
-// units), so every sum is exact integer arithmetic and a row's choice is reproducible.
+// units), so every sum is exact integer arithmetic and a row's choice is reproducible. Once at most 32 candidates
+// are left under the bits found so far, one warp orders them and the descent ends there. Where a thread's stripe of
+// the vocabulary is at most eight logits (up to 65,536 tokens with eight blocks a row), they stay in registers from
+// the division by the temperature to the end of the search.
 // Scratch, given by the caller: per logit one float (the probability) and one double (the exponential).
 #include "common.cuh"
 

@@ -278,8 +278,8 @@ TMA_STREAM_BYTES = 48 << 20
 def streams_through_shared_memory(rows: int, outputs: int, inner: int) -> bool:
     """Whether a decode-sized product takes the kernel that streams W through a ring of shared-memory stages.
     Measured against the kernel that streams through registers: it wins (0.71 to 0.97 of the HBM rate against 0.65 to
-    0.89) for one or two rows of activations, long rows of W (its copies are 2 KB pieces of a row) and matrices of
-    tens of megabytes; with more rows the copies of the activations cost it the lead."""
+    0.89) for few rows of activations, long rows of W (its copies are 2 KB pieces of a row) and matrices of tens of
+    megabytes; with more rows the copies of the activations cost it the lead."""
     if inner % 64 or 2 * outputs * inner < TMA_STREAM_BYTES:
         return False
     # (up to 4 rows its lead holds, 6144 x 4096: 11.3 µs against 12.2; up to 8 rows only for very long rows of W,
@@ -303,9 +303,25 @@ def takes_weights_as_rows(rows: int, outputs: int, inner: int) -> bool:
 
 
 SPLIT_MIN_BYTES = 16 << 20
+MAX_REDUCTION_SPLIT = 8
 
 
-def reduction_split(rows: int, outputs: int, inner: int, multiprocessors: int = 148) -> int:
+B200_MULTIPROCESSORS = 148
+
+
+_sm_count = 0
+
+
+def _multiprocessors() -> int:
+    """The device's multiprocessors (a B200's where no device is present: the rules are plain functions of sizes)."""
+    global _sm_count
+    if _sm_count == 0:
+        _sm_count = (torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+                     if torch.cuda.is_available() else B200_MULTIPROCESSORS)
+    return _sm_count
+
+
+def reduction_split(rows: int, outputs: int, inner: int, multiprocessors: int | None = None) -> int:
     """Into how many stretches the reduction of a residual product with 33 to 64 rows of activations is cut, 1 for
     not at all. A W of few rows and a long reduction (an output or down projection: 4096 x 14336, 2048 x 8192) has
     fewer 128-row tiles than the device has multiprocessors, and a multiprocessor takes in about 80 GB/s: with 32
@@ -316,11 +332,13 @@ def reduction_split(rows: int, outputs: int, inner: int, multiprocessors: int = 
     reduction over a cluster is as fast or faster (2048 x 2048 with 64 rows: 7.6 against 8.9)."""
     if not (32 < rows <= GEMV_MAX_ROWS) or inner % 8 or outputs % 4 or 2 * outputs * inner <= SPLIT_MIN_BYTES:
         return 1
+    multiprocessors = multiprocessors or _multiprocessors()
     tiles, k_tiles = -(-outputs // 128), -(-inner // 64)
     if tiles >= multiprocessors:
         return 1
+    # doubled while the work items stay within two a multiprocessor and a stretch keeps eight k tiles or more
     split = 1
-    while split < 8 and tiles * split * 2 <= 2 * multiprocessors and k_tiles // (split * 2) >= 8:
+    while split < MAX_REDUCTION_SPLIT and tiles * split <= multiprocessors and k_tiles // (split * 2) >= 8:
         split *= 2
     return split
 
@@ -335,9 +353,6 @@ def _parts_buffer(device, floats: int) -> torch.Tensor:
     if key not in _parts:
         _parts[key] = torch.empty(floats, device=device, dtype=torch.float32)
     return _parts[key]
-
-
-MAX_REDUCTION_SPLIT = 8
 
 
 def gemm_parts(a: torch.Tensor, w: torch.Tensor, split: int) -> torch.Tensor:
