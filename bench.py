@@ -2,7 +2,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--repeats R] [--layers L] [--impl ours|reference]
                     [--shape smollm2-135m|smollm2-1.7b|llama-3.1-8b] [--batch B] [--no-points]
-                    [--profile decode|prefill|kernels|ablate|ablate-fused|feed-forward|gemm|attention|stream]
+                    [--profile decode|prefill|kernels|ablate|ablate-fused|feed-forward|gemm|attention|stream|cluster|cut]
 
 Default workload: the SmolLM2-135M shape (30 layers, hidden 576, 9 heads, 3 kv heads, head_dim 64, intermediate 1536,
 vocabulary 49152, tied head) with seeded random bfloat16 weights; a batch of 8 sequences with unequal prompt lengths
@@ -354,6 +354,34 @@ def stream_table() -> int:
                     us, fraction = run(m, n, k, epilogue, 7, split)
                     cells.append(f"{us:.1f} {fraction:.2f}")
             print(f"{m} {n} x {k} {epilogue} | " + " | ".join(cells))
+    return 0
+
+
+def cut_reduction_case() -> int:
+    """One narrow product with a long reduction and 64 rows (4096 x 14336, the residual epilogue) as the tile kernel
+    runs it with the reduction cut into 8 stretches: a few launches over three copies of W, a small case for ncu."""
+    import torch
+
+    from etalii.dllm_b200.kernels import ops
+
+    device = "cuda:0"
+    m, n, k, split = 64, 4096, 14336, 8
+    ws = [(torch.randn(n, k, device=device) * 0.05).bfloat16() for _ in range(3)]
+    x = torch.randn(m, k, device=device).bfloat16()
+    c = torch.zeros(m, n, device=device, dtype=torch.float32)
+    for i in range(3):
+        ops.gemm(c, x, ws[i % 3], ops.EPI_RESIDUAL, kernel=7, cluster=split)
+    torch.cuda.synchronize()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record()
+    for i in range(3):
+        ops.gemm(c, x, ws[i % 3], ops.EPI_RESIDUAL, kernel=7, cluster=split)
+    end.record()
+    torch.cuda.synchronize()
+    ops.raise_if_failed()
+    us = begin.elapsed_time(end) / 3 * 1e3
+    print(f"profile cut: {m} x {n} x {k} in {split} stretches, {us:.1f} us a product with its sum (launched one by "
+          f"one), {n * k * 2 / us / 1e3:.0f} GB/s of weights")
     return 0
 
 
@@ -747,7 +775,7 @@ def main() -> int:
     parser.add_argument("--impl", default="ours", choices=("ours", "reference", "reference-worker"))
     parser.add_argument("--budget", type=float, default=REFERENCE_BUDGET_S, help=argparse.SUPPRESS)
     parser.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 and the float32 points")
-    parser.add_argument("--profile", choices=("decode", "prefill", "gemm", "attention", "stream", "cluster", "kernels",
+    parser.add_argument("--profile", choices=("decode", "prefill", "gemm", "attention", "stream", "cluster", "cut", "kernels",
                                               "ablate", "ablate-fused", "feed-forward"),
                         help="run only a few decode steps (or one prefill) and print no JSON: a small case for ncu")
     args = parser.parse_args()
@@ -763,6 +791,8 @@ def main() -> int:
         return stream_table()
     if args.profile == "cluster":
         return cluster_table(args.batch if args.batch > 8 else 64)
+    if args.profile == "cut":
+        return cut_reduction_case()
     if args.gpus != 1:
         print(f"bench.py measures one GPU: --gpus {args.gpus} is not supported (this library runs on a single device)")
         return 2
