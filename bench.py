@@ -2,7 +2,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--repeats R] [--layers L] [--impl ours|reference]
                     [--shape smollm2-135m|smollm2-1.7b|llama-3.1-8b] [--batch B] [--no-points]
-                    [--profile decode|prefill|kernels|ablate|ablate-fused|feed-forward|gemm|attention|stream|cluster|cut]
+                    [--profile decode|prefill|kernels|ablate|ablate-fused|feed-forward|gemm|attention|stream|cluster|cut|sampling]
 
 Default workload: the SmolLM2-135M shape (30 layers, hidden 576, 9 heads, 3 kv heads, head_dim 64, intermediate 1536,
 vocabulary 49152, tied head) with seeded random bfloat16 weights; a batch of 8 sequences with unequal prompt lengths
@@ -382,6 +382,48 @@ def cut_reduction_case() -> int:
     us = begin.elapsed_time(end) / 3 * 1e3
     print(f"profile cut: {m} x {n} x {k} in {split} stretches, {us:.1f} us a product with its sum (launched one by "
           f"one), {n * k * 2 / us / 1e3:.0f} GB/s of weights")
+    return 0
+
+
+def sampling_table() -> int:
+    """Times the token-choice kernel alone: rows of seeded random logits (standard deviation 3, or 12 for a peaked
+    distribution), greedy and at temperature 0.8 without and with top-p and top-k, as 20 launches in a CUDA graph."""
+    import torch
+
+    from etalii.dllm_b200.kernels import ops
+
+    device = "cuda:0"
+
+    def run(rows, vocab, temperature, top_k=0, top_p=1.0, spread=3.0):
+        generator = torch.Generator(device=device).manual_seed(rows + vocab)
+        logits = torch.randn(rows, vocab, device=device, generator=generator) * spread
+        out = torch.zeros(rows, dtype=torch.int32, device=device)
+        scratch = torch.empty(ops.sample_scratch(rows, vocab), dtype=torch.float32, device=device)
+        rng = torch.zeros(rows, 4, dtype=torch.int64, device=device)
+        rng_rows = torch.arange(rows, dtype=torch.int32, device=device)
+        ops.seed_rng(rng, rng_rows, torch.arange(rows, dtype=torch.int64, device=device) + 5)
+        for _ in range(3):
+            ops.sample(out, logits, scratch, rng, rng_rows, temperature, top_k, top_p)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(20):
+                ops.sample(out, logits, scratch, rng, rng_rows, temperature, top_k, top_p)
+        graph.replay()
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        graph.replay()
+        end.record()
+        torch.cuda.synchronize()
+        return begin.elapsed_time(end) / 20 * 1e3
+
+    print("rows x vocabulary | greedy | temperature 0.8 | + top-p 0.9 | + top-k 50 | temperature 0.8, peaked   (us)")
+    for rows in (1, 8, 64):
+        for vocab in (49152, 128256):
+            print(f"{rows} x {vocab} | {run(rows, vocab, 0.0):.1f} | {run(rows, vocab, 0.8):.1f} | "
+                  f"{run(rows, vocab, 0.8, 0, 0.9):.1f} | {run(rows, vocab, 0.8, 50):.1f} | "
+                  f"{run(rows, vocab, 0.8, spread=12.0):.1f}", flush=True)
     return 0
 
 
@@ -775,7 +817,7 @@ def main() -> int:
     parser.add_argument("--impl", default="ours", choices=("ours", "reference", "reference-worker"))
     parser.add_argument("--budget", type=float, default=REFERENCE_BUDGET_S, help=argparse.SUPPRESS)
     parser.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 and the float32 points")
-    parser.add_argument("--profile", choices=("decode", "prefill", "gemm", "attention", "stream", "cluster", "cut", "kernels",
+    parser.add_argument("--profile", choices=("decode", "prefill", "gemm", "attention", "stream", "cluster", "cut", "sampling", "kernels",
                                               "ablate", "ablate-fused", "feed-forward"),
                         help="run only a few decode steps (or one prefill) and print no JSON: a small case for ncu")
     args = parser.parse_args()
@@ -793,6 +835,8 @@ def main() -> int:
         return cluster_table(args.batch if args.batch > 8 else 64)
     if args.profile == "cut":
         return cut_reduction_case()
+    if args.profile == "sampling":
+        return sampling_table()
     if args.gpus != 1:
         print(f"bench.py measures one GPU: --gpus {args.gpus} is not supported (this library runs on a single device)")
         return 2
