@@ -348,7 +348,7 @@ _parts: dict = {}
 
 def _parts_buffer(device, floats: int) -> torch.Tensor:
     """Scratch for partial results, one buffer per size for the life of the process: a captured graph may hold its
-    address."""
+    address. Like the work buffers, it serves one stream: a product's parts are read by the kernel behind it."""
     key = (str(device), floats)
     if key not in _parts:
         _parts[key] = torch.empty(floats, device=device, dtype=torch.float32)
